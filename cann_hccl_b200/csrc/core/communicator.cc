@@ -1,0 +1,955 @@
+#include "core/communicator.h"
+#include <sys/time.h>
+#include <time.h>
+#include <unistd.h>
+#include <algorithm>
+#include <chrono>
+#include <cstdlib>
+#include <cstring>
+#include <sstream>
+#include <cuda_runtime.h>
+#include "bootstrap/socket.h"
+#include "common/dtype_host.h"
+#include "common/env.h"
+#include "common/log.h"
+#include "health/consistency.h"
+#include "health/fault_inject.h"
+#include "p2p/p2p_backend.h"
+#include "transport/host_exec.h"
+
+namespace hcclb {
+
+namespace {
+std::mutex g_hub_mu;
+std::map<std::string, Hub *> g_hubs;
+double now_us()
+{
+    struct timespec ts;
+    clock_gettime(CLOCK_MONOTONIC, &ts);
+    return ts.tv_sec * 1e6 + ts.tv_nsec * 1e-3;
+}
+constexpr size_t kTraceCap = 4096;
+constexpr uint64_t kP2pSlot = 256u << 10;
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+}  // namespace
+
+void register_hub(const std::string &ident, Hub *hub)
+{
+    std::lock_guard<std::mutex> lk(g_hub_mu);
+    g_hubs[ident] = hub;
+}
+Hub *adopt_hub(const std::string &ident)
+{
+    std::lock_guard<std::mutex> lk(g_hub_mu);
+    auto it = g_hubs.find(ident);
+    if (it == g_hubs.end()) return nullptr;
+    Hub *h = it->second;
+    g_hubs.erase(it);
+    return h;
+}
+std::string make_identifier(const std::string &ip, int port)
+{
+    struct timeval tv;
+    gettimeofday(&tv, nullptr);
+    static std::atomic<uint32_t> ctr{0};
+    char buf[128];
+    snprintf(buf, sizeof(buf), "%s_%d_%d_%llu_%u", ip.c_str(), port, (int)getpid(),
+             (unsigned long long)tv.tv_sec * 1000000ull + tv.tv_usec, ctr.fetch_add(1));
+    return buf;
+}
+
+bool Communicator::deterministic() const
+{
+    const EnvConfig &e = env_config();
+    if (e.deterministic >= 0) return e.deterministic != 0;  // the environment wins (reference: op_base.cc:1204)
+    return settings_.deterministic;
+}
+
+// ------------------------------------------------------------------------------------------------ creation
+HcclResult Communicator::create(uint32_t nranks, const RootHandle &root, uint32_t rank, const CommSettings &st,
+                                Communicator **out)
+{
+    const EnvConfig &env = env_config();
+    CHK_RET_LOG(nranks == 0 || nranks > (uint32_t)kMaxRanks, HCCL_E_PARA, "rank count %u outside [1,%d]", nranks, kMaxRanks);
+    CHK_RET_LOG(rank >= nranks, HCCL_E_PARA, "rank %u not below rank count %u", rank, nranks);
+    CHK_RET_LOG(root.magic != kRootMagic, HCCL_E_PARA, "root info was not produced by HcclGetRootInfo");
+    std::unique_ptr<Communicator> c(new Communicator());
+    c->settings_ = st;
+    c->nranks_ = (int)nranks;
+    c->local_ranks_ = {(int)rank};
+    c->root_ = root;
+    c->ident_ = root.identifier;
+    c->name_ = st.name.empty() ? c->ident_ : st.name;
+    c->key_prefix_ = c->ident_;
+    if (Hub *h = adopt_hub(c->ident_)) c->owned_hub_.reset(h);
+    int tmo = env.connect_timeout_s * 1000;
+    c->hub_ = std::make_shared<HubClient>();
+    CHK_RET(c->hub_->connect(root.ip, (int)root.port, (int)root.family, tmo));
+    // rank table exchange: every rank publishes {rank, pid, host, device, transport}; the table is checked for
+    // duplicates and mixed transports (reference: TopoInfoExchangeAgent::VerifyClusterInfo, exchange_agent.cc:376)
+    struct Entry { uint32_t rank, pid, device, transport; char host[64]; } me;
+    memset(&me, 0, sizeof(me));
+    me.rank = rank; me.pid = (uint32_t)getpid(); me.device = (uint32_t)st.device; me.transport = (uint32_t)st.transport;
+    gethostname(me.host, sizeof(me.host) - 1);
+    std::vector<std::string> table;
+    CHK_RET(c->hub_->rendezvous(c->key_prefix_ + "/ranktable", nranks, rank, std::string((const char *)&me, sizeof(me)), &table, tmo));
+    for (uint32_t r = 0; r < nranks; ++r) {
+        Entry e;
+        CHK_RET_LOG(table[r].size() != sizeof(e), HCCL_E_INTERNAL, "malformed rank table entry %u", r);
+        memcpy(&e, table[r].data(), sizeof(e));
+        CHK_RET_LOG(e.rank != r, HCCL_E_PARA, "rank table entry %u carries rank %u", r, e.rank);
+        CHK_RET_LOG(e.transport != me.transport, HCCL_E_PARA, "rank %u uses a different transport", r);
+        CHK_RET_LOG(strcmp(e.host, me.host) != 0, HCCL_E_NOT_SUPPORT, "rank %u is on host %s: one NVSwitch domain per communicator", r, e.host);
+    }
+    if (st.transport == TR_HOST) c->alloc_.reset(make_host_shm_allocator(c->hub_.get(), c->ident_, (int)rank, (int)nranks, tmo));
+    else {
+        CHK_RET_LOG(cudaSetDevice(st.device) != cudaSuccess, HCCL_E_RUNTIME, "cudaSetDevice(%d) failed", st.device);
+        bool want_nvls = env.nvls_enable != 0 && nranks > 1;
+        c->alloc_.reset(make_device_vmm_allocator(c->hub_.get(), c->ident_, (int)rank, (int)nranks, st.device, want_nvls, tmo));
+    }
+    CHK_RET(c->init_common());
+    if (st.heartbeat && nranks > 1) {
+        c->hb_conn_.reset(new HubClient());
+        if (c->hb_conn_->connect(root.ip, (int)root.port, (int)root.family, tmo) == HCCL_SUCCESS)
+            c->hb_thread_ = std::thread([p = c.get()] { p->heartbeat_loop(); });
+    }
+    if (st.transport == TR_DEVICE && nranks > 1 && P2pBackend::available()) {
+        c->p2p_conn_.reset(new HubClient());
+        if (c->p2p_conn_->connect(root.ip, (int)root.port, (int)root.family, tmo) == HCCL_SUCCESS) P2pBackend::create(c.get(), &c->p2p_);
+    }
+    *out = c.release();
+    return HCCL_SUCCESS;
+}
+
+HcclResult Communicator::create_local(uint32_t nranks, const CommSettings &st, Communicator **out)
+{
+    CHK_RET_LOG(nranks == 0 || nranks > (uint32_t)kMaxRanks, HCCL_E_PARA, "rank count %u outside [1,%d]", nranks, kMaxRanks);
+    std::unique_ptr<Communicator> c(new Communicator());
+    c->settings_ = st;
+    c->nranks_ = (int)nranks;
+    for (uint32_t r = 0; r < nranks; ++r) c->local_ranks_.push_back((int)r);
+    c->all_local_ = true;
+    c->ident_ = make_identifier("local", 0);
+    c->name_ = st.name.empty() ? c->ident_ : st.name;
+    if (st.transport == TR_HOST) c->alloc_.reset(make_host_local_allocator((int)nranks));
+    else {
+        CHK_RET_LOG(cudaSetDevice(st.device) != cudaSuccess, HCCL_E_RUNTIME, "cudaSetDevice(%d) failed", st.device);
+        c->alloc_.reset(make_device_local_allocator((int)nranks, st.device));
+    }
+    CHK_RET(c->init_common());
+    *out = c.release();
+    return HCCL_SUCCESS;
+}
+
+HcclResult Communicator::create_sub(uint32_t rank_num, const uint32_t *rank_ids, uint64_t sub_id, uint32_t sub_rank,
+                                    const CommSettings &st, Communicator **out)
+{
+    // Sub-communicator = new identifier "<parent>_sub_<id>" (reference: op_base.cc:650-790), same hub, own memory.
+    CHK_RET_LOG(all_local_, HCCL_E_NOT_SUPPORT, "sub-communicators of all-local communicators are not supported");
+    CHK_RET_LOG(rank_num == 0 || rank_num > (uint32_t)nranks_ || sub_rank >= rank_num, HCCL_E_PARA, "bad sub-communicator shape");
+    CHK_RET_LOG(rank_ids[sub_rank] != (uint32_t)rank(), HCCL_E_PARA, "rankIds[%u] is %u but this rank is %d", sub_rank, rank_ids[sub_rank], rank());
+    const EnvConfig &env = env_config();
+    int tmo = env.connect_timeout_s * 1000;
+    std::unique_ptr<Communicator> c(new Communicator());
+    c->settings_ = st;
+    c->settings_.transport = settings_.transport;
+    c->settings_.device = settings_.device;
+    c->nranks_ = (int)rank_num;
+    c->local_ranks_ = {(int)sub_rank};
+    c->root_ = root_;
+    c->ident_ = ident_ + "_sub_" + std::to_string(sub_id);
+    c->name_ = st.name.empty() ? c->ident_ : st.name;
+    c->key_prefix_ = c->ident_;
+    c->hub_ = std::make_shared<HubClient>();
+    CHK_RET(c->hub_->connect(root_.ip, (int)root_.port, (int)root_.family, tmo));
+    // members check that they agree on the member list
+    std::string ids((const char *)rank_ids, rank_num * sizeof(uint32_t));
+    std::vector<std::string> all;
+    CHK_RET(c->hub_->rendezvous(c->key_prefix_ + "/members", rank_num, sub_rank, ids, &all, tmo));
+    for (auto &a : all) CHK_RET_LOG(a != ids, HCCL_E_PARA, "sub-communicator members disagree on the rank list");
+    if (settings_.transport == TR_HOST) c->alloc_.reset(make_host_shm_allocator(c->hub_.get(), c->ident_, (int)sub_rank, (int)rank_num, tmo));
+    else c->alloc_.reset(make_device_vmm_allocator(c->hub_.get(), c->ident_, (int)sub_rank, (int)rank_num, settings_.device, env.nvls_enable != 0, tmo));
+    CHK_RET(c->init_common());
+    *out = c.release();
+    return HCCL_SUCCESS;
+}
+
+HcclResult Communicator::init_common()
+{
+    const EnvConfig &env = env_config();
+    int nl = nlocal();
+    p2p_slot_ = kP2pSlot;
+    size_t flags_bytes = kFlagPageBytes;
+    size_t p2p_bytes = align_up((size_t)nranks_ * p2p_slot_, 4096);
+    size_t half = align_up((size_t)settings_.stage_half_bytes, 4096);
+    settings_.stage_half_bytes = half;
+    size_t total = flags_bytes + p2p_bytes + 2 * half;
+    CHK_RET(alloc_->alloc(total, true, &seg_));
+    CHK_RET_LOG((int)seg_.size() != nl, HCCL_E_INTERNAL, "allocator returned %zu segments for %d local ranks", seg_.size(), nl);
+    nvls_ = seg_[0].mc != nullptr;
+    bool dev = settings_.transport == TR_DEVICE;
+    size_t blk = align_up(sizeof(DevStatus), 64) + 64;
+    if (dev) {
+        CHK_RET_LOG(cudaHostAlloc(&pinned_, blk * nl, cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess, HCCL_E_MEMORY, "cudaHostAlloc failed");
+    } else {
+        pinned_ = calloc(nl, blk);
+        CHK_RET_LOG(!pinned_, HCCL_E_MEMORY, "out of host memory");
+    }
+    memset(pinned_, 0, blk * nl);
+    double tmo_ms = env.exec_timeout_ms > 0 ? env.exec_timeout_ms : (env.exec_timeout_s > 0 ? env.exec_timeout_s * 1000.0 : 3600e3);
+    if (tmo_ms > 3600e3) tmo_ms = 3600e3;  // never unbounded: a wait always ends
+    ctx_.assign(nl, RankCtx());
+    status_.assign(nl, nullptr);
+    abort_.assign(nl, nullptr);
+    if (dev) {
+        CHK_RET_LOG(cudaMalloc(&dev_exit_, sizeof(uint32_t) * 2 * nl) != cudaSuccess, HCCL_E_MEMORY, "cudaMalloc failed");
+        cudaMemset(dev_exit_, 0, sizeof(uint32_t) * 2 * nl);
+    }
+    for (int li = 0; li < nl; ++li) {
+        RankCtx &x = ctx_[li];
+        memset(&x, 0, sizeof(x));
+        x.rank = local_ranks_[li];
+        x.nranks = nranks_;
+        for (int q = 0; q < nranks_; ++q) {
+            uint8_t *base = seg_[li].peer[q];
+            x.flags[q] = (uint64_t *)base;
+            x.p2p[q] = base + flags_bytes;
+            x.stage[q] = base + flags_bytes + p2p_bytes;
+        }
+        x.mc_stage = seg_[li].mc ? seg_[li].mc + flags_bytes + p2p_bytes : nullptr;
+        uint8_t *pb = (uint8_t *)pinned_ + blk * li;
+        status_[li] = (DevStatus *)pb;
+        abort_[li] = (volatile uint32_t *)(pb + align_up(sizeof(DevStatus), 64));
+        x.status = status_[li];
+        x.abort = abort_[li];
+        x.exit_counter = dev ? (uint32_t *)dev_exit_ + 2 * li : nullptr;
+        x.stage_half = half;
+        x.timeout_ns = (uint64_t)(tmo_ms * 1e6);
+    }
+    if (dev) {
+        CHK_RET_LOG(cudaMalloc(&dev_ctx_, sizeof(RankCtx) * nl) != cudaSuccess, HCCL_E_MEMORY, "cudaMalloc failed");
+        CHK_RET_LOG(cudaMemcpy(dev_ctx_, ctx_.data(), sizeof(RankCtx) * nl, cudaMemcpyHostToDevice) != cudaSuccess, HCCL_E_RUNTIME, "cudaMemcpy failed");
+        cudaDeviceSynchronize();
+    }
+    trace_.resize(kTraceCap);
+    HLOG_INFO("communicator %s: %d ranks, %d local, transport %s, staging 2x%zu MB, nvls %d", name_.c_str(), nranks_, nl,
+              dev ? "device" : "host", half >> 20, (int)nvls_);
+    return HCCL_SUCCESS;
+}
+
+Communicator::~Communicator()
+{
+    hb_stop_.store(true);
+    { std::lock_guard<std::mutex> lk(hb_mu_); hb_cv_.notify_all(); }
+    if (hb_thread_.joinable()) hb_thread_.join();
+    p2p_.reset();
+    bool dev = settings_.transport == TR_DEVICE;
+    if (dev) {
+        cudaSetDevice(settings_.device);
+        cudaDeviceSynchronize();
+        for (auto &kv : plans_)
+            for (Step *s : kv.second.dev_steps) cudaFree(s);
+    }
+    for (auto &kv : user_segs_) alloc_->release(&kv.second);
+    if (alloc_) alloc_->release(&seg_);
+    if (dev) {
+        if (dev_ctx_) cudaFree(dev_ctx_);
+        if (dev_exit_) cudaFree(dev_exit_);
+        if (pinned_) cudaFreeHost(pinned_);
+    } else free(pinned_);
+    alloc_.reset();
+    if (hb_conn_) hb_conn_->bye();
+    if (p2p_conn_) p2p_conn_->bye();
+    if (hub_) hub_->bye();
+    owned_hub_.reset();
+}
+
+HcclResult Communicator::destroy()
+{
+    int st = state_.load();
+    if (st == CS_INUSE || st == CS_BUILDING) return HCCL_E_AGAIN;  // reference: HcclCommDestroy while in use
+    if (!all_local_ && nranks_ > 1 && hub_ && hub_->connected()) {
+        // leave together so that no rank unmaps memory a peer's kernel may still touch; bounded wait
+        if (settings_.transport == TR_DEVICE) { cudaSetDevice(settings_.device); cudaDeviceSynchronize(); }
+        hub_->barrier(key_prefix_ + "/destroy", nranks_, rank(), 10000);
+    }
+    delete this;
+    return HCCL_SUCCESS;
+}
+
+// ------------------------------------------------------------------------------------------------ plans
+HcclResult Communicator::get_plan(const OpDesc &d, const std::string &key, CachedPlan **out)
+{
+    auto it = plans_.find(key);
+    if (it != plans_.end()) { *out = &it->second; return HCCL_SUCCESS; }
+    if (plans_.size() >= 2048) {  // bound memory: drop everything once nothing is in flight
+        if (settings_.transport == TR_DEVICE) {
+            cudaDeviceSynchronize();
+            for (auto &kv : plans_)
+                for (Step *s : kv.second.dev_steps) cudaFree(s);
+        }
+        plans_.clear();
+    }
+    CachedPlan cp;
+    CHK_RET(build_plan(d, local_ranks_, &cp.plan));
+    if (settings_.transport == TR_DEVICE) {
+        for (auto &steps : cp.plan.steps) {
+            Step *ds = nullptr;
+            size_t bytes = std::max<size_t>(steps.size(), 1) * sizeof(Step);
+            CHK_RET_LOG(cudaMalloc(&ds, bytes) != cudaSuccess, HCCL_E_MEMORY, "cudaMalloc(plan) failed");
+            if (!steps.empty()) cudaMemcpy(ds, steps.data(), steps.size() * sizeof(Step), cudaMemcpyHostToDevice);
+            cp.dev_steps.push_back(ds);
+        }
+    }
+    stats_.plans_built++;
+    auto ins = plans_.emplace(key, std::move(cp));
+    *out = &ins.first->second;
+    return HCCL_SUCCESS;
+}
+
+HcclResult Communicator::run_plan(const Plan &plan, const void *dev_steps_base, const OpRequest &rq, uint64_t seq,
+                                  int dtype, int redop, bool track_done, const std::vector<const void *> &in,
+                                  const std::vector<void *> &out)
+{
+    int nl = (int)plan.steps.size();
+    const Step *const *dsteps = (const Step *const *)dev_steps_base;
+    std::vector<ExecArgs> args(nl);
+    for (int li = 0; li < nl; ++li) {
+        ExecArgs &a = args[li];
+        memset(&a, 0, sizeof(a));
+        a.steps = settings_.transport == TR_DEVICE ? dsteps[li] : plan.steps[li].data();
+        a.nsteps = (int)plan.steps[li].size();
+        a.nchan = plan.nchan;
+        a.seq = seq;
+        a.in = (const uint8_t *)in[li];
+        a.out = (uint8_t *)out[li];
+        a.dtype = dtype;
+        a.redop = redop;
+        a.track_done = track_done ? 1 : 0;
+    }
+    stats_.launches++;
+    if (settings_.transport == TR_DEVICE) {
+        // map local index -> context: the plan may cover a subset of the local ranks (local Send/Recv)
+        return launch_exec_plan((const RankCtx *)dev_ctx_, args.data(), nl, plan.nchan, rq.stream);
+    }
+    if (nl == 1) return exec_plan_host(ctx_[0], args[0]);
+    std::vector<HcclResult> rcs(nl, HCCL_SUCCESS);
+    std::vector<std::thread> th;
+    for (int li = 0; li < nl; ++li) th.emplace_back([&, li] { rcs[li] = exec_plan_host(ctx_[li], args[li]); });
+    for (auto &t : th) t.join();
+    for (auto r : rcs)
+        if (r != HCCL_SUCCESS) return r;
+    return HCCL_SUCCESS;
+}
+
+HcclResult Communicator::check_ready()
+{
+    if (state_.load() == CS_SUSPENDED) return HCCL_E_SUSPENDING;
+    for (auto *s : status_)
+        if (s && s->code != 0) return (HcclResult)s->code;
+    uint32_t re = remote_error_.load();
+    if (re) return (HcclResult)re;
+    return HCCL_SUCCESS;
+}
+
+Selection Communicator::select(int coll, uint64_t count, int dtype, int redop) const
+{
+    const EnvConfig &env = env_config();
+    SelectInput si;
+    si.coll = coll;
+    si.bytes = count * (uint64_t)dtype_size(dtype);
+    si.nranks = nranks_;
+    si.dtype = dtype;
+    si.redop = redop;
+    si.deterministic = deterministic();
+    si.nvls = nvls_;
+    si.device = settings_.transport == TR_DEVICE;
+    si.expansion_mode = settings_.expansion_mode ? settings_.expansion_mode : env.expansion_mode;
+    si.max_channels = si.device ? 32 : 2;
+    si.forced = forced_algo_for(env, coll);
+    Selection s = select_algo(si, model_);
+    if (env.channels > 0) s.nchan = env.channels;
+    if (all_local_ && si.device) {
+        // virtual ranks share one GPU: all CTAs of all ranks must be resident together (cooperative launch)
+        int cap = std::max(1, 128 / std::max(1, nranks_));
+        s.nchan = std::min(s.nchan, cap);
+    }
+    return s;
+}
+
+void Communicator::record_trace(const OpRequest &rq, int algo, int nchan, uint64_t bytes, double us)
+{
+    std::lock_guard<std::mutex> lk(trace_mu_);
+    TraceRecord &t = trace_[trace_pos_++ % kTraceCap];
+    t.seq = seq_;
+    t.coll = rq.coll; t.algo = algo; t.nchan = nchan;
+    t.count = rq.count; t.bytes = bytes; t.dtype = rq.dtype; t.redop = rq.redop; t.root = rq.root;
+    t.host_us = us;
+}
+std::vector<TraceRecord> Communicator::trace_snapshot()
+{
+    std::lock_guard<std::mutex> lk(trace_mu_);
+    std::vector<TraceRecord> out;
+    size_t n = std::min(trace_pos_, kTraceCap);
+    for (size_t i = 0; i < n; ++i) out.push_back(trace_[(trace_pos_ - n + i) % kTraceCap]);
+    return out;
+}
+std::string Communicator::stats_json()
+{
+    std::ostringstream o;
+    o << "{\"name\":\"" << name_ << "\",\"ranks\":" << nranks_ << ",\"rank\":" << rank() << ",\"nvls\":" << (nvls_ ? 1 : 0)
+      << ",\"launches\":" << stats_.launches << ",\"plans_built\":" << stats_.plans_built << ",\"retries\":" << stats_.retries
+      << ",\"timeouts\":" << stats_.timeouts << ",\"ops\":{";
+    bool first = true;
+    for (int c = 0; c < COLL_COUNT; ++c) {
+        if (!stats_.ops[c]) continue;
+        o << (first ? "" : ",") << "\"" << coll_name(c) << "\":{\"calls\":" << stats_.ops[c] << ",\"bytes\":" << stats_.bytes[c] << "}";
+        first = false;
+    }
+    o << "},\"algos\":{";
+    first = true;
+    for (int a = 0; a < ALGO_COUNT; ++a) {
+        if (!stats_.algo_hist[a]) continue;
+        o << (first ? "" : ",") << "\"" << algo_name(a) << "\":" << stats_.algo_hist[a];
+        first = false;
+    }
+    o << "},\"model\":{\"alpha_us\":" << model_.alpha_us << ",\"beta_gbps\":" << model_.beta_gbps << ",\"nvls_gbps\":" << model_.nvls_gbps
+      << ",\"gamma_gbps\":" << model_.gamma_gbps << ",\"launch_us\":" << model_.launch_us << "}}";
+    return o.str();
+}
+
+// ------------------------------------------------------------------------------------------------ collectives
+HcclResult Communicator::collective(const OpRequest &rq)
+{
+    std::lock_guard<std::mutex> lk(op_mu_);
+    CHK_RET(check_ready());
+    StateGuard guard(state_, CS_INUSE);
+    double t0 = now_us();
+    ++op_index_;
+    fault::before_op(rank(), op_index_);
+    if (fault_hook_) fault_hook_(op_index_);
+    HcclResult rc = run_collective_once(rq);
+    if (rc != HCCL_SUCCESS && (rc == HCCL_E_TIMEOUT || rc == HCCL_E_REMOTE)) {
+        stats_.timeouts++;
+        rc = maybe_retry(rq, rc);
+    }
+    if (env_config().entry_log)
+        HLOG_RUN("%s count=%llu dtype=%d op=%d root=%d -> %d, took %.1f us", coll_name(rq.coll), (unsigned long long)rq.count,
+                 rq.dtype, rq.redop, rq.root, (int)rc, now_us() - t0);
+    return rc;
+}
+
+HcclResult Communicator::run_collective_once(const OpRequest &rq)
+{
+    const int p = nranks_, nl = nlocal();
+    const int es = dtype_size(rq.dtype);
+    double t0 = now_us();
+    bool is_v = rq.coll == COLL_ALLGATHER_V || rq.coll == COLL_REDUCE_SCATTER_V;
+    bool is_a2av = rq.coll == COLL_ALLTOALLV || rq.coll == COLL_ALLTOALLVC;
+    // total window over which the staging loop iterates (elements)
+    uint64_t window = rq.count;
+    if (is_v) {
+        window = 0;
+        for (int j = 0; j < p; ++j) window = std::max(window, rq.counts[j]);
+    }
+    uint64_t sel_count = rq.count;
+    if (rq.coll == COLL_ALLTOALL) sel_count = rq.count * p;
+    if (is_a2av) {
+        sel_count = 0;
+        for (int j = 0; j < p; ++j) sel_count += rq.send_counts[j];
+    }
+    if (is_v) sel_count = window;
+    Selection sel = select(rq.coll, sel_count, rq.dtype, rq.redop);
+    if (rq.algo != ALGO_AUTO) sel.algo = rq.algo;
+    if (rq.nchan > 0) sel.nchan = rq.nchan;
+    if (p == 1) sel.algo = ALGO_SINGLE;
+    if (rq.coll == COLL_BARRIER) { sel.algo = p == 1 ? ALGO_SINGLE : ALGO_MESH; sel.nchan = 1; }
+    if ((sel.algo == ALGO_NVLS || sel.algo == ALGO_NVLS_ONESHOT) && !nvls_) {
+        HLOG_ERROR("NVLS algorithm requested but no multicast mapping exists on this communicator");
+        return HCCL_E_NOT_SUPPORT;
+    }
+    CHK_RET(consistency_check(rq, sel.algo));
+
+    OpDesc d;
+    d.coll = rq.coll; d.algo = sel.algo; d.nranks = p; d.root = rq.root; d.dtype = rq.dtype; d.redop = rq.redop;
+    d.nchan = sel.nchan; d.count = rq.count;
+    if (is_v) { d.counts.assign(rq.counts, rq.counts + p); d.displs.assign(rq.displs, rq.displs + p); }
+    if (is_a2av) {
+        d.send_counts.assign(rq.send_counts, rq.send_counts + (size_t)nl * p);
+        d.send_displs.assign(rq.send_displs, rq.send_displs + (size_t)nl * p);
+        d.recv_counts.assign(rq.recv_counts, rq.recv_counts + (size_t)nl * p);
+        d.recv_displs.assign(rq.recv_displs, rq.recv_displs + (size_t)nl * p);
+        d.slot_bytes = (settings_.stage_half_bytes / p) / 256 * 256;
+        CHK_RET_LOG(d.slot_bytes < 256, HCCL_E_MEMORY, "staging buffer too small for AlltoAllV over %d ranks", p);
+    }
+    std::vector<const void *> in(nl);
+    std::vector<void *> out(nl);
+    for (int li = 0; li < nl; ++li) { in[li] = rq.in ? rq.in[li] : nullptr; out[li] = rq.out ? rq.out[li] : nullptr; }
+
+    // staging loop (reference: CollAllReduceExecutor::RunLoop, coll_all_reduce_executor.cc:160-211)
+    uint64_t max_chunk = window;
+    if (!is_a2av && rq.coll != COLL_BARRIER && p > 1) {
+        d.chunk_off = 0; d.chunk_count = window;
+        if (plan_stage_bytes(d) > settings_.stage_half_bytes) {
+            uint64_t lo = 1, hi = window;
+            while (lo < hi) {
+                uint64_t mid = lo + (hi - lo + 1) / 2;
+                d.chunk_count = mid;
+                if (plan_stage_bytes(d) <= settings_.stage_half_bytes) lo = mid; else hi = mid - 1;
+            }
+            uint64_t vec = es >= 16 ? 1 : 16 / es;
+            max_chunk = lo > vec ? lo / vec * vec : lo;
+            d.chunk_count = max_chunk;
+            CHK_RET_LOG(plan_stage_bytes(d) > settings_.stage_half_bytes, HCCL_E_MEMORY, "staging buffer too small for one element per rank");
+        }
+    }
+    HcclResult rc = HCCL_SUCCESS;
+    uint64_t off = 0;
+    do {
+        uint64_t n = std::min(max_chunk, window - off);
+        d.chunk_off = off; d.chunk_count = n;
+        std::ostringstream key;
+        key << rq.coll << ':' << d.algo << ':' << d.nchan << ':' << rq.dtype << ':' << rq.root << ':' << rq.count << ':' << off << ':' << n;
+        if (is_v) for (int j = 0; j < p; ++j) key << ',' << d.counts[j] << '@' << d.displs[j];
+        if (is_a2av) {
+            uint32_t crc = crc32(d.send_counts.data(), d.send_counts.size() * 8, 0);
+            crc = crc32(d.send_displs.data(), d.send_displs.size() * 8, crc);
+            crc = crc32(d.recv_counts.data(), d.recv_counts.size() * 8, crc);
+            crc = crc32(d.recv_displs.data(), d.recv_displs.size() * 8, crc);
+            key << ",a2av" << crc << '/' << d.send_counts.size();
+            for (size_t i = 0; i < std::min<size_t>(d.send_counts.size(), 4); ++i) key << '.' << d.send_counts[i];
+        }
+        CachedPlan *cp = nullptr;
+        CHK_RET(get_plan(d, key.str(), &cp));
+        rc = run_plan(cp->plan, cp->dev_steps.data(), rq, seq_, rq.dtype, rq.redop, true, in, out);
+        ++seq_;
+        if (rc != HCCL_SUCCESS) break;
+        off += n;
+    } while (off < window);
+    uint64_t bytes = sel_count * es;
+    stats_.ops[rq.coll]++;
+    stats_.bytes[rq.coll] += bytes;
+    stats_.algo_hist[sel.algo]++;
+    record_trace(rq, sel.algo, sel.nchan, bytes, now_us() - t0);
+    return rc;
+}
+
+HcclResult Communicator::consistency_check(const OpRequest &rq, int algo)
+{
+    if (all_local_ || nranks_ == 1 || !consistency_enabled()) return HCCL_SUCCESS;
+    // one check per distinct op shape: the parameter frame of every rank must hash identically
+    // (reference: RankConsistentcyChecker, common/health/rank_consistentcy_checker.cc)
+    OpFrame f;
+    memset(&f, 0, sizeof(f));
+    f.coll = rq.coll; f.dtype = rq.dtype; f.redop = rq.redop; f.root = rq.root; f.algo = algo;
+    bool uniform = !(rq.coll == COLL_ALLTOALLV || rq.coll == COLL_ALLTOALLVC);
+    f.count = uniform ? rq.count : 0;
+    f.stage_half = settings_.stage_half_bytes;
+    if (rq.counts) f.counts_crc = crc32(rq.counts, 8 * (size_t)nranks_, 0);
+    if (rq.displs) f.displs_crc = crc32(rq.displs, 8 * (size_t)nranks_, 0);
+    std::string key((const char *)&f, sizeof(f));
+    if (checked_.count(key)) return HCCL_SUCCESS;
+    std::vector<std::string> all;
+    int tmo = env_config().connect_timeout_s * 1000;
+    uint32_t mine = crc32(&f, sizeof(f), 0);
+    char tag[64];
+    snprintf(tag, sizeof(tag), "/check/%llu", (unsigned long long)checked_.size());
+    CHK_RET(hub_->rendezvous(key_prefix_ + tag, nranks_, rank(), std::string((const char *)&f, sizeof(f)), &all, tmo));
+    for (int r = 0; r < nranks_; ++r) {
+        if (all[r].size() != sizeof(f) || crc32(all[r].data(), sizeof(f), 0) != mine) {
+            OpFrame o;
+            memset(&o, 0, sizeof(o));
+            if (all[r].size() == sizeof(o)) memcpy(&o, all[r].data(), sizeof(o));
+            HLOG_ERROR("op parameters differ between rank %d and rank %d: %s count %llu dtype %d op %d root %d vs %s count %llu dtype %d op %d root %d",
+                       rank(), r, coll_name(f.coll), (unsigned long long)f.count, f.dtype, f.redop, f.root, coll_name(o.coll),
+                       (unsigned long long)o.count, o.dtype, o.redop, o.root);
+            return HCCL_E_PARA;
+        }
+    }
+    checked_[key] = true;
+    return HCCL_SUCCESS;
+}
+
+// ------------------------------------------------------------------------------------------------ p2p
+HcclResult Communicator::p2p_plan_exec(bool is_send, int peer, const void *sbuf, void *rbuf, uint64_t count, int dtype, void *stream)
+{
+    int me = rank();
+    OpDesc d;
+    d.coll = is_send ? COLL_SEND : COLL_RECV;
+    d.algo = ALGO_MESH; d.nranks = nranks_; d.dtype = dtype; d.nchan = 2; d.count = count; d.peer = peer;
+    d.p2p_slot = p2p_slot_;
+    auto pr = is_send ? std::make_pair(me, peer) : std::make_pair(peer, me);
+    d.p2p_round0 = p2p_rounds_[pr];
+    int es = dtype_size(dtype);
+    uint64_t slotE = (p2p_slot_ / es) / (es >= 16 ? 1 : 16 / es) * (es >= 16 ? 1 : 16 / es);
+    uint32_t rounds = (uint32_t)ceil_div_u64(count, slotE);
+    std::ostringstream key;
+    key << "p2p:" << is_send << ':' << peer << ':' << dtype << ':' << count << ':' << d.p2p_round0;
+    CachedPlan *cp = nullptr;
+    CHK_RET(get_plan(d, key.str(), &cp));
+    p2p_rounds_[pr] += rounds;
+    OpRequest rq;
+    rq.stream = stream;
+    std::vector<const void *> in{sbuf};
+    std::vector<void *> out{rbuf};
+    return run_plan(cp->plan, cp->dev_steps.data(), rq, 0, dtype, HCCL_REDUCE_SUM, false, in, out);
+}
+
+HcclResult Communicator::send(const void *buf, uint64_t count, int dtype, int dest, void *stream)
+{
+    std::lock_guard<std::mutex> lk(op_mu_);
+    CHK_RET(check_ready());
+    CHK_RET_LOG(all_local_, HCCL_E_NOT_SUPPORT, "use the local send/recv entry on all-local communicators");
+    StateGuard guard(state_, CS_INUSE);
+    stats_.ops[COLL_SEND]++;
+    stats_.bytes[COLL_SEND] += count * dtype_size(dtype);
+    if (p2p_) return p2p_->send(buf, count, dtype, dest, stream);
+    return p2p_plan_exec(true, dest, buf, nullptr, count, dtype, stream);
+}
+HcclResult Communicator::recv(void *buf, uint64_t count, int dtype, int src, void *stream)
+{
+    std::lock_guard<std::mutex> lk(op_mu_);
+    CHK_RET(check_ready());
+    CHK_RET_LOG(all_local_, HCCL_E_NOT_SUPPORT, "use the local send/recv entry on all-local communicators");
+    StateGuard guard(state_, CS_INUSE);
+    stats_.ops[COLL_RECV]++;
+    stats_.bytes[COLL_RECV] += count * dtype_size(dtype);
+    if (p2p_) return p2p_->recv(buf, count, dtype, src, stream);
+    return p2p_plan_exec(false, src, nullptr, buf, count, dtype, stream);
+}
+
+HcclResult Communicator::batch_send_recv(HcclSendRecvItem *items, uint32_t n, void *stream)
+{
+    std::lock_guard<std::mutex> lk(op_mu_);
+    CHK_RET(check_ready());
+    CHK_RET_LOG(all_local_, HCCL_E_NOT_SUPPORT, "use the local send/recv entry on all-local communicators");
+    StateGuard guard(state_, CS_INUSE);
+    stats_.ops[COLL_BATCH_SENDRECV]++;
+    int me = rank(), p = nranks_;
+    // Pairwise ordering relative to this rank (reference: coll_batch_send_recv_executor.cc): sends ordered by
+    // (dest - me) mod p, receives by (me - src) mod p, so that matching pairs meet in the same round everywhere.
+    std::vector<HcclSendRecvItem *> sends, recvs;
+    for (uint32_t i = 0; i < n; ++i) (items[i].sendRecvType == HCCL_SEND ? sends : recvs).push_back(&items[i]);
+    std::stable_sort(sends.begin(), sends.end(), [&](auto *a, auto *b) { return (a->remoteRank + p - me) % p < (b->remoteRank + p - me) % p; });
+    std::stable_sort(recvs.begin(), recvs.end(), [&](auto *a, auto *b) { return (me + p - a->remoteRank) % p < (me + p - b->remoteRank) % p; });
+    // a send to self paired with a receive from self is a local copy
+    for (auto si = sends.begin(); si != sends.end();) {
+        if ((int)(*si)->remoteRank != me) { ++si; continue; }
+        auto ri = std::find_if(recvs.begin(), recvs.end(), [&](auto *r) { return (int)r->remoteRank == me; });
+        CHK_RET_LOG(ri == recvs.end(), HCCL_E_PARA, "send to self without a matching receive from self");
+        size_t bytes = std::min((*si)->count, (*ri)->count) * dtype_size((*si)->dataType);
+        if (settings_.transport == TR_DEVICE) cudaMemcpyAsync((*ri)->buf, (*si)->buf, bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream);
+        else memmove((*ri)->buf, (*si)->buf, bytes);
+        recvs.erase(ri);
+        si = sends.erase(si);
+    }
+    if (p2p_) return p2p_->batch(sends, recvs, stream);
+    if (settings_.transport == TR_DEVICE) {
+        // mailbox path on the device: interleave in pairwise rounds, each a pair of executor launches on two streams
+        // is unnecessary because every plan launch is asynchronous and short messages fit a mailbox slot
+        HcclResult rc = HCCL_SUCCESS;
+        size_t m = std::max(sends.size(), recvs.size());
+        for (size_t i = 0; i < m && rc == HCCL_SUCCESS; ++i) {
+            if (i < sends.size()) {
+                CHK_RET_LOG(sends[i]->count * dtype_size(sends[i]->dataType) > p2p_slot_, HCCL_E_NOT_SUPPORT,
+                            "BatchSendRecv items above %llu bytes need the NCCL p2p backend", (unsigned long long)p2p_slot_);
+                rc = p2p_plan_exec(true, sends[i]->remoteRank, sends[i]->buf, nullptr, sends[i]->count, sends[i]->dataType, stream);
+            }
+            if (i < recvs.size() && rc == HCCL_SUCCESS)
+                rc = p2p_plan_exec(false, recvs[i]->remoteRank, nullptr, recvs[i]->buf, recvs[i]->count, recvs[i]->dataType, stream);
+        }
+        return rc;
+    }
+    // host transport: sends on a helper thread, receives on the caller (reference: sends on the main stream,
+    // receives on a slave stream), so multi-round transfers in both directions cannot block each other
+    HcclResult src = HCCL_SUCCESS, rrc = HCCL_SUCCESS;
+    std::vector<std::pair<CachedPlan *, HcclSendRecvItem *>> splans;
+    // plans are built on this thread (the cache is not thread safe); execution of the sends moves to the helper
+    for (auto *s : sends) {
+        OpDesc d;
+        d.coll = COLL_SEND; d.algo = ALGO_MESH; d.nranks = p; d.dtype = s->dataType; d.nchan = 2; d.count = s->count;
+        d.peer = (int)s->remoteRank; d.p2p_slot = p2p_slot_;
+        auto pr = std::make_pair(me, (int)s->remoteRank);
+        d.p2p_round0 = p2p_rounds_[pr];
+        int es = dtype_size(s->dataType);
+        uint64_t vec = es >= 16 ? 1 : 16 / es, slotE = (p2p_slot_ / es) / vec * vec;
+        p2p_rounds_[pr] += (uint32_t)ceil_div_u64(s->count, slotE);
+        std::ostringstream key;
+        key << "p2p:1:" << s->remoteRank << ':' << s->dataType << ':' << s->count << ':' << d.p2p_round0;
+        CachedPlan *cp = nullptr;
+        CHK_RET(get_plan(d, key.str(), &cp));
+        splans.push_back({cp, s});
+    }
+    std::thread sender([&] {
+        for (auto &ps : splans) {
+            OpRequest rq;
+            std::vector<const void *> in{ps.second->buf};
+            std::vector<void *> out{nullptr};
+            ExecArgs a;
+            memset(&a, 0, sizeof(a));
+            a.steps = ps.first->plan.steps[0].data(); a.nsteps = (int)ps.first->plan.steps[0].size(); a.nchan = ps.first->plan.nchan;
+            a.in = (const uint8_t *)ps.second->buf; a.dtype = ps.second->dataType;
+            HcclResult r = exec_plan_host(ctx_[0], a);
+            if (r != HCCL_SUCCESS) { src = r; break; }
+        }
+    });
+    for (auto *r : recvs) {
+        rrc = p2p_plan_exec(false, (int)r->remoteRank, nullptr, r->buf, r->count, r->dataType, stream);
+        if (rrc != HCCL_SUCCESS) break;
+    }
+    sender.join();
+    return src != HCCL_SUCCESS ? src : rrc;
+}
+
+HcclResult Communicator::local_send_recv(int src, int dst, const void *sbuf, void *rbuf, uint64_t count, int dtype, void *stream)
+{
+    std::lock_guard<std::mutex> lk(op_mu_);
+    CHK_RET(check_ready());
+    CHK_RET_LOG(!all_local_, HCCL_E_NOT_SUPPORT, "local send/recv needs an all-local communicator");
+    CHK_RET_LOG(src < 0 || dst < 0 || src >= nranks_ || dst >= nranks_ || src == dst, HCCL_E_PARA, "bad rank pair %d -> %d", src, dst);
+    StateGuard guard(state_, CS_INUSE);
+    int es = dtype_size(dtype);
+    uint64_t vec = es >= 16 ? 1 : 16 / es, slotE = (p2p_slot_ / es) / vec * vec;
+    auto pr = std::make_pair(src, dst);
+    OpDesc d;
+    d.algo = ALGO_MESH; d.nranks = nranks_; d.dtype = dtype; d.nchan = 2; d.count = count; d.p2p_slot = p2p_slot_;
+    d.p2p_round0 = p2p_rounds_[pr];
+    p2p_rounds_[pr] += (uint32_t)ceil_div_u64(count, slotE);
+    Plan ps, prv;
+    d.coll = COLL_SEND; d.peer = dst;
+    CHK_RET(build_plan(d, {src}, &ps));
+    d.coll = COLL_RECV; d.peer = src;
+    CHK_RET(build_plan(d, {dst}, &prv));
+    stats_.launches++;
+    ExecArgs a[2];
+    memset(a, 0, sizeof(a));
+    Step *dsteps[2] = {nullptr, nullptr};
+    const Plan *pl[2] = {&ps, &prv};
+    int ranks[2] = {src, dst};
+    bool dev = settings_.transport == TR_DEVICE;
+    for (int i = 0; i < 2; ++i) {
+        const auto &steps = pl[i]->steps[0];
+        if (dev) {
+            cudaMalloc(&dsteps[i], std::max<size_t>(1, steps.size()) * sizeof(Step));
+            cudaMemcpy(dsteps[i], steps.data(), steps.size() * sizeof(Step), cudaMemcpyHostToDevice);
+        }
+        a[i].steps = dev ? dsteps[i] : steps.data();
+        a[i].nsteps = (int)steps.size();
+        a[i].nchan = 2;
+        a[i].dtype = dtype;
+        a[i].in = (const uint8_t *)(i == 0 ? sbuf : nullptr);
+        a[i].out = (uint8_t *)(i == 1 ? rbuf : nullptr);
+    }
+    if (dev) {
+        // the executor indexes contexts by blockIdx.y, so pass a two-entry context array for (src, dst)
+        RankCtx two[2] = {ctx_[src], ctx_[dst]};
+        RankCtx *dtwo = nullptr;
+        cudaMalloc(&dtwo, sizeof(two));
+        cudaMemcpy(dtwo, two, sizeof(two), cudaMemcpyHostToDevice);
+        HcclResult rc = launch_exec_plan(dtwo, a, 2, 2, stream);
+        cudaStreamSynchronize((cudaStream_t)stream);
+        cudaFree(dtwo); cudaFree(dsteps[0]); cudaFree(dsteps[1]);
+        return rc != HCCL_SUCCESS ? rc : check_ready();
+    }
+    HcclResult rcs[2];
+    std::thread t([&] { rcs[0] = exec_plan_host(ctx_[ranks[0]], a[0]); });
+    rcs[1] = exec_plan_host(ctx_[ranks[1]], a[1]);
+    t.join();
+    return rcs[0] != HCCL_SUCCESS ? rcs[0] : rcs[1];
+}
+
+// ------------------------------------------------------------------------------------------------ health
+HcclResult Communicator::suspend()
+{
+    // Raise the abort word polled by every wait (reference: Suspend/StopExec, hccl_communicator.cc:4383-4500).
+    for (auto *a : abort_) *a = 1;
+    state_.store(CS_SUSPENDED);
+    return HCCL_SUCCESS;
+}
+
+HcclResult Communicator::resume()
+{
+    std::lock_guard<std::mutex> lk(op_mu_);
+    return resume_locked();
+}
+
+HcclResult Communicator::resume_locked()
+{
+    bool dev = settings_.transport == TR_DEVICE;
+    if (dev) { cudaSetDevice(settings_.device); cudaDeviceSynchronize(); }
+    int tmo = env_config().connect_timeout_s * 1000;
+    // every rank must have stopped before flags are re-armed, and re-armed before anyone runs again
+    std::string tag = key_prefix_ + "/resume/" + std::to_string(++resume_gen_);
+    std::vector<std::string> seqs;
+    if (!all_local_ && nranks_ > 1) {
+        CHK_RET(hub_->rendezvous(tag + "/a", nranks_, rank(), std::string((const char *)&seq_, 8), &seqs, tmo));
+        uint64_t mx = seq_;
+        for (auto &s : seqs) { uint64_t v; memcpy(&v, s.data(), 8); mx = std::max(mx, v); }
+        seq_ = mx + 2;  // a fresh, common sequence: flags of abandoned ops are all smaller
+    } else seq_ += 2;
+    for (int li = 0; li < nlocal(); ++li) {
+        *abort_[li] = 0;
+        memset(status_[li], 0, sizeof(DevStatus));
+        // done words restart at the new sequence so the first ops after resume do not wait for abandoned ones
+        std::vector<uint64_t> done(kMaxRanks, seq_);
+        uint8_t *dst = (uint8_t *)(ctx_[li].flags[ctx_[li].rank] + done_index(0));
+        if (dev) cudaMemcpy(dst, done.data(), kMaxRanks * 8, cudaMemcpyHostToDevice);
+        else memcpy(dst, done.data(), kMaxRanks * 8);
+    }
+    remote_error_.store(0);
+    remote_bad_rank_.store(-1);
+    if (!all_local_ && nranks_ > 1) CHK_RET(hub_->barrier(tag + "/b", nranks_, rank(), tmo));
+    state_.store(CS_IDLE);
+    return HCCL_SUCCESS;
+}
+
+HcclResult Communicator::async_error()
+{
+    for (auto *s : status_)
+        if (s && s->code != 0) return (HcclResult)s->code;
+    uint32_t re = remote_error_.load();
+    return (HcclResult)re;
+}
+
+HcclResult Communicator::sync_stream(void *stream)
+{
+    if (settings_.transport == TR_DEVICE) {
+        cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream);
+        CHK_RET_LOG(e != cudaSuccess, HCCL_E_RUNTIME, "stream synchronize failed: %s", cudaGetErrorString(e));
+    }
+    return async_error();
+}
+
+void Communicator::heartbeat_loop()
+{
+    const EnvConfig &env = env_config();
+    uint64_t last_head = 0, last_tail = 0;
+    double stuck_since = 0;
+    while (!hb_stop_.load()) {
+        HeartbeatMsg m;
+        memset(&m, 0, sizeof(m));
+        m.rank = (uint32_t)rank(); m.nranks = (uint32_t)nranks_;
+        m.lost_ms = (uint32_t)env.heartbeat_lost_ms;
+        DevStatus *s = status_[0];
+        m.head = s->head; m.tail = s->tail;
+        m.status = PEER_OK;
+        if (s->code != 0) { m.status = PEER_ERROR; m.error_code = s->code; }
+        // stuck: an op started (head) and its completion (tail) has not followed for the configured time
+        // (reference: Heartbeat::StuckDetection, heartbeat.cc:1073-1104, comparing OpExeCounter head/tail)
+        if (m.head != m.tail && m.head == last_head && m.tail == last_tail) {
+            if (stuck_since == 0) stuck_since = now_us();
+            else if (now_us() - stuck_since > env.stuck_ms * 1e3 && m.status == PEER_OK) m.status = PEER_STUCK;
+        } else stuck_since = 0;
+        last_head = m.head; last_tail = m.tail;
+        if (!fault::drop_heartbeat(rank())) {
+            HeartbeatSummary sum;
+            HcclResult rc = hb_conn_->heartbeat(key_prefix_ + "/hb", m, &sum, std::max(1000, env.heartbeat_lost_ms));
+            if (rc != HCCL_SUCCESS) {
+                // the hub lives in the root rank's process: losing it means the root is gone
+                if (!hb_stop_.load() && remote_error_.load() == 0) {
+                    remote_bad_rank_.store(0);
+                    remote_error_.store(HCCL_E_REMOTE);
+                    for (auto *a : abort_) if (*a == 0) *a = 2;
+                    HLOG_ERROR("heartbeat: bootstrap hub (rank 0) unreachable");
+                }
+            } else if (sum.first_bad_rank != 0xffffffffu && (int)sum.first_bad_rank != rank()) {
+                if (remote_error_.load() == 0) {
+                    uint32_t st = sum.status[sum.first_bad_rank];
+                    uint32_t code = st == PEER_STUCK ? HCCL_E_TIMEOUT : HCCL_E_REMOTE;
+                    remote_bad_rank_.store((int)sum.first_bad_rank);
+                    remote_error_.store(code);
+                    for (auto *a : abort_) if (*a == 0) *a = 2;  // in-flight waits give up instead of running into their bound
+                    HLOG_ERROR("heartbeat: rank %u reported %s", sum.first_bad_rank, st == PEER_LOST ? "lost" : st == PEER_STUCK ? "stuck" : "error");
+                }
+            }
+        }
+        std::unique_lock<std::mutex> lk(hb_mu_);
+        hb_cv_.wait_for(lk, std::chrono::milliseconds(env.heartbeat_ms), [&] { return hb_stop_.load(); });
+    }
+}
+
+HcclResult Communicator::maybe_retry(const OpRequest &rq, HcclResult failure)
+{
+    // Operator retry (reference: cluster_maintenance/recovery/operator_retry, max 3 attempts): every rank that
+    // failed meets at the hub, agrees that all members failed the same op and can re-run it (input untouched),
+    // re-arms flags under a common new sequence and executes the op again.
+    const EnvConfig &env = env_config();
+    if (!env.retry_enable || all_local_ || nranks_ == 1) return failure;
+    bool inplace = false;
+    for (int li = 0; li < nlocal(); ++li)
+        if (rq.in && rq.out && rq.in[li] == rq.out[li] && rq.coll != COLL_BROADCAST) inplace = true;
+    HcclResult rc = failure;
+    for (int attempt = 1; attempt <= env.retry_max && rc != HCCL_SUCCESS; ++attempt) {
+        struct Vote { uint64_t op_index; uint32_t can_retry; uint32_t code; } v{op_index_, inplace ? 0u : 1u, (uint32_t)rc};
+        std::vector<std::string> votes;
+        char tag[96];
+        snprintf(tag, sizeof(tag), "/retry/%llu/%d", (unsigned long long)op_index_, attempt);
+        int tmo = env.retry_hold_ms + (int)(ctx_[0].timeout_ns / 1000000) + 2000;
+        HcclResult rr = hub_->rendezvous(key_prefix_ + tag, nranks_, rank(), std::string((const char *)&v, sizeof(v)), &votes, tmo);
+        if (rr != HCCL_SUCCESS) return failure;  // not everyone arrived: some rank did not fail this op or is gone
+        bool ok = true;
+        for (auto &s : votes) {
+            Vote o;
+            memcpy(&o, s.data(), sizeof(o));
+            ok &= o.op_index == op_index_ && o.can_retry;
+        }
+        if (!ok) { HLOG_ERROR("op %llu cannot be retried (in-place input or ranks out of step)", (unsigned long long)op_index_); return failure; }
+        usleep((useconds_t)env.retry_interval_ms * 1000);
+        state_.store(CS_SUSPENDED);
+        HcclResult rs = resume_locked();
+        if (rs != HCCL_SUCCESS) return failure;
+        state_.store(CS_INUSE);
+        stats_.retries++;
+        HLOG_WARN("retrying %s (attempt %d of %d)", coll_name(rq.coll), attempt, env.retry_max);
+        rc = run_collective_once(rq);
+    }
+    return rc;
+}
+
+// ------------------------------------------------------------------------------------------------ symmetric user memory
+HcclResult Communicator::sym_alloc(size_t bytes, void **local_ptrs, int *handle)
+{
+    std::lock_guard<std::mutex> lk(op_mu_);
+    StateGuard guard(state_, CS_BUILDING);
+    std::vector<SymSegment> segs;
+    CHK_RET(alloc_->alloc(bytes, true, &segs));
+    for (int li = 0; li < nlocal(); ++li) local_ptrs[li] = segs[li].peer[local_ranks_[li]];
+    *handle = next_handle_++;
+    user_segs_[*handle] = std::move(segs);
+    return HCCL_SUCCESS;
+}
+HcclResult Communicator::sym_free(int handle)
+{
+    std::lock_guard<std::mutex> lk(op_mu_);
+    auto it = user_segs_.find(handle);
+    if (it == user_segs_.end()) return HCCL_E_NOT_FOUND;
+    if (!all_local_ && nranks_ > 1) hub_->barrier(key_prefix_ + "/symfree/" + std::to_string(handle), nranks_, rank(), 10000);
+    alloc_->release(&it->second);
+    user_segs_.erase(it);
+    return HCCL_SUCCESS;
+}
+HcclResult Communicator::sym_query(int handle, void **peer_ptrs, void **mc_ptrs, size_t *bytes)
+{
+    auto it = user_segs_.find(handle);
+    if (it == user_segs_.end()) return HCCL_E_NOT_FOUND;
+    for (int li = 0; li < nlocal(); ++li) {
+        for (int q = 0; q < nranks_; ++q) peer_ptrs[li * nranks_ + q] = it->second[li].peer[q];
+        if (mc_ptrs) mc_ptrs[li] = it->second[li].mc;
+    }
+    if (bytes) *bytes = it->second[0].bytes;
+    return HCCL_SUCCESS;
+}
+
+HcclResult Communicator::exchange_p2p(const std::string &tag, const std::string &mine, std::vector<std::string> *all)
+{
+    if (!p2p_conn_) return HCCL_E_UNAVAIL;
+    return p2p_conn_->rendezvous(key_prefix_ + "/p2p/" + tag, nranks_, rank(), mine, all, env_config().connect_timeout_s * 1000);
+}
+
+HcclResult Communicator::exchange(const std::string &tag, const std::string &mine, std::vector<std::string> *all)
+{
+    if (all_local_ || nranks_ == 1) { all->assign(1, mine); return HCCL_SUCCESS; }
+    return hub_->rendezvous(key_prefix_ + "/x/" + tag, nranks_, rank(), mine, all, env_config().connect_timeout_s * 1000);
+}
+
+}  // namespace hcclb

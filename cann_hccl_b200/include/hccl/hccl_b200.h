@@ -1,0 +1,88 @@
+/*
+ * Extensions of the HCCL-compatible API that exist only in the B200 library:
+ * the rooted Gather and the count-matrix AlltoAllVC that HCCL keeps internal, all-local communicators
+ * (every rank a virtual rank of one GPU or a CPU thread; used for single-GPU validation of the multi-rank
+ * kernels), forced-algorithm collectives, symmetric memory, selector / statistics / trace queries, and the
+ * fused tensor-parallel and MoE kernels.
+ */
+#ifndef HCCL_B200_H_
+#define HCCL_B200_H_
+#include "hccl.h"
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Collective kinds and algorithm ids accepted by HcclB200Collective / HcclB200Select. */
+enum { HCCL_B200_ALLREDUCE = 0, HCCL_B200_BROADCAST, HCCL_B200_REDUCE_SCATTER, HCCL_B200_REDUCE_SCATTER_V,
+       HCCL_B200_SCATTER, HCCL_B200_ALLGATHER, HCCL_B200_ALLGATHER_V, HCCL_B200_BARRIER, HCCL_B200_ALLTOALL,
+       HCCL_B200_ALLTOALLV, HCCL_B200_ALLTOALLVC, HCCL_B200_REDUCE, HCCL_B200_GATHER };
+enum { HCCL_B200_ALGO_AUTO = 0, HCCL_B200_ALGO_MESH, HCCL_B200_ALGO_MESH_ONESHOT, HCCL_B200_ALGO_RING,
+       HCCL_B200_ALGO_RHD, HCCL_B200_ALGO_PAIRWISE, HCCL_B200_ALGO_STAR, HCCL_B200_ALGO_TREE, HCCL_B200_ALGO_NVLS,
+       HCCL_B200_ALGO_NVLS_ONESHOT, HCCL_B200_ALGO_SINGLE };
+
+typedef struct HcclB200OpDef {
+    int32_t coll;       /* HCCL_B200_* collective */
+    int32_t algo;       /* HCCL_B200_ALGO_*, AUTO lets the selector decide */
+    int32_t nchan;      /* CTAs per rank, 0 = selector */
+    int32_t dataType;   /* HcclDataType */
+    int32_t op;         /* HcclReduceOp */
+    int32_t root;
+    uint64_t count;     /* per-API count (see hccl.h) */
+    const uint64_t *counts, *displs;                       /* AllGatherV / ReduceScatterV, nRanks entries */
+    const uint64_t *sendCounts, *sdispls, *recvCounts, *rdispls; /* AlltoAllV: [local ranks][nRanks] */
+} HcclB200Op;
+
+/* Rooted gather: root's recvBuf receives nRanks blocks of sendCount elements in rank order. */
+extern HcclResult HcclGather(void *sendBuf, void *recvBuf, uint64_t sendCount, HcclDataType dataType, uint32_t root,
+                             HcclComm comm, aclrtStream stream);
+/* AlltoAll with the full nRanks x nRanks send-count matrix (row i = counts rank i sends), blocks packed in rank order. */
+extern HcclResult HcclAlltoAllVC(const void *sendBuf, const void *sendCountMatrix, HcclDataType sendType,
+                                 const void *recvBuf, HcclDataType recvType, HcclComm comm, aclrtStream stream);
+
+/* All ranks in this process: transport 0 = host memory + threads, 1 = virtual ranks on `device`. */
+extern HcclResult HcclB200CommInitLocal(uint32_t nRanks, int transport, int device, const HcclCommConfig *config,
+                                        HcclComm *comm);
+/* Generic collective entry; sendBufs / recvBufs hold one pointer per local rank. */
+extern HcclResult HcclB200Collective(HcclComm comm, const HcclB200Op *op, void *const *sendBufs, void *const *recvBufs,
+                                     aclrtStream stream);
+extern HcclResult HcclB200LocalSendRecv(HcclComm comm, uint32_t src, uint32_t dst, const void *sendBuf, void *recvBuf,
+                                        uint64_t count, HcclDataType dataType, aclrtStream stream);
+/* Wait for the stream and return the status the kernels left (HCCL_E_TIMEOUT, HCCL_E_SUSPENDING, ...). */
+extern HcclResult HcclB200StreamSync(HcclComm comm, aclrtStream stream);
+
+typedef struct HcclB200StatusDef {
+    uint32_t code, step; int32_t peer; uint32_t chan;
+    uint64_t expected, seen, seq, head, tail;
+} HcclB200Status;
+extern HcclResult HcclB200GetStatus(HcclComm comm, uint32_t localRank, HcclB200Status *status);
+/* Human readable decoding of a status block (role of the reference's task exception handler). */
+extern HcclResult HcclB200DescribeStatus(HcclComm comm, uint32_t localRank, char *text, size_t cap);
+
+extern HcclResult HcclB200Select(HcclComm comm, int32_t coll, uint64_t count, HcclDataType dataType, HcclReduceOp op,
+                                 int32_t *algo, int32_t *nchan, double *estimateUs);
+extern HcclResult HcclB200GetStatsJson(HcclComm comm, char *json, size_t cap);
+extern HcclResult HcclB200GetTraceJson(HcclComm comm, char *json, size_t cap);
+extern HcclResult HcclB200Calibrate(HcclComm comm, aclrtStream stream);
+extern HcclResult HcclB200SetCostModel(HcclComm comm, double alphaUs, double betaGBps, double nvlsGBps, double gammaGBps,
+                                       double launchUs);
+extern const char *HcclB200GetLastError(void);
+extern const char *HcclB200AlgoName(int32_t algo);
+extern HcclResult HcclB200HasNvls(HcclComm comm, int32_t *has);
+extern HcclResult HcclB200GetLocalRankNum(HcclComm comm, uint32_t *n);
+
+/* Symmetric memory: same-size allocation on every rank, peers mapped.  localPtrs gets one pointer per local rank. */
+extern HcclResult HcclB200MemAlloc(HcclComm comm, size_t bytes, void **localPtrs, int32_t *handle);
+extern HcclResult HcclB200MemFree(HcclComm comm, int32_t handle);
+/* peerPtrs[local * nRanks + q] = rank q's copy as mapped for the local rank; mcPtrs[local] = multicast mapping or NULL. */
+extern HcclResult HcclB200MemQuery(HcclComm comm, int32_t handle, void **peerPtrs, void **mcPtrs, size_t *bytes);
+/* All-gather `len` bytes per rank over the bootstrap hub (control plane; not for bulk data). */
+extern HcclResult HcclB200Exchange(HcclComm comm, const char *tag, const void *mine, size_t len, void *all);
+/* Context handed to custom kernels (role of the reference's MC2 resource export, op_base.cc:3137-3284):
+ * device array of per-local-rank contexts with peer staging / flag pointers, plus the next op sequence number. */
+extern HcclResult HcclB200GetDeviceContext(HcclComm comm, void **devCtxArray, uint64_t *nextSeq);
+extern HcclResult HcclB200ReloadEnv(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
