@@ -419,11 +419,13 @@ void rs_rhd(Prog &P, const Slots &S, uint64_t out_off)
         return S.st_off[lo];
     };
     hd_reduce_scatter(P, H, off, [](int) { return ~0ull; });
+    std::vector<int> lastidx(p);
+    for (int r = 0; r < p; ++r) lastidx[r] = P.last(r);
     for (int r = 0; r < p; ++r) {
         bool odd_p1 = r < H.part1 && (r & 1);
         int owner = odd_p1 ? r - 1 : r;
         Step st = P.copy(BUF_STAGE, owner == r ? RANK_SELF : owner, S.st_off[r], BUF_OUT, RANK_SELF, out_off, S.len[r]);
-        if (owner != r) P.wait_allch(st, owner, P.last(owner));
+        if (owner != r) P.wait_allch(st, owner, lastidx[owner]);
         P.add(r, st);
     }
 }

@@ -120,6 +120,7 @@ bool Hub::handle_frame(int fd)
             if (st == PEER_OK && now - it->second.last_ms > it->second.msg.lost_ms) st = PEER_LOST;
             s.status[r] = st;
             s.error_code[r] = it->second.msg.error_code;
+            s.epoch[r] = it->second.msg.epoch;
             if (st != PEER_OK && s.first_bad_rank == 0xffffffffu) s.first_bad_rank = r;
         }
         ReplyHdr r{kHubMagic, HCCL_SUCCESS, (uint32_t)sizeof(s)};

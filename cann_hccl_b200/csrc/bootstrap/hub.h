@@ -31,11 +31,12 @@ struct HeartbeatMsg {
     uint32_t error_code;  // HcclResult when status == PEER_ERROR
     uint64_t head, tail;  // op-execution counters
     uint32_t lost_ms;     // silence after which the hub declares this group's members lost
-    uint32_t pad;
+    uint32_t epoch;       // number of resumes the rank has gone through; older reports are stale
 };
 struct HeartbeatSummary {
     uint32_t status[16];      // per rank PeerHealth as the hub sees it
     uint32_t error_code[16];  // per rank last reported error
+    uint32_t epoch[16];       // per rank resume epoch of that report
     uint32_t first_bad_rank;  // 0xffffffff when all fine
     uint32_t pad;
 };

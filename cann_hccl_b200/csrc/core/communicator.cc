@@ -422,13 +422,17 @@ std::string Communicator::stats_json()
 HcclResult Communicator::collective(const OpRequest &rq)
 {
     std::lock_guard<std::mutex> lk(op_mu_);
-    CHK_RET(check_ready());
-    StateGuard guard(state_, CS_INUSE);
     double t0 = now_us();
     ++op_index_;
     fault::before_op(rank(), op_index_);
     if (fault_hook_) fault_hook_(op_index_);
-    HcclResult rc = run_collective_once(rq);
+    HcclResult ready = check_ready();
+    // a failure reported by a peer while this rank was between ops counts as a failure of this op: with operator
+    // retry enabled the rank joins the peers' retry round instead of giving up
+    bool peer_failed = ready != HCCL_SUCCESS && remote_error_.load() == (uint32_t)ready && env_config().retry_enable;
+    if (ready != HCCL_SUCCESS && !peer_failed) return ready;
+    StateGuard guard(state_, CS_INUSE);
+    HcclResult rc = peer_failed ? ready : run_collective_once(rq);
     if (rc != HCCL_SUCCESS && (rc == HCCL_E_TIMEOUT || rc == HCCL_E_REMOTE)) {
         stats_.timeouts++;
         rc = maybe_retry(rq, rc);
@@ -779,7 +783,8 @@ HcclResult Communicator::resume_locked()
     if (dev) { cudaSetDevice(settings_.device); cudaDeviceSynchronize(); }
     int tmo = env_config().connect_timeout_s * 1000;
     // every rank must have stopped before flags are re-armed, and re-armed before anyone runs again
-    std::string tag = key_prefix_ + "/resume/" + std::to_string(++resume_gen_);
+    uint64_t gen = resume_gen_.load() + 1;
+    std::string tag = key_prefix_ + "/resume/" + std::to_string(gen);
     std::vector<std::string> seqs;
     if (!all_local_ && nranks_ > 1) {
         CHK_RET(hub_->rendezvous(tag + "/a", nranks_, rank(), std::string((const char *)&seq_, 8), &seqs, tmo));
@@ -788,7 +793,6 @@ HcclResult Communicator::resume_locked()
         seq_ = mx + 2;  // a fresh, common sequence: flags of abandoned ops are all smaller
     } else seq_ += 2;
     for (int li = 0; li < nlocal(); ++li) {
-        *abort_[li] = 0;
         memset(status_[li], 0, sizeof(DevStatus));
         // done words restart at the new sequence so the first ops after resume do not wait for abandoned ones
         std::vector<uint64_t> done(kMaxRanks, seq_);
@@ -796,8 +800,13 @@ HcclResult Communicator::resume_locked()
         if (dev) cudaMemcpy(dst, done.data(), kMaxRanks * 8, cudaMemcpyHostToDevice);
         else memcpy(dst, done.data(), kMaxRanks * 8);
     }
+    if (dev && dev_exit_) cudaMemset(dev_exit_, 0, sizeof(uint32_t) * 2 * nlocal());
+    // order matters for the heartbeat thread: own status is clean, then the epoch moves (peers' older error reports
+    // become stale), then what it may have recorded from those reports is dropped
+    resume_gen_.store(gen);
     remote_error_.store(0);
     remote_bad_rank_.store(-1);
+    for (int li = 0; li < nlocal(); ++li) *abort_[li] = 0;
     if (!all_local_ && nranks_ > 1) CHK_RET(hub_->barrier(tag + "/b", nranks_, rank(), tmo));
     state_.store(CS_IDLE);
     return HCCL_SUCCESS;
@@ -830,6 +839,7 @@ void Communicator::heartbeat_loop()
         memset(&m, 0, sizeof(m));
         m.rank = (uint32_t)rank(); m.nranks = (uint32_t)nranks_;
         m.lost_ms = (uint32_t)env.heartbeat_lost_ms;
+        m.epoch = (uint32_t)resume_gen_.load();
         DevStatus *s = status_[0];
         m.head = s->head; m.tail = s->tail;
         m.status = PEER_OK;
@@ -852,8 +862,13 @@ void Communicator::heartbeat_loop()
                     for (auto *a : abort_) if (*a == 0) *a = 2;
                     HLOG_ERROR("heartbeat: bootstrap hub (rank 0) unreachable");
                 }
-            } else if (sum.first_bad_rank != 0xffffffffu && (int)sum.first_bad_rank != rank()) {
-                if (remote_error_.load() == 0) {
+            } else {
+                // first peer whose bad report is current (reports from before this rank's last resume are stale)
+                int bad = -1;
+                for (int q = 0; q < nranks_ && bad < 0; ++q)
+                    if (q != rank() && sum.status[q] != PEER_OK && (sum.status[q] == PEER_LOST || sum.epoch[q] >= m.epoch)) bad = q;
+                if (bad >= 0 && remote_error_.load() == 0 && m.epoch == (uint32_t)resume_gen_.load()) {
+                    sum.first_bad_rank = (uint32_t)bad;
                     uint32_t st = sum.status[sum.first_bad_rank];
                     uint32_t code = st == PEER_STUCK ? HCCL_E_TIMEOUT : HCCL_E_REMOTE;
                     remote_bad_rank_.store((int)sum.first_bad_rank);

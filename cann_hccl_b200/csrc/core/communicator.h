@@ -183,7 +183,7 @@ private:
     std::mutex op_mu_;
     std::atomic<int> state_{CS_IDLE};
     uint64_t seq_ = 1;
-    uint64_t resume_gen_ = 0;
+    std::atomic<uint64_t> resume_gen_{0};
     std::map<std::string, CachedPlan> plans_;
     std::map<std::string, bool> checked_;
     std::map<std::pair<int, int>, uint32_t> p2p_rounds_;  // (src,dst) -> rounds exchanged

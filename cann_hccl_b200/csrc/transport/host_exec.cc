@@ -26,7 +26,7 @@ struct Waiter {
             seen = __atomic_load_n(p, __ATOMIC_ACQUIRE);
             if (seen >= want) return 0;
             if ((it & 63) == 63) {
-                if (c.abort && *c.abort) return HCCL_E_SUSPENDING;
+                if (c.abort && *c.abort) return *c.abort == 2 ? HCCL_E_REMOTE : HCCL_E_SUSPENDING;
                 if (now_ns() > deadline) return HCCL_E_TIMEOUT;
                 sched_yield();
             }

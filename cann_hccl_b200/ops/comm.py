@@ -33,7 +33,7 @@ class Communicator:
     def get_root_info():
         info = L.RootInfo()
         L.check(L.lib().HcclGetRootInfo(C.byref(info)), "HcclGetRootInfo")
-        return bytes(info.internal)
+        return C.string_at(C.addressof(info), L.HCCL_ROOT_INFO_BYTES)
 
     @classmethod
     def init_root(cls, nranks, root_info, rank, config=None, device=None):

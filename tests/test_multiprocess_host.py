@@ -1,0 +1,65 @@
+"""Multi-process CPU ranks over the host-memory transport: bootstrap, C API signatures, p2p, sub-communicators,
+consistency checking, and the failure paths (all failures are produced on the host)."""
+import pytest
+
+from mp_util import run_ranks
+
+
+def test_baseline_config_a_allreduce_ring_8mb_world2():
+    res = run_ranks(2, "allreduce_ring_8mb")
+    assert all("check_result: success" in out for _, out in res)
+
+
+@pytest.mark.parametrize("p", [2, 3, 4])
+def test_c_api_sweep(p):
+    res = run_ranks(p, "sweep")
+    assert all("sweep ok" in out for _, out in res)
+
+
+@pytest.mark.parametrize("p", [2, 4])
+def test_send_recv_batch(p):
+    res = run_ranks(p, "sendrecv")
+    assert all("sendrecv ok" in out for _, out in res)
+
+
+def test_sub_communicator():
+    res = run_ranks(4, "subcomm")
+    assert all("subcomm ok" in out for _, out in res)
+
+
+def test_param_mismatch_detected():
+    res = run_ranks(3, "mismatch")
+    assert all("mismatch detected" in out for _, out in res)
+
+
+def test_bounded_wait_times_out_when_peer_absent():
+    res = run_ranks(3, "timeout_absent_peer", env={"HCCL_EXEC_TIMEOUT_MS": "400", "HCCL_CONSISTENCY_CHECK": "0"}, args=[2.0])
+    assert "timeout after" in res[0][1] and "timeout after" in res[2][1]
+    assert "waiting for rank 1" in res[0][1]
+
+
+def test_operator_retry_after_stall():
+    env = {"HCCL_EXEC_TIMEOUT_MS": "500", "HCCL_OP_RETRY_ENABLE": "L0:1", "HCCL_OP_RETRY_PARAMS": "MaxCnt:3,HoldTime:3000,IntervalTime:50",
+           "HCCL_FAULT_INJECT": "stall_rank:rank=1,op=2,ms=1500", "HCCL_CONSISTENCY_CHECK": "0"}
+    res = run_ranks(2, "retry", env=env)
+    assert all("retries:" in out for _, out in res)
+
+
+def test_peer_exit_is_reported():
+    env = {"HCCL_EXEC_TIMEOUT_MS": "3000", "HCCL_FAULT_INJECT": "exit_rank:rank=2,op=2", "HCCL_HEARTBEAT_LOST_MS": "300",
+           "HCCL_HEARTBEAT_INTERVAL_MS": "50", "HCCL_CONSISTENCY_CHECK": "0"}
+    res = run_ranks(3, "peer_exit", env=env, expect_fail_ranks=(2,))
+    assert res[2][0] == 17
+    assert "peer loss seen" in res[0][1] and "peer loss seen" in res[1][1]
+
+
+def test_suspend_resume():
+    res = run_ranks(2, "suspend_resume")
+    assert all("suspend/resume ok" in out for _, out in res)
+
+
+def test_stuck_detection_via_heartbeat():
+    env = {"HCCL_EXEC_TIMEOUT_MS": "4000", "HCCL_STUCK_DETECT_MS": "500", "HCCL_HEARTBEAT_INTERVAL_MS": "50",
+           "HCCL_CONSISTENCY_CHECK": "0"}
+    res = run_ranks(2, "stuck", env=env)
+    assert "stuck peer reported" in res[1][1]
