@@ -641,6 +641,11 @@ HcclResult HcclB200StreamSync(HcclComm comm, aclrtStream stream)
     GET_COMM("HcclB200StreamSync");
     return c->sync_stream(stream);
 }
+HcclResult HcclB200WaitProbe(HcclComm comm, uint32_t localRank, double timeoutMs, aclrtStream stream)
+{
+    GET_COMM("HcclB200WaitProbe");
+    return c->wait_probe((int)localRank, timeoutMs, stream);
+}
 HcclResult HcclB200GetStatus(HcclComm comm, uint32_t localRank, HcclB200Status *st)
 {
     GET_COMM("HcclB200GetStatus");

@@ -829,6 +829,42 @@ HcclResult Communicator::sync_stream(void *stream)
     return async_error();
 }
 
+HcclResult Communicator::wait_probe(int local, double timeout_ms, void *stream)
+{
+    std::lock_guard<std::mutex> lk(op_mu_);
+    CHK_RET_LOG(local < 0 || local >= nlocal() || nranks_ < 2, HCCL_E_PARA, "wait probe needs a valid local rank and at least two ranks");
+    Step s;
+    memset(&s, 0, sizeof(s));
+    s.op = ST_NOP;
+    s.a_buf = s.b_buf = s.d_buf = s.d2_buf = BUF_NONE;
+    s.a_rank = s.b_rank = s.d_rank = RANK_SELF;
+    s.sig_rank = RANK_NONE;
+    s.wait_rank = (int16_t)((ctx_[local].rank + 1) % nranks_);
+    s.wait_val = 0xFFFFFu;  // a step value no plan ever signals
+    s.chan_lo = 0; s.chan_n = 1;
+    ExecArgs a;
+    memset(&a, 0, sizeof(a));
+    a.nsteps = 1; a.nchan = 1; a.seq = seq_ + 1000000; a.dtype = HCCL_DATA_TYPE_FP32;
+    RankCtx x = ctx_[local];
+    x.timeout_ns = (uint64_t)(timeout_ms * 1e6);
+    if (settings_.transport != TR_DEVICE) {
+        a.steps = &s;
+        return exec_plan_host(x, a);
+    }
+    Step *ds = nullptr;
+    RankCtx *dx = nullptr;
+    CHK_RET_LOG(cudaMalloc(&ds, sizeof(s)) != cudaSuccess || cudaMalloc(&dx, sizeof(x)) != cudaSuccess, HCCL_E_MEMORY, "cudaMalloc failed");
+    cudaMemcpy(ds, &s, sizeof(s), cudaMemcpyHostToDevice);
+    cudaMemcpy(dx, &x, sizeof(x), cudaMemcpyHostToDevice);
+    a.steps = ds;
+    HcclResult rc = launch_exec_plan(dx, &a, 1, 1, stream);
+    cudaStreamSynchronize((cudaStream_t)stream);
+    cudaFree(ds);
+    cudaFree(dx);
+    if (rc != HCCL_SUCCESS) return rc;
+    return (HcclResult)status_[local]->code;
+}
+
 void Communicator::heartbeat_loop()
 {
     const EnvConfig &env = env_config();

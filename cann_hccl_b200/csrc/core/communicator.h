@@ -114,6 +114,9 @@ public:
     HcclResult resume_locked();
     HcclResult async_error();  // first error seen by this rank or reported by a peer
     HcclResult sync_stream(void *stream);  // wait for enqueued device work and return its status
+    // Diagnostic: make local rank `local` wait for a flag that no rank ever sets, with a bound of timeout_ms.
+    // The wait must run out and leave HCCL_E_TIMEOUT in the status block; resume() re-arms the communicator.
+    HcclResult wait_probe(int local, double timeout_ms, void *stream);
 
     // Symmetric user memory (zero-copy paths, fused kernels).  Collective over the communicator.
     HcclResult sym_alloc(size_t bytes, void **local_ptrs /*nlocal*/, int *handle);

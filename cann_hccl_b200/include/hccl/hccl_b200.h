@@ -54,6 +54,10 @@ typedef struct HcclB200StatusDef {
     uint32_t code, step; int32_t peer; uint32_t chan;
     uint64_t expected, seen, seq, head, tail;
 } HcclB200Status;
+/* Diagnostic: local rank waits (bounded by timeoutMs) for a flag nothing sets; returns HCCL_E_TIMEOUT and fills the
+ * status block.  The communicator must be resumed afterwards.  Proves that a starved wait ends and leaves the
+ * context usable. */
+extern HcclResult HcclB200WaitProbe(HcclComm comm, uint32_t localRank, double timeoutMs, aclrtStream stream);
 extern HcclResult HcclB200GetStatus(HcclComm comm, uint32_t localRank, HcclB200Status *status);
 /* Human readable decoding of a status block (role of the reference's task exception handler). */
 extern HcclResult HcclB200DescribeStatus(HcclComm comm, uint32_t localRank, char *text, size_t cap);

@@ -208,6 +208,10 @@ class Communicator:
     def sync(self, stream=None):
         return L.lib().HcclB200StreamSync(self._h, self._stream(stream))
 
+    def wait_probe(self, local=0, timeout_ms=200.0, stream=None):
+        """Starve one bounded wait on purpose; returns the result code the wait ended with."""
+        return L.lib().HcclB200WaitProbe(self._h, local, float(timeout_ms), self._stream(stream))
+
     def async_error(self):
         e = C.c_int()
         L.check(L.lib().HcclGetCommAsyncError(self._h, C.byref(e)), "HcclGetCommAsyncError")

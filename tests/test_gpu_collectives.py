@@ -1,0 +1,264 @@
+"""GPU executor kernel: every collective and algorithm with virtual ranks on one GPU (one cooperative launch runs all
+ranks, peers are other regions of the same device), against a plain PyTorch fp32 reference of the same op."""
+import pytest
+
+torch = pytest.importorskip("torch")
+import cann_hccl_b200 as H  # noqa: E402
+from cann_hccl_b200 import _lib as L  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def comms():
+    if not torch.cuda.is_available():
+        pytest.skip("no GPU")
+    cache = {}
+
+    def get(p):
+        if p not in cache:
+            cfg = L.CommConfig.default()
+            cfg.hcclBufferSize = 4
+            cache[p] = H.Communicator.init_local(p, device=True, device_id=0, config=cfg)
+        return cache[p]
+
+    yield get
+    for c in cache.values():
+        assert c.destroy() == L.SUCCESS
+
+
+def ok(c):
+    rc = c.sync()
+    assert rc == 0, c.describe_status()
+
+
+def ref_reduce(ins, op):
+    acc = ins[0].float() if ins[0].dtype in (torch.float16, torch.bfloat16) else ins[0].clone()
+    for x in ins[1:]:
+        y = x.float() if x.dtype in (torch.float16, torch.bfloat16) else x
+        acc = {L.SUM: acc + y, L.PROD: acc * y, L.MAX: torch.maximum(acc, y), L.MIN: torch.minimum(acc, y)}[op]
+    return acc.to(ins[0].dtype)
+
+
+def rnd(p, n, dtype, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    if dtype.is_floating_point:
+        return [(torch.rand(n, device="cuda", generator=g) * 2 - 1).to(dtype) for _ in range(p)]
+    return [torch.randint(-3, 4, (n,), device="cuda", generator=g).to(dtype) for _ in range(p)]
+
+
+def close(a, b, dtype, p):
+    if dtype == torch.float32:
+        torch.testing.assert_close(a, b, rtol=1e-6 * p, atol=1e-6 * p)
+    elif dtype in (torch.float16, torch.bfloat16):
+        torch.testing.assert_close(a.float(), b.float(), rtol=1.6e-2, atol=1.6e-2 * p)
+    else:
+        assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("p", [2, 3, 4, 8])
+@pytest.mark.parametrize("algo", [L.ALGO_MESH_ONESHOT, L.ALGO_MESH, L.ALGO_RING, L.ALGO_RHD])
+@pytest.mark.parametrize("n", [1, 1000, 262147])
+def test_allreduce(comms, p, algo, n):
+    c = comms(p)
+    ins = rnd(p, n, torch.float32)
+    outs = [torch.zeros(n, device="cuda") for _ in range(p)]
+    c.all_reduce(ins, outs, algo=algo)
+    ok(c)
+    ref = ref_reduce(ins, L.SUM)
+    for o in outs:
+        close(o, ref, torch.float32, p)
+
+
+@pytest.mark.parametrize("dtype", [torch.int8, torch.uint8, torch.int16, torch.int32, torch.int64, torch.float16, torch.bfloat16,
+                                   torch.float32, torch.float64])
+@pytest.mark.parametrize("op", [L.SUM, L.PROD, L.MAX, L.MIN])
+def test_allreduce_dtypes_ops(comms, dtype, op):
+    p, n = 4, 4099
+    c = comms(p)
+    if dtype == torch.uint8:
+        ins = [torch.randint(0, 3, (n,), device="cuda", dtype=torch.uint8) for _ in range(p)]
+    else:
+        ins = rnd(p, n, dtype, seed=3)
+    outs = [torch.zeros(n, device="cuda", dtype=dtype) for _ in range(p)]
+    c.all_reduce(ins, outs, op=op, algo=L.ALGO_MESH)
+    ok(c)
+    ref = ref_reduce(ins, op)
+    for o in outs:
+        close(o, ref, dtype, p)
+
+
+def test_allreduce_staging_loop_in_place_unaligned(comms):
+    p = 4
+    c = comms(p)
+    n = 3_000_001  # 12 MB through 4 MB staging halves
+    for algo in (L.ALGO_MESH, L.ALGO_RING, L.ALGO_MESH_ONESHOT, L.ALGO_RHD):
+        base = rnd(p, n + 1, torch.float32, seed=algo)
+        ins = [b[1:] for b in base]  # 4-byte aligned only: the scalar path of the kernel
+        ref = ref_reduce(ins, L.SUM)
+        c.all_reduce(ins, ins, algo=algo)
+        ok(c)
+        for o in ins:
+            close(o, ref, torch.float32, p)
+
+
+@pytest.mark.parametrize("p", [2, 3, 8])
+@pytest.mark.parametrize("algo", [L.ALGO_MESH, L.ALGO_RING, L.ALGO_RHD])
+def test_reduce_scatter_all_gather(comms, p, algo):
+    c = comms(p)
+    n = 5003
+    ins = rnd(p, n * p, torch.bfloat16, seed=1)
+    outs = [torch.zeros(n, device="cuda", dtype=torch.bfloat16) for _ in range(p)]
+    c.reduce_scatter(ins, outs, algo=algo)
+    ok(c)
+    ref = ref_reduce(ins, L.SUM)
+    for r, o in enumerate(outs):
+        close(o, ref[r * n:(r + 1) * n], torch.bfloat16, p)
+    gins = rnd(p, n, torch.int32, seed=2)
+    gouts = [torch.zeros(n * p, device="cuda", dtype=torch.int32) for _ in range(p)]
+    c.all_gather(gins, gouts, algo=algo)
+    ok(c)
+    for o in gouts:
+        assert torch.equal(o, torch.cat(gins))
+
+
+@pytest.mark.parametrize("p", [2, 5, 8])
+def test_rooted(comms, p):
+    c = comms(p)
+    n = 7001
+    for root in (0, p - 1):
+        for algo in (L.ALGO_STAR, L.ALGO_RING, L.ALGO_TREE):
+            bufs = rnd(p, n, torch.float32, seed=root)
+            ref = bufs[root].clone()
+            c.broadcast(bufs, root, algo=algo)
+            ok(c)
+            for b in bufs:
+                assert torch.equal(b, ref)
+        for algo in (L.ALGO_STAR, L.ALGO_RING, L.ALGO_TREE, L.ALGO_RHD):
+            ins = rnd(p, n, torch.float32, seed=9)
+            outs = [torch.zeros(n, device="cuda") for _ in range(p)]
+            c.reduce(ins, outs, root, algo=algo)
+            ok(c)
+            close(outs[root], ref_reduce(ins, L.SUM), torch.float32, p)
+        for algo in (L.ALGO_STAR, L.ALGO_RING):
+            ins = rnd(p, n * p, torch.int32, seed=4)
+            outs = [torch.zeros(n, device="cuda", dtype=torch.int32) for _ in range(p)]
+            c.scatter(ins, outs, root, algo=algo)
+            ok(c)
+            for r in range(p):
+                assert torch.equal(outs[r], ins[root][r * n:(r + 1) * n])
+            gins = rnd(p, n, torch.int32, seed=5)
+            gouts = [torch.zeros(n * p, device="cuda", dtype=torch.int32) for _ in range(p)]
+            c.gather(gins, gouts, root, algo=algo)
+            ok(c)
+            assert torch.equal(gouts[root], torch.cat(gins))
+
+
+@pytest.mark.parametrize("p", [2, 4, 8])
+@pytest.mark.parametrize("algo", [L.ALGO_MESH, L.ALGO_PAIRWISE])
+def test_all_to_all_and_v(comms, p, algo):
+    import numpy as np
+    c = comms(p)
+    n = 513
+    ins = rnd(p, n * p, torch.float32, seed=6)
+    outs = [torch.zeros(n * p, device="cuda") for _ in range(p)]
+    c.all_to_all(ins, outs, algo=algo)
+    ok(c)
+    for r in range(p):
+        for q in range(p):
+            assert torch.equal(outs[r][q * n:(q + 1) * n], ins[q][r * n:(r + 1) * n])
+    rng = np.random.default_rng(7)
+    m = rng.integers(0, 300_000 // p, (p, p)).astype(np.uint64)
+    sd = np.zeros((p, p), np.uint64)
+    rd = np.zeros((p, p), np.uint64)
+    for i in range(p):
+        sd[i] = np.concatenate([[0], np.cumsum(m[i])[:-1]])
+        rd[i] = np.concatenate([[0], np.cumsum(m[:, i])[:-1]])
+    vin = [torch.randn(int(m[i].sum()) + 1, device="cuda") for i in range(p)]
+    vout = [torch.zeros(int(m[:, i].sum()) + 1, device="cuda") for i in range(p)]
+    c.all_to_all_v(vin, m, sd, vout, np.ascontiguousarray(m.T), rd, algo=algo)
+    ok(c)
+    for i in range(p):
+        for j in range(p):
+            assert torch.equal(vout[j][int(rd[j, i]):int(rd[j, i] + m[i, j])], vin[i][int(sd[i, j]):int(sd[i, j] + m[i, j])])
+
+
+def test_v_variants_barrier_sendrecv(comms):
+    import numpy as np
+    p = 4
+    c = comms(p)
+    counts = np.array([5, 0, 1000, 33], np.uint64)
+    displs = np.array([0, 8, 16, 1100], np.uint64)
+    total = 1140
+    ins = [torch.randn(int(counts[r]), device="cuda") for r in range(p)]
+    outs = [torch.full((total,), -1.0, device="cuda") for _ in range(p)]
+    c.all_gather_v(ins, outs, counts, displs, algo=L.ALGO_MESH)
+    ok(c)
+    for o in outs:
+        for j in range(p):
+            assert torch.equal(o[int(displs[j]):int(displs[j] + counts[j])], ins[j])
+    rin = [torch.randn(total, device="cuda") for _ in range(p)]
+    rout = [torch.zeros(max(1, int(counts[r])), device="cuda") for r in range(p)]
+    c.reduce_scatter_v(rin, rout, counts, displs, algo=L.ALGO_RING)
+    ok(c)
+    ref = ref_reduce(rin, L.SUM)
+    for r in range(p):
+        close(rout[r][:int(counts[r])], ref[int(displs[r]):int(displs[r] + counts[r])], torch.float32, p)
+    c.barrier()
+    ok(c)
+    a = torch.randn(200_000, device="cuda")
+    b = torch.zeros_like(a)
+    c.local_send_recv(0, 2, a, b)
+    ok(c)
+    assert torch.equal(a, b)
+
+
+def test_bounded_wait_reports_timeout_and_recovers():
+    """A wait for a flag that nothing sets must end after its bound with HCCL_E_TIMEOUT in the host-visible status
+    block, the CUDA context must stay usable, and the communicator must work again after resume."""
+    import time
+    cfg = L.CommConfig.default()
+    cfg.hcclBufferSize = 1
+    c = H.Communicator.init_local(2, device=True, device_id=0, config=cfg)
+    x = [torch.ones(1024, device="cuda") for _ in range(2)]
+    y = [torch.zeros(1024, device="cuda") for _ in range(2)]
+    c.all_reduce(x, y)
+    assert c.sync() == 0
+    t0 = time.time()
+    assert c.wait_probe(0, timeout_ms=300.0) == L.E_TIMEOUT
+    assert 0.25 < time.time() - t0 < 5.0
+    st = c.status(0)
+    assert st.code == L.E_TIMEOUT and st.peer == 1 and st.seen < st.expected
+    assert "waiting for rank 1" in c.describe_status(0)
+    with pytest.raises(H.HcclError) as e:
+        c.all_reduce(x, y)  # refused until resumed
+    assert e.value.code == L.E_TIMEOUT
+    c.resume()
+    c.all_reduce(x, y)
+    assert c.sync() == 0 and torch.all(y[0] == 2)
+    # suspend: the abort word refuses new work; resume re-arms
+    c.suspend()
+    with pytest.raises(H.HcclError) as e:
+        c.all_reduce(x, y)
+    assert e.value.code == L.E_SUSPENDING
+    c.resume()
+    c.all_reduce(x, y)
+    assert c.sync() == 0
+    assert float(torch.ones(4, device="cuda").sum()) == 4.0  # context still healthy
+    c.destroy()
+
+
+def test_single_rank_c_api_and_stats():
+    c = H.Communicator.init_root(1, H.Communicator.get_root_info(), 0, device=True)
+    x = torch.randn(1 << 18, device="cuda")
+    y = torch.zeros_like(x)
+    c.all_reduce(x, y)
+    ok(c)
+    assert torch.equal(x, y)
+    g = torch.zeros_like(x)
+    c.all_gather(x, g)
+    ok(c)
+    assert torch.equal(x, g)
+    st = c.stats()
+    assert st["launches"] >= 2 and st["ops"]["AllReduce"]["calls"] == 1
+    c.destroy()
