@@ -1,0 +1,165 @@
+"""One GPU rank (one process per GPU) of a multi-GPU scenario; see test_multigpu.py."""
+import os
+import sys
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import torch  # noqa: E402
+
+import cann_hccl_b200 as H  # noqa: E402
+from cann_hccl_b200 import _lib as L  # noqa: E402
+
+
+def make_comm(p, r, root_file):
+    if r == 0:
+        info = H.Communicator.get_root_info()
+        with open(root_file + ".tmp", "wb") as f:
+            f.write(info)
+        os.rename(root_file + ".tmp", root_file)
+    else:
+        t0 = time.time()
+        while not os.path.exists(root_file):
+            assert time.time() - t0 < 60, "root info never appeared"
+            time.sleep(0.01)
+        with open(root_file, "rb") as f:
+            info = f.read()
+    cfg = L.CommConfig.default()
+    cfg.hcclBufferSize = int(os.environ.get("TEST_BUFFSIZE_MB", "16"))
+    return H.Communicator.init_root(p, info, r, config=cfg, device=True)
+
+
+def inp(rank, n, dtype=torch.float32, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(1000 * seed + rank)
+    if dtype.is_floating_point:
+        return (torch.rand(n, device="cuda", generator=g) * 2 - 1).to(dtype)
+    return torch.randint(-3, 4, (n,), device="cuda", generator=g).to(dtype)
+
+
+def red(xs, op):
+    acc = xs[0].float() if xs[0].dtype in (torch.float16, torch.bfloat16) else xs[0].clone()
+    for x in xs[1:]:
+        y = x.float() if x.dtype in (torch.float16, torch.bfloat16) else x
+        acc = {L.SUM: acc + y, L.PROD: acc * y, L.MAX: torch.maximum(acc, y), L.MIN: torch.minimum(acc, y)}[op]
+    return acc.to(xs[0].dtype)
+
+
+def close(a, b, dtype, p):
+    if dtype == torch.float32:
+        torch.testing.assert_close(a, b, rtol=2e-6 * p, atol=2e-6 * p)
+    elif dtype in (torch.float16, torch.bfloat16):
+        torch.testing.assert_close(a.float(), b.float(), rtol=1.6e-2, atol=1.6e-2 * p)
+    else:
+        assert torch.equal(a, b)
+
+
+def ok(c):
+    rc = c.sync()
+    assert rc == 0, c.describe_status()
+
+
+def scenario_collectives(c, p, r, args):
+    nvls = c.has_nvls()
+    print("rank %d: nvls=%s" % (r, nvls))
+    ar_algos = [L.ALGO_AUTO, L.ALGO_MESH_ONESHOT, L.ALGO_MESH, L.ALGO_RING, L.ALGO_RHD] + ([L.ALGO_NVLS, L.ALGO_NVLS_ONESHOT] if nvls else [])
+    for n in (4, 1000, 262144, 6_000_000):  # the last one runs the staging loop (24 MB through 16 MB halves)
+        for algo in ar_algos:
+            if algo in (L.ALGO_NVLS, L.ALGO_NVLS_ONESHOT) and (n * 4) % 16:
+                continue
+            for dtype, op in ((torch.float32, L.SUM), (torch.bfloat16, L.SUM), (torch.bfloat16, L.MAX), (torch.int32, L.MIN)):
+                if algo in (L.ALGO_NVLS, L.ALGO_NVLS_ONESHOT) and (n * dtype.itemsize) % 16:
+                    continue
+                if n > 1_000_000 and dtype != torch.float32:
+                    continue
+                xs = [inp(q, n, dtype, seed=n % 97) for q in range(p)]
+                out = torch.zeros(n, device="cuda", dtype=dtype)
+                c.all_reduce(xs[r], out, op=op, algo=algo)
+                ok(c)
+                close(out, red(xs, op), dtype, p)
+    for algo in [L.ALGO_MESH, L.ALGO_RING, L.ALGO_RHD] + ([L.ALGO_NVLS] if nvls else []):
+        n = 40_000
+        xs = [inp(q, n * p, torch.float32, seed=3) for q in range(p)]
+        out = torch.zeros(n, device="cuda")
+        c.reduce_scatter(xs[r], out, algo=algo)
+        ok(c)
+        close(out, red(xs, L.SUM)[r * n:(r + 1) * n], torch.float32, p)
+        g = torch.zeros(n * p, device="cuda", dtype=torch.bfloat16)
+        gs = [inp(q, n, torch.bfloat16, seed=4) for q in range(p)]
+        c.all_gather(gs[r], g, algo=algo)
+        ok(c)
+        assert torch.equal(g, torch.cat(gs))
+    for root in (0, p - 1):
+        for algo in [L.ALGO_STAR, L.ALGO_RING, L.ALGO_TREE] + ([L.ALGO_NVLS] if nvls else []):
+            b = inp(r, 50_000, torch.float32, seed=5)
+            c.broadcast(b, root, algo=algo)
+            ok(c)
+            assert torch.equal(b, inp(root, 50_000, torch.float32, seed=5))
+        for algo in (L.ALGO_STAR, L.ALGO_RING, L.ALGO_TREE, L.ALGO_RHD):
+            xs = [inp(q, 50_000, torch.float32, seed=6) for q in range(p)]
+            out = torch.zeros(50_000, device="cuda")
+            c.reduce(xs[r], out, root, algo=algo)
+            ok(c)
+            if r == root:
+                close(out, red(xs, L.SUM), torch.float32, p)
+    n = 3000
+    for algo in (L.ALGO_MESH, L.ALGO_PAIRWISE):
+        xs = [inp(q, n * p, torch.float32, seed=7) for q in range(p)]
+        out = torch.zeros(n * p, device="cuda")
+        c.all_to_all(xs[r], out, algo=algo)
+        ok(c)
+        for q in range(p):
+            assert torch.equal(out[q * n:(q + 1) * n], xs[q][r * n:(r + 1) * n])
+    c.barrier()
+    ok(c)
+    # Send/Recv ring over the NCCL p2p backend
+    x = inp(r, 100_000, torch.float32, seed=8)
+    y = torch.zeros_like(x)
+    c.batch_send_recv([("send", x, (r + 1) % p), ("recv", y, (r - 1 + p) % p)])
+    ok(c)
+    assert torch.equal(y, inp((r - 1 + p) % p, 100_000, torch.float32, seed=8))
+    if r % 2 == 0 and r + 1 < p:
+        c.send(x, r + 1)
+    elif r % 2 == 1:
+        c.recv(y, r - 1)
+        ok(c)
+        assert torch.equal(y, inp(r - 1, 100_000, torch.float32, seed=8))
+    ok(c)
+    print("rank %d collectives ok; stats %s" % (r, c.stats()["algos"]))
+
+
+def scenario_perf(c, p, r, args):
+    """Quick device-timed look at the main algorithms (not a bench number: short, no NCCL)."""
+    c.calibrate()
+    if r == 0:
+        print("model", c.stats()["model"])
+    for size in (8 << 10, 256 << 10, 4 << 20, 64 << 20):
+        n = size // 4
+        x = torch.rand(n, device="cuda")
+        y = torch.empty_like(x)
+        algos = [L.ALGO_MESH_ONESHOT, L.ALGO_MESH, L.ALGO_RING, L.ALGO_RHD] + ([L.ALGO_NVLS, L.ALGO_NVLS_ONESHOT] if c.has_nvls() else [])
+        for algo in algos:
+            if algo in (L.ALGO_MESH_ONESHOT, L.ALGO_NVLS_ONESHOT) and size > (4 << 20):
+                continue
+            for nchan in (0,):
+                iters = 20
+                for _ in range(3):
+                    c.all_reduce(x, y, algo=algo, nchan=nchan)
+                c.barrier()
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(iters):
+                    c.all_reduce(x, y, algo=algo, nchan=nchan)
+                b.record()
+                torch.cuda.synchronize()
+                us = a.elapsed_time(b) * 1e3 / iters
+                if r == 0:
+                    print("size %9d algo %-13s %8.1f us  %7.1f GB/s" % (size, L.ALGO_NAMES[algo], us, size / us / 1e3))
+    ok(c)
+
+
+if __name__ == "__main__":
+    scenario, p, r, root_file = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), sys.argv[4]
+    torch.cuda.set_device(r)
+    comm = make_comm(p, r, root_file)
+    globals()["scenario_" + scenario](comm, p, r, sys.argv[5:])
+    assert comm.destroy() == L.SUCCESS

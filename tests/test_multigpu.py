@@ -1,0 +1,58 @@
+"""Real multi-GPU runs (one process per GPU): symmetric-memory mapping, NVLS, every algorithm, NCCL p2p.
+Skipped when fewer than two GPUs are visible."""
+import os
+import subprocess
+import sys
+import tempfile
+
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def run_gpu_ranks(p, scenario, env=None, timeout=600, args=()):
+    tmp = tempfile.mkdtemp(prefix="hcclb_gpu_")
+    root_file = os.path.join(tmp, "root.bin")
+    procs = []
+    for r in range(p):
+        e = dict(os.environ)
+        e.setdefault("HCCL_EXEC_TIMEOUT_MS", "20000")
+        e["HCCL_CONNECT_TIMEOUT"] = "120"
+        if env:
+            e.update(env)
+        cmd = [sys.executable, os.path.join(HERE, "_gpu_worker.py"), scenario, str(p), str(r), root_file] + [str(a) for a in args]
+        procs.append(subprocess.Popen(cmd, env=e, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, errors="replace"))
+    outs = []
+    for pr in procs:
+        try:
+            out, _ = pr.communicate(timeout=timeout)
+        except subprocess.TimeoutExpired:
+            pr.kill()
+            out, _ = pr.communicate()
+            out += "\n[killed by test timeout]"
+        outs.append((pr.returncode, out))
+    for r, (code, out) in enumerate(outs):
+        assert code == 0, "rank %d failed (%s):\n%s" % (r, code, out[-4000:])
+    return outs
+
+
+def ngpu():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+@pytest.mark.parametrize("p", [2, 4, 8])
+def test_collectives_multi_gpu(p):
+    if ngpu() < p:
+        pytest.skip("needs %d GPUs" % p)
+    outs = run_gpu_ranks(p, "collectives")
+    assert all("collectives ok" in o for _, o in outs)
+
+
+def test_collectives_multi_gpu_p2p_only():
+    """Same sweep with the multicast mapping switched off: plain peer loads/stores only."""
+    if ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    outs = run_gpu_ranks(2, "collectives", env={"HCCL_NVLS_ENABLE": "0"})
+    assert all("nvls=False" in o for _, o in outs)
