@@ -24,8 +24,9 @@ DTYPE_SIZE = {INT8: 1, INT16: 2, INT32: 4, FP16: 2, FP32: 4, INT64: 8, UINT64: 8
 (ALLREDUCE, BROADCAST, REDUCE_SCATTER, REDUCE_SCATTER_V, SCATTER, ALLGATHER, ALLGATHER_V, BARRIER, ALLTOALL,
  ALLTOALLV, ALLTOALLVC, REDUCE, GATHER) = range(13)
 (ALGO_AUTO, ALGO_MESH, ALGO_MESH_ONESHOT, ALGO_RING, ALGO_RHD, ALGO_PAIRWISE, ALGO_STAR, ALGO_TREE, ALGO_NVLS,
- ALGO_NVLS_ONESHOT, ALGO_SINGLE) = range(11)
-ALGO_NAMES = ["auto", "mesh", "mesh_oneshot", "ring", "rhd", "pairwise", "star", "tree", "nvls", "nvls_oneshot", "single"]
+ ALGO_NVLS_ONESHOT, ALGO_SINGLE, ALGO_MESH_PIPE, ALGO_NVLS_PIPE) = range(13)
+ALGO_NAMES = ["auto", "mesh", "mesh_oneshot", "ring", "rhd", "pairwise", "star", "tree", "nvls", "nvls_oneshot", "single",
+              "mesh_pipe", "nvls_pipe"]
 
 
 class RootInfo(C.Structure):
@@ -140,6 +141,8 @@ def lib():
         "HcclCommDeactivateCommMemory": [vp, vp],
         "HcclB200CommInitLocal": [u32, C.c_int, C.c_int, P(CommConfig), P(vp)],
         "HcclB200Collective": [vp, P(B200Op), P(vp), P(vp), vp],
+        "HcclB200Repeat": [vp, P(B200Op), P(vp), P(vp), u32, u64, u32, vp],
+        "HcclB200NcclAllReduceRepeat": [vp, vp, vp, u64, C.c_int, C.c_int, u32, u64, u32, vp],
         "HcclB200LocalSendRecv": [vp, u32, u32, vp, vp, u64, C.c_int, vp],
         "HcclB200StreamSync": [vp, vp],
         "HcclB200GetStatus": [vp, u32, P(B200Status)],

@@ -29,6 +29,8 @@ enum AlgoId : int {
     ALGO_NVLS,          // in-switch reduction / multicast (two-shot for AllReduce)
     ALGO_NVLS_ONESHOT,  // AllReduce: multimem.ld_reduce of the whole message on every rank
     ALGO_SINGLE,        // one rank: local copy
+    ALGO_MESH_PIPE,     // AllReduce / ReduceScatter / AllGather: mesh with CTA groups pipelining copy-in, reduce and gather over chunks
+    ALGO_NVLS_PIPE,     // same with in-switch reduction / multicast stores
     ALGO_COUNT
 };
 const char *algo_name(int algo);
@@ -46,6 +48,7 @@ struct OpDesc {
     uint64_t chunk_off = 0;    // window of `count` this plan covers (staging loop)
     uint64_t chunk_count = 0;
     uint64_t slot_bytes = 0;   // AlltoAllV: bytes of one per-sender staging slot
+    uint64_t pipe_chunk_bytes = 0;  // pipelined algorithms: bytes per pipeline chunk (0 = default)
     // V variants (arrays of nranks entries, elements).  AllGatherV: counts/displs describe the receive
     // layout; ReduceScatterV: the send layout.  AlltoAllV: this rank's four rows, only valid for
     // plans built for a single local rank; AlltoAllVC and emulated ranks pass the full matrix instead.

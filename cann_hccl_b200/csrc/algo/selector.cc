@@ -42,7 +42,7 @@ bool nvls_reduce_supported(int dtype, int redop, uint64_t bytes)
 static bool algo_exists(int coll, int algo)
 {
     switch (coll) {
-        case COLL_ALLREDUCE: return algo == ALGO_MESH || algo == ALGO_MESH_ONESHOT || algo == ALGO_RING || algo == ALGO_RHD || algo == ALGO_NVLS || algo == ALGO_NVLS_ONESHOT;
+        case COLL_ALLREDUCE: return algo == ALGO_MESH || algo == ALGO_MESH_ONESHOT || algo == ALGO_RING || algo == ALGO_RHD || algo == ALGO_NVLS || algo == ALGO_NVLS_ONESHOT || algo == ALGO_MESH_PIPE || algo == ALGO_NVLS_PIPE;
         case COLL_REDUCE_SCATTER: case COLL_ALLGATHER: return algo == ALGO_MESH || algo == ALGO_RING || algo == ALGO_RHD || algo == ALGO_NVLS;
         case COLL_REDUCE_SCATTER_V: case COLL_ALLGATHER_V: return algo == ALGO_MESH || algo == ALGO_RING || algo == ALGO_NVLS;
         case COLL_BROADCAST: return algo == ALGO_STAR || algo == ALGO_RING || algo == ALGO_TREE || algo == ALGO_NVLS;
@@ -70,6 +70,9 @@ double estimate_us(int coll, int algo, uint64_t bytes, int p, const CostModel &m
                 case ALGO_RHD: return L + (2 * lg + (pow2 ? 0 : 2)) * (a + s) + (pow2 ? 2 * f : 2.0 * (2 * p - 1) / p) * n / B + n / G;
                 case ALGO_NVLS_ONESHOT: return L + a + p * n / Bn + n / G + 2 * s;
                 case ALGO_NVLS: return L + 2 * a + (1.0 + 1.0 / p) * n / Bn + 2 * n / G + (p + 2) * s;
+                // pipelined: local copies hide behind the transfers; costs a pipeline fill of roughly one chunk per phase
+                case ALGO_MESH_PIPE: return L + 4 * a + std::max(2 * f * n / B, 2 * n / G) + 3 * std::min(n, 4.0 * (1 << 20)) / B + 6 * s;
+                case ALGO_NVLS_PIPE: return L + 4 * a + std::max((1.0 + 1.0 / p) * n / Bn, 2 * n / G) + 3 * std::min(n, 4.0 * (1 << 20)) / Bn + 6 * s;
             }
             break;
         case COLL_REDUCE_SCATTER: case COLL_REDUCE_SCATTER_V:  // bytes = one rank's result
@@ -144,7 +147,8 @@ Selection select_algo(const SelectInput &in, const CostModel &m)
                    (reducing ? nvls_reduce_supported(in.dtype, in.redop, nvls_bytes) : in.bytes % 16 == 0);
     auto allowed = [&](int algo) {
         if (!algo_exists(in.coll, algo)) return false;
-        if (algo == ALGO_NVLS || algo == ALGO_NVLS_ONESHOT) return nvls_ok;
+        if (algo == ALGO_NVLS || algo == ALGO_NVLS_ONESHOT || algo == ALGO_NVLS_PIPE) return nvls_ok;
+        if ((algo == ALGO_MESH_PIPE || algo == ALGO_NVLS_PIPE) && (!in.device || sel.nchan < 6)) return false;
         return true;
     };
     if (!in.forced.empty()) {
@@ -159,7 +163,7 @@ Selection select_algo(const SelectInput &in, const CostModel &m)
             return sel;
         }
     }
-    static const int order[] = {ALGO_MESH_ONESHOT, ALGO_MESH, ALGO_STAR, ALGO_NVLS_ONESHOT, ALGO_NVLS, ALGO_PAIRWISE, ALGO_RING, ALGO_TREE, ALGO_RHD};
+    static const int order[] = {ALGO_MESH_ONESHOT, ALGO_MESH, ALGO_STAR, ALGO_NVLS_ONESHOT, ALGO_NVLS, ALGO_MESH_PIPE, ALGO_NVLS_PIPE, ALGO_PAIRWISE, ALGO_RING, ALGO_TREE, ALGO_RHD};
     double best = -1;
     for (int a : order) {
         if (!allowed(a)) continue;

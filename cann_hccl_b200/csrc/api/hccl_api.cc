@@ -628,6 +628,33 @@ HcclResult HcclB200Collective(HcclComm comm, const HcclB200Op *op, void *const *
     rq.out = recvBufs;
     return c->collective(rq);
 }
+HcclResult HcclB200Repeat(HcclComm comm, const HcclB200Op *op, void *const *sendBufs, void *const *recvBufs, uint32_t iters,
+                          uint64_t strideBytes, uint32_t nwin, aclrtStream stream)
+{
+    // hccl_test-style loop in C: `iters` back-to-back calls; call i uses the buffers shifted by (i % nwin) * strideBytes
+    GET_COMM("HcclB200Repeat");
+    CHK_RET_LOG(!op || !sendBufs || !recvBufs, HCCL_E_PTR, "[EI0003] HcclB200Repeat: null pointer");
+    int nl = c->nlocal();
+    std::vector<void *> s(nl), r(nl);
+    if (nwin == 0) nwin = 1;
+    for (uint32_t i = 0; i < iters; ++i) {
+        uint64_t off = (uint64_t)(i % nwin) * strideBytes;
+        for (int l = 0; l < nl; ++l) { s[l] = (char *)sendBufs[l] + off; r[l] = (char *)recvBufs[l] + off; }
+        CHK_RET(HcclB200Collective(comm, op, s.data(), r.data(), stream));
+    }
+    return HCCL_SUCCESS;
+}
+HcclResult HcclB200NcclAllReduceRepeat(HcclComm comm, void *sendBuf, void *recvBuf, uint64_t count, HcclDataType dataType, HcclReduceOp op,
+                                       uint32_t iters, uint64_t strideBytes, uint32_t nwin, aclrtStream stream)
+{
+    GET_COMM("HcclB200NcclAllReduceRepeat");
+    if (nwin == 0) nwin = 1;
+    for (uint32_t i = 0; i < iters; ++i) {
+        uint64_t off = (uint64_t)(i % nwin) * strideBytes;
+        CHK_RET(c->nccl_baseline_allreduce((char *)sendBuf + off, (char *)recvBuf + off, count, dataType, op, stream));
+    }
+    return HCCL_SUCCESS;
+}
 HcclResult HcclB200LocalSendRecv(HcclComm comm, uint32_t src, uint32_t dst, const void *sendBuf, void *recvBuf, uint64_t count,
                                  HcclDataType dataType, aclrtStream stream)
 {

@@ -13,7 +13,7 @@
 namespace hcclb {
 
 constexpr int kMaxRanks = 16;     // one NVSwitch domain (reference AIV path: MAX_RANK_SIZE 16, hccl_aiv.h:40)
-constexpr int kMaxChannels = 64;  // CTAs ("channels") a plan may use per rank
+constexpr int kMaxChannels = 128; // CTAs ("channels") a plan may use per rank
 constexpr int kFlagBanks = 4;     // 0 data, 1 ack, 2 p2p data, 3 p2p ack
 constexpr int kSeqShift = 20;     // flag value = (sequence << kSeqShift) + step value
 

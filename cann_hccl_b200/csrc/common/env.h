@@ -35,6 +35,7 @@ struct EnvConfig {
     int stuck_ms = 300000;         // HCCL_STUCK_DETECT_TIME (seconds in env; reference STUCK_INTERVAL 300 s)
     int heartbeat_lost_ms = 3000;  // HCCL_HEARTBEAT_LOST_MS: silence after which a peer counts as lost
     int channels = 0;              // HCCL_CHANNELS: force CTAs per op (0 = selector decides)
+    uint64_t pipe_chunk_bytes = 0; // HCCL_PIPE_CHUNK_KB: chunk of the pipelined large-message algorithms (0 = default)
     std::string ncc_lib;           // HCCL_NCCL_LIB: path of libnccl.so.2 for Send/Recv
     bool valid = true;
     std::string error;             // first parse error, if any

@@ -365,7 +365,7 @@ Selection Communicator::select(int coll, uint64_t count, int dtype, int redop) c
     si.nvls = nvls_;
     si.device = settings_.transport == TR_DEVICE;
     si.expansion_mode = settings_.expansion_mode ? settings_.expansion_mode : env.expansion_mode;
-    si.max_channels = si.device ? 32 : 2;
+    si.max_channels = si.device ? 64 : 2;
     si.forced = forced_algo_for(env, coll);
     Selection s = select_algo(si, model_);
     if (env.channels > 0) s.nchan = env.channels;
@@ -468,7 +468,7 @@ HcclResult Communicator::run_collective_once(const OpRequest &rq)
     if (rq.nchan > 0) sel.nchan = rq.nchan;
     if (p == 1) sel.algo = ALGO_SINGLE;
     if (rq.coll == COLL_BARRIER) { sel.algo = p == 1 ? ALGO_SINGLE : ALGO_MESH; sel.nchan = 1; }
-    if ((sel.algo == ALGO_NVLS || sel.algo == ALGO_NVLS_ONESHOT) && !nvls_) {
+    if ((sel.algo == ALGO_NVLS || sel.algo == ALGO_NVLS_ONESHOT || sel.algo == ALGO_NVLS_PIPE) && !nvls_) {
         HLOG_ERROR("NVLS algorithm requested but no multicast mapping exists on this communicator");
         return HCCL_E_NOT_SUPPORT;
     }
@@ -477,6 +477,7 @@ HcclResult Communicator::run_collective_once(const OpRequest &rq)
     OpDesc d;
     d.coll = rq.coll; d.algo = sel.algo; d.nranks = p; d.root = rq.root; d.dtype = rq.dtype; d.redop = rq.redop;
     d.nchan = sel.nchan; d.count = rq.count;
+    d.pipe_chunk_bytes = env_config().pipe_chunk_bytes;
     if (is_v) { d.counts.assign(rq.counts, rq.counts + p); d.displs.assign(rq.displs, rq.displs + p); }
     if (is_a2av) {
         d.send_counts.assign(rq.send_counts, rq.send_counts + (size_t)nl * p);
@@ -513,7 +514,7 @@ HcclResult Communicator::run_collective_once(const OpRequest &rq)
         uint64_t n = std::min(max_chunk, window - off);
         d.chunk_off = off; d.chunk_count = n;
         std::ostringstream key;
-        key << rq.coll << ':' << d.algo << ':' << d.nchan << ':' << rq.dtype << ':' << rq.root << ':' << rq.count << ':' << off << ':' << n;
+        key << rq.coll << ':' << d.algo << ':' << d.nchan << ':' << d.pipe_chunk_bytes << ':' << rq.dtype << ':' << rq.root << ':' << rq.count << ':' << off << ':' << n;
         if (is_v) for (int j = 0; j < p; ++j) key << ',' << d.counts[j] << '@' << d.displs[j];
         if (is_a2av) {
             uint32_t crc = crc32(d.send_counts.data(), d.send_counts.size() * 8, 0);
@@ -620,6 +621,12 @@ HcclResult Communicator::recv(void *buf, uint64_t count, int dtype, int src, voi
     stats_.bytes[COLL_RECV] += count * dtype_size(dtype);
     if (p2p_) return p2p_->recv(buf, count, dtype, src, stream);
     return p2p_plan_exec(false, src, nullptr, buf, count, dtype, stream);
+}
+
+HcclResult Communicator::nccl_baseline_allreduce(const void *send, void *recv, uint64_t count, int dtype, int op, void *stream)
+{
+    if (!p2p_) return HCCL_E_UNAVAIL;
+    return p2p_->baseline_allreduce(send, recv, count, dtype, op, stream);
 }
 
 HcclResult Communicator::batch_send_recv(HcclSendRecvItem *items, uint32_t n, void *stream)

@@ -109,6 +109,8 @@ public:
     HcclResult batch_send_recv(HcclSendRecvItem *items, uint32_t n, void *stream);
     HcclResult local_send_recv(int src, int dst, const void *sbuf, void *rbuf, uint64_t count, int dtype, void *stream);
 
+    // NCCL all-reduce baseline on the p2p backend's communicator (benchmarks only).
+    HcclResult nccl_baseline_allreduce(const void *send, void *recv, uint64_t count, int dtype, int op, void *stream);
     HcclResult suspend();
     HcclResult resume();
     HcclResult resume_locked();

@@ -18,6 +18,7 @@ struct NcclApi {
     int (*CommAbort)(void *);
     int (*Send)(const void *, size_t, int, int, void *, void *);
     int (*Recv)(void *, size_t, int, int, void *, void *);
+    int (*AllReduce)(const void *, void *, size_t, int, int, void *, void *);
     int (*GroupStart)();
     int (*GroupEnd)();
     const char *(*GetErrorString)(int);
@@ -42,6 +43,7 @@ NcclApi &api()
         a.CommAbort = (decltype(a.CommAbort))sym("ncclCommAbort");
         a.Send = (decltype(a.Send))sym("ncclSend");
         a.Recv = (decltype(a.Recv))sym("ncclRecv");
+        a.AllReduce = (decltype(a.AllReduce))sym("ncclAllReduce");
         a.GroupStart = (decltype(a.GroupStart))sym("ncclGroupStart");
         a.GroupEnd = (decltype(a.GroupEnd))sym("ncclGroupEnd");
         a.GetErrorString = (decltype(a.GetErrorString))sym("ncclGetErrorString");
@@ -111,6 +113,29 @@ HcclResult P2pBackend::recv(void *buf, uint64_t count, int dtype, int peer, void
     CHK_RET_LOG(rc != 0, HCCL_E_INTERNAL, "ncclRecv failed: %s", api().GetErrorString(rc));
     return HCCL_SUCCESS;
 }
+HcclResult P2pBackend::baseline_allreduce(const void *send, void *recv, uint64_t count, int dtype, int op, void *stream)
+{
+    CHK_RET(wait_ready());
+    int nt;
+    switch (dtype) {
+        case HCCL_DATA_TYPE_INT8: nt = 0; break;
+        case HCCL_DATA_TYPE_UINT8: nt = 1; break;
+        case HCCL_DATA_TYPE_INT32: nt = 2; break;
+        case HCCL_DATA_TYPE_UINT32: nt = 3; break;
+        case HCCL_DATA_TYPE_INT64: nt = 4; break;
+        case HCCL_DATA_TYPE_UINT64: nt = 5; break;
+        case HCCL_DATA_TYPE_FP16: nt = 6; break;
+        case HCCL_DATA_TYPE_FP32: nt = 7; break;
+        case HCCL_DATA_TYPE_FP64: nt = 8; break;
+        case HCCL_DATA_TYPE_BFP16: nt = 9; break;
+        default: return HCCL_E_NOT_SUPPORT;
+    }
+    if (!api().AllReduce) return HCCL_E_UNAVAIL;
+    int rc = api().AllReduce(send, recv, count, nt, op, nccl_comm_, stream);
+    CHK_RET_LOG(rc != 0, HCCL_E_INTERNAL, "ncclAllReduce failed: %s", api().GetErrorString(rc));
+    return HCCL_SUCCESS;
+}
+
 HcclResult P2pBackend::batch(const std::vector<HcclSendRecvItem *> &sends, const std::vector<HcclSendRecvItem *> &recvs, void *stream)
 {
     CHK_RET(wait_ready());

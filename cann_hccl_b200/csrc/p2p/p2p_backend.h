@@ -19,6 +19,8 @@ public:
     ~P2pBackend();
     HcclResult send(const void *buf, uint64_t count, int dtype, int peer, void *stream);
     HcclResult recv(void *buf, uint64_t count, int dtype, int peer, void *stream);
+    // NCCL all-reduce on the same communicator: the measured baseline next to our own kernels (never used by a collective).
+    HcclResult baseline_allreduce(const void *send, void *recv, uint64_t count, int dtype, int op, void *stream);
     HcclResult batch(const std::vector<HcclSendRecvItem *> &sends, const std::vector<HcclSendRecvItem *> &recvs, void *stream);
 
 private:

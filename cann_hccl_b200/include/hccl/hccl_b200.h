@@ -18,7 +18,7 @@ enum { HCCL_B200_ALLREDUCE = 0, HCCL_B200_BROADCAST, HCCL_B200_REDUCE_SCATTER, H
        HCCL_B200_ALLTOALLV, HCCL_B200_ALLTOALLVC, HCCL_B200_REDUCE, HCCL_B200_GATHER };
 enum { HCCL_B200_ALGO_AUTO = 0, HCCL_B200_ALGO_MESH, HCCL_B200_ALGO_MESH_ONESHOT, HCCL_B200_ALGO_RING,
        HCCL_B200_ALGO_RHD, HCCL_B200_ALGO_PAIRWISE, HCCL_B200_ALGO_STAR, HCCL_B200_ALGO_TREE, HCCL_B200_ALGO_NVLS,
-       HCCL_B200_ALGO_NVLS_ONESHOT, HCCL_B200_ALGO_SINGLE };
+       HCCL_B200_ALGO_NVLS_ONESHOT, HCCL_B200_ALGO_SINGLE, HCCL_B200_ALGO_MESH_PIPE, HCCL_B200_ALGO_NVLS_PIPE };
 
 typedef struct HcclB200OpDef {
     int32_t coll;       /* HCCL_B200_* collective */
@@ -45,6 +45,13 @@ extern HcclResult HcclB200CommInitLocal(uint32_t nRanks, int transport, int devi
 /* Generic collective entry; sendBufs / recvBufs hold one pointer per local rank. */
 extern HcclResult HcclB200Collective(HcclComm comm, const HcclB200Op *op, void *const *sendBufs, void *const *recvBufs,
                                      aclrtStream stream);
+/* hccl_test-style loop issued from C: `iters` back-to-back collectives; call i shifts every buffer by
+ * (i % nwin) * strideBytes so that successive calls touch different memory. */
+extern HcclResult HcclB200Repeat(HcclComm comm, const HcclB200Op *op, void *const *sendBufs, void *const *recvBufs, uint32_t iters,
+                                 uint64_t strideBytes, uint32_t nwin, aclrtStream stream);
+/* The measured baseline: ncclAllReduce issued the same way on the NCCL communicator that carries Send/Recv. */
+extern HcclResult HcclB200NcclAllReduceRepeat(HcclComm comm, void *sendBuf, void *recvBuf, uint64_t count, HcclDataType dataType,
+                                              HcclReduceOp op, uint32_t iters, uint64_t strideBytes, uint32_t nwin, aclrtStream stream);
 extern HcclResult HcclB200LocalSendRecv(HcclComm comm, uint32_t src, uint32_t dst, const void *sendBuf, void *recvBuf,
                                         uint64_t count, HcclDataType dataType, aclrtStream stream);
 /* Wait for the stream and return the status the kernels left (HCCL_E_TIMEOUT, HCCL_E_SUSPENDING, ...). */

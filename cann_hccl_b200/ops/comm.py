@@ -96,8 +96,7 @@ class Communicator:
             return None
         if stream is not None:
             return C.c_void_p(stream if isinstance(stream, int) else stream.cuda_stream)
-        import torch
-        return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        return C.c_void_p(_raw_stream())
 
     def _bufs(self, x):
         """one pointer per local rank"""
@@ -127,6 +126,20 @@ class Communicator:
             ra, _ = self._bufs(recv)
         code = L.lib().HcclB200Collective(self._h, C.byref(o), sa, ra, self._stream(stream))
         L.check(code, "HcclB200Collective(%d)" % coll)
+
+    def repeat(self, coll, send, recv, count, dtype, iters, stride_bytes=0, nwin=1, op=L.SUM, root=0, algo=L.ALGO_AUTO, nchan=0,
+               stream=None):
+        """hccl_test-style loop issued from C (no per-call Python cost): `iters` calls, buffers shifted per call."""
+        o = L.B200Op()
+        o.coll, o.algo, o.nchan, o.dataType, o.op, o.root, o.count = coll, algo, nchan, dtype, op, root, int(count)
+        sa, _ = self._bufs(send)
+        ra, _ = self._bufs(recv)
+        L.check(L.lib().HcclB200Repeat(self._h, C.byref(o), sa, ra, iters, stride_bytes, nwin, self._stream(stream)), "HcclB200Repeat")
+
+    def nccl_allreduce_repeat(self, send, recv, count, dtype, iters, stride_bytes=0, nwin=1, op=L.SUM, stream=None):
+        """The NCCL baseline issued the same way (needs the NCCL p2p backend, i.e. a multi-GPU communicator)."""
+        return L.lib().HcclB200NcclAllReduceRepeat(self._h, data_ptr(send), data_ptr(recv), int(count), dtype, op, iters, stride_bytes,
+                                                   nwin, self._stream(stream))
 
     # ------------------------------------------------------------------ collectives (HCCL semantics)
     def _first(self, x):
@@ -299,6 +312,20 @@ class Communicator:
     @property
     def handle(self):
         return self._h
+
+
+_RAW = None
+
+
+def _raw_stream():
+    """Raw handle of torch's current CUDA stream (the cheap private accessor when it exists)."""
+    global _RAW
+    import torch
+    if _RAW is None:
+        _RAW = getattr(torch._C, "_cuda_getCurrentRawStream", False)
+    if _RAW:
+        return _RAW(torch.cuda.current_device())
+    return torch.cuda.current_stream().cuda_stream
 
 
 def _have_gpu():

@@ -19,11 +19,17 @@ def _torch_map():
     return m
 
 
+_TORCH = None
+
+
 def hccl_dtype(x):
     """HcclDataType of a numpy array or torch tensor."""
+    global _TORCH
     if isinstance(x, np.ndarray):
         return _NP[x.dtype]
-    return _torch_map()[x.dtype]
+    if _TORCH is None:
+        _TORCH = _torch_map()
+    return _TORCH[x.dtype]
 
 
 def data_ptr(x):

@@ -60,19 +60,21 @@ def ok(c):
 def scenario_collectives(c, p, r, args):
     nvls = c.has_nvls()
     print("rank %d: nvls=%s" % (r, nvls))
-    ar_algos = [L.ALGO_AUTO, L.ALGO_MESH_ONESHOT, L.ALGO_MESH, L.ALGO_RING, L.ALGO_RHD] + ([L.ALGO_NVLS, L.ALGO_NVLS_ONESHOT] if nvls else [])
+    ar_algos = [L.ALGO_AUTO, L.ALGO_MESH_ONESHOT, L.ALGO_MESH, L.ALGO_RING, L.ALGO_RHD, L.ALGO_MESH_PIPE] + ([L.ALGO_NVLS, L.ALGO_NVLS_ONESHOT, L.ALGO_NVLS_PIPE] if nvls else [])
     for n in (4, 1000, 262144, 6_000_000):  # the last one runs the staging loop (24 MB through 16 MB halves)
         for algo in ar_algos:
-            if algo in (L.ALGO_NVLS, L.ALGO_NVLS_ONESHOT) and (n * 4) % 16:
+            if algo in (L.ALGO_NVLS, L.ALGO_NVLS_ONESHOT, L.ALGO_NVLS_PIPE) and (n * 4) % 16:
+                continue
+            if algo in (L.ALGO_MESH_PIPE, L.ALGO_NVLS_PIPE) and n < 1000:
                 continue
             for dtype, op in ((torch.float32, L.SUM), (torch.bfloat16, L.SUM), (torch.bfloat16, L.MAX), (torch.int32, L.MIN)):
-                if algo in (L.ALGO_NVLS, L.ALGO_NVLS_ONESHOT) and (n * dtype.itemsize) % 16:
+                if algo in (L.ALGO_NVLS, L.ALGO_NVLS_ONESHOT, L.ALGO_NVLS_PIPE) and (n * dtype.itemsize) % 16:
                     continue
                 if n > 1_000_000 and dtype != torch.float32:
                     continue
                 xs = [inp(q, n, dtype, seed=n % 97) for q in range(p)]
                 out = torch.zeros(n, device="cuda", dtype=dtype)
-                c.all_reduce(xs[r], out, op=op, algo=algo)
+                c.all_reduce(xs[r], out, op=op, algo=algo, nchan=12 if algo in (L.ALGO_MESH_PIPE, L.ALGO_NVLS_PIPE) else 0)
                 ok(c)
                 close(out, red(xs, op), dtype, p)
     for algo in [L.ALGO_MESH, L.ALGO_RING, L.ALGO_RHD] + ([L.ALGO_NVLS] if nvls else []):
@@ -126,34 +128,49 @@ def scenario_collectives(c, p, r, args):
     print("rank %d collectives ok; stats %s" % (r, c.stats()["algos"]))
 
 
+def _time_repeat(c, fn, iters):
+    fn(3)
+    c.barrier()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    fn(iters)
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) * 1e3 / iters
+
+
 def scenario_perf(c, p, r, args):
-    """Quick device-timed look at the main algorithms (not a bench number: short, no NCCL)."""
+    """Device-timed look at the algorithms, issued from C (hccl_test style), next to ncclAllReduce issued the same way."""
     c.calibrate()
     if r == 0:
         print("model", c.stats()["model"])
-    for size in (8 << 10, 256 << 10, 4 << 20, 64 << 20):
+    sizes = [int(a) for a in args] if args else [8 << 10, 64 << 10, 512 << 10, 4 << 20, 64 << 20, 256 << 20]
+    buf_bytes = max(sizes) * 2
+    x = torch.rand(buf_bytes // 4, device="cuda")
+    y = torch.empty_like(x)
+    nv = c.has_nvls()
+    for size in sizes:
         n = size // 4
-        x = torch.rand(n, device="cuda")
-        y = torch.empty_like(x)
-        algos = [L.ALGO_MESH_ONESHOT, L.ALGO_MESH, L.ALGO_RING, L.ALGO_RHD] + ([L.ALGO_NVLS, L.ALGO_NVLS_ONESHOT] if c.has_nvls() else [])
+        nwin = max(1, min(16, buf_bytes // size))
+        iters = 30 if size <= (4 << 20) else 8
+        rows = []
+        t = _time_repeat(c, lambda it: c.nccl_allreduce_repeat(y, y, n, L.FP32, it, size, nwin), iters)
+        rows.append(("nccl", 0, t))
+        algos = [L.ALGO_AUTO, L.ALGO_MESH_ONESHOT, L.ALGO_MESH, L.ALGO_RING, L.ALGO_RHD, L.ALGO_MESH_PIPE] + ([L.ALGO_NVLS, L.ALGO_NVLS_ONESHOT, L.ALGO_NVLS_PIPE] if nv else [])
         for algo in algos:
             if algo in (L.ALGO_MESH_ONESHOT, L.ALGO_NVLS_ONESHOT) and size > (4 << 20):
                 continue
-            for nchan in (0,):
-                iters = 20
-                for _ in range(3):
-                    c.all_reduce(x, y, algo=algo, nchan=nchan)
-                c.barrier()
-                torch.cuda.synchronize()
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record()
-                for _ in range(iters):
-                    c.all_reduce(x, y, algo=algo, nchan=nchan)
-                b.record()
-                torch.cuda.synchronize()
-                us = a.elapsed_time(b) * 1e3 / iters
-                if r == 0:
-                    print("size %9d algo %-13s %8.1f us  %7.1f GB/s" % (size, L.ALGO_NAMES[algo], us, size / us / 1e3))
+            if algo in (L.ALGO_MESH_PIPE, L.ALGO_NVLS_PIPE) and size < (4 << 20):
+                continue
+            chans = (0,) if size < (4 << 20) else (0, 32, 96)
+            for nchan in chans:
+                t = _time_repeat(c, lambda it: c.repeat(L.ALLREDUCE, x, y, n, L.FP32, it, size, nwin, algo=algo, nchan=nchan), iters)
+                rows.append((L.ALGO_NAMES[algo], nchan, t))
+        ok(c)
+        if r == 0:
+            for name, nchan, t in rows:
+                print("size %10d  %-13s nchan %3d  %9.1f us  %7.1f GB/s" % (size, name, nchan, t, size / t / 1e3))
     ok(c)
 
 

@@ -88,6 +88,20 @@ def test_allreduce_dtypes_ops(comms, dtype, op):
         close(o, ref, dtype, p)
 
 
+@pytest.mark.parametrize("p", [2, 4, 8])
+def test_allreduce_pipelined_groups(comms, p):
+    """Large-message algorithm: copy-in, reduce and gather CTA groups of one kernel pipelined over chunks."""
+    c = comms(p)
+    n = 900_001
+    ins = rnd(p, n, torch.float32, seed=11)
+    outs = [torch.zeros(n, device="cuda") for _ in range(p)]
+    c.all_reduce(ins, outs, algo=L.ALGO_MESH_PIPE, nchan=9)
+    ok(c)
+    ref = ref_reduce(ins, L.SUM)
+    for o in outs:
+        close(o, ref, torch.float32, p)
+
+
 def test_allreduce_staging_loop_in_place_unaligned(comms):
     p = 4
     c = comms(p)

@@ -56,6 +56,18 @@ def test_allreduce_dtypes_ops(comms, dtype, op):
         np.testing.assert_allclose(o.astype(np.float64), ref.astype(np.float64), **tol(dtype, p))
 
 
+@pytest.mark.parametrize("p", [2, 3, 8])
+def test_allreduce_pipelined_groups_schedule(comms, p):
+    c = comms(p)
+    n = 200_003
+    ins = make_inputs(p, n, np.float32)
+    outs = [np.zeros(n, np.float32) for _ in range(p)]
+    c.all_reduce(ins, outs, algo=L.ALGO_MESH_PIPE, nchan=7)
+    ref = np_reduce(ins, L.SUM)
+    for o in outs:
+        np.testing.assert_allclose(o, ref, **tol(np.float32, p))
+
+
 def test_allreduce_bf16_bits(comms):
     """bf16 travels as uint16 through numpy; the library reduces it in fp32 and rounds once."""
     import ctypes as C
