@@ -36,6 +36,7 @@ constexpr int16_t RANK_ALL = -2;   // every other rank (wait / signal), or the N
 enum StepFlags : uint8_t {
     SF_SKIP_SELF = 1,   // GATHER_ALL: do not copy the executing rank's own block
     SF_WAIT_ALLCH = 2,  // wait for every channel [wait_clo, wait_clo+wait_cn) of the producer, not only my lane
+    SF_INCLUDE_SELF = 8,  // RANK_ALL waits / signals also cover the executing rank (dependencies between its own CTA groups)
     SF_ABS_VALS = 4,    // wait_val / sig_val are absolute flag values (Send/Recv), not relative to the op sequence
 };
 

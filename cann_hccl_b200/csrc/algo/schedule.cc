@@ -254,7 +254,7 @@ void ar_mesh_pipelined(Prog &P, const OpDesc &d, bool nvls)
             uint64_t len = std::min(ce, n - c0);
             Step a = P.copy(BUF_IN, RANK_SELF, uoff + c0 * P.es, BUF_STAGE, RANK_SELF, c0 * P.es, len);
             a.chan_lo = 0; a.chan_n = (uint16_t)nA;
-            a.sig_rank = RANK_ALL; a.sig_val = k + 1;
+            a.sig_rank = RANK_ALL; a.sig_val = k + 1; a.flags |= SF_INCLUDE_SELF;  // this rank's own reduce group waits on it too
             P.add(r, a, true);
         }
         k = 0;
@@ -269,7 +269,7 @@ void ar_mesh_pipelined(Prog &P, const OpDesc &d, bool nvls)
             else { b.d_rank = RANK_SELF; b.d_off = so; }
             b.d2_buf = BUF_OUT; b.d2_off = uoff + so;
             b.chan_lo = (uint16_t)nA; b.chan_n = (uint16_t)nB;
-            b.wait_rank = RANK_ALL; b.wait_val = k + 1; b.flags |= SF_WAIT_ALLCH; b.wait_clo = 0; b.wait_cn = (uint16_t)nA;
+            b.wait_rank = RANK_ALL; b.wait_val = k + 1; b.flags |= SF_WAIT_ALLCH | SF_INCLUDE_SELF; b.wait_clo = 0; b.wait_cn = (uint16_t)nA;
             b.sig_rank = RANK_ALL; b.sig_val = k + 1;
             P.add(r, b, true);
         }

@@ -125,8 +125,9 @@ double estimate_us(int coll, int algo, uint64_t bytes, int p, const CostModel &m
 
 int pick_channels(uint64_t bytes, int max_channels)
 {
-    // one CTA per 64 KiB keeps tiny messages at a single CTA pair of flag hops and lets large ones fill the links
-    uint64_t c = bytes / (64u << 10);
+    // one CTA per 16 KiB: a CTA keeps about 64 KB of loads in flight, so small messages finish in one round trip per
+    // phase while large ones spread over enough CTAs to fill the links
+    uint64_t c = bytes / (16u << 10);
     if (c < 1) c = 1;
     if (c > (uint64_t)max_channels) c = (uint64_t)max_channels;
     return (int)c;

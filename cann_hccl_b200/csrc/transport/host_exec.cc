@@ -99,7 +99,7 @@ HcclResult exec_plan_host(const RankCtx &c, const ExecArgs &a)
                 uint64_t want = flag_value(a, s, s.wait_val);
                 int q0 = s.wait_rank == RANK_ALL ? 0 : s.wait_rank, q1 = s.wait_rank == RANK_ALL ? p : s.wait_rank + 1;
                 for (int q = q0; q < q1; ++q) {
-                    if (q == me) continue;
+                    if (q == me && !(s.flags & SF_INCLUDE_SELF)) continue;
                     int c0 = (s.flags & SF_WAIT_ALLCH) ? s.wait_clo : chan;
                     int c1 = (s.flags & SF_WAIT_ALLCH) ? s.wait_clo + s.wait_cn : chan + 1;
                     for (int cc = c0; cc < c1; ++cc) {
@@ -179,7 +179,7 @@ HcclResult exec_plan_host(const RankCtx &c, const ExecArgs &a)
                 uint64_t val = flag_value(a, s, s.sig_val);
                 int q0 = s.sig_rank == RANK_ALL ? 0 : s.sig_rank, q1 = s.sig_rank == RANK_ALL ? p : s.sig_rank + 1;
                 for (int q = q0; q < q1; ++q) {
-                    if (q == me) continue;
+                    if (q == me && !(s.flags & SF_INCLUDE_SELF)) continue;
                     __atomic_store_n(&c.flags[q][flag_index(s.sig_bank, me, chan)], val, __ATOMIC_RELEASE);
                 }
             }

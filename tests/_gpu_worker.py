@@ -76,7 +76,13 @@ def scenario_collectives(c, p, r, args):
                 out = torch.zeros(n, device="cuda", dtype=dtype)
                 c.all_reduce(xs[r], out, op=op, algo=algo, nchan=12 if algo in (L.ALGO_MESH_PIPE, L.ALGO_NVLS_PIPE) else 0)
                 ok(c)
-                close(out, red(xs, op), dtype, p)
+                try:
+                    close(out, red(xs, op), dtype, p)
+                except AssertionError as e:
+                    bad = (out.float() - red(xs, op).float()).abs() > 1e-3
+                    idx = bad.nonzero().flatten()
+                    raise AssertionError("allreduce n=%d algo=%s dtype=%s op=%d: %d bad elements, first %d last %d\n%s" % (
+                        n, L.ALGO_NAMES[algo], dtype, op, int(bad.sum()), int(idx[0]), int(idx[-1]), str(e)[:300]))
     for algo in [L.ALGO_MESH, L.ALGO_RING, L.ALGO_RHD] + ([L.ALGO_NVLS] if nvls else []):
         n = 40_000
         xs = [inp(q, n * p, torch.float32, seed=3) for q in range(p)]
