@@ -62,6 +62,7 @@ struct RankCtx {
     uint8_t *stage[kMaxRanks];   // staging buffer of rank q mapped into this rank's address space
     uint64_t *flags[kMaxRanks];  // flag page of rank q (layout: flag_index())
     uint8_t *p2p[kMaxRanks];     // p2p mailbox area of rank q
+    uint8_t *ll[kMaxRanks];      // low-latency AllReduce mailboxes of rank q
     uint8_t *mc_stage;           // NVLS multicast mapping of the staging buffer (null when unavailable)
     DevStatus *status;           // host-mapped status block of this rank
     volatile uint32_t *abort;    // host-mapped abort word, non-zero = give up

@@ -31,6 +31,7 @@ struct SelectInput {
     bool device = true;         // false: host transport (NVLS never applies)
     int expansion_mode = 0;     // 1 = host-orchestrated: plain algorithms only
     int max_channels = 32;
+    uint64_t ll_max_bytes = 0;  // largest message the LL kernel may take (0 = LL unavailable)
     std::string forced;         // algorithm name from HCCL_ALGO for this collective ("" = none)
 };
 struct Selection {

@@ -14,6 +14,7 @@
 #include "common/log.h"
 #include "health/consistency.h"
 #include "health/fault_inject.h"
+#include "kernels/ar_ll.h"
 #include "p2p/p2p_backend.h"
 #include "transport/host_exec.h"
 
@@ -183,7 +184,10 @@ HcclResult Communicator::init_common()
     size_t p2p_bytes = align_up((size_t)nranks_ * p2p_slot_, 4096);
     size_t half = align_up((size_t)settings_.stage_half_bytes, 4096);
     settings_.stage_half_bytes = half;
-    size_t total = flags_bytes + p2p_bytes + 2 * half;
+    bool dev0 = settings_.transport == TR_DEVICE;
+    size_t ll_bytes = dev0 ? align_up((size_t)2 * nranks_ * kLlSlotBytes, 4096) : 0;
+    ll_ok_ = dev0 && nranks_ > 1;
+    size_t total = flags_bytes + p2p_bytes + ll_bytes + 2 * half;
     CHK_RET(alloc_->alloc(total, true, &seg_));
     CHK_RET_LOG((int)seg_.size() != nl, HCCL_E_INTERNAL, "allocator returned %zu segments for %d local ranks", seg_.size(), nl);
     nvls_ = seg_[0].mc != nullptr;
@@ -214,9 +218,10 @@ HcclResult Communicator::init_common()
             uint8_t *base = seg_[li].peer[q];
             x.flags[q] = (uint64_t *)base;
             x.p2p[q] = base + flags_bytes;
-            x.stage[q] = base + flags_bytes + p2p_bytes;
+            x.ll[q] = base + flags_bytes + p2p_bytes;
+            x.stage[q] = base + flags_bytes + p2p_bytes + ll_bytes;
         }
-        x.mc_stage = seg_[li].mc ? seg_[li].mc + flags_bytes + p2p_bytes : nullptr;
+        x.mc_stage = seg_[li].mc ? seg_[li].mc + flags_bytes + p2p_bytes + ll_bytes : nullptr;
         uint8_t *pb = (uint8_t *)pinned_ + blk * li;
         status_[li] = (DevStatus *)pb;
         abort_[li] = (volatile uint32_t *)(pb + align_up(sizeof(DevStatus), 64));
@@ -367,6 +372,7 @@ Selection Communicator::select(int coll, uint64_t count, int dtype, int redop) c
     si.expansion_mode = settings_.expansion_mode ? settings_.expansion_mode : env.expansion_mode;
     si.max_channels = si.device ? 64 : 2;
     si.forced = forced_algo_for(env, coll);
+    si.ll_max_bytes = ll_ok_ ? kLlMaxPayload : 0;
     Selection s = select_algo(si, model_);
     if (env.channels > 0) s.nchan = env.channels;
     if (all_local_ && si.device) {
@@ -473,6 +479,20 @@ HcclResult Communicator::run_collective_once(const OpRequest &rq)
         return HCCL_E_NOT_SUPPORT;
     }
     CHK_RET(consistency_check(rq, sel.algo));
+    if (sel.algo == ALGO_LL) {
+        bool fits = rq.coll == COLL_ALLREDUCE && ll_ok_ && rq.count * es <= kLlMaxPayload;
+        for (int li = 0; li < nl && fits; ++li) fits = (((uintptr_t)rq.in[li] | (uintptr_t)rq.out[li]) & 7) == 0;
+        if (fits) {
+            HcclResult lrc = run_ll_allreduce(rq);
+            stats_.ops[rq.coll]++;
+            stats_.bytes[rq.coll] += rq.count * es;
+            stats_.algo_hist[ALGO_LL]++;
+            record_trace(rq, ALGO_LL, 0, rq.count * es, now_us() - t0);
+            return lrc;
+        }
+        CHK_RET_LOG(rq.algo == ALGO_LL && !ll_ok_, HCCL_E_NOT_SUPPORT, "the LL AllReduce needs the device transport and more than one rank");
+        sel.algo = ALGO_MESH_ONESHOT;  // unaligned or oversized: the plan executor handles every layout
+    }
 
     OpDesc d;
     d.coll = rq.coll; d.algo = sel.algo; d.nranks = p; d.root = rq.root; d.dtype = rq.dtype; d.redop = rq.redop;
@@ -537,6 +557,35 @@ HcclResult Communicator::run_collective_once(const OpRequest &rq)
     stats_.algo_hist[sel.algo]++;
     record_trace(rq, sel.algo, sel.nchan, bytes, now_us() - t0);
     return rc;
+}
+
+HcclResult Communicator::run_ll_allreduce(const OpRequest &rq)
+{
+    int nl = nlocal();
+    ++ll_seq_;
+    uint32_t tag = (uint32_t)(ll_seq_ & 0xffffffffu);
+    if (tag == 0) { ++ll_seq_; tag = 1; }
+    std::vector<LlArgs> args(nl);
+    for (int li = 0; li < nl; ++li) {
+        LlArgs &a = args[li];
+        memset(&a, 0, sizeof(a));
+        for (int q = 0; q < nranks_; ++q) a.ll[q] = ctx_[li].ll[q];
+        a.in = rq.in[li];
+        a.out = rq.out[li];
+        a.count = rq.count;
+        a.slot_bytes = kLlSlotBytes;
+        a.timeout_ns = ctx_[li].timeout_ns;
+        a.seq = seq_;
+        a.status = status_[li];
+        a.abort = abort_[li];
+        a.local_fail = ctx_[li].exit_counter + 1;
+        a.rank = ctx_[li].rank;
+        a.nranks = nranks_;
+        a.tag = tag;
+        a.parity = (uint32_t)(ll_seq_ & 1);
+    }
+    stats_.launches++;
+    return launch_ar_ll(args.data(), nl, rq.dtype, rq.redop, rq.stream);
 }
 
 HcclResult Communicator::consistency_check(const OpRequest &rq, int algo)

@@ -155,6 +155,7 @@ private:
     };
     HcclResult get_plan(const OpDesc &d, const std::string &key, CachedPlan **out);
     HcclResult run_collective_once(const OpRequest &rq);
+    HcclResult run_ll_allreduce(const OpRequest &rq);
     HcclResult consistency_check(const OpRequest &rq, int algo);
     HcclResult maybe_retry(const OpRequest &rq, HcclResult failure);
     void heartbeat_loop();
@@ -184,6 +185,8 @@ private:
     void *dev_exit_ = nullptr;
     void *pinned_ = nullptr;               // host-mapped block holding status + abort words
     uint64_t p2p_slot_ = 0;
+    uint64_t ll_seq_ = 0;                  // number of LL operations issued (tag and mailbox parity)
+    bool ll_ok_ = false;
 
     std::mutex op_mu_;
     std::atomic<int> state_{CS_IDLE};

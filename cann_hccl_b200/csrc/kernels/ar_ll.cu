@@ -1,0 +1,178 @@
+// Small-message AllReduce for sm_100a, low-latency protocol: every rank pushes its contribution straight into a
+// mailbox on every peer as 16-byte lines {data, tag, data, tag} (8 payload bytes per line; a line is valid when both
+// tags equal this operation's tag), then polls its own mailboxes and reduces in rank order.  No fence, no separate
+// flag hop, no staging copy and no step table: one NVLink store latency separates the first instruction from the
+// result.  This is the latency path that the reference gives to its AIV small-data kernels
+// (algorithm/base/alg_aiv_template/aiv_all_reduce_910b_smalldata.h: one-shot, <= 64 KB); there the flag is a
+// separate 32-byte word and the wait is unbounded, here the flag travels with the data and every poll is bounded.
+//
+// Mailboxes are double buffered by the parity of the LL operation count: a rank can only start LL operation k+2 after
+// it has received every peer's lines of k+1, which those peers sent after they finished reading k.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include "common/log.h"
+#include "kernels/ar_ll.h"
+#include "kernels/prims.cuh"
+
+namespace hcclb {
+
+namespace {
+
+template <class T> struct LNum { using Acc = T; static __device__ __forceinline__ Acc up(T v) { return v; } static __device__ __forceinline__ T down(Acc v) { return v; } };
+template <> struct LNum<__half> { using Acc = float; static __device__ __forceinline__ float up(__half v) { return __half2float(v); } static __device__ __forceinline__ __half down(float v) { return __float2half_rn(v); } };
+template <> struct LNum<__nv_bfloat16> { using Acc = float; static __device__ __forceinline__ float up(__nv_bfloat16 v) { return __bfloat162float(v); } static __device__ __forceinline__ __nv_bfloat16 down(float v) { return __float2bfloat16_rn(v); } };
+
+template <int OP, class A> __device__ __forceinline__ A ll_op(A x, A y)
+{
+    if (OP == HCCL_REDUCE_SUM) return (A)(x + y);
+    if (OP == HCCL_REDUCE_PROD) return (A)(x * y);
+    if (OP == HCCL_REDUCE_MAX) return x > y ? x : y;
+    return x < y ? x : y;
+}
+
+template <class T> union Pay8 {
+    uint2 u;
+    T e[8 / sizeof(T)];
+};
+
+__device__ __forceinline__ void st_line(uint8_t *p, uint32_t d0, uint32_t d1, uint32_t tag)
+{
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(d0), "r"(tag), "r"(d1), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint4 ld_line(const uint8_t *p)
+{
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+template <class T, int OP>
+__global__ void __launch_bounds__(kLlThreads) ar_ll_kernel(const LlArgsArray args)
+{
+    const LlArgs &a = args.a[blockIdx.y];
+    using N = LNum<T>;
+    using Acc = typename N::Acc;
+    constexpr int E = 8 / sizeof(T);
+    const int me = a.rank, p = a.nranks;
+    const uint64_t nlines = (a.count + E - 1) / E;
+    const uint64_t parity_off = (uint64_t)a.parity * (uint64_t)p * a.slot_bytes;
+    const uint64_t deadline = global_timer_ns() + a.timeout_ns;
+    const T *in = (const T *)a.in;
+    T *out = (T *)a.out;
+    for (uint64_t line = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; line < nlines; line += (uint64_t)gridDim.x * blockDim.x) {
+        Pay8<T> mine;
+        const uint64_t e0 = line * E;
+        if (e0 + E <= a.count) mine.u = *(const uint2 *)(in + e0);
+        else {
+            mine.u = make_uint2(0, 0);
+            for (int k = 0; k < E; ++k)
+                if (e0 + k < a.count) mine.e[k] = in[e0 + k];
+        }
+        const uint64_t loff = parity_off + (uint64_t)me * a.slot_bytes + line * 16;
+        for (int i = 1; i < p; ++i) {  // start at the next rank so that the peers' links are hit evenly
+            int q = me + i;
+            if (q >= p) q -= p;
+            st_line(a.ll[q] + loff, mine.u.x, mine.u.y, a.tag);
+        }
+        Acc acc[E];
+        bool have = false;
+        bool failed = false;
+        for (int q = 0; q < p && !failed; ++q) {
+            Pay8<T> v;
+            if (q == me) v = mine;
+            else {
+                const uint8_t *src = a.ll[me] + parity_off + (uint64_t)q * a.slot_bytes + line * 16;
+                uint4 l = ld_line(src);
+                for (uint32_t it = 0; l.y != a.tag || l.w != a.tag; ++it) {
+                    if ((it & 255) == 255) {
+                        int code = 0;
+                        if (global_timer_ns() > deadline) code = HCCL_E_TIMEOUT;
+                        else if (*(volatile uint32_t *)a.local_fail) code = (int)*(volatile uint32_t *)a.local_fail;
+                        else if ((it & 8191) == 8191 && *a.abort) code = *a.abort == 2 ? HCCL_E_REMOTE : HCCL_E_SUSPENDING;
+                        if (code) {
+                            if (atomicCAS(a.local_fail, 0u, (uint32_t)code) == 0u) {
+                                DevStatus *s = a.status;
+                                s->step = 0; s->peer = q; s->chan = blockIdx.x; s->expected = a.tag; s->seen = l.y; s->seq = a.seq;
+                                __threadfence_system();
+                                *(volatile uint32_t *)&s->code = (uint32_t)code;
+                            }
+                            failed = true;
+                            break;
+                        }
+                    }
+                    l = ld_line(src);
+                }
+                v.u = make_uint2(l.x, l.z);
+            }
+            if (!have) {
+#pragma unroll
+                for (int k = 0; k < E; ++k) acc[k] = N::up(v.e[k]);
+                have = true;
+            } else {
+#pragma unroll
+                for (int k = 0; k < E; ++k) acc[k] = ll_op<OP>(acc[k], N::up(v.e[k]));
+            }
+        }
+        if (failed) return;
+        Pay8<T> r;
+#pragma unroll
+        for (int k = 0; k < E; ++k) r.e[k] = N::down(acc[k]);
+        if (e0 + E <= a.count) *(uint2 *)(out + e0) = r.u;
+        else
+            for (int k = 0; k < E; ++k)
+                if (e0 + k < a.count) out[e0 + k] = r.e[k];
+    }
+}
+
+template <class T> const void *ll_kernel_of(int op)
+{
+    switch (op) {
+        case HCCL_REDUCE_SUM: return (const void *)ar_ll_kernel<T, HCCL_REDUCE_SUM>;
+        case HCCL_REDUCE_PROD: return (const void *)ar_ll_kernel<T, HCCL_REDUCE_PROD>;
+        case HCCL_REDUCE_MAX: return (const void *)ar_ll_kernel<T, HCCL_REDUCE_MAX>;
+        default: return (const void *)ar_ll_kernel<T, HCCL_REDUCE_MIN>;
+    }
+}
+
+}  // namespace
+
+HcclResult launch_ar_ll(const LlArgs *args, int nlocal, int dtype, int op, void *stream)
+{
+    const void *fn = nullptr;
+    switch (dtype) {
+        case HCCL_DATA_TYPE_INT8: fn = ll_kernel_of<int8_t>(op); break;
+        case HCCL_DATA_TYPE_UINT8: fn = ll_kernel_of<uint8_t>(op); break;
+        case HCCL_DATA_TYPE_INT16: fn = ll_kernel_of<int16_t>(op); break;
+        case HCCL_DATA_TYPE_UINT16: fn = ll_kernel_of<uint16_t>(op); break;
+        case HCCL_DATA_TYPE_INT32: fn = ll_kernel_of<int32_t>(op); break;
+        case HCCL_DATA_TYPE_UINT32: fn = ll_kernel_of<uint32_t>(op); break;
+        case HCCL_DATA_TYPE_INT64: fn = ll_kernel_of<long long>(op); break;
+        case HCCL_DATA_TYPE_UINT64: fn = ll_kernel_of<unsigned long long>(op); break;
+        case HCCL_DATA_TYPE_FP32: fn = ll_kernel_of<float>(op); break;
+        case HCCL_DATA_TYPE_FP64: fn = ll_kernel_of<double>(op); break;
+        case HCCL_DATA_TYPE_FP16: fn = ll_kernel_of<__half>(op); break;
+        case HCCL_DATA_TYPE_BFP16: fn = ll_kernel_of<__nv_bfloat16>(op); break;
+        default: return HCCL_E_NOT_SUPPORT;
+    }
+    if (nlocal < 1 || nlocal > kMaxRanks) return HCCL_E_PARA;
+    LlArgsArray arr;
+    for (int i = 0; i < nlocal; ++i) arr.a[i] = args[i];
+    int es = dtype_size(dtype);
+    uint64_t nlines = (args[0].count * es + 7) / 8;
+    unsigned ctas = (unsigned)((nlines + kLlThreads - 1) / kLlThreads);
+    unsigned cap = nlocal > 1 ? (unsigned)(128 / nlocal) : 48u;
+    if (ctas > cap) ctas = cap;
+    if (ctas < 1) ctas = 1;
+    dim3 grid(ctas, (unsigned)nlocal), block(kLlThreads);
+    void *kargs[] = {(void *)&arr};
+    cudaError_t e = nlocal > 1 ? cudaLaunchCooperativeKernel(fn, grid, block, kargs, 0, (cudaStream_t)stream)
+                               : cudaLaunchKernel(fn, grid, block, kargs, 0, (cudaStream_t)stream);
+    if (e != cudaSuccess) {
+        HLOG_ERROR("LL allreduce launch failed: %s", cudaGetErrorString(e));
+        return HCCL_E_RUNTIME;
+    }
+    return HCCL_SUCCESS;
+}
+
+}  // namespace hcclb

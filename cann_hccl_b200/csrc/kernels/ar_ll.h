@@ -1,0 +1,27 @@
+// Launch interface of the low-latency small-message AllReduce kernel (kernels/ar_ll.cu).
+#pragma once
+#include "algo/plan.h"
+namespace hcclb {
+constexpr int kLlThreads = 256;
+constexpr uint64_t kLlMaxPayload = 256u << 10;        // largest message the LL path takes (bytes)
+constexpr uint64_t kLlSlotBytes = 2 * kLlMaxPayload;  // 16-byte lines carry 8 payload bytes
+struct LlArgs {
+    uint8_t *ll[kMaxRanks];   // mailbox region of rank q mapped into this rank's address space
+    const void *in;
+    void *out;
+    uint64_t count;           // elements
+    uint64_t slot_bytes;
+    uint64_t timeout_ns;
+    uint64_t seq;
+    DevStatus *status;
+    volatile uint32_t *abort;
+    uint32_t *local_fail;
+    int32_t rank, nranks;
+    uint32_t tag, parity;
+};
+struct LlArgsArray {
+    LlArgs a[kMaxRanks];
+};
+// One launch runs the listed local ranks (more than one: virtual ranks of one GPU, cooperative launch).
+HcclResult launch_ar_ll(const LlArgs *args, int nlocal, int dtype, int op, void *stream);
+}  // namespace hcclb

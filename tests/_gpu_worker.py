@@ -60,12 +60,14 @@ def ok(c):
 def scenario_collectives(c, p, r, args):
     nvls = c.has_nvls()
     print("rank %d: nvls=%s" % (r, nvls))
-    ar_algos = [L.ALGO_AUTO, L.ALGO_MESH_ONESHOT, L.ALGO_MESH, L.ALGO_RING, L.ALGO_RHD, L.ALGO_MESH_PIPE] + ([L.ALGO_NVLS, L.ALGO_NVLS_ONESHOT, L.ALGO_NVLS_PIPE] if nvls else [])
+    ar_algos = [L.ALGO_AUTO, L.ALGO_LL, L.ALGO_MESH_ONESHOT, L.ALGO_MESH, L.ALGO_RING, L.ALGO_RHD, L.ALGO_MESH_PIPE] + ([L.ALGO_NVLS, L.ALGO_NVLS_ONESHOT, L.ALGO_NVLS_PIPE] if nvls else [])
     for n in (4, 1000, 262144, 6_000_000):  # the last one runs the staging loop (24 MB through 16 MB halves)
         for algo in ar_algos:
             if algo in (L.ALGO_NVLS, L.ALGO_NVLS_ONESHOT, L.ALGO_NVLS_PIPE) and (n * 4) % 16:
                 continue
             if algo in (L.ALGO_MESH_PIPE, L.ALGO_NVLS_PIPE) and n < 1000:
+                continue
+            if algo == L.ALGO_LL and n > 60000:
                 continue
             for dtype, op in ((torch.float32, L.SUM), (torch.bfloat16, L.SUM), (torch.bfloat16, L.MAX), (torch.int32, L.MIN)):
                 if algo in (L.ALGO_NVLS, L.ALGO_NVLS_ONESHOT, L.ALGO_NVLS_PIPE) and (n * dtype.itemsize) % 16:
@@ -163,11 +165,13 @@ def scenario_perf(c, p, r, args):
         rows = []
         t = _time_repeat(c, lambda it: c.nccl_allreduce_repeat(y, y, n, L.FP32, it, size, nwin), iters)
         rows.append(("nccl", 0, t))
-        algos = [L.ALGO_AUTO, L.ALGO_MESH_ONESHOT, L.ALGO_MESH, L.ALGO_RING, L.ALGO_RHD, L.ALGO_MESH_PIPE] + ([L.ALGO_NVLS, L.ALGO_NVLS_ONESHOT, L.ALGO_NVLS_PIPE] if nv else [])
+        algos = [L.ALGO_AUTO, L.ALGO_LL, L.ALGO_MESH_ONESHOT, L.ALGO_MESH, L.ALGO_RING, L.ALGO_RHD, L.ALGO_MESH_PIPE] + ([L.ALGO_NVLS, L.ALGO_NVLS_ONESHOT, L.ALGO_NVLS_PIPE] if nv else [])
         for algo in algos:
             if algo in (L.ALGO_MESH_ONESHOT, L.ALGO_NVLS_ONESHOT) and size > (4 << 20):
                 continue
             if algo in (L.ALGO_MESH_PIPE, L.ALGO_NVLS_PIPE) and size < (4 << 20):
+                continue
+            if algo == L.ALGO_LL and size > (256 << 10):
                 continue
             chans = (0,) if size < (4 << 20) else (0, 32, 96)
             for nchan in chans:

@@ -88,6 +88,24 @@ def test_allreduce_dtypes_ops(comms, dtype, op):
         close(o, ref, dtype, p)
 
 
+@pytest.mark.parametrize("p", [2, 3, 8])
+@pytest.mark.parametrize("dtype,op", [(torch.float32, L.SUM), (torch.bfloat16, L.SUM), (torch.float16, L.MAX), (torch.int8, L.MIN),
+                                      (torch.int64, L.PROD), (torch.float64, L.SUM)])
+def test_allreduce_low_latency_protocol(comms, p, dtype, op):
+    """LL kernel: data and tag in the same 16-byte line, double-buffered mailboxes; repeated calls alternate parity."""
+    c = comms(p)
+    for n in (1, 2, 1023, 30001):
+        ins = rnd(p, n, dtype, seed=n)
+        outs = [torch.zeros(n, device="cuda", dtype=dtype) for _ in range(p)]
+        for _ in range(3):
+            c.all_reduce(ins, outs, op=op, algo=L.ALGO_LL)
+        ok(c)
+        ref = ref_reduce(ins, op)
+        for o in outs:
+            close(o, ref, dtype, p)
+    assert c.stats()["algos"].get("ll", 0) >= 12
+
+
 @pytest.mark.parametrize("p", [2, 4, 8])
 def test_allreduce_pipelined_groups(comms, p):
     """Large-message algorithm: copy-in, reduce and gather CTA groups of one kernel pipelined over chunks."""
