@@ -146,6 +146,7 @@ def lib():
         "HcclB200LocalSendRecv": [vp, u32, u32, vp, vp, u64, C.c_int, vp],
         "HcclB200StreamSync": [vp, vp],
         "HcclB200GetStatus": [vp, u32, P(B200Status)],
+        "HcclB200GetKernelTrace": [vp, u32, P(u64), C.c_size_t, P(i32)],
         "HcclB200WaitProbe": [vp, u32, C.c_double, vp],
         "HcclB200DescribeStatus": [vp, u32, C.c_char_p, C.c_size_t],
         "HcclB200Select": [vp, i32, u64, C.c_int, C.c_int, P(i32), P(i32), P(C.c_double)],

@@ -67,6 +67,7 @@ struct RankCtx {
     DevStatus *status;           // host-mapped status block of this rank
     volatile uint32_t *abort;    // host-mapped abort word, non-zero = give up
     uint32_t *exit_counter;      // local counter used to find the last CTA of an op
+    uint64_t *trace;             // optional in-kernel timestamps (HCCL_KERNEL_TRACE=1): [0] kernel start, then 3 per step
     uint64_t stage_half;         // bytes per staging half
     uint64_t timeout_ns;         // bound of every wait
 };
@@ -87,6 +88,8 @@ struct ExecArgs {
 // Flag page layout: [bank][source rank][channel] 64-bit words, then one "done" word per source rank.
 HCCLB_HD size_t flag_index(int bank, int src, int chan) { return ((size_t)bank * kMaxRanks + src) * kMaxChannels + chan; }
 HCCLB_HD size_t done_index(int src) { return (size_t)kFlagBanks * kMaxRanks * kMaxChannels + src; }
+constexpr int kTraceSteps = 340;  // steps whose timestamps fit the trace buffer
+constexpr size_t kTraceWords = 1 + 3 * kTraceSteps;
 constexpr size_t kFlagWords = (size_t)kFlagBanks * kMaxRanks * kMaxChannels + kMaxRanks;
 constexpr size_t kFlagPageBytes = ((kFlagWords * 8 + 4095) / 4096) * 4096;
 

@@ -668,6 +668,15 @@ HcclResult HcclB200StreamSync(HcclComm comm, aclrtStream stream)
     GET_COMM("HcclB200StreamSync");
     return c->sync_stream(stream);
 }
+HcclResult HcclB200GetKernelTrace(HcclComm comm, uint32_t localRank, uint64_t *out, size_t capWords, int32_t *nsteps)
+{
+    GET_COMM("HcclB200GetKernelTrace");
+    CHK_RET_LOG(!out, HCCL_E_PTR, "[EI0003] HcclB200GetKernelTrace: out is null");
+    int n = 0;
+    CHK_RET(c->kernel_trace((int)localRank, out, capWords, &n));
+    if (nsteps) *nsteps = n;
+    return HCCL_SUCCESS;
+}
 HcclResult HcclB200WaitProbe(HcclComm comm, uint32_t localRank, double timeoutMs, aclrtStream stream)
 {
     GET_COMM("HcclB200WaitProbe");

@@ -209,6 +209,10 @@ HcclResult Communicator::init_common()
         CHK_RET_LOG(cudaMalloc(&dev_exit_, sizeof(uint32_t) * 2 * nl) != cudaSuccess, HCCL_E_MEMORY, "cudaMalloc failed");
         cudaMemset(dev_exit_, 0, sizeof(uint32_t) * 2 * nl);
     }
+    if (dev && getenv("HCCL_KERNEL_TRACE") && atoi(getenv("HCCL_KERNEL_TRACE")) > 0) {
+        CHK_RET_LOG(cudaMalloc(&dev_trace_, sizeof(uint64_t) * kTraceWords * nl) != cudaSuccess, HCCL_E_MEMORY, "cudaMalloc failed");
+        cudaMemset(dev_trace_, 0, sizeof(uint64_t) * kTraceWords * nl);
+    }
     for (int li = 0; li < nl; ++li) {
         RankCtx &x = ctx_[li];
         memset(&x, 0, sizeof(x));
@@ -229,6 +233,7 @@ HcclResult Communicator::init_common()
         x.abort = abort_[li];
         x.exit_counter = dev ? (uint32_t *)dev_exit_ + 2 * li : nullptr;
         x.stage_half = half;
+        x.trace = dev_trace_ ? (uint64_t *)dev_trace_ + (size_t)li * kTraceWords : nullptr;
         x.timeout_ns = (uint64_t)(tmo_ms * 1e6);
     }
     if (dev) {
@@ -260,6 +265,7 @@ Communicator::~Communicator()
     if (dev) {
         if (dev_ctx_) cudaFree(dev_ctx_);
         if (dev_exit_) cudaFree(dev_exit_);
+        if (dev_trace_) cudaFree(dev_trace_);
         if (pinned_) cudaFreeHost(pinned_);
     } else free(pinned_);
     alloc_.reset();
@@ -883,6 +889,17 @@ HcclResult Communicator::sync_stream(void *stream)
         CHK_RET_LOG(e != cudaSuccess, HCCL_E_RUNTIME, "stream synchronize failed: %s", cudaGetErrorString(e));
     }
     return async_error();
+}
+
+HcclResult Communicator::kernel_trace(int local, uint64_t *out, size_t cap_words, int *nsteps)
+{
+    if (!dev_trace_) return HCCL_E_UNAVAIL;
+    if (local < 0 || local >= nlocal() || cap_words < 1) return HCCL_E_PARA;
+    size_t n = std::min(cap_words, kTraceWords);
+    cudaDeviceSynchronize();
+    CHK_RET_LOG(cudaMemcpy(out, (uint64_t *)dev_trace_ + (size_t)local * kTraceWords, n * 8, cudaMemcpyDeviceToHost) != cudaSuccess, HCCL_E_RUNTIME, "cudaMemcpy failed");
+    if (nsteps) *nsteps = (int)((n - 1) / 3);
+    return HCCL_SUCCESS;
 }
 
 HcclResult Communicator::wait_probe(int local, double timeout_ms, void *stream)

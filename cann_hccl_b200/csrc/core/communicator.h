@@ -136,6 +136,9 @@ public:
     HcclResult exchange(const std::string &tag, const std::string &mine, std::vector<std::string> *all);
     // Same, over the dedicated connection of the p2p backend's helper thread.
     HcclResult exchange_p2p(const std::string &tag, const std::string &mine, std::vector<std::string> *all);
+    // Timestamps of the newest executor launch of local rank `local` (ns): out[0] kernel start, then per step
+    // {after wait, after data movement, after signal} as seen by the first channel of the step.  Needs HCCL_KERNEL_TRACE=1.
+    HcclResult kernel_trace(int local, uint64_t *out, size_t cap_words, int *nsteps);
     DevStatus *status(int local) { return status_[local]; }
     const RankCtx &ctx(int local) const { return ctx_[local]; }
     void *device_ctx_array() const { return dev_ctx_; }
@@ -183,6 +186,7 @@ private:
     std::vector<volatile uint32_t *> abort_;
     void *dev_ctx_ = nullptr;              // device array of RankCtx
     void *dev_exit_ = nullptr;
+    void *dev_trace_ = nullptr;            // in-kernel timestamp buffers (kTraceWords per local rank) when enabled
     void *pinned_ = nullptr;               // host-mapped block holding status + abort words
     uint64_t p2p_slot_ = 0;
     uint64_t ll_seq_ = 0;                  // number of LL operations issued (tag and mailbox parity)

@@ -294,6 +294,7 @@ __global__ void __launch_bounds__(kExecThreads, 1) exec_plan_kernel(const RankCt
     w.local_fail = c.exit_counter + 1;
     const uint64_t half_off = a.track_done ? (a.seq & 1) * c.stage_half : 0;
 
+    if (c.trace && chan == 0 && tid == 0) c.trace[0] = global_timer_ns();
     if (a.track_done) {
         if (chan == 0 && tid == 0) *(volatile uint64_t *)&c.status->head = a.seq;
         if (a.seq >= 2) {  // the peers must have left the op that used this staging half before
@@ -309,6 +310,7 @@ __global__ void __launch_bounds__(kExecThreads, 1) exec_plan_kernel(const RankCt
         const Step &s = a.steps[si];
         if (chan < s.chan_lo || chan >= s.chan_lo + s.chan_n) continue;
         const int ci = chan - s.chan_lo;
+        const bool tr = c.trace && ci == 0 && tid == 0 && si < kTraceSteps;
         // ---- wait
         if (s.wait_rank != RANK_NONE) {
             const uint64_t want = flag_value(a, s, s.wait_val);
@@ -326,6 +328,7 @@ __global__ void __launch_bounds__(kExecThreads, 1) exec_plan_kernel(const RankCt
             __syncthreads();
             if (s_fail) break;
         }
+        if (tr) c.trace[1 + 3 * si] = global_timer_ns();
         // ---- move / reduce
         uint64_t lo, hi;
         switch (s.op) {
@@ -394,6 +397,7 @@ __global__ void __launch_bounds__(kExecThreads, 1) exec_plan_kernel(const RankCt
             }
             default: break;
         }
+        if (tr) { __threadfence(); c.trace[2 + 3 * si] = global_timer_ns(); }
         // ---- signal
         if (s.sig_rank != RANK_NONE) {
             __syncthreads();  // every thread's stores of this step precede the fence of the signalling threads
@@ -405,6 +409,7 @@ __global__ void __launch_bounds__(kExecThreads, 1) exec_plan_kernel(const RankCt
                 st_release_sys(c.flags[s.sig_rank] + flag_index(s.sig_bank, me, chan), val);
             }
         }
+        if (tr) c.trace[3 + 3 * si] = global_timer_ns();
     }
     // ---- completion: the last CTA of this rank tells every peer that this op no longer touches their memory
     if (a.track_done) {

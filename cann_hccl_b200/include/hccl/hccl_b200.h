@@ -61,6 +61,9 @@ typedef struct HcclB200StatusDef {
     uint32_t code, step; int32_t peer; uint32_t chan;
     uint64_t expected, seen, seq, head, tail;
 } HcclB200Status;
+/* In-kernel timestamps of the newest executor launch (needs HCCL_KERNEL_TRACE=1 at communicator creation):
+ * out[0] = kernel start (globaltimer ns), then per step {after wait, after data movement, after signal}. */
+extern HcclResult HcclB200GetKernelTrace(HcclComm comm, uint32_t localRank, uint64_t *out, size_t capWords, int32_t *nsteps);
 /* Diagnostic: local rank waits (bounded by timeoutMs) for a flag nothing sets; returns HCCL_E_TIMEOUT and fills the
  * status block.  The communicator must be resumed afterwards.  Proves that a starved wait ends and leaves the
  * context usable. */

@@ -221,6 +221,23 @@ class Communicator:
     def sync(self, stream=None):
         return L.lib().HcclB200StreamSync(self._h, self._stream(stream))
 
+    def kernel_trace(self, local=0, max_steps=64):
+        """Per-step timestamps (us since kernel start) of the newest executor launch: list of (wait_done, moved, signalled)."""
+        n = 1 + 3 * max_steps
+        buf = (C.c_uint64 * n)()
+        ns = C.c_int32()
+        rc = L.lib().HcclB200GetKernelTrace(self._h, local, buf, n, C.byref(ns))
+        if rc != L.SUCCESS:
+            return None
+        t0 = buf[0]
+        out = []
+        for i in range(ns.value):
+            w, m, s = buf[1 + 3 * i], buf[2 + 3 * i], buf[3 + 3 * i]
+            if w == 0 and m == 0:
+                continue
+            out.append((i, (w - t0) / 1e3, (m - t0) / 1e3, (s - t0) / 1e3 if s else None))
+        return out
+
     def wait_probe(self, local=0, timeout_ms=200.0, stream=None):
         """Starve one bounded wait on purpose; returns the result code the wait ended with."""
         return L.lib().HcclB200WaitProbe(self._h, local, float(timeout_ms), self._stream(stream))

@@ -177,6 +177,10 @@ def scenario_perf(c, p, r, args):
             for nchan in chans:
                 t = _time_repeat(c, lambda it: c.repeat(L.ALLREDUCE, x, y, n, L.FP32, it, size, nwin, algo=algo, nchan=nchan), iters)
                 rows.append((L.ALGO_NAMES[algo], nchan, t))
+                if r == 0 and os.environ.get("HCCL_KERNEL_TRACE") and nchan == 0:
+                    tr = c.kernel_trace(0)
+                    if tr:
+                        print("  trace %s size %d: " % (L.ALGO_NAMES[algo], size) + " ".join("s%d[w%.0f m%.0f g%.0f]" % (i, w, m, g or 0) for i, w, m, g in tr[:14]))
         ok(c)
         if r == 0:
             for name, nchan, t in rows:

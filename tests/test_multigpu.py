@@ -33,8 +33,8 @@ def run_gpu_ranks(p, scenario, env=None, timeout=600, args=()):
             out, _ = pr.communicate()
             out += "\n[killed by test timeout]"
         outs.append((pr.returncode, out))
-    for r, (code, out) in enumerate(outs):
-        assert code == 0, "rank %d failed (%s):\n%s" % (r, code, out[-4000:])
+    bad = [(r, code, out) for r, (code, out) in enumerate(outs) if code != 0]
+    assert not bad, "\n".join("rank %d failed (%s):\n%s" % (r, code, out[-1500:]) for r, code, out in bad)
     return outs
 
 
