@@ -66,7 +66,8 @@ struct RankCtx {
     uint8_t *mc_stage;           // NVLS multicast mapping of the staging buffer (null when unavailable)
     DevStatus *status;           // host-mapped status block of this rank
     volatile uint32_t *abort;    // host-mapped abort word, non-zero = give up
-    uint32_t *exit_counter;      // local counter used to find the last CTA of an op
+    uint32_t *exit_counter;      // local counter used to find the last CTA of an op; [1] = first failure code of this rank
+    uint64_t *dev_tail;          // device word: sequence number of the newest completed op
     uint64_t *trace;             // optional in-kernel timestamps (HCCL_KERNEL_TRACE=1): [0] kernel start, then 3 per step
     uint64_t stage_half;         // bytes per staging half
     uint64_t timeout_ns;         // bound of every wait

@@ -72,8 +72,8 @@ double estimate_us(int coll, int algo, uint64_t bytes, int p, const CostModel &m
                 case ALGO_NVLS_ONESHOT: return L + a + p * n / Bn + n / G + 2 * s;
                 case ALGO_NVLS: return L + 2 * a + (1.0 + 1.0 / p) * n / Bn + 2 * n / G + (p + 2) * s;
                 // pipelined: local copies hide behind the transfers; costs a pipeline fill of roughly one chunk per phase
-                case ALGO_MESH_PIPE: return L + 4 * a + std::max(2 * f * n / B, 2 * n / G) + 3 * std::min(n, 4.0 * (1 << 20)) / B + 6 * s;
-                case ALGO_NVLS_PIPE: return L + 4 * a + std::max((1.0 + 1.0 / p) * n / Bn, 2 * n / G) + 3 * std::min(n, 4.0 * (1 << 20)) / Bn + 6 * s;
+                case ALGO_MESH_PIPE: return L + 4 * a + std::max(2 * f * n / B, 2 * n / G) + 3 * std::min(n, 4.0 * (1 << 20)) / B + 6 * s + std::ceil(n / (4.0 * (1 << 20))) * 3 * (2 * a + 4);
+                case ALGO_NVLS_PIPE: return L + 4 * a + std::max((1.0 + 1.0 / p) * n / Bn, 2 * n / G) + 3 * std::min(n, 4.0 * (1 << 20)) / Bn + 6 * s + std::ceil(n / (4.0 * (1 << 20))) * 3 * (2 * a + 4);
             }
             break;
         case COLL_REDUCE_SCATTER: case COLL_REDUCE_SCATTER_V:  // bytes = one rank's result

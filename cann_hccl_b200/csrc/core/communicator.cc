@@ -206,8 +206,8 @@ HcclResult Communicator::init_common()
     status_.assign(nl, nullptr);
     abort_.assign(nl, nullptr);
     if (dev) {
-        CHK_RET_LOG(cudaMalloc(&dev_exit_, sizeof(uint32_t) * 2 * nl) != cudaSuccess, HCCL_E_MEMORY, "cudaMalloc failed");
-        cudaMemset(dev_exit_, 0, sizeof(uint32_t) * 2 * nl);
+        CHK_RET_LOG(cudaMalloc(&dev_exit_, sizeof(uint32_t) * 4 * nl) != cudaSuccess, HCCL_E_MEMORY, "cudaMalloc failed");
+        cudaMemset(dev_exit_, 0, sizeof(uint32_t) * 4 * nl);
     }
     if (dev && getenv("HCCL_KERNEL_TRACE") && atoi(getenv("HCCL_KERNEL_TRACE")) > 0) {
         CHK_RET_LOG(cudaMalloc(&dev_trace_, sizeof(uint64_t) * kTraceWords * nl) != cudaSuccess, HCCL_E_MEMORY, "cudaMalloc failed");
@@ -231,7 +231,8 @@ HcclResult Communicator::init_common()
         abort_[li] = (volatile uint32_t *)(pb + align_up(sizeof(DevStatus), 64));
         x.status = status_[li];
         x.abort = abort_[li];
-        x.exit_counter = dev ? (uint32_t *)dev_exit_ + 2 * li : nullptr;
+        x.exit_counter = dev ? (uint32_t *)dev_exit_ + 4 * li : nullptr;
+        x.dev_tail = dev ? (uint64_t *)((uint32_t *)dev_exit_ + 4 * li + 2) : nullptr;
         x.stage_half = half;
         x.trace = dev_trace_ ? (uint64_t *)dev_trace_ + (size_t)li * kTraceWords : nullptr;
         x.timeout_ns = (uint64_t)(tmo_ms * 1e6);
@@ -252,6 +253,7 @@ Communicator::~Communicator()
     hb_stop_.store(true);
     { std::lock_guard<std::mutex> lk(hb_mu_); hb_cv_.notify_all(); }
     if (hb_thread_.joinable()) hb_thread_.join();
+    if (hb_stream_) cudaStreamDestroy((cudaStream_t)hb_stream_);
     p2p_.reset();
     bool dev = settings_.transport == TR_DEVICE;
     if (dev) {
@@ -337,8 +339,15 @@ HcclResult Communicator::run_plan(const Plan &plan, const void *dev_steps_base, 
         a.dtype = dtype;
         a.redop = redop;
         a.track_done = track_done ? 1 : 0;
+        if (track_done && settings_.transport == TR_DEVICE) status_[li]->head = seq;  // completion (tail) is a device word
     }
     stats_.launches++;
+    if (settings_.transport == TR_DEVICE && dev_trace_) {
+        for (int li = 0; li < nlocal(); ++li) {  // the last two words (end of this / of the previous launch) persist
+            cudaMemsetAsync((uint64_t *)dev_trace_ + (size_t)li * kTraceWords, 0, sizeof(uint64_t) * (kTraceWords - 2), (cudaStream_t)rq.stream);
+            cudaMemsetAsync((uint64_t *)dev_trace_ + (size_t)li * kTraceWords, 0xff, 8, (cudaStream_t)rq.stream);
+        }
+    }
     if (settings_.transport == TR_DEVICE) {
         // map local index -> context: the plan may cover a subset of the local ranks (local Send/Recv)
         return launch_exec_plan((const RankCtx *)dev_ctx_, args.data(), nl, plan.nchan, rq.stream);
@@ -862,7 +871,8 @@ HcclResult Communicator::resume_locked()
         if (dev) cudaMemcpy(dst, done.data(), kMaxRanks * 8, cudaMemcpyHostToDevice);
         else memcpy(dst, done.data(), kMaxRanks * 8);
     }
-    if (dev && dev_exit_) cudaMemset(dev_exit_, 0, sizeof(uint32_t) * 2 * nlocal());
+    if (dev && dev_exit_)
+        for (int li = 0; li < nlocal(); ++li) cudaMemset((uint32_t *)dev_exit_ + 4 * li, 0, sizeof(uint32_t) * 2);  // counter + failure code
     // order matters for the heartbeat thread: own status is clean, then the epoch moves (peers' older error reports
     // become stale), then what it may have recorded from those reports is dropped
     resume_gen_.store(gen);
@@ -950,6 +960,17 @@ void Communicator::heartbeat_loop()
         m.lost_ms = (uint32_t)env.heartbeat_lost_ms;
         m.epoch = (uint32_t)resume_gen_.load();
         DevStatus *s = status_[0];
+        if (settings_.transport == TR_DEVICE && ctx_[0].dev_tail) {
+            if (!hb_stream_) {
+                cudaSetDevice(settings_.device);
+                cudaStream_t st;
+                if (cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) == cudaSuccess) hb_stream_ = st;
+            }
+            uint64_t tail = 0;
+            if (hb_stream_ && cudaMemcpyAsync(&tail, ctx_[0].dev_tail, 8, cudaMemcpyDeviceToHost, (cudaStream_t)hb_stream_) == cudaSuccess &&
+                cudaStreamSynchronize((cudaStream_t)hb_stream_) == cudaSuccess)
+                s->tail = tail;
+        }
         m.head = s->head; m.tail = s->tail;
         m.status = PEER_OK;
         if (s->code != 0) { m.status = PEER_ERROR; m.error_code = s->code; }

@@ -60,7 +60,8 @@ __global__ void __launch_bounds__(kLlThreads) ar_ll_kernel(const LlArgsArray arg
     const uint64_t deadline = global_timer_ns() + a.timeout_ns;
     const T *in = (const T *)a.in;
     T *out = (T *)a.out;
-    for (uint64_t line = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; line < nlines; line += (uint64_t)gridDim.x * blockDim.x) {
+    const uint64_t first = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (uint64_t)gridDim.x * blockDim.x;
+    auto load_mine = [&](uint64_t line) {
         Pay8<T> mine;
         const uint64_t e0 = line * E;
         if (e0 + E <= a.count) mine.u = *(const uint2 *)(in + e0);
@@ -69,12 +70,22 @@ __global__ void __launch_bounds__(kLlThreads) ar_ll_kernel(const LlArgsArray arg
             for (int k = 0; k < E; ++k)
                 if (e0 + k < a.count) mine.e[k] = in[e0 + k];
         }
+        return mine;
+    };
+    // phase 1: push every line of this thread to every peer; the stores pipeline freely
+    for (uint64_t line = first; line < nlines; line += stride) {
+        Pay8<T> mine = load_mine(line);
         const uint64_t loff = parity_off + (uint64_t)me * a.slot_bytes + line * 16;
         for (int i = 1; i < p; ++i) {  // start at the next rank so that the peers' links are hit evenly
             int q = me + i;
             if (q >= p) q -= p;
             st_line(a.ll[q] + loff, mine.u.x, mine.u.y, a.tag);
         }
+    }
+    // phase 2: collect the peers' lines (mostly arrived by now) and reduce in rank order
+    for (uint64_t line = first; line < nlines; line += stride) {
+        Pay8<T> mine = load_mine(line);
+        const uint64_t e0 = line * E;
         Acc acc[E];
         bool have = false;
         bool failed = false;
@@ -161,7 +172,7 @@ HcclResult launch_ar_ll(const LlArgs *args, int nlocal, int dtype, int op, void 
     int es = dtype_size(dtype);
     uint64_t nlines = (args[0].count * es + 7) / 8;
     unsigned ctas = (unsigned)((nlines + kLlThreads - 1) / kLlThreads);
-    unsigned cap = nlocal > 1 ? (unsigned)(128 / nlocal) : 48u;
+    unsigned cap = nlocal > 1 ? (unsigned)(128 / nlocal) : 96u;
     if (ctas > cap) ctas = cap;
     if (ctas < 1) ctas = 1;
     dim3 grid(ctas, (unsigned)nlocal), block(kLlThreads);

@@ -13,6 +13,7 @@
 namespace hcclb {
 
 constexpr int kExecThreads = 512;
+constexpr int kSmemSteps = 96;  // steps of a plan kept in shared memory (longer plans read the rest from global memory)
 
 struct ExecArgsArray {
     ExecArgs a[kMaxRanks];
@@ -280,23 +281,37 @@ HCCLB_MC_OK(uint32_t)
 template <class T, int OP>
 __global__ void __launch_bounds__(kExecThreads, 1) exec_plan_kernel(const RankCtx *ctxs, const ExecArgsArray args)
 {
-    const RankCtx &c = ctxs[blockIdx.y];
     const ExecArgs &a = args.a[blockIdx.y];
-    const int chan = blockIdx.x, tid = threadIdx.x, me = c.rank, p = c.nranks;
+    const int chan = blockIdx.x, tid = threadIdx.x;
+    // the rank context and the first steps are staged in shared memory: one coalesced read instead of a dependent
+    // global load per field and step
+    __shared__ RankCtx s_ctx;
+    __shared__ Step s_steps[kSmemSteps];
+    {
+        const uint64_t *gs = (const uint64_t *)&ctxs[blockIdx.y];
+        for (int i = tid; i < (int)(sizeof(RankCtx) / 8); i += blockDim.x) ((uint64_t *)&s_ctx)[i] = gs[i];
+        const int nsm = a.nsteps < kSmemSteps ? a.nsteps : kSmemSteps;
+        const uint64_t *gp = (const uint64_t *)a.steps;
+        for (int i = tid; i < nsm * (int)(sizeof(Step) / 8); i += blockDim.x) ((uint64_t *)s_steps)[i] = gp[i];
+    }
+    const RankCtx &c = s_ctx;
     const int es = dtype_size(a.dtype);
     __shared__ int s_fail;
     __shared__ const uint8_t *s_src[kMaxRanks];
     if (tid == 0) s_fail = 0;
     __syncthreads();
+    const int me = c.rank, p = c.nranks;
     WaitCtx w;
     w.deadline = global_timer_ns() + c.timeout_ns;
     w.abort = c.abort;
     w.local_fail = c.exit_counter + 1;
     const uint64_t half_off = a.track_done ? (a.seq & 1) * c.stage_half : 0;
 
-    if (c.trace && chan == 0 && tid == 0) c.trace[0] = global_timer_ns();
+    if (c.trace && tid == 0) {
+        if (chan == 0) c.trace[kTraceWords - 2] = c.trace[kTraceWords - 1];  // end of the previous launch
+        atomicMin((unsigned long long *)&c.trace[0], (unsigned long long)global_timer_ns());
+    }
     if (a.track_done) {
-        if (chan == 0 && tid == 0) *(volatile uint64_t *)&c.status->head = a.seq;
         if (a.seq >= 2) {  // the peers must have left the op that used this staging half before
             if (tid < p && tid != me) {
                 uint64_t seen;
@@ -307,10 +322,10 @@ __global__ void __launch_bounds__(kExecThreads, 1) exec_plan_kernel(const RankCt
         }
     }
     for (int si = 0; si < a.nsteps && !s_fail; ++si) {
-        const Step &s = a.steps[si];
+        const Step &s = si < kSmemSteps ? s_steps[si] : a.steps[si];
         if (chan < s.chan_lo || chan >= s.chan_lo + s.chan_n) continue;
         const int ci = chan - s.chan_lo;
-        const bool tr = c.trace && ci == 0 && tid == 0 && si < kTraceSteps;
+        const bool tr = c.trace && tid == 0 && si < kTraceSteps;  // slowest channel of the step: atomicMax over its channels
         // ---- wait
         if (s.wait_rank != RANK_NONE) {
             const uint64_t want = flag_value(a, s, s.wait_val);
@@ -328,7 +343,7 @@ __global__ void __launch_bounds__(kExecThreads, 1) exec_plan_kernel(const RankCt
             __syncthreads();
             if (s_fail) break;
         }
-        if (tr) c.trace[1 + 3 * si] = global_timer_ns();
+        if (tr) atomicMax((unsigned long long *)&c.trace[1 + 3 * si], (unsigned long long)global_timer_ns());
         // ---- move / reduce
         uint64_t lo, hi;
         switch (s.op) {
@@ -397,7 +412,10 @@ __global__ void __launch_bounds__(kExecThreads, 1) exec_plan_kernel(const RankCt
             }
             default: break;
         }
-        if (tr) { __threadfence(); c.trace[2 + 3 * si] = global_timer_ns(); }
+        if (c.trace && si < kTraceSteps) {  // uniform across the CTA
+            __syncthreads();
+            if (tid == 0) atomicMax((unsigned long long *)&c.trace[2 + 3 * si], (unsigned long long)global_timer_ns());
+        }
         // ---- signal
         if (s.sig_rank != RANK_NONE) {
             __syncthreads();  // every thread's stores of this step precede the fence of the signalling threads
@@ -409,8 +427,9 @@ __global__ void __launch_bounds__(kExecThreads, 1) exec_plan_kernel(const RankCt
                 st_release_sys(c.flags[s.sig_rank] + flag_index(s.sig_bank, me, chan), val);
             }
         }
-        if (tr) c.trace[3 + 3 * si] = global_timer_ns();
+        if (tr) atomicMax((unsigned long long *)&c.trace[3 + 3 * si], (unsigned long long)global_timer_ns());
     }
+    if (c.trace && tid == 0) atomicMax((unsigned long long *)&c.trace[kTraceWords - 1], (unsigned long long)global_timer_ns());
     // ---- completion: the last CTA of this rank tells every peer that this op no longer touches their memory
     if (a.track_done) {
         __syncthreads();
@@ -424,7 +443,7 @@ __global__ void __launch_bounds__(kExecThreads, 1) exec_plan_kernel(const RankCt
         __syncthreads();
         if (s_last && !s_fail) {
             if (tid < p && tid != me) { fence_sys(); st_release_sys(c.flags[tid] + done_index(me), a.seq); }
-            if (tid == 0) *(volatile uint64_t *)&c.status->tail = a.seq;
+            if (tid == 0) *c.dev_tail = a.seq;  // read by the heartbeat thread with an asynchronous copy
         }
     }
 }

@@ -223,7 +223,7 @@ class Communicator:
 
     def kernel_trace(self, local=0, max_steps=64):
         """Per-step timestamps (us since kernel start) of the newest executor launch: list of (wait_done, moved, signalled)."""
-        n = 1 + 3 * max_steps
+        n = 1 + 3 * 340
         buf = (C.c_uint64 * n)()
         ns = C.c_int32()
         rc = L.lib().HcclB200GetKernelTrace(self._h, local, buf, n, C.byref(ns))
@@ -236,7 +236,8 @@ class Communicator:
             if w == 0 and m == 0:
                 continue
             out.append((i, (w - t0) / 1e3, (m - t0) / 1e3, (s - t0) / 1e3 if s else None))
-        return out
+        self.last_launch = {"gap_before_us": (t0 - buf[n - 2]) / 1e3 if buf[n - 2] else None, "kernel_us": (buf[n - 1] - t0) / 1e3}
+        return out[:max_steps]
 
     def wait_probe(self, local=0, timeout_ms=200.0, stream=None):
         """Starve one bounded wait on purpose; returns the result code the wait ended with."""

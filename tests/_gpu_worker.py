@@ -166,20 +166,23 @@ def scenario_perf(c, p, r, args):
         t = _time_repeat(c, lambda it: c.nccl_allreduce_repeat(y, y, n, L.FP32, it, size, nwin), iters)
         rows.append(("nccl", 0, t))
         algos = [L.ALGO_AUTO, L.ALGO_LL, L.ALGO_MESH_ONESHOT, L.ALGO_MESH, L.ALGO_RING, L.ALGO_RHD, L.ALGO_MESH_PIPE] + ([L.ALGO_NVLS, L.ALGO_NVLS_ONESHOT, L.ALGO_NVLS_PIPE] if nv else [])
+        if os.environ.get("PERF_ALGOS"):
+            algos = [L.ALGO_NAMES.index(x) for x in os.environ["PERF_ALGOS"].split(",") if x in L.ALGO_NAMES and (nv or "nvls" not in x)]
         for algo in algos:
             if algo in (L.ALGO_MESH_ONESHOT, L.ALGO_NVLS_ONESHOT) and size > (4 << 20):
                 continue
             if algo in (L.ALGO_MESH_PIPE, L.ALGO_NVLS_PIPE) and size < (4 << 20):
                 continue
-            if algo == L.ALGO_LL and size > (256 << 10):
+            if algo == L.ALGO_LL and size > (1 << 20):
                 continue
-            chans = (0,) if size < (4 << 20) else (0, 32, 96)
+            chans = [int(x) for x in os.environ.get("PERF_NCHAN", "0").split(",")]
             for nchan in chans:
                 t = _time_repeat(c, lambda it: c.repeat(L.ALLREDUCE, x, y, n, L.FP32, it, size, nwin, algo=algo, nchan=nchan), iters)
                 rows.append((L.ALGO_NAMES[algo], nchan, t))
                 if r == 0 and os.environ.get("HCCL_KERNEL_TRACE") and nchan == 0:
                     tr = c.kernel_trace(0)
                     if tr:
+                        print("  launch %s" % c.last_launch)
                         print("  trace %s size %d: " % (L.ALGO_NAMES[algo], size) + " ".join("s%d[w%.0f m%.0f g%.0f]" % (i, w, m, g or 0) for i, w, m, g in tr[:14]))
         ok(c)
         if r == 0:
