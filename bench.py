@@ -6,8 +6,9 @@
         bench.py --gpus 8 --steps 20 --warmup 5
 
 A "step" is one HcclAllReduce of the headline message (64 MiB per rank, fp32, sum, algorithm chosen by the
-selector).  The K timed steps are bracketed by a barrier + torch.cuda.synchronize() and timed with CUDA events on the
-launching stream; the reported time is the max over ranks.  Successive steps rotate through buffer sets whose total
+selector).  The K timed steps are issued back to back from C (the way the C program hccl_test does), bracketed by a
+barrier + torch.cuda.synchronize() and timed with CUDA events on the launching stream; the reported time is the max
+over ranks.  The NCCL baseline is ncclAllReduce issued by the same kind of loop on the same buffers.  Successive steps rotate through buffer sets whose total
 size exceeds the 126 MB L2, so no step finds its input in cache.  The JSON line also carries a size sweep
 (8 KiB .. 256 MiB: aveg_time us / alg_bandwidth GB/s for this library and for NCCL), the end-to-end number
 (pinned host -> device copy of the input, the collective, device -> host copy of the result, every step), SM clock
@@ -154,11 +155,31 @@ def main():
     n = HEADLINE_BYTES // 4
     nset = 4  # 4 x (64 MiB in + 64 MiB out) = 512 MiB rotated > 126 MB L2
     g = torch.Generator(device="cuda").manual_seed(1234 + rank)
-    ins = [torch.rand(n, device="cuda", generator=g) * 2 - 1 for _ in range(nset)]
-    outs = [torch.empty(n, device="cuda") for _ in range(nset)]
+
+    # the nset buffer sets are contiguous slices of one allocation so that the C-level loop can rotate through them
+    big_in = torch.empty(n * nset, device="cuda")
+    big_out = torch.empty(n * nset, device="cuda")
+    big_in.uniform_(-1, 1, generator=g)
+    ins = [big_in[i * n:(i + 1) * n] for i in range(nset)]
+    outs = [big_out[i * n:(i + 1) * n] for i in range(nset)]
 
     def step(i):
         comm.all_reduce(ins[i % nset], outs[i % nset])
+
+    def run_steps(k):
+        # hccl_test style: k back-to-back HcclAllReduce calls issued from C, buffer set i % nset for call i
+        comm.repeat(L.ALLREDUCE, big_in, big_out, n, L.FP32, k, HEADLINE_BYTES, nset)
+
+    def timed(fn_k, k):
+        sync()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn_k(k)
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b)
+        sync()
+        return ms
 
     # correctness first (check_result): against NCCL when there are peers, against the input itself otherwise
     step(0)
@@ -170,15 +191,12 @@ def main():
     else:
         check = bool(torch.equal(outs[0], ins[0]))
     sampler = ClockSampler(local_rank)
-    launches0 = comm.stats()["launches"]
     sync()
     sampler.start()
-    # warm-up launches are excluded from the launch count below
-    for i in range(warmup):
-        step(i)
+    run_steps(warmup)            # untimed warm-up steps
     sync()
     launches0 = comm.stats()["launches"]
-    ms = time_steps(step, steps, 0, sync)
+    ms = timed(run_steps, steps)
     launches = comm.stats()["launches"] - launches0
     clocks = sampler.stop()
     assert comm.sync() == 0, comm.describe_status()
@@ -189,13 +207,12 @@ def main():
 
     nccl_ms = None
     if world > 1:
-        def nccl_step(i):
-            outs[i % nset].copy_(ins[i % nset])
-            dist.all_reduce(outs[i % nset])
-        # NCCL all_reduce is in-place: time it without the copy by reducing the rotating buffers directly
-        def nccl_step_inplace(i):
-            dist.all_reduce(outs[i % nset])
-        nccl_ms = max_over_ranks(time_steps(nccl_step_inplace, steps, warmup, sync)) / steps
+        def nccl_steps(k):
+            # the baseline issued the same way: ncclAllReduce in a C loop on the same rotating buffers (in place)
+            rc = comm.nccl_allreduce_repeat(big_out, big_out, n, L.FP32, k, HEADLINE_BYTES, nset)
+            assert rc == 0, "NCCL baseline unavailable (%d)" % rc
+        nccl_steps(warmup)
+        nccl_ms = max_over_ranks(timed(nccl_steps, steps)) / steps
 
     # ---------------------------------------------------------------- end to end through the public API, host to host
     hin = [torch.empty(n, dtype=torch.float32).pin_memory() for _ in range(2)]
@@ -218,32 +235,33 @@ def main():
     sweep = []
     if not args.no_sweep:
         size = 8 << 10
-        big_in, big_out = torch.empty(max(args.sweep_max, HEADLINE_BYTES) // 4, device="cuda"), None
-        big_in.uniform_(-1, 1)
-        big_out = torch.empty_like(big_in)
+        sw_in = torch.empty(max(args.sweep_max, HEADLINE_BYTES) // 4, device="cuda")
+        sw_in.uniform_(-1, 1)
+        sw_out = torch.empty_like(sw_in)
         while size <= args.sweep_max:
             cnt = size // 4
             # rotate through disjoint windows of the big buffers so that small messages also miss L2 between iterations
-            nwin = max(1, min(64, big_in.numel() // cnt))
+            nwin = max(1, min(64, sw_in.numel() // cnt))
             iters = 50 if size <= (1 << 20) else (20 if size <= (32 << 20) else 8)
 
-            def ours(i, cnt=cnt, nwin=nwin):
-                w = (i % nwin) * cnt
-                comm.all_reduce(big_in[w:w + cnt], big_out[w:w + cnt])
-            t_ours = max_over_ranks(time_steps(ours, iters, 5, sync)) / iters
+            def ours(k, cnt=cnt, nwin=nwin, size=size):
+                comm.repeat(L.ALLREDUCE, sw_in, sw_out, cnt, L.FP32, k, size, nwin)
+            ours(5)
+            t_ours = max_over_ranks(timed(ours, iters)) / iters
             row = {"data_size": size, "aveg_time_us": round(t_ours * 1e3, 2), "alg_bandwidth_GBps": round(size / t_ours / 1e6, 2),
                    "algo": comm.select(L.ALLREDUCE, cnt, L.FP32)[0]}
             if world > 1:
-                def nccl(i, cnt=cnt, nwin=nwin):
-                    w = (i % nwin) * cnt
-                    dist.all_reduce(big_out[w:w + cnt])
-                t_n = max_over_ranks(time_steps(nccl, iters, 5, sync)) / iters
+                def nccl(k, cnt=cnt, nwin=nwin, size=size):
+                    rc = comm.nccl_allreduce_repeat(sw_out, sw_out, cnt, L.FP32, k, size, nwin)
+                    assert rc == 0
+                nccl(5)
+                t_n = max_over_ranks(timed(nccl, iters)) / iters
                 row["nccl_time_us"] = round(t_n * 1e3, 2)
                 row["nccl_alg_bandwidth_GBps"] = round(size / t_n / 1e6, 2)
             sweep.append(row)
             size *= 2
         assert comm.sync() == 0, comm.describe_status()
-        del big_in, big_out
+        del sw_in, sw_out
 
     extras = {}
     if not args.no_extras:

@@ -9,10 +9,12 @@
 #include <vector>
 #include "common/log.h"
 #include "core/communicator.h"
+#include "kernels/ar_ll.h"
 
 namespace hcclb {
 
 namespace {
+uint64_t si_ll_max() { return kLlMaxPayload; }
 struct Timer {
     cudaEvent_t a, b;
     cudaStream_t s;
@@ -83,6 +85,45 @@ HcclResult Communicator::calibrate(void *stream)
     model_.launch_us = avg[1];
     model_.beta_gbps = avg[2];
     if (avg[3] > 0) model_.nvls_gbps = avg[3];
+    // ---- measured AllReduce table: every candidate algorithm at a ladder of sizes, agreed over all ranks
+    {
+        static const int cands[] = {ALGO_LL, ALGO_MESH_ONESHOT, ALGO_NVLS_ONESHOT, ALGO_MESH, ALGO_NVLS, ALGO_RING};
+        std::vector<uint64_t> sizes;
+        for (uint64_t sz = 16u << 10; sz <= (256u << 20) && sz <= settings_.stage_half_bytes / 2; sz *= 4) sizes.push_back(sz);
+        size_t maxb = sizes.empty() ? 0 : sizes.back();
+        std::vector<void *> tin(nl), tout(nl);
+        bool okalloc = maxb > 0;
+        for (int li = 0; li < nl && okalloc; ++li)
+            okalloc = cudaMalloc(&tin[li], maxb) == cudaSuccess && cudaMalloc(&tout[li], maxb) == cudaSuccess;
+        if (okalloc) {
+            for (int li = 0; li < nl; ++li) cudaMemsetAsync(tin[li], 0, maxb, st);
+            std::vector<double> mine(sizes.size() * ALGO_COUNT, 0.0);
+            for (size_t b = 0; b < sizes.size(); ++b) {
+                for (int algo : cands) {
+                    bool is_nvls = algo == ALGO_NVLS || algo == ALGO_NVLS_ONESHOT;
+                    if (is_nvls && !nvls_) continue;
+                    if (algo == ALGO_LL && (!ll_ok_ || sizes[b] > si_ll_max())) continue;
+                    if ((algo == ALGO_MESH_ONESHOT || algo == ALGO_NVLS_ONESHOT) && sizes[b] > (8u << 20)) continue;
+                    if (algo == ALGO_RING && sizes[b] < (1u << 20)) continue;
+                    int iters = sizes[b] <= (1u << 20) ? 12 : (sizes[b] <= (16u << 20) ? 6 : 3);
+                    OpRequest rq;
+                    rq.coll = COLL_ALLREDUCE; rq.algo = algo; rq.count = sizes[b] / 4; rq.dtype = HCCL_DATA_TYPE_FP32; rq.redop = HCCL_REDUCE_SUM;
+                    rq.in = (const void *const *)tin.data(); rq.out = tout.data(); rq.stream = stream;
+                    mine[b * ALGO_COUNT + algo] = t.us(iters, [&] { HcclResult r = collective(rq); if (r != HCCL_SUCCESS) rc = r; });
+                }
+            }
+            for (int li = 0; li < nl; ++li) { cudaFree(tin[li]); cudaFree(tout[li]); }
+            CHK_RET(rc);
+            std::vector<std::string> allt;
+            CHK_RET(exchange("tune/" + std::to_string(seq_), std::string((const char *)mine.data(), mine.size() * sizeof(double)), &allt));
+            tuned_us_.assign(sizes.size(), std::vector<double>(ALGO_COUNT, 0.0));
+            for (auto &sblob : allt) {
+                const double *v = (const double *)sblob.data();
+                for (size_t i = 0; i < mine.size(); ++i) tuned_us_[i / ALGO_COUNT][i % ALGO_COUNT] += v[i] / allt.size();
+            }
+            tuned_sizes_ = sizes;
+        }
+    }
     HLOG_INFO("calibrated: alpha %.2f us, launch %.2f us, beta %.0f GB/s, nvls %.0f GB/s", model_.alpha_us, model_.launch_us,
               model_.beta_gbps, model_.nvls_gbps);
     return HCCL_SUCCESS;

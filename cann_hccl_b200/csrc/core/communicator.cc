@@ -4,6 +4,7 @@
 #include <unistd.h>
 #include <algorithm>
 #include <chrono>
+#include <cmath>
 #include <cstdlib>
 #include <cstring>
 #include <sstream>
@@ -385,10 +386,30 @@ Selection Communicator::select(int coll, uint64_t count, int dtype, int redop) c
     si.nvls = nvls_;
     si.device = settings_.transport == TR_DEVICE;
     si.expansion_mode = settings_.expansion_mode ? settings_.expansion_mode : env.expansion_mode;
-    si.max_channels = si.device ? 64 : 2;
+    si.max_channels = si.device ? (nranks_ == 1 ? 128 : 64) : 2;  // a single rank never waits: all SMs may copy
     si.forced = forced_algo_for(env, coll);
     si.ll_max_bytes = ll_ok_ ? kLlMaxPayload : 0;
     Selection s = select_algo(si, model_);
+    if (coll == COLL_ALLREDUCE && !tuned_sizes_.empty() && si.forced.empty() && nranks_ > 1) {
+        // nearest bucket on a log scale; candidates must be legal for this dtype / op / determinism setting
+        size_t best_b = 0;
+        double best_d = 1e300;
+        for (size_t b = 0; b < tuned_sizes_.size(); ++b) {
+            double d = std::fabs(std::log2((double)std::max<uint64_t>(si.bytes, 1)) - std::log2((double)tuned_sizes_[b]));
+            if (d < best_d) { best_d = d; best_b = b; }
+        }
+        bool nvls_ok = nvls_ && !si.deterministic && si.expansion_mode != 1 && nvls_reduce_supported(dtype, redop, si.bytes);
+        double bt = -1;
+        for (int a = 0; a < ALGO_COUNT; ++a) {
+            double t = tuned_us_[best_b][a];
+            if (t <= 0) continue;
+            if ((a == ALGO_NVLS || a == ALGO_NVLS_ONESHOT || a == ALGO_NVLS_PIPE) && !nvls_ok) continue;
+            if (a == ALGO_LL && (si.bytes > si.ll_max_bytes || si.expansion_mode == 1)) continue;
+            if ((a == ALGO_MESH_PIPE || a == ALGO_NVLS_PIPE) && s.nchan < 6) continue;
+            if (bt < 0 || t < bt) { bt = t; s.algo = a; }
+        }
+        if (bt > 0) s.est_us = bt;
+    }
     if (env.channels > 0) s.nchan = env.channels;
     if (all_local_ && si.device) {
         // virtual ranks share one GPU: all CTAs of all ranks must be resident together (cooperative launch)

@@ -201,6 +201,10 @@ private:
     std::map<std::string, bool> checked_;
     std::map<std::pair<int, int>, uint32_t> p2p_rounds_;  // (src,dst) -> rounds exchanged
     CostModel model_;
+    // Measured AllReduce times per (size bucket, algorithm) from calibrate(); empty until calibrated.  When present the
+    // selector picks the fastest measured algorithm that is allowed for the (dtype, op) at hand instead of the model's guess.
+    std::vector<uint64_t> tuned_sizes_;
+    std::vector<std::vector<double>> tuned_us_;  // [bucket][algo], <= 0 = not measured
     CommStats stats_;
     std::vector<TraceRecord> trace_;
     size_t trace_pos_ = 0;
