@@ -146,6 +146,9 @@ def lib():
         "HcclB200LocalSendRecv": [vp, u32, u32, vp, vp, u64, C.c_int, vp],
         "HcclB200StreamSync": [vp, vp],
         "HcclB200GetStatus": [vp, u32, P(B200Status)],
+        "HcclB200GemmBf16": [vp, vp, vp, i32, i32, i32, vp],
+        "HcclB200AllGatherMatmul": [vp, P(vp), P(vp), P(vp), i32, i32, i32, vp],
+        "HcclB200MatmulReduceScatter": [vp, P(vp), P(vp), P(vp), i32, i32, i32, vp],
         "HcclB200GetKernelTrace": [vp, u32, P(u64), C.c_size_t, P(i32)],
         "HcclB200WaitProbe": [vp, u32, C.c_double, vp],
         "HcclB200DescribeStatus": [vp, u32, C.c_char_p, C.c_size_t],

@@ -668,6 +668,25 @@ HcclResult HcclB200StreamSync(HcclComm comm, aclrtStream stream)
     GET_COMM("HcclB200StreamSync");
     return c->sync_stream(stream);
 }
+HcclResult HcclB200GemmBf16(const void *A, const void *B, void *C, int32_t M, int32_t N, int32_t K, aclrtStream stream)
+{
+    CHK_RET_LOG(!A || !B || !C, HCCL_E_PTR, "[EI0003] HcclB200GemmBf16: null pointer");
+    return gemm_bf16_plain(A, B, C, M, N, K, stream);
+}
+HcclResult HcclB200AllGatherMatmul(HcclComm comm, void *const *xShards, void *const *weights, void *const *outs, int32_t M, int32_t N, int32_t K,
+                                   aclrtStream stream)
+{
+    GET_COMM("HcclB200AllGatherMatmul");
+    CHK_RET_LOG(!xShards || !weights || !outs, HCCL_E_PTR, "[EI0003] HcclB200AllGatherMatmul: null pointer");
+    return c->tp_all_gather_matmul((const void *const *)xShards, (const void *const *)weights, outs, M, N, K, stream);
+}
+HcclResult HcclB200MatmulReduceScatter(HcclComm comm, void *const *inputs, void *const *weights, void *const *outs, int32_t M, int32_t N,
+                                       int32_t K, aclrtStream stream)
+{
+    GET_COMM("HcclB200MatmulReduceScatter");
+    CHK_RET_LOG(!inputs || !weights || !outs, HCCL_E_PTR, "[EI0003] HcclB200MatmulReduceScatter: null pointer");
+    return c->tp_matmul_reduce_scatter((const void *const *)inputs, (const void *const *)weights, outs, M, N, K, stream);
+}
 HcclResult HcclB200GetKernelTrace(HcclComm comm, uint32_t localRank, uint64_t *out, size_t capWords, int32_t *nsteps)
 {
     GET_COMM("HcclB200GetKernelTrace");

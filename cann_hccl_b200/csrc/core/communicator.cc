@@ -263,6 +263,7 @@ Communicator::~Communicator()
         for (auto &kv : plans_)
             for (Step *s : kv.second.dev_steps) cudaFree(s);
     }
+    tp_release_workspaces();
     for (auto &kv : user_segs_) alloc_->release(&kv.second);
     if (alloc_) alloc_->release(&seg_);
     if (dev) {

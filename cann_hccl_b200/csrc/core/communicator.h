@@ -126,6 +126,11 @@ public:
     // Peer pointer table of a symmetric allocation: ptrs[local][rank]; mc[local]
     HcclResult sym_query(int handle, void **peer_ptrs, void **mc_ptrs, size_t *bytes);
 
+    // Fused tensor-parallel operators (kernels/fused/tp_gemm_sm100.cu).  Pointers per local rank; bf16; weights [N, K].
+    //   all_gather_matmul:     y[M,N]     = all_gather(x_shard[M/p,K]) * w[N,K]^T
+    //   matmul_reduce_scatter: out[M/p,N] = reduce_scatter_rows(h[M,K] * w[N,K]^T)
+    HcclResult tp_all_gather_matmul(const void *const *x_shard, const void *const *w, void *const *y, int M, int N, int K, void *stream);
+    HcclResult tp_matmul_reduce_scatter(const void *const *h, const void *const *w, void *const *out, int M, int N, int K, void *stream);
     // Selection only (no execution).
     Selection select(int coll, uint64_t count, int dtype, int redop) const;
     const CommStats &stats() const { return stats_; }
@@ -159,6 +164,8 @@ private:
     HcclResult get_plan(const OpDesc &d, const std::string &key, CachedPlan **out);
     HcclResult run_collective_once(const OpRequest &rq);
     HcclResult run_ll_allreduce(const OpRequest &rq);
+    HcclResult tp_workspace(const std::string &key, size_t data_bytes, int M, void **ws_out);
+    void tp_release_workspaces();
     HcclResult consistency_check(const OpRequest &rq, int algo);
     HcclResult maybe_retry(const OpRequest &rq, HcclResult failure);
     void heartbeat_loop();
@@ -235,6 +242,8 @@ private:
     int prev_;
 };
 
+// Plain tcgen05 GEMM C[M,N] = A[M,K] * B[N,K]^T in bf16 (no communicator needed).
+HcclResult gemm_bf16_plain(const void *A, const void *B, void *C, int M, int N, int K, void *stream);
 // Device executor entry (kernels/exec_plan.cu).
 HcclResult launch_exec_plan(const RankCtx *dev_ctx, const ExecArgs *args, int nlocal, int nchan, void *stream);
 // Unique identifier helper used by HcclGetRootInfo.

@@ -1,0 +1,552 @@
+// Fused tensor-parallel GEMM kernels for sm_100a (bf16 in, fp32 accumulate in TMEM, bf16 out).
+//
+//   mode PLAIN : C[M,N] = A[M,K] * B[N,K]^T                                   (building block, TP = 1)
+//   mode AG    : all-gather(X shards) -> Y = X * W^T   (column-parallel layer; X sharded by rows over the ranks)
+//   mode RS    : P = H * W^T -> reduce-scatter(P) by rows  (row-parallel layer; every rank ends with its row block)
+//
+// One persistent kernel does the transfer and the math.  CTAs [0, n_gemm) run a warp-specialised tcgen05 GEMM:
+// warp 0 feeds a 4-stage shared-memory ring with TMA (cp.async.bulk.tensor, 128-byte swizzle, never multicast, always
+// from this GPU's own memory), warp 1 issues tcgen05.mma (128x256x16, cta_group::1) into one of two 256-column TMEM
+// accumulators, warps 2..5 drain the other accumulator with tcgen05.ld, convert to bf16 and store.  The remaining
+// CTAs move data between GPUs while the tensor cores work:
+//   AG: they stage this rank's shard into its slot of the symmetric X buffer, tell the peers, then pull the peers'
+//       shards over NVLink with bulk asynchronous copies (peer global -> shared -> local global) in the order in which
+//       the GEMM consumes them, and publish each 128-row block with a flag the TMA producer waits on;
+//   RS: the GEMM epilogue stores every bf16 partial tile straight into the owner rank's receive slot over NVLink and
+//       bumps a counter there; the comm CTAs of the owner sum the p slots in fp32 (fixed rank order) as soon as a
+//       row block is complete on all ranks.
+// Role of the reference's MC2 hooks (framework/op_base/src/op_base.cc:3137-3284: resources exported so that a fused
+// matmul+communication kernel can be written elsewhere); here the fused kernels are part of the library.
+//
+// Every wait (mbarrier, flag, counter) is bounded: after the limit the waiting thread raises a CTA-wide failure word,
+// every role leaves its loop, outstanding bulk copies are drained, TMEM is freed and the kernel returns with an
+// error code in the status block.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <algorithm>
+#include <cstring>
+#include "common/log.h"
+#include "core/device_api.h"
+#include "kernels/fused/tp_gemm.h"
+#include "kernels/prims.cuh"
+
+namespace hcclb {
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16;
+constexpr int kStages = 4;
+constexpr int kThreads = 256;  // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue, warps 6-7 idle in GEMM CTAs; all 8 copy in comm CTAs
+constexpr uint32_t kABytes = BM * BK * 2, kBBytes = BN * BK * 2, kStageBytes = kABytes + kBBytes;
+constexpr uint32_t kTmemCols = 512;
+constexpr int kCommBuf = 32 * 1024, kCommDepth = 6;  // bulk-copy ring of a comm CTA
+constexpr uint32_t kSpinLimit = 1u << 28;            // iterations of an mbarrier poll before it gives up (seconds)
+
+struct SharedStorage {
+    alignas(1024) uint8_t tiles[kStages * kStageBytes];  // also the bulk-copy ring of comm CTAs
+    alignas(8) uint64_t full_bar[kStages];
+    uint64_t empty_bar[kStages];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint64_t comm_bar[kCommDepth];
+    uint32_t tmem_base;
+    uint32_t fail;
+};
+
+// ---------------------------------------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the limit ran out or another role already failed.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile uint32_t *fail)
+{
+    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 1023) == 1023 && *fail) return false;
+    }
+    *fail = HCCL_E_TIMEOUT;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, uint64_t *bar, int x, int y)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void bulk_s2g(void *dst, const void *src, uint32_t bytes)
+{
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(src)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+template <int N> __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ bool elect_one()
+{
+    uint32_t pred;
+    asm volatile("{\n .reg .pred p;\n elect.sync _|p, 0xffffffff;\n selp.u32 %0, 1, 0, p;\n}" : "=r"(pred));
+    return pred != 0;
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows 128 bytes apart, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_smem_desc(const void *ptr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_u32(ptr) & 0x3FFFF) >> 4);   // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                            // leading-dimension byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;                  // stride-dimension byte offset: 8 rows x 128 bytes
+    d |= (uint64_t)1 << 46;                            // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: D fp32, A and B bf16, both K-major, N = 256, M = 128.
+constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate)
+{
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(kInstrDesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,"
+        "%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t pack_bf16(uint32_t a, uint32_t b)
+{
+    __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(a), __uint_as_float(b));
+    return *(uint32_t *)&v;
+}
+__device__ __forceinline__ void red_add_release_sys(uint64_t *p, uint64_t v)
+{
+    asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ void st_release_gpu(uint64_t *p, uint64_t v)
+{
+    asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint64_t ld_acquire_gpu(const uint64_t *p)
+{
+    uint64_t v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Bounded wait on a global word (device or system scope); returns false after the time limit or a CTA failure.
+__device__ __forceinline__ bool wait_word_ge(const uint64_t *p, uint64_t want, bool sys, uint64_t deadline, volatile uint32_t *fail)
+{
+    for (uint32_t it = 0;; ++it) {
+        uint64_t v = sys ? ld_acquire_sys(p) : ld_acquire_gpu(p);
+        if (v >= want) return true;
+        if ((it & 63) == 63) {
+            if (*fail) return false;
+            if (global_timer_ns() > deadline) { *fail = HCCL_E_TIMEOUT; return false; }
+        }
+    }
+}
+
+__device__ __forceinline__ void report(const TpGemmParams &P, uint32_t code, int where)
+{
+    if (!P.status) return;
+    if (atomicCAS(P.fail_word, 0u, code) != 0u) return;
+    DevStatus *s = P.status;
+    s->step = (uint32_t)where;
+    s->peer = -1;
+    s->chan = blockIdx.x;
+    s->seq = P.epoch;
+    __threadfence_system();
+    *(volatile uint32_t *)&s->code = code;
+}
+
+// Logical tile index -> (m tile, n tile).  Tiles walk n fastest; the m order starts at this rank's own row blocks
+// (already local) and continues with the next ranks' blocks in the order in which the comm CTAs fetch them (AG), or
+// starts with the next rank's blocks so that remote partial tiles leave early and the own blocks come last (RS).
+__device__ __forceinline__ void tile_coords(const TpGemmParams &P, int t, int n_tiles, int m_tiles, int &mt, int &nt)
+{
+    int ml = t / n_tiles;
+    nt = t % n_tiles;
+    if (P.mode == TP_MODE_PLAIN || P.nranks == 1) { mt = ml; return; }
+    int per = m_tiles / P.nranks;  // m tiles per rank
+    int shift = P.mode == TP_MODE_AG ? P.rank * per : ((P.rank + 1) % P.nranks) * per;
+    mt = (ml + shift) % m_tiles;
+}
+
+// ---------------------------------------------------------------------------------------------- comm CTAs
+// Copy `bytes` from src (any global memory, possibly a peer's) to dst (local global) with bulk asynchronous copies
+// through the shared-memory ring: loads run kCommDepth-1 pieces ahead of the stores.  One thread drives it.
+// `g` counts pieces over the kernel's lifetime (ring slot = g % depth, mbarrier parity = (g / depth) & 1).
+// On return every piece has been loaded and its store issued; the caller waits for the stores (wait_group 0).
+__device__ bool bulk_copy(SharedStorage &S, uint8_t *dst, const uint8_t *src, uint64_t bytes, uint32_t &g, volatile uint32_t *fail)
+{
+    const uint32_t np = (uint32_t)((bytes + kCommBuf - 1) / kCommBuf), g0 = g;
+    auto piece_len = [&](uint32_t i) { return (uint32_t)(((uint64_t)(i + 1) * kCommBuf <= bytes) ? kCommBuf : (bytes - (uint64_t)i * kCommBuf)); };
+    auto issue_load = [&](uint32_t i) {
+        uint32_t slot = (g0 + i) % kCommDepth, len = piece_len(i);
+        mbar_expect_tx(&S.comm_bar[slot], len);
+        bulk_g2s(S.tiles + (size_t)slot * kCommBuf, src + (uint64_t)i * kCommBuf, len, &S.comm_bar[slot]);
+    };
+    for (uint32_t i = 0; i < np && i < (uint32_t)(kCommDepth - 1); ++i) issue_load(i);
+    for (uint32_t i = 0; i < np; ++i) {
+        uint32_t slot = (g0 + i) % kCommDepth, parity = ((g0 + i) / kCommDepth) & 1;
+        if (!mbar_wait(&S.comm_bar[slot], parity, fail)) return false;
+        bulk_s2g(dst + (uint64_t)i * kCommBuf, S.tiles + (size_t)slot * kCommBuf, piece_len(i));
+        bulk_commit();
+        bulk_wait_read<1>();  // the store of piece i-1 has read its slot: that slot takes the next load
+        uint32_t n = i + kCommDepth - 1;
+        if (n < np) issue_load(n);
+    }
+    g = g0 + np;
+    return true;
+}
+
+// Flag words of a rank in AG mode (uint64):
+//   [src]          ready: m tiles of src's shard staged in src's own slot, counted by src (epoch * per when complete)
+//   [p + src]      done : comm CTAs of src that finished pulling from this rank (epoch * nc when complete)
+//   [2p + m tile]  local: epoch once the rows of that m tile are in this rank's gathered X
+__device__ void comm_role_ag(const TpGemmParams &P, SharedStorage &S, int c, int nc)
+{
+    const int p = P.nranks, me = P.rank;
+    const int m_tiles = P.M / BM, per = m_tiles / p;
+    const uint64_t tile_bytes = (uint64_t)P.K * 2 * BM;
+    uint64_t *myflags = P.flags[me];
+    const uint64_t deadline = global_timer_ns() + P.timeout_ns;
+    volatile uint32_t *fail = &S.fail;
+    if (threadIdx.x != 0) return;  // one thread drives the bulk copies
+    uint32_t g = 0;
+    // the peers' pulls of the previous call from my slot must be over before I overwrite it
+    for (int q = 0; q < p; ++q)
+        if (q != me && !wait_word_ge(myflags + p + q, (P.epoch - 1) * (uint64_t)nc, true, deadline, fail)) { report(P, *fail, 100 + q); return; }
+    // stage my shard into my slot of the gathered buffer: m tiles [me*per, (me+1)*per), split over the comm CTAs
+    for (int j = c; j < per; j += nc) {
+        int mt = me * per + j;
+        if (!bulk_copy(S, (uint8_t *)P.xfull[me] + (uint64_t)mt * tile_bytes, (const uint8_t *)P.x_shard + (uint64_t)j * tile_bytes, tile_bytes, g, fail)) { report(P, *fail, 200); return; }
+        bulk_wait_all<0>();
+        fence_proxy_async();
+        st_release_gpu(myflags + 2 * p + mt, P.epoch);                // the GEMM may load it
+        __threadfence_system();
+        for (int q = 0; q < p; ++q)
+            if (q != me) red_add_release_sys(P.flags[q] + me, 1);     // and the peers may pull it
+    }
+    // pull the peers' shards in the order in which the GEMM consumes them
+    for (int i = 1; i < p; ++i) {
+        int q = (me + i) % p;
+        if (!wait_word_ge(myflags + q, P.epoch * (uint64_t)per, true, deadline, fail)) { report(P, *fail, 300 + q); return; }
+        for (int j = c; j < per; j += nc) {
+            int mt = q * per + j;
+            if (!bulk_copy(S, (uint8_t *)P.xfull[me] + (uint64_t)mt * tile_bytes, (const uint8_t *)P.xfull[q] + (uint64_t)mt * tile_bytes, tile_bytes, g, fail)) { report(P, *fail, 400 + q); return; }
+            bulk_wait_all<0>();
+            fence_proxy_async();
+            st_release_gpu(myflags + 2 * p + mt, P.epoch);
+        }
+    }
+    // this CTA no longer reads any peer's slot
+    __threadfence_system();
+    for (int q = 0; q < p; ++q)
+        if (q != me) red_add_release_sys(P.flags[q] + p + me, 1);
+}
+
+// Flag words of a rank in RS mode (uint64):
+//   [src * per + j]  n tiles of this rank's row block j delivered by src (epoch * n_tiles when complete)
+//   [p * per + o]    comm CTAs of owner o that finished reducing (epoch * nc when complete): o's slots may be rewritten
+__device__ void comm_role_rs(const TpGemmParams &P, SharedStorage &S, int c, int nc)
+{
+    const int p = P.nranks, me = P.rank;
+    const int m_tiles = P.M / BM, per = m_tiles / p, n_tiles = P.N / BN;
+    uint64_t *myflags = P.flags[me];
+    const uint64_t deadline = global_timer_ns() + P.timeout_ns;
+    volatile uint32_t *fail = &S.fail;
+    const uint64_t slot_elems = (uint64_t)(P.M / p) * P.N;  // one source's partial rows for me
+    // row block j of mine is complete when every source delivered all n tiles of it
+    for (int j = c; j < per; j += nc) {
+        if (threadIdx.x < p) {
+            if (!wait_word_ge(myflags + (uint64_t)threadIdx.x * per + j, P.epoch * (uint64_t)n_tiles, true, deadline, fail)) report(P, *fail, 500 + threadIdx.x);
+        }
+        __syncthreads();
+        if (S.fail) return;
+        // out rows [j*BM, (j+1)*BM) = sum over sources, fp32, fixed order
+        const uint64_t base = (uint64_t)j * BM * P.N, nvec = (uint64_t)BM * P.N / 8;
+        for (uint64_t v = threadIdx.x; v < nvec; v += blockDim.x) {
+            float acc[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+            for (int q = 0; q < p; ++q) {
+                uint4 x = ld_stream((const uint4 *)(P.partial[me] + (uint64_t)q * slot_elems + base) + v);
+                const __nv_bfloat162 *h = (const __nv_bfloat162 *)&x;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    float2 f = __bfloat1622float2(h[k]);
+                    acc[2 * k] += f.x;
+                    acc[2 * k + 1] += f.y;
+                }
+            }
+            uint4 o;
+            o.x = pack_bf16(__float_as_uint(acc[0]), __float_as_uint(acc[1]));
+            o.y = pack_bf16(__float_as_uint(acc[2]), __float_as_uint(acc[3]));
+            o.z = pack_bf16(__float_as_uint(acc[4]), __float_as_uint(acc[5]));
+            o.w = pack_bf16(__float_as_uint(acc[6]), __float_as_uint(acc[7]));
+            ((uint4 *)(P.out + base))[v] = o;
+        }
+        __syncthreads();
+    }
+    // all my row blocks handled by this CTA are reduced: sources may overwrite my slots in the next call once every
+    // comm CTA said so; done[me] on each source counts comm CTAs
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        for (int q = 0; q < p; ++q) red_add_release_sys(P.flags[q] + (uint64_t)p * per + me, 1);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------- the kernel
+__global__ void __launch_bounds__(kThreads, 1) tp_gemm_kernel(const __grid_constant__ TpGemmParamsArray PA)
+{
+    const TpGemmParams &P = PA.r[blockIdx.y];
+    extern __shared__ uint8_t smem_raw[];
+    SharedStorage &S = *(SharedStorage *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int m_tiles = P.M / BM, n_tiles = P.N / BN, k_iters = P.K / BK;
+    const int total_tiles = m_tiles * n_tiles;
+    const bool is_gemm = (int)blockIdx.x < P.n_gemm_ctas;
+    volatile uint32_t *fail = &S.fail;
+
+    if (threadIdx.x == 0) {
+        S.fail = 0;
+        for (int i = 0; i < kStages; ++i) { mbar_init(&S.full_bar[i], 1); mbar_init(&S.empty_bar[i], 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&S.tmem_full[i], 1); mbar_init(&S.tmem_empty[i], 128); }
+        for (int i = 0; i < kCommDepth; ++i) mbar_init(&S.comm_bar[i], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (!is_gemm) {
+        int c = blockIdx.x - P.n_gemm_ctas, nc = gridDim.x - P.n_gemm_ctas;
+        if (P.mode == TP_MODE_AG) comm_role_ag(P, S, c, nc);
+        else if (P.mode == TP_MODE_RS) comm_role_rs(P, S, c, nc);
+        if (threadIdx.x == 0) bulk_wait_all<0>();
+        return;
+    }
+
+    if (warp == 1) {  // TMEM allocation by one full warp
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&S.tmem_base)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = S.tmem_base;
+    const uint64_t deadline = global_timer_ns() + P.timeout_ns;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (elect_one()) {
+            uint32_t it = 0;
+            const uint64_t *chunk_ready = P.mode == TP_MODE_AG ? P.flags[P.rank] + 2 * P.nranks : nullptr;
+            for (int t = blockIdx.x; t < total_tiles && !*fail; t += P.n_gemm_ctas) {
+                int mt, nt;
+                tile_coords(P, t, n_tiles, m_tiles, mt, nt);
+                if (chunk_ready) {  // rows of this block have to be in local memory (staged or pulled by the comm CTAs)
+                    if (!wait_word_ge(chunk_ready + mt, P.epoch, false, deadline, fail)) { report(P, *fail, 600 + mt); break; }
+                    fence_proxy_async();
+                }
+                for (int k = 0; k < k_iters; ++k, ++it) {
+                    uint32_t s = it % kStages, ph = (it / kStages) & 1;
+                    if (!mbar_wait(&S.empty_bar[s], ph ^ 1, fail)) { report(P, *fail, 700); break; }
+                    uint8_t *sa = S.tiles + (size_t)s * kStageBytes, *sb = sa + kABytes;
+                    mbar_expect_tx(&S.full_bar[s], kStageBytes);
+                    tma_load_2d(sa, &P.tmA, &S.full_bar[s], k * BK, mt * BM);
+                    tma_load_2d(sb, &P.tmB, &S.full_bar[s], k * BK, nt * BN);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (elect_one()) {
+            uint32_t it = 0, tile_i = 0;
+            for (int t = blockIdx.x; t < total_tiles && !*fail; t += P.n_gemm_ctas, ++tile_i) {
+                uint32_t buf = tile_i & 1, use = tile_i >> 1;
+                if (!mbar_wait(&S.tmem_empty[buf], (use & 1) ^ 1, fail)) { report(P, *fail, 800); break; }
+                tc_fence_after();
+                uint32_t d = tmem_base + buf * BN;
+                for (int k = 0; k < k_iters; ++k, ++it) {
+                    uint32_t s = it % kStages, ph = (it / kStages) & 1;
+                    if (!mbar_wait(&S.full_bar[s], ph, fail)) { report(P, *fail, 900); break; }
+                    tc_fence_after();
+                    uint8_t *sa = S.tiles + (size_t)s * kStageBytes, *sb = sa + kABytes;
+                    uint64_t da = make_smem_desc(sa), db = make_smem_desc(sb);
+#pragma unroll
+                    for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+                        // advance 16 bf16 = 32 bytes along K inside the 128-byte swizzle atom: +2 in 16-byte units
+                        umma(d, da + (uint64_t)(2 * kk), db + (uint64_t)(2 * kk), (k | kk) != 0);
+                    }
+                    umma_commit(&S.empty_bar[s]);  // frees the stage when the MMAs that read it are done
+                }
+                umma_commit(&S.tmem_full[buf]);    // accumulator complete
+            }
+        }
+    } else if (warp >= 2 && warp < 6) {
+        // ------------------------------------------------------------------ epilogue: TMEM -> registers -> bf16 -> global
+        const int q4 = warp & 3;  // a warp may only touch the TMEM lane quarter given by its index modulo 4
+        uint32_t tile_i = 0;
+        const int per = P.nranks > 0 ? m_tiles / P.nranks : m_tiles;
+        for (int t = blockIdx.x; t < total_tiles && !*fail; t += P.n_gemm_ctas, ++tile_i) {
+            int mt, nt;
+            tile_coords(P, t, n_tiles, m_tiles, mt, nt);
+            uint32_t buf = tile_i & 1, use = tile_i >> 1;
+            if (!mbar_wait(&S.tmem_full[buf], use & 1, fail)) { report(P, *fail, 1000); break; }
+            tc_fence_after();
+            const int row = mt * BM + q4 * 32 + lane;
+            __nv_bfloat16 *dst_row;
+            int owner = 0;
+            if (P.mode == TP_MODE_RS) {
+                owner = mt / per;  // rows of block mt belong to rank `owner`; my partial goes to its slot number P.rank
+                // the owner must have finished reducing the previous call's data in that slot
+                if (!wait_word_ge(P.flags[P.rank] + (uint64_t)P.nranks * per + owner, (P.epoch - 1) * (uint64_t)(gridDim.x - P.n_gemm_ctas), true, deadline, fail)) { report(P, *fail, 1100 + owner); break; }
+                const uint64_t slot_elems = (uint64_t)(P.M / P.nranks) * P.N;
+                dst_row = P.partial[owner] + (uint64_t)P.rank * slot_elems + (uint64_t)(row - owner * per * BM) * P.N + (uint64_t)nt * BN;
+            } else {
+                dst_row = P.C + (uint64_t)row * P.ldc + (uint64_t)nt * BN;
+            }
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + buf * BN + c0 + ((uint32_t)(q4 * 32) << 16), r);
+                tmem_ld_wait();
+                uint4 *o = (uint4 *)(dst_row + c0);
+#pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                    uint4 w;
+                    w.x = pack_bf16(r[8 * v + 0], r[8 * v + 1]);
+                    w.y = pack_bf16(r[8 * v + 2], r[8 * v + 3]);
+                    w.z = pack_bf16(r[8 * v + 4], r[8 * v + 5]);
+                    w.w = pack_bf16(r[8 * v + 6], r[8 * v + 7]);
+                    o[v] = w;
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(&S.tmem_empty[buf]);  // 128 arrivals free the accumulator for the tile after next
+            if (P.mode == TP_MODE_RS) {
+                // the four epilogue warps finished their rows: one of them publishes the tile to the owner
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (warp == 2 && lane == 0) {
+                    __threadfence_system();
+                    red_add_release_sys(P.flags[owner] + (uint64_t)P.rank * per + (mt - owner * per), 1);
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+HcclResult encode_2d(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows)
+{
+    const DriverApi &d = driver_api();
+    if (!d.ok || !d.TensorMapEncodeTiled) return HCCL_E_DRV;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = d.TensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
+                                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        HLOG_ERROR("cuTensorMapEncodeTiled failed: %s", cu_err(r));
+        return HCCL_E_DRV;
+    }
+    return HCCL_SUCCESS;
+}
+
+}  // namespace
+
+size_t tp_gemm_smem_bytes() { return sizeof(SharedStorage) + 1024; }
+
+HcclResult launch_tp_gemm(TpGemmParams *P, const void *const *A, const void *const *B, int nlocal, int n_comm_ctas, void *stream)
+{
+    if (nlocal < 1 || nlocal > kTpMaxLocal) return HCCL_E_PARA;
+    const TpGemmParams &P0 = P[0];
+    if (P0.M % BM || P0.N % BN || P0.K % BK || P0.M <= 0 || P0.N <= 0 || P0.K <= 0) {
+        HLOG_ERROR("fused GEMM needs M %% %d == 0, N %% %d == 0, K %% %d == 0 (got %d x %d x %d)", BM, BN, BK, P0.M, P0.N, P0.K);
+        return HCCL_E_PARA;
+    }
+    if (P0.mode != TP_MODE_PLAIN && P0.nranks > 1 && (P0.M / BM) % P0.nranks) {
+        HLOG_ERROR("fused GEMM needs the %d row blocks to divide evenly over %d ranks", P0.M / BM, P0.nranks);
+        return HCCL_E_PARA;
+    }
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (P0.mode == TP_MODE_PLAIN) n_comm_ctas = 0;
+    else if (n_comm_ctas < 1) n_comm_ctas = 1;
+    int per_rank = sms / nlocal;  // all CTAs of all local ranks must be resident together
+    if (n_comm_ctas > per_rank / 2) n_comm_ctas = std::max(1, per_rank / 2);
+    int total = (P0.M / BM) * (P0.N / BN);
+    int n_gemm = std::min(total, std::max(1, per_rank - n_comm_ctas));
+    TpGemmParamsArray arr;
+    memset(&arr, 0, sizeof(arr));
+    for (int i = 0; i < nlocal; ++i) {
+        if ((((uintptr_t)A[i]) | ((uintptr_t)B[i])) & 15) return HCCL_E_PARA;
+        P[i].n_gemm_ctas = n_gemm;
+        CHK_RET(encode_2d(&P[i].tmA, A[i], (uint64_t)P[i].M, (uint64_t)P[i].K, BM));
+        CHK_RET(encode_2d(&P[i].tmB, B[i], (uint64_t)P[i].N, (uint64_t)P[i].K, BN));
+        arr.r[i] = P[i];
+    }
+    static bool attr_set = false;
+    size_t smem = tp_gemm_smem_bytes();
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(tp_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { HLOG_ERROR("cannot raise dynamic shared memory to %zu: %s", smem, cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
+        attr_set = true;
+    }
+    dim3 grid((unsigned)(n_gemm + n_comm_ctas), (unsigned)nlocal), block(kThreads);
+    cudaError_t e;
+    if (nlocal > 1) {
+        void *kargs[] = {(void *)&arr};
+        e = cudaLaunchCooperativeKernel((const void *)tp_gemm_kernel, grid, block, kargs, smem, (cudaStream_t)stream);
+    } else {
+        tp_gemm_kernel<<<grid, block, smem, (cudaStream_t)stream>>>(arr);
+        e = cudaGetLastError();
+    }
+    if (e != cudaSuccess) { HLOG_ERROR("fused GEMM launch failed: %s", cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
+    return HCCL_SUCCESS;
+}
+
+}  // namespace hcclb

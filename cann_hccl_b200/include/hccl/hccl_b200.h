@@ -61,6 +61,15 @@ typedef struct HcclB200StatusDef {
     uint32_t code, step; int32_t peer; uint32_t chan;
     uint64_t expected, seen, seq, head, tail;
 } HcclB200Status;
+/* ---- fused tensor-parallel kernels (tcgen05 GEMM + NVLink transfer in one sm_100a kernel); bf16, weights [N, K] ---- */
+/* C[M,N] = A[M,K] * B[N,K]^T (no communication). M % 128 == 0, N % 256 == 0, K % 64 == 0. */
+extern HcclResult HcclB200GemmBf16(const void *A, const void *B, void *C, int32_t M, int32_t N, int32_t K, aclrtStream stream);
+/* Column-parallel layer: outs = all_gather_rows(xShards [M/p, K]) * weights[N, K]^T -> [M, N].  One pointer per local rank. */
+extern HcclResult HcclB200AllGatherMatmul(HcclComm comm, void *const *xShards, void *const *weights, void *const *outs, int32_t M,
+                                          int32_t N, int32_t K, aclrtStream stream);
+/* Row-parallel layer: outs [M/p, N] = reduce_scatter_rows(inputs [M, K] * weights[N, K]^T). */
+extern HcclResult HcclB200MatmulReduceScatter(HcclComm comm, void *const *inputs, void *const *weights, void *const *outs, int32_t M,
+                                              int32_t N, int32_t K, aclrtStream stream);
 /* In-kernel timestamps of the newest executor launch (needs HCCL_KERNEL_TRACE=1 at communicator creation):
  * out[0] = kernel start (globaltimer ns), then per step {after wait, after data movement, after signal}. */
 extern HcclResult HcclB200GetKernelTrace(HcclComm comm, uint32_t localRank, uint64_t *out, size_t capWords, int32_t *nsteps);

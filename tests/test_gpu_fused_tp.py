@@ -1,0 +1,106 @@
+"""tcgen05 GEMM and the fused GEMM + collective kernels against a plain PyTorch fp32 reference.
+Multi-rank cases run as virtual ranks of one GPU (one cooperative launch, peers = other buffers of the same device)."""
+import pytest
+
+torch = pytest.importorskip("torch")
+import cann_hccl_b200 as H  # noqa: E402
+from cann_hccl_b200 import _lib as L  # noqa: E402
+from cann_hccl_b200.parallel import fused_tp  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+
+def _need_gpu():
+    if not torch.cuda.is_available():
+        pytest.skip("no GPU")
+
+
+def rel_err(a, b):
+    return float((a.float() - b.float()).norm() / (b.float().norm() + 1e-12))
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 256, 128), (512, 1024, 4096), (2048, 768, 320)])
+def test_gemm_bf16(M, N, K):
+    _need_gpu()
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    a = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", generator=g).to(torch.bfloat16)
+    c = fused_tp.gemm(a, b)
+    torch.cuda.synchronize()
+    ref = a.float() @ b.float().t()
+    assert rel_err(c, ref) < 1e-2
+    # a second shape-identical call reuses the pipeline state machine from scratch
+    c2 = fused_tp.gemm(a, b)
+    torch.cuda.synchronize()
+    assert torch.equal(c, c2)
+
+
+def test_gemm_rejects_bad_shapes():
+    _need_gpu()
+    a = torch.zeros(100, 64, device="cuda", dtype=torch.bfloat16)
+    b = torch.zeros(256, 64, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(H.HcclError):
+        fused_tp.gemm(a, b)
+
+
+@pytest.fixture(scope="module")
+def comms():
+    _need_gpu()
+    cache = {}
+
+    def get(p):
+        if p not in cache:
+            cfg = L.CommConfig.default()
+            cfg.hcclBufferSize = 2
+            cache[p] = H.Communicator.init_local(p, device=True, device_id=0, config=cfg)
+        return cache[p]
+
+    yield get
+    for c in cache.values():
+        assert c.destroy() == L.SUCCESS
+
+
+@pytest.mark.parametrize("p", [1, 2, 4])
+def test_all_gather_matmul(comms, p):
+    c = comms(p)
+    Ms, K, N = 256, 512, 512
+    g = torch.Generator(device="cuda").manual_seed(p)
+    xs = [torch.randn(Ms, K, device="cuda", generator=g).to(torch.bfloat16) for _ in range(p)]
+    ws = [(torch.randn(N, K, device="cuda", generator=g) * 0.05).to(torch.bfloat16) for _ in range(p)]
+    for _ in range(3):  # epochs of the workspace flags advance call by call
+        ys = fused_tp.all_gather_matmul(c, xs if p > 1 else xs[0], ws if p > 1 else ws[0])
+        assert c.sync() == 0, c.describe_status()
+    ys = ys if p > 1 else [ys]
+    xfull = torch.cat([x.float() for x in xs])
+    for r in range(p):
+        assert rel_err(ys[r], xfull @ ws[r].float().t()) < 1e-2
+
+
+@pytest.mark.parametrize("p", [1, 2, 4])
+def test_matmul_reduce_scatter(comms, p):
+    c = comms(p)
+    M, K, N = 256 * p, 256, 512
+    g = torch.Generator(device="cuda").manual_seed(10 + p)
+    hs = [torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16) for _ in range(p)]
+    ws = [(torch.randn(N, K, device="cuda", generator=g) * 0.05).to(torch.bfloat16) for _ in range(p)]
+    for _ in range(3):
+        outs = fused_tp.matmul_reduce_scatter(c, hs if p > 1 else hs[0], ws if p > 1 else ws[0])
+        assert c.sync() == 0, c.describe_status()
+    outs = outs if p > 1 else [outs]
+    full = sum(h.float() @ w.float().t() for h, w in zip(hs, ws))
+    rows = M // p
+    for r in range(p):
+        assert rel_err(outs[r], full[r * rows:(r + 1) * rows]) < 2e-2
+
+
+def test_tensor_parallel_mlp_forward(comms):
+    from cann_hccl_b200.models.tp_mlp import TensorParallelMLP
+    p = 2
+    c = comms(p)
+    mlp = TensorParallelMLP(c, hidden=512, ffn=1024, seed=3)
+    xs = [torch.randn(128, 512, device="cuda").to(torch.bfloat16) for _ in range(p)]
+    ys = mlp.forward(xs)
+    assert c.sync() == 0, c.describe_status()
+    ref = mlp.reference_forward(xs)
+    for got, want in zip(ys, ref):
+        assert rel_err(got, want) < 3e-2
