@@ -146,6 +146,10 @@ def lib():
         "HcclB200LocalSendRecv": [vp, u32, u32, vp, vp, u64, C.c_int, vp],
         "HcclB200StreamSync": [vp, vp],
         "HcclB200GetStatus": [vp, u32, P(B200Status)],
+        "HcclB200MoeCount": [vp, C.c_int64, i32, vp, vp, vp],
+        "HcclB200MoeOffsets": [vp, i32, i32, i32, vp, vp, vp, C.c_int64, vp, vp],
+        "HcclB200MoeDispatch": [vp, vp, vp, vp, C.c_int64, i32, i32, i32, i32, i32, i32, P(vp), vp, C.c_int64, vp],
+        "HcclB200MoeCombine": [P(vp), vp, vp, vp, C.c_int64, i32, i32, i32, i32, i32, i32, vp, C.c_int64, vp],
         "HcclB200GemmBf16": [vp, vp, vp, i32, i32, i32, vp],
         "HcclB200AllGatherMatmul": [vp, P(vp), P(vp), P(vp), i32, i32, i32, vp],
         "HcclB200MatmulReduceScatter": [vp, P(vp), P(vp), P(vp), i32, i32, i32, vp],

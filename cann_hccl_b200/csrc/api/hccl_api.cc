@@ -19,6 +19,7 @@
 #include "hccl/hccl_b200.h"
 #include "health/consistency.h"
 #include "health/fault_inject.h"
+#include "kernels/moe_a2a.h"
 
 using namespace hcclb;
 
@@ -667,6 +668,31 @@ HcclResult HcclB200StreamSync(HcclComm comm, aclrtStream stream)
 {
     GET_COMM("HcclB200StreamSync");
     return c->sync_stream(stream);
+}
+HcclResult HcclB200MoeCount(const int32_t *topkIdx, int64_t nPairs, int32_t nExperts, int32_t *hist, int32_t *pos, aclrtStream stream)
+{
+    CHK_RET_LOG(!topkIdx || !hist || !pos, HCCL_E_PTR, "[EI0003] HcclB200MoeCount: null pointer");
+    return moe_count(topkIdx, nPairs, nExperts, hist, pos, stream);
+}
+HcclResult HcclB200MoeOffsets(const int32_t *counts, int32_t nRanks, int32_t nExperts, int32_t rank, int32_t *base, int32_t *expertOffsets,
+                              int32_t *recvRows, int64_t capacityRows, int32_t *overflow, aclrtStream stream)
+{
+    CHK_RET_LOG(!counts || !base || !expertOffsets || !recvRows || !overflow, HCCL_E_PTR, "[EI0003] HcclB200MoeOffsets: null pointer");
+    return moe_offsets(counts, nRanks, nExperts, rank, base, expertOffsets, recvRows, capacityRows, overflow, stream);
+}
+HcclResult HcclB200MoeDispatch(const void *x, const int32_t *topkIdx, const int32_t *pos, const int32_t *base, int64_t tokens, int32_t topk,
+                               int32_t hidden, int32_t nExperts, int32_t nRanks, int32_t rank, int32_t pairwise, void *const *recvPeers,
+                               int32_t *dstRow, int64_t capacityRows, aclrtStream stream)
+{
+    CHK_RET_LOG(!x || !topkIdx || !pos || !base || !recvPeers || !dstRow, HCCL_E_PTR, "[EI0003] HcclB200MoeDispatch: null pointer");
+    return moe_dispatch(x, topkIdx, pos, base, tokens, topk, hidden, nExperts, nRanks, rank, pairwise, recvPeers, dstRow, capacityRows, stream);
+}
+HcclResult HcclB200MoeCombine(void *const *yPeers, const int32_t *topkIdx, const float *gates, const int32_t *dstRow, int64_t tokens,
+                              int32_t topk, int32_t hidden, int32_t nExperts, int32_t nRanks, int32_t rank, int32_t pairwise, void *out,
+                              int64_t capacityRows, aclrtStream stream)
+{
+    CHK_RET_LOG(!yPeers || !topkIdx || !gates || !dstRow || !out, HCCL_E_PTR, "[EI0003] HcclB200MoeCombine: null pointer");
+    return moe_combine(yPeers, topkIdx, gates, dstRow, tokens, topk, hidden, nExperts, nRanks, rank, pairwise, out, capacityRows, stream);
 }
 HcclResult HcclB200GemmBf16(const void *A, const void *B, void *C, int32_t M, int32_t N, int32_t K, aclrtStream stream)
 {

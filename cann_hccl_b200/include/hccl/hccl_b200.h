@@ -61,6 +61,21 @@ typedef struct HcclB200StatusDef {
     uint32_t code, step; int32_t peer; uint32_t chan;
     uint64_t expected, seen, seq, head, tail;
 } HcclB200Status;
+/* ---- MoE expert-parallel dispatch / combine (kernels/moe_a2a.cu); bf16 rows, int32 expert ids, fp32 gates ---- */
+/* hist[e] = pairs routed to expert e, pos[i] = arrival index of pair i inside its expert group. */
+extern HcclResult HcclB200MoeCount(const int32_t *topkIdx, int64_t nPairs, int32_t nExperts, int32_t *hist, int32_t *pos, aclrtStream stream);
+/* From the all-gathered histograms counts[nRanks][nExperts]: base[e] (first receive row of this rank's block for expert e on
+ * its owner), this rank's expertOffsets[nExperts/nRanks + 1], recvRows, and overflow = 1 when recvRows > capacityRows. */
+extern HcclResult HcclB200MoeOffsets(const int32_t *counts, int32_t nRanks, int32_t nExperts, int32_t rank, int32_t *base,
+                                     int32_t *expertOffsets, int32_t *recvRows, int64_t capacityRows, int32_t *overflow, aclrtStream stream);
+/* Store every (token, k) row into the owner's receive buffer (recvPeers[q] = rank q's buffer); records dstRow[i]. */
+extern HcclResult HcclB200MoeDispatch(const void *x, const int32_t *topkIdx, const int32_t *pos, const int32_t *base, int64_t tokens,
+                                      int32_t topk, int32_t hidden, int32_t nExperts, int32_t nRanks, int32_t rank, int32_t pairwise,
+                                      void *const *recvPeers, int32_t *dstRow, int64_t capacityRows, aclrtStream stream);
+/* out[t] = sum_k gates[t,k] * yPeers[owner][dstRow[t,k]] : the gate-weighted combine happens while the rows are received. */
+extern HcclResult HcclB200MoeCombine(void *const *yPeers, const int32_t *topkIdx, const float *gates, const int32_t *dstRow, int64_t tokens,
+                                     int32_t topk, int32_t hidden, int32_t nExperts, int32_t nRanks, int32_t rank, int32_t pairwise, void *out,
+                                     int64_t capacityRows, aclrtStream stream);
 /* ---- fused tensor-parallel kernels (tcgen05 GEMM + NVLink transfer in one sm_100a kernel); bf16, weights [N, K] ---- */
 /* C[M,N] = A[M,K] * B[N,K]^T (no communication). M % 128 == 0, N % 256 == 0, K % 64 == 0. */
 extern HcclResult HcclB200GemmBf16(const void *A, const void *B, void *C, int32_t M, int32_t N, int32_t K, aclrtStream stream);

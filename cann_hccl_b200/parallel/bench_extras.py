@@ -1,0 +1,95 @@
+"""Side benchmarks reported inside bench.py's JSON line: the fused tensor-parallel MLP kernels (Llama-3-70B shapes:
+8192 tokens, hidden 8192, FFN 28672 split over the ranks) next to cuBLAS + NCCL, and the MoE dispatch/combine exchange
+next to NCCL all-to-all.  Device-timed with CUDA events, max over ranks."""
+import json
+import os
+
+import torch
+
+from . import fused_tp
+
+TOKENS, HIDDEN, FFN = 8192, 8192, 28672
+
+
+def _peaks():
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return float(d.get("bf16_tflops_sustained", 1387.8)), "measured"
+    except Exception:
+        return 1400.0, "fallback"
+
+
+def _time(fn, iters, sync):
+    for _ in range(3):
+        fn()
+    sync()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / iters
+    sync()
+    return ms
+
+
+def run(comm, world, rank, dist, max_over_ranks, sync, time_steps):
+    out = {}
+    peak_tflops, peak_kind = _peaks()
+    link_gbs = 770.0
+    fl = FFN // world
+    ms_rows = TOKENS // world
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x_shard = torch.randn(ms_rows, HIDDEN, device="cuda", generator=g).to(torch.bfloat16)
+    w_up = (torch.randn(fl, HIDDEN, device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    w_down = (torch.randn(HIDDEN, fl, device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    h = torch.randn(TOKENS, fl, device="cuda", generator=g).to(torch.bfloat16)
+    y = torch.empty(TOKENS, fl, device="cuda", dtype=torch.bfloat16)
+    o = torch.empty(ms_rows, HIDDEN, device="cuda", dtype=torch.bfloat16)
+    flops = 2.0 * TOKENS * HIDDEN * fl
+    comm_bytes = (world - 1) / world * TOKENS * HIDDEN * 2
+    roof_ms = max(flops / (peak_tflops * 1e9), comm_bytes / (link_gbs * 1e6))
+    iters = 10
+    # ---- all-gather(X) -> X W_up^T
+    t = max_over_ranks(_time(lambda: fused_tp.all_gather_matmul(comm, x_shard, w_up, out=y), iters, sync))
+    assert comm.sync() == 0, comm.describe_status()
+    row = {"ms": round(t, 4), "tflops_per_gpu": round(flops / t / 1e9, 1), "roofline_ms": round(roof_ms, 4),
+           "roofline_fraction": round(roof_ms / t, 3), "roofline_kind": "of %s peak (%.0f TFLOP/s sustained, %.0f GB/s link)" % (peak_kind, peak_tflops, link_gbs)}
+    xfull = torch.empty(TOKENS, HIDDEN, device="cuda", dtype=torch.bfloat16)
+    if dist is not None:
+        def base_ag():
+            dist.all_gather_into_tensor(xfull, x_shard)
+            torch.matmul(xfull, w_up.t(), out=y)
+    else:
+        def base_ag():
+            torch.matmul(x_shard, w_up.t(), out=y)
+    tb = max_over_ranks(_time(base_ag, iters, sync))
+    row["cublas_nccl_ms"] = round(tb, 4)
+    row["speedup_vs_cublas_nccl"] = round(tb / t, 3)
+    out["ag_gemm"] = row
+    # ---- H W_down^T -> reduce-scatter
+    t = max_over_ranks(_time(lambda: fused_tp.matmul_reduce_scatter(comm, h, w_down, out=o), iters, sync))
+    assert comm.sync() == 0, comm.describe_status()
+    row = {"ms": round(t, 4), "tflops_per_gpu": round(flops / t / 1e9, 1), "roofline_ms": round(roof_ms, 4), "roofline_fraction": round(roof_ms / t, 3)}
+    part = torch.empty(TOKENS, HIDDEN, device="cuda", dtype=torch.bfloat16)
+    if dist is not None:
+        def base_rs():
+            torch.matmul(h, w_down.t(), out=part)
+            dist.reduce_scatter_tensor(o, part)
+    else:
+        def base_rs():
+            torch.matmul(h, w_down.t(), out=part)
+    tb = max_over_ranks(_time(base_rs, iters, sync))
+    row["cublas_nccl_ms"] = round(tb, 4)
+    row["speedup_vs_cublas_nccl"] = round(tb / t, 3)
+    out["gemm_rs"] = row
+    out["shape"] = {"tokens": TOKENS, "hidden": HIDDEN, "ffn_per_gpu": fl, "dtype": "bf16"}
+    try:
+        from . import moe
+        out["moe"] = moe.bench(comm, world, rank, dist, max_over_ranks, sync)
+    except ImportError:
+        pass
+    return out

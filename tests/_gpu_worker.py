@@ -191,6 +191,56 @@ def scenario_perf(c, p, r, args):
     ok(c)
 
 
+def scenario_fused_tp(c, p, r, args):
+    """Fused all-gather+GEMM and GEMM+reduce-scatter across real GPUs against the fp32 PyTorch statement."""
+    from cann_hccl_b200.parallel import fused_tp
+    Ms, K, N = 256, 1024, 768
+    g = lambda q, shape, seed, scale=1.0: (torch.randn(*shape, device="cuda", generator=torch.Generator(device="cuda").manual_seed(100 * seed + q)) * scale).to(torch.bfloat16)
+    xs = [g(q, (Ms, K), 1) for q in range(p)]
+    w = g(r, (N, K), 2, 0.05)
+    for _ in range(4):
+        y = fused_tp.all_gather_matmul(c, xs[r], w)
+        ok(c)
+    ref = torch.cat([x.float() for x in xs]) @ w.float().t()
+    err = float((y.float() - ref).norm() / ref.norm())
+    assert err < 1e-2, err
+    M = Ms * p
+    hs = [g(q, (M, K), 3) for q in range(p)]
+    ws = [g(q, (N, K), 4, 0.05) for q in range(p)]
+    for _ in range(4):
+        o = fused_tp.matmul_reduce_scatter(c, hs[r], ws[r])
+        ok(c)
+    full = sum(hq.float() @ wq.float().t() for hq, wq in zip(hs, ws))
+    err = float((o.float() - full[r * Ms:(r + 1) * Ms]).norm() / full.norm())
+    assert err < 2e-2, err
+    print("rank %d fused_tp ok" % r)
+
+
+def scenario_extras(c, p, r, args):
+    """bench_extras (config-e shapes and MoE) with torch.distributed NCCL as the baseline."""
+    import json
+    import torch.distributed as dist
+    from cann_hccl_b200.parallel import bench_extras
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29533")
+    dist.init_process_group("nccl", rank=r, world_size=p, device_id=torch.device("cuda", r))
+
+    def sync():
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    def mx(v):
+        t = torch.tensor([v], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+    res = bench_extras.run(c, p, r, dist, mx, sync, None)
+    if r == 0:
+        print("EXTRAS " + json.dumps(res))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 if __name__ == "__main__":
     scenario, p, r, root_file = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), sys.argv[4]
     torch.cuda.set_device(r)

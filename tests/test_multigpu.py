@@ -56,3 +56,11 @@ def test_collectives_multi_gpu_p2p_only():
         pytest.skip("needs 2 GPUs")
     outs = run_gpu_ranks(2, "collectives", env={"HCCL_NVLS_ENABLE": "0"})
     assert all("nvls=False" in o for _, o in outs)
+
+
+@pytest.mark.parametrize("p", [2, 8])
+def test_fused_tp_multi_gpu(p):
+    if ngpu() < p:
+        pytest.skip("needs %d GPUs" % p)
+    outs = run_gpu_ranks(p, "fused_tp")
+    assert all("fused_tp ok" in o for _, o in outs)
