@@ -1,6 +1,8 @@
 // Host side of the fused tensor-parallel operators: symmetric workspaces (gathered X / partial-sum slots + flag words),
 // per-workspace call epochs, and the launch of the fused sm_100a kernel (kernels/fused/tp_gemm_sm100.cu).
 #include <cuda_runtime.h>
+#include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <sstream>
 #include "common/log.h"
@@ -94,7 +96,9 @@ HcclResult Communicator::tp_all_gather_matmul(const void *const *x_shard, const 
     }
     stats_.launches++;
     stats_.ops[COLL_ALLGATHER]++;
-    return launch_tp_gemm(P.data(), A.data(), B.data(), nl, nranks_ > 1 ? 16 : 1, stream);
+    int ncomm = nranks_ > 1 ? 8 : 1;
+    if (const char *e = getenv("HCCL_TP_COMM_CTAS")) ncomm = std::max(1, atoi(e));
+    return launch_tp_gemm(P.data(), A.data(), B.data(), nl, ncomm, stream);
 }
 
 HcclResult Communicator::tp_matmul_reduce_scatter(const void *const *h, const void *const *w, void *const *out, int M, int N, int K, void *stream)
@@ -126,7 +130,7 @@ HcclResult Communicator::tp_matmul_reduce_scatter(const void *const *h, const vo
     }
     stats_.launches++;
     stats_.ops[COLL_REDUCE_SCATTER]++;
-    return launch_tp_gemm(P.data(), A.data(), B.data(), nl, 16, stream);
+    return launch_tp_gemm(P.data(), A.data(), B.data(), nl, 0, stream);
 }
 
 }  // namespace hcclb

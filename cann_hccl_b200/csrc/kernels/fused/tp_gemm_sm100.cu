@@ -4,17 +4,20 @@
 //   mode AG    : all-gather(X shards) -> Y = X * W^T   (column-parallel layer; X sharded by rows over the ranks)
 //   mode RS    : P = H * W^T -> reduce-scatter(P) by rows  (row-parallel layer; every rank ends with its row block)
 //
-// One persistent kernel does the transfer and the math.  CTAs [0, n_gemm) run a warp-specialised tcgen05 GEMM:
-// warp 0 feeds a 4-stage shared-memory ring with TMA (cp.async.bulk.tensor, 128-byte swizzle, never multicast, always
-// from this GPU's own memory), warp 1 issues tcgen05.mma (128x256x16, cta_group::1) into one of two 256-column TMEM
-// accumulators, warps 2..5 drain the other accumulator with tcgen05.ld, convert to bf16 and store.  The remaining
-// CTAs move data between GPUs while the tensor cores work:
-//   AG: they stage this rank's shard into its slot of the symmetric X buffer, tell the peers, then pull the peers'
-//       shards over NVLink with bulk asynchronous copies (peer global -> shared -> local global) in the order in which
-//       the GEMM consumes them, and publish each 128-row block with a flag the TMA producer waits on;
-//   RS: the GEMM epilogue stores every bf16 partial tile straight into the owner rank's receive slot over NVLink and
-//       bumps a counter there; the comm CTAs of the owner sum the p slots in fp32 (fixed rank order) as soon as a
-//       row block is complete on all ranks.
+// One persistent kernel does the transfer and the math, one CTA per SM:
+//   warp 0    feeds a 4-stage shared-memory ring with TMA (cp.async.bulk.tensor, 128-byte swizzle, never multicast,
+//             always from this GPU's own memory);
+//   warp 1    issues tcgen05.mma (128x256x16, cta_group::1) into one of two 256-column TMEM accumulators;
+//   warps 2-5 drain the other accumulator with tcgen05.ld, convert to bf16 and send each 128-byte row piece off with a
+//             bulk asynchronous store (to local memory, or in RS mode straight into the owner rank's receive slot
+//             over NVLink, followed by a counter increment there);
+//   AG        a handful of extra CTAs move data instead: they stage this rank's shard into its slot of the symmetric
+//             X buffer and pull the peers' shards over NVLink with bulk asynchronous copies (peer global -> shared ->
+//             local global, six 32 KB pieces in flight per CTA) in the order in which the GEMM consumes the 128-row
+//             blocks; the TMA producer waits on a per-block flag.
+//   RS tail   after its last tile every CTA sums receive slots (fp32, fixed rank order) for the (row block, n tile)
+//             items whose partial tiles have arrived from all ranks.
+// Tiles are rasterised in L2-sized panels of n tiles so that a panel's weights are read from HBM once.
 // Role of the reference's MC2 hooks (framework/op_base/src/op_base.cc:3137-3284: resources exported so that a fused
 // matmul+communication kernel can be written elsewhere); here the fused kernels are part of the library.
 //
@@ -37,14 +40,16 @@ namespace {
 
 constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16;
 constexpr int kStages = 4;
-constexpr int kThreads = 256;  // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue, warps 6-7 idle in GEMM CTAs; all 8 copy in comm CTAs
+constexpr int kThreads = 256;  // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue, warps 6-7 move data between GPUs (AG)
 constexpr uint32_t kABytes = BM * BK * 2, kBBytes = BN * BK * 2, kStageBytes = kABytes + kBBytes;
 constexpr uint32_t kTmemCols = 512;
-constexpr int kCommBuf = 32 * 1024, kCommDepth = 6;  // bulk-copy ring of a comm CTA
+constexpr int kCommBuf = 32 * 1024, kCommDepth = 6;  // bulk-copy ring of a data-movement CTA (lives in the tile buffers)
+constexpr int kEpiCols = 64, kEpiStride = kEpiCols * 2 + 16;  // epilogue chunk: 64 bf16 per row, padded against bank conflicts
 constexpr uint32_t kSpinLimit = 1u << 28;            // iterations of an mbarrier poll before it gives up (seconds)
 
 struct SharedStorage {
-    alignas(1024) uint8_t tiles[kStages * kStageBytes];  // also the bulk-copy ring of comm CTAs
+    alignas(1024) uint8_t tiles[kStages * kStageBytes];
+    alignas(16) uint8_t epi[128 * kEpiStride];          // one 128-byte (+16 pad) row slot per epilogue thread
     alignas(8) uint64_t full_bar[kStages];
     uint64_t empty_bar[kStages];
     uint64_t tmem_full[2];
@@ -103,6 +108,7 @@ __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.comm
 template <int N> __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
 template <int N> __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ bool elect_one()
@@ -157,6 +163,10 @@ __device__ __forceinline__ void red_add_release_sys(uint64_t *p, uint64_t v)
 {
     asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
+__device__ __forceinline__ void red_add_release_gpu(uint64_t *p, uint64_t v)
+{
+    asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
 __device__ __forceinline__ void st_release_gpu(uint64_t *p, uint64_t v)
 {
     asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
@@ -194,13 +204,27 @@ __device__ __forceinline__ void report(const TpGemmParams &P, uint32_t code, int
     *(volatile uint32_t *)&s->code = code;
 }
 
-// Logical tile index -> (m tile, n tile).  Tiles walk n fastest; the m order starts at this rank's own row blocks
-// (already local) and continues with the next ranks' blocks in the order in which the comm CTAs fetch them (AG), or
-// starts with the next rank's blocks so that remote partial tiles leave early and the own blocks come last (RS).
-__device__ __forceinline__ void tile_coords(const TpGemmParams &P, int t, int n_tiles, int m_tiles, int &mt, int &nt)
+// Logical tile index -> (m tile, n tile, panel).  The n tiles are cut into panels narrow enough for the panel's
+// weights (panel width x 256 rows x K) to stay in L2 while all m tiles stream past; inside a panel tiles walk n
+// fastest.  The m order starts at this rank's own row blocks (already local) and continues with the next ranks'
+// blocks in the order in which the comm CTAs fetch them (AG), or starts with the next rank's blocks so that remote
+// partial tiles leave early and the own blocks come last (RS).
+__device__ __forceinline__ int panel_width(const TpGemmParams &P, int n_tiles)
 {
-    int ml = t / n_tiles;
-    nt = t % n_tiles;
+    long long w = (40ll << 20) / ((long long)BN * P.K * 2);
+    if (w < 1) w = 1;
+    if (w > n_tiles) w = n_tiles;
+    return (int)w;
+}
+__device__ __forceinline__ void tile_coords(const TpGemmParams &P, int t, int n_tiles, int m_tiles, int pw, int &mt, int &nt, int &panel)
+{
+    int per_panel = m_tiles * pw;
+    panel = t / per_panel;
+    int n0 = panel * pw;
+    int w = n_tiles - n0 < pw ? n_tiles - n0 : pw;  // the last panel may be narrower
+    int r = t - panel * per_panel;
+    int ml = r / w;
+    nt = n0 + r % w;
     if (P.mode == TP_MODE_PLAIN || P.nranks == 1) { mt = ml; return; }
     int per = m_tiles / P.nranks;  // m tiles per rank
     int shift = P.mode == TP_MODE_AG ? P.rank * per : ((P.rank + 1) % P.nranks) * per;
@@ -281,10 +305,14 @@ __device__ void comm_role_ag(const TpGemmParams &P, SharedStorage &S, int c, int
         if (q != me) red_add_release_sys(P.flags[q] + p + me, 1);
 }
 
+__device__ __forceinline__ uint64_t rs_done_index(const TpGemmParams &P, int per, int npanels) { return (uint64_t)P.nranks * per * npanels; }
+
 // Flag words of a rank in RS mode (uint64):
-//   [src * per + j]  n tiles of this rank's row block j delivered by src (epoch * n_tiles when complete)
-//   [p * per + o]    comm CTAs of owner o that finished reducing (epoch * nc when complete): o's slots may be rewritten
-__device__ void comm_role_rs(const TpGemmParams &P, SharedStorage &S, int c, int nc)
+//   [(src * per + j) * panels + panel]  n tiles of panel `panel` of this rank's row block j delivered by src
+//   [p * per * panels + o]  CTAs of owner o that finished reducing (epoch * G when complete): o's slots may be rewritten
+// After its GEMM tiles every CTA turns into a reducer: item = (panel, my row block j, n tile) -> 128 x 256 outputs, summed
+// over the p receive slots in fp32 in rank order as soon as all sources have delivered that panel of block j.
+__device__ void reduce_tail_rs(const TpGemmParams &P, SharedStorage &S, int pw, int npanels)
 {
     const int p = P.nranks, me = P.rank;
     const int m_tiles = P.M / BM, per = m_tiles / p, n_tiles = P.N / BN;
@@ -292,21 +320,29 @@ __device__ void comm_role_rs(const TpGemmParams &P, SharedStorage &S, int c, int
     const uint64_t deadline = global_timer_ns() + P.timeout_ns;
     volatile uint32_t *fail = &S.fail;
     const uint64_t slot_elems = (uint64_t)(P.M / p) * P.N;  // one source's partial rows for me
-    // row block j of mine is complete when every source delivered all n tiles of it
-    for (int j = c; j < per; j += nc) {
-        if (threadIdx.x < p) {
-            if (!wait_word_ge(myflags + (uint64_t)threadIdx.x * per + j, P.epoch * (uint64_t)n_tiles, true, deadline, fail)) report(P, *fail, 500 + threadIdx.x);
+    const int items = per * n_tiles;
+    for (int item = blockIdx.x; item < items; item += gridDim.x) {
+        // items are ordered like the GEMM's production: panel major, then row block, then n tile
+        int panel = 0, rem = item;
+        for (;; ++panel) {
+            int n0p = panel * pw, wp = (n_tiles - n0p < pw) ? n_tiles - n0p : pw;
+            if (rem < per * wp) break;
+            rem -= per * wp;
         }
-        __syncthreads();
-        if (S.fail) return;
-        // out rows [j*BM, (j+1)*BM) = sum over sources, fp32, fixed order
-        const uint64_t base = (uint64_t)j * BM * P.N, nvec = (uint64_t)BM * P.N / 8;
-        for (uint64_t v = threadIdx.x; v < nvec; v += blockDim.x) {
+        const int n0 = panel * pw, w = (n_tiles - n0 < pw) ? n_tiles - n0 : pw;
+        const int j = rem / w, nt = n0 + rem % w;
+        if (threadIdx.x < p) {
+            if (!wait_word_ge(myflags + ((uint64_t)threadIdx.x * per + j) * npanels + panel, P.epoch * (uint64_t)w, true, deadline, fail)) report(P, *fail, 500 + threadIdx.x);
+        }
+        if (__syncthreads_or((int)*fail)) return;
+        constexpr int vec_per_row = BN / 8;
+        for (int v = threadIdx.x; v < BM * vec_per_row; v += blockDim.x) {
+            const uint64_t eoff = ((uint64_t)j * BM + v / vec_per_row) * P.N + (uint64_t)nt * BN + (uint64_t)(v % vec_per_row) * 8;
             float acc[8];
 #pragma unroll
             for (int k = 0; k < 8; ++k) acc[k] = 0.f;
             for (int q = 0; q < p; ++q) {
-                uint4 x = ld_stream((const uint4 *)(P.partial[me] + (uint64_t)q * slot_elems + base) + v);
+                uint4 x = ld_stream((const uint4 *)(P.partial[me] + (uint64_t)q * slot_elems + eoff));
                 const __nv_bfloat162 *h = (const __nv_bfloat162 *)&x;
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
@@ -320,15 +356,14 @@ __device__ void comm_role_rs(const TpGemmParams &P, SharedStorage &S, int c, int
             o.y = pack_bf16(__float_as_uint(acc[2]), __float_as_uint(acc[3]));
             o.z = pack_bf16(__float_as_uint(acc[4]), __float_as_uint(acc[5]));
             o.w = pack_bf16(__float_as_uint(acc[6]), __float_as_uint(acc[7]));
-            ((uint4 *)(P.out + base))[v] = o;
+            *(uint4 *)(P.out + eoff) = o;
         }
         __syncthreads();
     }
-    // all my row blocks handled by this CTA are reduced: sources may overwrite my slots in the next call once every
-    // comm CTA said so; done[me] on each source counts comm CTAs
-    if (threadIdx.x == 0) {
+    // this CTA is done reading my receive slots: sources may overwrite them in the next call once every CTA said so
+    if (threadIdx.x < p) {
         __threadfence_system();
-        for (int q = 0; q < p; ++q) red_add_release_sys(P.flags[q] + (uint64_t)p * per + me, 1);
+        red_add_release_sys(P.flags[threadIdx.x] + rs_done_index(P, per, npanels) + me, 1);
     }
 }
 
@@ -341,7 +376,7 @@ __global__ void __launch_bounds__(kThreads, 1) tp_gemm_kernel(const __grid_const
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int m_tiles = P.M / BM, n_tiles = P.N / BN, k_iters = P.K / BK;
     const int total_tiles = m_tiles * n_tiles;
-    const bool is_gemm = (int)blockIdx.x < P.n_gemm_ctas;
+    const int pw = panel_width(P, n_tiles), npanels = (n_tiles + pw - 1) / pw;
     volatile uint32_t *fail = &S.fail;
 
     if (threadIdx.x == 0) {
@@ -353,14 +388,11 @@ __global__ void __launch_bounds__(kThreads, 1) tp_gemm_kernel(const __grid_const
     }
     __syncthreads();
 
-    if (!is_gemm) {
-        int c = blockIdx.x - P.n_gemm_ctas, nc = gridDim.x - P.n_gemm_ctas;
-        if (P.mode == TP_MODE_AG) comm_role_ag(P, S, c, nc);
-        else if (P.mode == TP_MODE_RS) comm_role_rs(P, S, c, nc);
+    if ((int)blockIdx.x >= P.n_gemm_ctas) {  // data-movement CTA (AG): one thread drives bulk asynchronous copies
+        comm_role_ag(P, S, blockIdx.x - P.n_gemm_ctas, gridDim.x - P.n_gemm_ctas);
         if (threadIdx.x == 0) bulk_wait_all<0>();
         return;
     }
-
     if (warp == 1) {  // TMEM allocation by one full warp
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&S.tmem_base)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -377,8 +409,8 @@ __global__ void __launch_bounds__(kThreads, 1) tp_gemm_kernel(const __grid_const
             uint32_t it = 0;
             const uint64_t *chunk_ready = P.mode == TP_MODE_AG ? P.flags[P.rank] + 2 * P.nranks : nullptr;
             for (int t = blockIdx.x; t < total_tiles && !*fail; t += P.n_gemm_ctas) {
-                int mt, nt;
-                tile_coords(P, t, n_tiles, m_tiles, mt, nt);
+                int mt, nt, panel;
+                tile_coords(P, t, n_tiles, m_tiles, pw, mt, nt, panel);
                 if (chunk_ready) {  // rows of this block have to be in local memory (staged or pulled by the comm CTAs)
                     if (!wait_word_ge(chunk_ready + mt, P.epoch, false, deadline, fail)) { report(P, *fail, 600 + mt); break; }
                     fence_proxy_async();
@@ -421,11 +453,11 @@ __global__ void __launch_bounds__(kThreads, 1) tp_gemm_kernel(const __grid_const
     } else if (warp >= 2 && warp < 6) {
         // ------------------------------------------------------------------ epilogue: TMEM -> registers -> bf16 -> global
         const int q4 = warp & 3;  // a warp may only touch the TMEM lane quarter given by its index modulo 4
-        uint32_t tile_i = 0;
+        uint32_t tile_i = 0, owner_ok = 0;
         const int per = P.nranks > 0 ? m_tiles / P.nranks : m_tiles;
         for (int t = blockIdx.x; t < total_tiles && !*fail; t += P.n_gemm_ctas, ++tile_i) {
-            int mt, nt;
-            tile_coords(P, t, n_tiles, m_tiles, mt, nt);
+            int mt, nt, panel;
+            tile_coords(P, t, n_tiles, m_tiles, pw, mt, nt, panel);
             uint32_t buf = tile_i & 1, use = tile_i >> 1;
             if (!mbar_wait(&S.tmem_full[buf], use & 1, fail)) { report(P, *fail, 1000); break; }
             tc_fence_after();
@@ -434,47 +466,71 @@ __global__ void __launch_bounds__(kThreads, 1) tp_gemm_kernel(const __grid_const
             int owner = 0;
             if (P.mode == TP_MODE_RS) {
                 owner = mt / per;  // rows of block mt belong to rank `owner`; my partial goes to its slot number P.rank
-                // the owner must have finished reducing the previous call's data in that slot
-                if (!wait_word_ge(P.flags[P.rank] + (uint64_t)P.nranks * per + owner, (P.epoch - 1) * (uint64_t)(gridDim.x - P.n_gemm_ctas), true, deadline, fail)) { report(P, *fail, 1100 + owner); break; }
+                // the owner must have finished reducing the previous call's data in that slot (checked once per owner)
+                if (!(owner_ok & (1u << owner))) {
+                    if (!wait_word_ge(P.flags[P.rank] + rs_done_index(P, per, npanels) + owner, (P.epoch - 1) * (uint64_t)gridDim.x, true, deadline, fail)) { report(P, *fail, 1100 + owner); break; }
+                    owner_ok |= 1u << owner;
+                }
                 const uint64_t slot_elems = (uint64_t)(P.M / P.nranks) * P.N;
                 dst_row = P.partial[owner] + (uint64_t)P.rank * slot_elems + (uint64_t)(row - owner * per * BM) * P.N + (uint64_t)nt * BN;
             } else {
                 dst_row = P.C + (uint64_t)row * P.ldc + (uint64_t)nt * BN;
             }
+            // 64 columns at a time: TMEM -> registers -> bf16 -> this thread's 128-byte slot in shared memory -> one bulk
+            // asynchronous store of the whole 128-byte row piece (full lines on HBM and on NVLink, nothing blocks)
+            uint8_t *slot = S.epi + (size_t)(q4 * 32 + lane) * kEpiStride;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t r[32];
-                tmem_ld32(tmem_base + buf * BN + c0 + ((uint32_t)(q4 * 32) << 16), r);
+            for (int c0 = 0; c0 < BN; c0 += kEpiCols) {
+                uint32_t r0[32], r1[32];
+                tmem_ld32(tmem_base + buf * BN + c0 + ((uint32_t)(q4 * 32) << 16), r0);
+                tmem_ld32(tmem_base + buf * BN + c0 + 32 + ((uint32_t)(q4 * 32) << 16), r1);
                 tmem_ld_wait();
-                uint4 *o = (uint4 *)(dst_row + c0);
+                bulk_wait_read<0>();  // the previous piece has left the slot
+                uint4 *o = (uint4 *)slot;
 #pragma unroll
                 for (int v = 0; v < 4; ++v) {
                     uint4 w;
-                    w.x = pack_bf16(r[8 * v + 0], r[8 * v + 1]);
-                    w.y = pack_bf16(r[8 * v + 2], r[8 * v + 3]);
-                    w.z = pack_bf16(r[8 * v + 4], r[8 * v + 5]);
-                    w.w = pack_bf16(r[8 * v + 6], r[8 * v + 7]);
+                    w.x = pack_bf16(r0[8 * v + 0], r0[8 * v + 1]);
+                    w.y = pack_bf16(r0[8 * v + 2], r0[8 * v + 3]);
+                    w.z = pack_bf16(r0[8 * v + 4], r0[8 * v + 5]);
+                    w.w = pack_bf16(r0[8 * v + 6], r0[8 * v + 7]);
                     o[v] = w;
                 }
+#pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                    uint4 w;
+                    w.x = pack_bf16(r1[8 * v + 0], r1[8 * v + 1]);
+                    w.y = pack_bf16(r1[8 * v + 2], r1[8 * v + 3]);
+                    w.z = pack_bf16(r1[8 * v + 4], r1[8 * v + 5]);
+                    w.w = pack_bf16(r1[8 * v + 6], r1[8 * v + 7]);
+                    o[4 + v] = w;
+                }
+                fence_proxy_async_smem();
+                bulk_s2g(dst_row + c0, slot, kEpiCols * 2);
+                bulk_commit();
             }
             tc_fence_before();
             mbar_arrive(&S.tmem_empty[buf]);  // 128 arrivals free the accumulator for the tile after next
             if (P.mode == TP_MODE_RS) {
                 // the four epilogue warps finished their rows: one of them publishes the tile to the owner
+                bulk_wait_all<0>();  // this thread's row pieces are written
+                __threadfence_system();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (warp == 2 && lane == 0) {
                     __threadfence_system();
-                    red_add_release_sys(P.flags[owner] + (uint64_t)P.rank * per + (mt - owner * per), 1);
+                    red_add_release_sys(P.flags[owner] + ((uint64_t)P.rank * per + (mt - owner * per)) * npanels + panel, 1);
                 }
             }
         }
     }
+    if (warp >= 2 && warp < 6) bulk_wait_all<0>();  // every row piece of this thread has been written
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
+    if (P.mode == TP_MODE_RS && !__syncthreads_or((int)*fail)) reduce_tail_rs(P, S, pw, npanels);
 }
 
 HcclResult encode_2d(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows)
@@ -514,12 +570,14 @@ HcclResult launch_tp_gemm(TpGemmParams *P, const void *const *A, const void *con
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (P0.mode == TP_MODE_PLAIN) n_comm_ctas = 0;
+    // AG: a few CTAs only move data (bulk asynchronous copies); RS needs none (reduce tail on every CTA)
+    if (P0.mode != TP_MODE_AG) n_comm_ctas = 0;
     else if (n_comm_ctas < 1) n_comm_ctas = 1;
     int per_rank = sms / nlocal;  // all CTAs of all local ranks must be resident together
-    if (n_comm_ctas > per_rank / 2) n_comm_ctas = std::max(1, per_rank / 2);
+    if (n_comm_ctas > per_rank / 4) n_comm_ctas = std::max(1, per_rank / 4);
+    // with communication every rank must run the same grid (completion counters count CTAs)
     int total = (P0.M / BM) * (P0.N / BN);
-    int n_gemm = std::min(total, std::max(1, per_rank - n_comm_ctas));
+    int n_gemm = P0.mode == TP_MODE_PLAIN ? std::min(total, per_rank) : per_rank - n_comm_ctas;
     TpGemmParamsArray arr;
     memset(&arr, 0, sizeof(arr));
     for (int i = 0; i < nlocal; ++i) {
