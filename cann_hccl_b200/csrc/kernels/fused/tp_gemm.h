@@ -5,9 +5,10 @@
 #include "algo/plan.h"
 namespace hcclb {
 enum TpMode : int { TP_MODE_PLAIN = 0, TP_MODE_AG = 1, TP_MODE_RS = 2 };
-constexpr int kTpMaxLocal = 4;  // virtual ranks of one GPU that one cooperative launch can run (single-GPU validation)
+constexpr int kTpMaxLocal = 4;   // virtual ranks of one GPU that one cooperative launch can run (single-GPU validation)
 struct alignas(64) TpGemmParams {
     CUtensorMap tmA, tmB;             // A [M,K] and B [N,K], both K-major bf16, this GPU's own memory
+    CUtensorMap tmX;                  // AG: this rank's own shard [M/p, K] in the caller's buffer
     __nv_bfloat16 *C;                 // PLAIN / AG: output [M, ldc]
     int ldc;
     int M, N, K;

@@ -205,10 +205,8 @@ __device__ __forceinline__ void report(const TpGemmParams &P, uint32_t code, int
 }
 
 // Logical tile index -> (m tile, n tile, panel).  The n tiles are cut into panels narrow enough for the panel's
-// weights (panel width x 256 rows x K) to stay in L2 while all m tiles stream past; inside a panel tiles walk n
-// fastest.  The m order starts at this rank's own row blocks (already local) and continues with the next ranks'
-// blocks in the order in which the comm CTAs fetch them (AG), or starts with the next rank's blocks so that remote
-// partial tiles leave early and the own blocks come last (RS).
+// weights (panel width x 256 rows x K) to stay in L2 while the m tiles of a shard stream past; inside a panel tiles
+// walk n fastest.
 __device__ __forceinline__ int panel_width(const TpGemmParams &P, int n_tiles)
 {
     long long w = (40ll << 20) / ((long long)BN * P.K * 2);
@@ -218,17 +216,26 @@ __device__ __forceinline__ int panel_width(const TpGemmParams &P, int n_tiles)
 }
 __device__ __forceinline__ void tile_coords(const TpGemmParams &P, int t, int n_tiles, int m_tiles, int pw, int &mt, int &nt, int &panel)
 {
-    int per_panel = m_tiles * pw;
-    panel = t / per_panel;
-    int n0 = panel * pw;
-    int w = n_tiles - n0 < pw ? n_tiles - n0 : pw;  // the last panel may be narrower
-    int r = t - panel * per_panel;
-    int ml = r / w;
-    nt = n0 + r % w;
+    // rows are handled shard by shard (one rank's row blocks at a time, all panels), so that the transfer of the next
+    // shard has the whole compute time of the current one; without communication there is a single "shard"
+    const bool comm = P.mode == TP_MODE_AG && P.nranks > 1;  // RS pushes asynchronously and keeps the L2-friendliest order
+    const int per = comm ? m_tiles / P.nranks : m_tiles;  // m tiles per shard
+    const int tiles_per_shard = per * n_tiles;
+    const int sidx = t / tiles_per_shard, r1 = t - sidx * tiles_per_shard;
+    const int per_panel = per * pw;
+    panel = r1 / per_panel;
+    const int n0 = panel * pw;
+    const int w = n_tiles - n0 < pw ? n_tiles - n0 : pw;  // the last panel may be narrower
+    const int r2 = r1 - panel * per_panel;
+    const int ml = r2 / w;
+    nt = n0 + r2 % w;
     if (P.mode == TP_MODE_PLAIN || P.nranks == 1) { mt = ml; return; }
-    int per = m_tiles / P.nranks;  // m tiles per rank
-    int shift = P.mode == TP_MODE_AG ? P.rank * per : ((P.rank + 1) % P.nranks) * per;
-    mt = (ml + shift) % m_tiles;
+    if (P.mode == TP_MODE_RS) {  // the next rank's rows first so that remote partial tiles leave early; my own rows last
+        mt = (ml + ((P.rank + 1) % P.nranks) * (m_tiles / P.nranks)) % m_tiles;
+        return;
+    }
+    // AG: own shard first (read straight from the caller's buffer), then the ranks after me in fetch order
+    mt = ((sidx + P.rank) % P.nranks) * per + ml;
 }
 
 // ---------------------------------------------------------------------------------------------- comm CTAs
@@ -411,16 +418,24 @@ __global__ void __launch_bounds__(kThreads, 1) tp_gemm_kernel(const __grid_const
             for (int t = blockIdx.x; t < total_tiles && !*fail; t += P.n_gemm_ctas) {
                 int mt, nt, panel;
                 tile_coords(P, t, n_tiles, m_tiles, pw, mt, nt, panel);
-                if (chunk_ready) {  // rows of this block have to be in local memory (staged or pulled by the comm CTAs)
-                    if (!wait_word_ge(chunk_ready + mt, P.epoch, false, deadline, fail)) { report(P, *fail, 600 + mt); break; }
-                    fence_proxy_async();
+                const CUtensorMap *amap = &P.tmA;
+                int arow = mt * BM;
+                if (chunk_ready) {
+                    const int per_r = m_tiles / P.nranks;
+                    if (mt / per_r == P.rank) {  // my own rows come straight from the caller's shard: nothing to wait for
+                        amap = &P.tmX;
+                        arow = (mt - P.rank * per_r) * BM;
+                    } else {  // a peer's rows have to be in local memory (pulled by the data-movement CTAs)
+                        if (!wait_word_ge(chunk_ready + mt, P.epoch, false, deadline, fail)) { report(P, *fail, 600 + mt); break; }
+                        fence_proxy_async();
+                    }
                 }
                 for (int k = 0; k < k_iters; ++k, ++it) {
                     uint32_t s = it % kStages, ph = (it / kStages) & 1;
                     if (!mbar_wait(&S.empty_bar[s], ph ^ 1, fail)) { report(P, *fail, 700); break; }
                     uint8_t *sa = S.tiles + (size_t)s * kStageBytes, *sb = sa + kABytes;
                     mbar_expect_tx(&S.full_bar[s], kStageBytes);
-                    tma_load_2d(sa, &P.tmA, &S.full_bar[s], k * BK, mt * BM);
+                    tma_load_2d(sa, amap, &S.full_bar[s], k * BK, arow);
                     tma_load_2d(sb, &P.tmB, &S.full_bar[s], k * BK, nt * BN);
                 }
             }
@@ -584,6 +599,10 @@ HcclResult launch_tp_gemm(TpGemmParams *P, const void *const *A, const void *con
         if ((((uintptr_t)A[i]) | ((uintptr_t)B[i])) & 15) return HCCL_E_PARA;
         P[i].n_gemm_ctas = n_gemm;
         CHK_RET(encode_2d(&P[i].tmA, A[i], (uint64_t)P[i].M, (uint64_t)P[i].K, BM));
+        if (P[i].mode == TP_MODE_AG) {
+            if (((uintptr_t)P[i].x_shard) & 15) return HCCL_E_PARA;
+            CHK_RET(encode_2d(&P[i].tmX, P[i].x_shard, (uint64_t)(P[i].M / P[i].nranks), (uint64_t)P[i].K, BM));
+        }
         CHK_RET(encode_2d(&P[i].tmB, B[i], (uint64_t)P[i].N, (uint64_t)P[i].K, BN));
         arr.r[i] = P[i];
     }
