@@ -151,7 +151,9 @@ void ar_mesh_twoshot(Prog &P, const OpDesc &d, bool nvls)
 {
     uint64_t n = d.chunk_count, uoff = d.chunk_off * P.es;
     Slices S = make_slices(n, P.p, P.vec);
-    uint64_t region2 = round_up_u64(S.sl * P.p * P.es, 256);  // NVLS: reduced slices land in a second region
+    // NVLS: the reduced slice is multicast over the raw slice in place: only its owner ever reads the raw slice, and it
+    // writes an element after having read it
+    uint64_t region2 = 0;
     for (int r = 0; r < P.p; ++r) {
         int last = 0;
         for (int j = 0; j < P.p; ++j) {  // per-slice copies keep channel lanes aligned with the consumers
@@ -236,9 +238,10 @@ void ring_ag(Prog &P, const SliceIo &io, int h, int first_idx)
 // AIV kernels with progress flags (aiv_all_reduce_910b_bigdata.h: producer and consumer blocks).
 void pipe_groups(int nchan, int &nA, int &nB, int &nC)
 {
-    nA = std::max(1, nchan / 6);
-    nB = std::max(1, (nchan - nA) / 2);
-    nC = std::max(1, nchan - nA - nB);
+    // copy-in and copy-out are HBM-bound and need few CTAs; the reduce group is link-bound and gets the rest
+    nA = std::max(1, nchan / 5);
+    nC = std::max(1, nchan / 5);
+    nB = std::max(1, nchan - nA - nC);
 }
 void ar_mesh_pipelined(Prog &P, const OpDesc &d, bool nvls)
 {
@@ -247,7 +250,7 @@ void ar_mesh_pipelined(Prog &P, const OpDesc &d, bool nvls)
     pipe_groups(P.nchan, nA, nB, nC);
     uint64_t unit = P.vec * (uint64_t)P.p;
     uint64_t ce = std::max<uint64_t>(unit, (d.pipe_chunk_bytes ? d.pipe_chunk_bytes : (4u << 20)) / P.es / unit * unit);
-    uint64_t region2 = round_up_u64(round_up_u64(n, P.vec) * P.es, 256);
+    uint64_t region2 = 0;  // NVLS multicasts the reduced slice over the raw one in place (only its owner reads the raw slice)
     for (int r = 0; r < P.p; ++r) {
         uint32_t k = 0;
         for (uint64_t c0 = 0; c0 < n; c0 += ce, ++k) {
@@ -936,8 +939,8 @@ uint64_t plan_stage_bytes(const OpDesc &d)
             uint64_t sl = std::max<uint64_t>(round_up_u64(ceil_div_u64(n, (uint64_t)m), vec), vec);
             uint64_t region = round_up_u64(sl * m * es, 256);
             if (d.algo == ALGO_MESH_PIPE) return round_up_u64(nA, 256);
-            if (d.algo == ALGO_NVLS_PIPE) return 2 * round_up_u64(nA, 256);
-            return d.algo == ALGO_NVLS ? 2 * region : std::max<uint64_t>(region, nA);
+            if (d.algo == ALGO_NVLS_PIPE) return round_up_u64(nA, 256);
+            return std::max<uint64_t>(region, nA);
         }
         case COLL_REDUCE_SCATTER: case COLL_ALLGATHER: case COLL_SCATTER: case COLL_GATHER: case COLL_ALLTOALL:
             return p * nA;
