@@ -32,6 +32,7 @@
 #include "common/log.h"
 #include "core/device_api.h"
 #include "kernels/fused/tp_gemm.h"
+#include "kernels/fused/tp_gemm_noalloc.h"
 #include "kernels/prims.cuh"
 
 namespace hcclb {
@@ -627,3 +628,56 @@ HcclResult launch_tp_gemm(TpGemmParams *P, const void *const *A, const void *con
 }
 
 }  // namespace hcclb
+
+// ---------------------------------------------------------------------------------------------- no-allocation entry point
+// See kernels/fused/tp_gemm_noalloc.h.  The scratch that the row-parallel kernel normally gets from the communicator's
+// symmetric heap (completion counters followed by the bf16 receive slot) lives in this file-scope device array instead.
+namespace {
+constexpr size_t kNoAllocFlagBytes = 64 * 1024;
+constexpr size_t kNoAllocScratchBytes = kNoAllocFlagBytes + HCCLB200_NOALLOC_MAX_OUT_ELEMS * 2;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+struct NoAllocDeviceState {
+    unsigned char *scratch = nullptr;  // device address of g_noalloc_scratch on that device
+};
+NoAllocDeviceState g_noalloc_state[64];
+}  // namespace
+
+extern "C" int hcclb200_matmul_reduce_noalloc(const void *h, const void *w, void *out, int M, int N, int K, void *stream)
+{
+    using namespace hcclb;
+    if (!h || !w || !out) return HCCL_E_PTR;
+    if (M <= 0 || N <= 0 || K <= 0 || M % BM || N % BN || K % BK) return HCCL_E_PARA;
+    if ((uint64_t)M * (uint64_t)N > HCCLB200_NOALLOC_MAX_OUT_ELEMS) {
+        HLOG_ERROR("hcclb200_matmul_reduce_noalloc: M x N = %llu exceeds the built-in scratch of %llu elements",
+                   (unsigned long long)M * N, (unsigned long long)HCCLB200_NOALLOC_MAX_OUT_ELEMS);
+        return HCCL_E_MEMORY;
+    }
+    if (tp_flag_words(M, 1) * 8 > kNoAllocFlagBytes) return HCCL_E_MEMORY;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return HCCL_E_RUNTIME;
+    NoAllocDeviceState &st = g_noalloc_state[dev];
+    if (!st.scratch) {
+        // first call on this device: in host code the array's name is only a stand-in, the kernel needs the device address
+        void *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || !p) {
+            HLOG_ERROR("cudaGetSymbolAddress(scratch) failed: %s", cudaGetErrorString(e));
+            return HCCL_E_RUNTIME;
+        }
+        st.scratch = (unsigned char *)p;
+    }
+    // the array keeps the previous call's contents and calls may differ in shape: the completion counters must start at
+    // zero for every call (the receive slot needs no clearing, it is rewritten before it is read)
+    if (cudaMemsetAsync(st.scratch, 0, kNoAllocFlagBytes, (cudaStream_t)stream) != cudaSuccess) return HCCL_E_RUNTIME;
+    TpGemmParams P;
+    memset(&P, 0, sizeof(P));
+    P.mode = TP_MODE_RS; P.M = M; P.N = N; P.K = K; P.rank = 0; P.nranks = 1;
+    P.epoch = 1;
+    P.timeout_ns = 10000000000ull;
+    P.out = (__nv_bfloat16 *)out;
+    P.flags[0] = (uint64_t *)st.scratch;
+    P.partial[0] = (__nv_bfloat16 *)(st.scratch + kNoAllocFlagBytes);
+    const void *a[1] = {h}, *b[1] = {w};
+    return launch_tp_gemm(&P, a, b, 1, 0, stream);
+}
