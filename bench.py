@@ -238,10 +238,14 @@ def main():
         sw_in = torch.empty(max(args.sweep_max, HEADLINE_BYTES) // 4, device="cuda")
         sw_in.uniform_(-1, 1)
         sw_out = torch.empty_like(sw_in)
+        zc_buf = zc_handle = None
+        if world > 1 and comm.has_nvls():
+            zc_handle, (zc_buf,) = comm.symmetric_empty(sw_in.numel(), torch.float32)
+            zc_buf.uniform_(-1, 1)
         while size <= args.sweep_max:
             cnt = size // 4
             # rotate through disjoint windows of the big buffers so that small messages also miss L2 between iterations
-            nwin = max(1, min(64, sw_in.numel() // cnt))
+            nwin = max(1, min(16, sw_in.numel() // cnt))
             iters = 50 if size <= (1 << 20) else (20 if size <= (32 << 20) else 8)
 
             def ours(k, cnt=cnt, nwin=nwin, size=size):
@@ -258,10 +262,21 @@ def main():
                 t_n = max_over_ranks(timed(nccl, iters)) / iters
                 row["nccl_time_us"] = round(t_n * 1e3, 2)
                 row["nccl_alg_bandwidth_GBps"] = round(size / t_n / 1e6, 2)
+            if world > 1 and zc_buf is not None and size >= (1 << 20):
+                # same collective on buffers in registered symmetric memory: the zero-copy NVLS path (in place)
+                def zc(k, cnt=cnt, nwin=nwin, size=size):
+                    comm.repeat(L.ALLREDUCE, zc_buf, zc_buf, cnt, L.FP32, k, size, nwin)
+                zc(max(5, nwin))
+                t_z = max_over_ranks(timed(zc, iters)) / iters
+                row["zero_copy_time_us"] = round(t_z * 1e3, 2)
+                row["zero_copy_alg_bandwidth_GBps"] = round(size / t_z / 1e6, 2)
             sweep.append(row)
             size *= 2
         assert comm.sync() == 0, comm.describe_status()
         del sw_in, sw_out
+        if zc_handle is not None:
+            del zc_buf
+            comm.mem_free(zc_handle)
 
     extras = {}
     if not args.no_extras:

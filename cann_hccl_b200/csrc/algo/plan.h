@@ -26,6 +26,8 @@ enum BufKind : uint8_t {
     BUF_OUT = 1,    // caller's receive buffer
     BUF_STAGE = 2,  // this op's half of the peer-mapped staging buffer
     BUF_P2P = 3,    // peer-mapped mailbox area used by Send/Recv on the host / emulated transports
+    BUF_ZIN = 4,    // caller's send buffer inside registered symmetric memory: addressable on every rank (zero-copy)
+    BUF_ZOUT = 5,   // caller's receive buffer inside registered symmetric memory
     BUF_NONE = 7,
 };
 
@@ -84,6 +86,12 @@ struct ExecArgs {
     int32_t dtype, redop;
     uint32_t track_done;   // 1: collective (ping-pong halves + done flags), 0: p2p plan
     uint32_t pad;
+    // zero-copy: the caller's buffers as mapped for every rank (arrays of nranks pointers) and their multicast mappings
+    uint8_t *const *z_in_peer;
+    uint8_t *const *z_out_peer;
+    uint8_t *z_in_mc;
+    uint8_t *z_out_mc;
+    uint64_t z_in_off, z_out_off;  // offsets of the caller's buffers inside their symmetric allocations (peer tables hold allocation bases)
 };
 
 // Flag page layout: [bank][source rank][channel] 64-bit words, then one "done" word per source rank.

@@ -13,6 +13,12 @@ HCCLB_HD uint8_t *resolve_addr(const RankCtx &c, const ExecArgs &a, uint8_t buf,
             if (rank == RANK_ALL) return c.mc_stage + half_off + off;
             return c.stage[rank == RANK_SELF ? c.rank : rank] + half_off + off;
         case BUF_P2P: return c.p2p[rank == RANK_SELF ? c.rank : rank] + off;
+        case BUF_ZIN:
+            if (rank == RANK_SELF) return const_cast<uint8_t *>(a.in) + off;
+            return (rank == RANK_ALL ? a.z_in_mc : a.z_in_peer[rank] + a.z_in_off) + off;
+        case BUF_ZOUT:
+            if (rank == RANK_SELF) return a.out + off;
+            return (rank == RANK_ALL ? a.z_out_mc : a.z_out_peer[rank] + a.z_out_off) + off;
         default: return nullptr;
     }
 }

@@ -15,7 +15,7 @@ const char *coll_name(int c)
 const char *algo_name(int a)
 {
     static const char *n[] = {"auto", "mesh", "mesh_oneshot", "ring", "rhd", "pairwise", "star", "tree", "nvls",
-                              "nvls_oneshot", "single", "mesh_pipe", "nvls_pipe", "ll"};
+                              "nvls_oneshot", "single", "mesh_pipe", "nvls_pipe", "nvls_zerocopy", "ll"};
     return (a >= 0 && a < ALGO_COUNT) ? n[a] : "unknown";
 }
 int algo_from_name(const std::string &s)
@@ -288,6 +288,30 @@ void ar_mesh_pipelined(Prog &P, const OpDesc &d, bool nvls)
             g.wait_rank = RANK_ALL; g.wait_val = k + 1; g.flags |= SF_WAIT_ALLCH; g.wait_clo = (uint16_t)nA; g.wait_cn = (uint16_t)nB;
             P.add(r, g, true);
         }
+    }
+}
+
+// Zero-copy NVLS AllReduce: both user buffers live in registered symmetric memory with a multicast mapping, so the
+// switch reduces straight from the send buffers and multicasts straight into the receive buffers
+// (role of the reference's zero-copy path for registered memory, hccl_communicator.cc:400-423 PrepareZeroCopy).
+void ar_nvls_zerocopy(Prog &P, const OpDesc &d)
+{
+    uint64_t n = d.chunk_count, uoff = d.chunk_off * P.es;
+    Slices S = make_slices(n, P.p, P.vec);
+    for (int r = 0; r < P.p; ++r) {
+        Step enter = P.mk(ST_NOP);  // my send buffer is final and my receive buffer may be written
+        enter.sig_rank = RANK_ALL;
+        int i0 = P.add(r, enter);
+        Step red = P.mk(ST_MC_REDUCE);
+        red.a_buf = BUF_ZIN; red.a_rank = RANK_ALL; red.a_off = uoff + S.off(r) * P.es;
+        red.d_buf = BUF_ZOUT; red.d_rank = RANK_ALL; red.d_off = uoff + S.off(r) * P.es;
+        red.count = S.len(r);
+        red.wait_rank = RANK_ALL; red.wait_val = (uint32_t)i0 + 1;
+        red.sig_rank = RANK_ALL;
+        int i1 = P.add(r, red);
+        Step fin = P.mk(ST_NOP);    // every slice has landed in my receive buffer and nobody reads my send buffer any more
+        fin.wait_rank = RANK_ALL; fin.wait_val = (uint32_t)i1 + 1;
+        P.add(r, fin);
     }
 }
 
@@ -938,6 +962,7 @@ uint64_t plan_stage_bytes(const OpDesc &d)
             int m = d.algo == ALGO_RHD ? make_block(d.nranks).B : d.nranks;
             uint64_t sl = std::max<uint64_t>(round_up_u64(ceil_div_u64(n, (uint64_t)m), vec), vec);
             uint64_t region = round_up_u64(sl * m * es, 256);
+            if (d.algo == ALGO_NVLS_ZC) return 0;
             if (d.algo == ALGO_MESH_PIPE) return round_up_u64(nA, 256);
             if (d.algo == ALGO_NVLS_PIPE) return round_up_u64(nA, 256);
             return std::max<uint64_t>(region, nA);
@@ -993,6 +1018,7 @@ HcclResult build_plan(const OpDesc &d, const std::vector<int> &local, Plan *plan
                     if (d.nchan < 3) return HCCL_E_PARA;
                     ar_mesh_pipelined(P, d, d.algo == ALGO_NVLS_PIPE);
                 }
+                else if (d.algo == ALGO_NVLS_ZC) ar_nvls_zerocopy(P, d);
                 else if (d.algo == ALGO_RING) ar_ring(P, d);
                 else if (d.algo == ALGO_RHD) ar_rhd(P, d);
                 else ok = false;

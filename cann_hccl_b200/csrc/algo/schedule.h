@@ -31,6 +31,7 @@ enum AlgoId : int {
     ALGO_SINGLE,        // one rank: local copy
     ALGO_MESH_PIPE,     // AllReduce / ReduceScatter / AllGather: mesh with CTA groups pipelining copy-in, reduce and gather over chunks
     ALGO_NVLS_PIPE,     // same with in-switch reduction / multicast stores
+    ALGO_NVLS_ZC,       // AllReduce on registered symmetric buffers: multimem.ld_reduce from the send buffers, multimem.st into the receive buffers, no staging
     ALGO_LL,            // AllReduce, small messages: data and flag travel together in 16-byte lines (device only)
     ALGO_COUNT
 };

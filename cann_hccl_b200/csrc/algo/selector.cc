@@ -42,7 +42,7 @@ bool nvls_reduce_supported(int dtype, int redop, uint64_t bytes)
 static bool algo_exists(int coll, int algo)
 {
     switch (coll) {
-        case COLL_ALLREDUCE: return algo == ALGO_MESH || algo == ALGO_MESH_ONESHOT || algo == ALGO_RING || algo == ALGO_RHD || algo == ALGO_NVLS || algo == ALGO_NVLS_ONESHOT || algo == ALGO_MESH_PIPE || algo == ALGO_NVLS_PIPE || algo == ALGO_LL;
+        case COLL_ALLREDUCE: return algo == ALGO_MESH || algo == ALGO_MESH_ONESHOT || algo == ALGO_RING || algo == ALGO_RHD || algo == ALGO_NVLS || algo == ALGO_NVLS_ONESHOT || algo == ALGO_MESH_PIPE || algo == ALGO_NVLS_PIPE || algo == ALGO_LL || algo == ALGO_NVLS_ZC;
         case COLL_REDUCE_SCATTER: case COLL_ALLGATHER: return algo == ALGO_MESH || algo == ALGO_RING || algo == ALGO_RHD || algo == ALGO_NVLS;
         case COLL_REDUCE_SCATTER_V: case COLL_ALLGATHER_V: return algo == ALGO_MESH || algo == ALGO_RING || algo == ALGO_NVLS;
         case COLL_BROADCAST: return algo == ALGO_STAR || algo == ALGO_RING || algo == ALGO_TREE || algo == ALGO_NVLS;
@@ -64,6 +64,7 @@ double estimate_us(int coll, int algo, uint64_t bytes, int p, const CostModel &m
     switch (coll) {
         case COLL_ALLREDUCE:
             switch (algo) {
+                case ALGO_NVLS_ZC: return L + 2 * a + (1.0 + 1.0 / p) * n / Bn + 3 * s;
                 case ALGO_LL: return L + 0.6 * a + 2.0 * (p - 1) * n / B + 2.0 * p * n / G;  // lines carry 50 % payload; no fence, no flag hop
                 case ALGO_MESH_ONESHOT: return L + a + (p - 1) * n / B + n / G + 2 * s;
                 case ALGO_MESH: return L + 2 * a + 2 * f * n / B + 2 * n / G + (p + 2) * s;
@@ -150,6 +151,7 @@ Selection select_algo(const SelectInput &in, const CostModel &m)
     auto allowed = [&](int algo) {
         if (!algo_exists(in.coll, algo)) return false;
         if (algo == ALGO_NVLS || algo == ALGO_NVLS_ONESHOT || algo == ALGO_NVLS_PIPE) return nvls_ok;
+        if (algo == ALGO_NVLS_ZC) return false;  // chosen by the communicator when the buffers are registered, never by the model
         if (algo == ALGO_LL) return in.device && in.expansion_mode != 1 && in.ll_max_bytes > 0 && in.bytes <= in.ll_max_bytes;
         if ((algo == ALGO_MESH_PIPE || algo == ALGO_NVLS_PIPE) && (!in.device || sel.nchan < 6)) return false;
         return true;

@@ -341,6 +341,13 @@ HcclResult Communicator::run_plan(const Plan &plan, const void *dev_steps_base, 
         a.dtype = dtype;
         a.redop = redop;
         a.track_done = track_done ? 1 : 0;
+        if (li < (int)zc_args_.size()) {
+            // the plan addresses the buffers relative to the caller's pointers: shift the segment bases by the buffer offsets
+            a.z_in_peer = zc_args_[li].in_tab; a.z_out_peer = zc_args_[li].out_tab;
+            a.z_in_mc = zc_args_[li].in_mc ? zc_args_[li].in_mc + zc_args_[li].oin : nullptr;
+            a.z_out_mc = zc_args_[li].out_mc ? zc_args_[li].out_mc + zc_args_[li].oout : nullptr;
+            a.z_in_off = zc_args_[li].oin; a.z_out_off = zc_args_[li].oout;
+        }
         if (track_done && settings_.transport == TR_DEVICE) status_[li]->head = seq;  // completion (tail) is a device word
     }
     stats_.launches++;
@@ -511,6 +518,48 @@ HcclResult Communicator::run_collective_once(const OpRequest &rq)
     if (rq.nchan > 0) sel.nchan = rq.nchan;
     if (p == 1) sel.algo = ALGO_SINGLE;
     if (rq.coll == COLL_BARRIER) { sel.algo = p == 1 ? ALGO_SINGLE : ALGO_MESH; sel.nchan = 1; }
+    // zero-copy: both buffers of every local rank inside registered symmetric memory with a multicast mapping, at offsets
+    // that all ranks share; agreed once per (buffers, count) over the hub so that every rank takes the same path
+    struct ZcInfo { int hin = 0, hout = 0; size_t oin = 0, oout = 0; };
+    std::vector<ZcInfo> zc(nl);
+    bool use_zc = false;
+    const bool host_tr = settings_.transport == TR_HOST;  // the host executor emulates the multicast accesses rank by rank
+    if (rq.coll == COLL_ALLREDUCE && p > 1 && (nvls_ || host_tr) && !user_segs_.empty() && (rq.algo == ALGO_AUTO || rq.algo == ALGO_NVLS_ZC) &&
+        (rq.algo == ALGO_NVLS_ZC || rq.count * es >= (512u << 10)) && !deterministic() &&
+        nvls_reduce_supported(rq.dtype, rq.redop, rq.count * es) && forced_algo_for(env_config(), rq.coll).empty()) {
+        bool mine = true;
+        for (int li = 0; li < nl && mine; ++li) {
+            zc[li].hin = find_user_seg(li, rq.in[li], rq.count * es, &zc[li].oin);
+            zc[li].hout = find_user_seg(li, rq.out[li], rq.count * es, &zc[li].oout);
+            mine = zc[li].hin && zc[li].hout && (host_tr || (user_segs_[zc[li].hin][li].mc && user_segs_[zc[li].hout][li].mc)) &&
+                   ((zc[li].oin | zc[li].oout) & 15) == 0;
+        }
+        std::ostringstream zk;
+        zk << rq.in[0] << ':' << rq.out[0] << ':' << rq.count << ':' << rq.dtype << ':' << rq.redop;
+        auto zit = zc_agreed_.find(zk.str());
+        if (zit == zc_agreed_.end()) {
+            struct { uint32_t ok; int32_t hin, hout; uint64_t oin, oout; } me_v{mine ? 1u : 0u, zc[0].hin, zc[0].hout, zc[0].oin, zc[0].oout};
+            std::vector<std::string> all;
+            int agreed = mine ? 1 : 0;
+            if (!all_local_) {
+                CHK_RET(exchange("zc/" + std::to_string(zc_agreed_.size()), std::string((const char *)&me_v, sizeof(me_v)), &all));
+                for (auto &sblob : all) {
+                    decltype(me_v) o;
+                    memcpy(&o, sblob.data(), sizeof(o));
+                    if (!o.ok || o.hin != me_v.hin || o.hout != me_v.hout || o.oin != me_v.oin || o.oout != me_v.oout) agreed = 0;
+                }
+            } else {
+                for (int li = 1; li < nl; ++li)
+                    if (zc[li].hin != zc[0].hin || zc[li].hout != zc[0].hout || zc[li].oin != zc[0].oin || zc[li].oout != zc[0].oout) agreed = 0;
+            }
+            zit = zc_agreed_.emplace(zk.str(), agreed).first;
+        }
+        use_zc = zit->second == 1;
+        CHK_RET_LOG(rq.algo == ALGO_NVLS_ZC && !use_zc, HCCL_E_PARA, "zero-copy AllReduce needs both buffers in registered symmetric memory at the same offsets on every rank");
+        if (use_zc) sel.algo = ALGO_NVLS_ZC;
+    } else {
+        CHK_RET_LOG(rq.algo == ALGO_NVLS_ZC, HCCL_E_NOT_SUPPORT, "zero-copy AllReduce needs NVLS, registered buffers, a reducible dtype/op pair and a multiple of 16 bytes");
+    }
     if ((sel.algo == ALGO_NVLS || sel.algo == ALGO_NVLS_ONESHOT || sel.algo == ALGO_NVLS_PIPE) && !nvls_) {
         HLOG_ERROR("NVLS algorithm requested but no multicast mapping exists on this communicator");
         return HCCL_E_NOT_SUPPORT;
@@ -583,7 +632,13 @@ HcclResult Communicator::run_collective_once(const OpRequest &rq)
         }
         CachedPlan *cp = nullptr;
         CHK_RET(get_plan(d, key.str(), &cp));
+        zc_args_.clear();
+        if (use_zc)
+            for (int li = 0; li < nl; ++li)
+                zc_args_.push_back({(uint8_t *const *)user_peer_tabs_[zc[li].hin][li], (uint8_t *const *)user_peer_tabs_[zc[li].hout][li],
+                                    user_segs_[zc[li].hin][li].mc, user_segs_[zc[li].hout][li].mc, zc[li].oin, zc[li].oout});
         rc = run_plan(cp->plan, cp->dev_steps.data(), rq, seq_, rq.dtype, rq.redop, true, in, out);
+        zc_args_.clear();
         ++seq_;
         if (rc != HCCL_SUCCESS) break;
         off += n;
@@ -1082,6 +1137,19 @@ HcclResult Communicator::sym_alloc(size_t bytes, void **local_ptrs, int *handle)
     CHK_RET(alloc_->alloc(bytes, true, &segs));
     for (int li = 0; li < nlocal(); ++li) local_ptrs[li] = segs[li].peer[local_ranks_[li]];
     *handle = next_handle_++;
+    std::vector<void *> tabs(nlocal(), nullptr);
+    for (int li = 0; li < nlocal(); ++li) {
+        std::vector<uint8_t *> tab(kMaxRanks, nullptr);
+        for (int q = 0; q < nranks_; ++q) tab[q] = segs[li].peer[q];
+        if (settings_.transport == TR_DEVICE) {
+            CHK_RET_LOG(cudaMalloc(&tabs[li], sizeof(uint8_t *) * kMaxRanks) != cudaSuccess, HCCL_E_MEMORY, "cudaMalloc failed");
+            cudaMemcpy(tabs[li], tab.data(), sizeof(uint8_t *) * kMaxRanks, cudaMemcpyHostToDevice);
+        } else {
+            tabs[li] = malloc(sizeof(uint8_t *) * kMaxRanks);
+            memcpy(tabs[li], tab.data(), sizeof(uint8_t *) * kMaxRanks);
+        }
+    }
+    user_peer_tabs_[*handle] = tabs;
     user_segs_[*handle] = std::move(segs);
     return HCCL_SUCCESS;
 }
@@ -1093,8 +1161,24 @@ HcclResult Communicator::sym_free(int handle)
     if (!all_local_ && nranks_ > 1) hub_->barrier(key_prefix_ + "/symfree/" + std::to_string(handle), nranks_, rank(), 10000);
     alloc_->release(&it->second);
     user_segs_.erase(it);
+    for (void *t : user_peer_tabs_[handle]) { if (settings_.transport == TR_DEVICE) cudaFree(t); else free(t); }
+    user_peer_tabs_.erase(handle);
+    zc_agreed_.clear();
     return HCCL_SUCCESS;
 }
+int Communicator::find_user_seg(int li, const void *ptr, size_t bytes, size_t *offset)
+{
+    for (auto &kv : user_segs_) {
+        const SymSegment &sg = kv.second[li];
+        const uint8_t *base = sg.peer[local_ranks_[li]];
+        if ((const uint8_t *)ptr >= base && (const uint8_t *)ptr + bytes <= base + sg.bytes) {
+            if (offset) *offset = (size_t)((const uint8_t *)ptr - base);
+            return kv.first;
+        }
+    }
+    return 0;
+}
+
 HcclResult Communicator::sym_query(int handle, void **peer_ptrs, void **mc_ptrs, size_t *bytes)
 {
     auto it = user_segs_.find(handle);

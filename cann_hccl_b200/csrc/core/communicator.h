@@ -218,7 +218,13 @@ private:
     std::mutex trace_mu_;
 
     std::map<int, std::vector<SymSegment>> user_segs_;
+    std::map<int, std::vector<void *>> user_peer_tabs_;   // per allocation and local rank: array of nranks peer pointers (device or host memory)
+    std::map<std::string, int> zc_agreed_;                 // (buffers, count) -> 1 when every rank can run the op zero-copy, 0 otherwise
+    // Finds the registered allocation that holds [ptr, ptr+bytes) of local rank li; returns its handle or 0.
+    int find_user_seg(int li, const void *ptr, size_t bytes, size_t *offset);
     int next_handle_ = 1;
+    struct ZcArgs { uint8_t *const *in_tab; uint8_t *const *out_tab; uint8_t *in_mc; uint8_t *out_mc; size_t oin, oout; };
+    std::vector<ZcArgs> zc_args_;   // zero-copy pointers of the op being launched (per local rank)
 
     std::thread hb_thread_;
     std::atomic<bool> hb_stop_{false};

@@ -94,6 +94,9 @@ __global__ void __launch_bounds__(256) moe_dispatch_kernel(const __nv_bfloat16 *
 }
 
 // one warp per token: out[t] = sum_k gate[t,k] * y@owner(expert[t,k])[dst_row[t,k]]   (fp32 accumulate, fixed k order)
+// The (owner pointer, gate) pairs of a token are resolved once; for every 16-byte column group the loads of up to eight
+// k rows are issued together before the first one is consumed, so a lane keeps eight peer loads in flight.
+constexpr int kCombineK = 8;
 __global__ void __launch_bounds__(256) moe_combine_kernel(PeerTable y, const int32_t *topk_idx, const float *gates, const int32_t *dst_row,
                                                           int64_t tokens, int topk, int hidden, int n_experts, int p, int me, int pairwise,
                                                           __nv_bfloat16 *out, int64_t capacity_rows)
@@ -102,37 +105,61 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(PeerTable y, const int
     const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     const int El = n_experts / p, nvec = hidden / 8;
     for (int64_t t = warp; t < tokens; t += nwarps) {
-        for (int v0 = 0; v0 < nvec; v0 += 32) {
-            int v = v0 + lane;
-            float acc[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-            // pairwise order: visit the k slots grouped by owner rank distance, which leaves the sum's k order unchanged
-            // per element because every (token, k) term is added exactly once; fp32 addition order is by k within a phase
-            for (int ph = 0; ph < (pairwise ? p : 1); ++ph) {
-                for (int k = 0; k < topk; ++k) {
+        for (int k0 = 0; k0 < topk; k0 += kCombineK) {  // batches of eight k slots (one batch for top-8 routing)
+            const uint4 *rowp[kCombineK];
+            float g[kCombineK];
+            int order[kCombineK];
+            // pairwise order visits the slots by owner distance from this rank; mesh keeps the k order
+            int n = 0;
+            for (int ph = 0; ph < (pairwise ? p : 1); ++ph)
+                for (int k = k0; k < topk && k < k0 + kCombineK; ++k) {
                     int e = topk_idx[t * topk + k];
                     if (e < 0 || e >= n_experts) continue;
                     int owner = e / El;
                     if (pairwise && owner != (me + ph) % p) continue;
                     int64_t row = dst_row[t * topk + k];
-                    if (row < 0 || row >= capacity_rows || v >= nvec) continue;
-                    float g = gates[t * topk + k];
-                    uint4 r = ((const uint4 *)(y.ptr[owner] + row * (int64_t)hidden))[v];
-                    const __nv_bfloat162 *h = (const __nv_bfloat162 *)&r;
+                    if (row < 0 || row >= capacity_rows) continue;
+                    order[n] = k;
+                    rowp[n] = (const uint4 *)(y.ptr[owner] + row * (int64_t)hidden);
+                    g[n] = gates[t * topk + k];
+                    ++n;
+                }
+            (void)order;
+            for (int v = lane; v < nvec; v += 32) {
+                uint4 r[kCombineK];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        float2 f = __bfloat1622float2(h[j]);
-                        acc[2 * j] += g * f.x;
-                        acc[2 * j + 1] += g * f.y;
+                for (int j = 0; j < kCombineK; ++j)
+                    if (j < n) r[j] = rowp[j][v];
+                float acc[8];
+                if (k0 == 0) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+                } else {  // more than eight experts per token: continue from the partial sum written by the previous batch
+                    uint4 o = ((const uint4 *)(out + t * (int64_t)hidden))[v];
+                    const __nv_bfloat162 *h = (const __nv_bfloat162 *)&o;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        float2 f = __bfloat1622float2(h[i]);
+                        acc[2 * i] = f.x;
+                        acc[2 * i + 1] = f.y;
                     }
                 }
-            }
-            if (v < nvec) {
+#pragma unroll
+                for (int j = 0; j < kCombineK; ++j) {
+                    if (j < n) {
+                        const __nv_bfloat162 *h = (const __nv_bfloat162 *)&r[j];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            float2 f = __bfloat1622float2(h[i]);
+                            acc[2 * i] += g[j] * f.x;
+                            acc[2 * i + 1] += g[j] * f.y;
+                        }
+                    }
+                }
                 uint4 o;
                 __nv_bfloat162 *h = (__nv_bfloat162 *)&o;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+                for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
                 ((uint4 *)(out + t * (int64_t)hidden))[v] = o;
             }
         }

@@ -310,6 +310,33 @@ class Communicator:
         L.check(L.lib().HcclB200MemAlloc(self._h, nbytes, ptrs, C.byref(h)), "HcclB200MemAlloc")
         return h.value, [ptrs[i] for i in range(self.nlocal)]
 
+    def symmetric_empty(self, numel, dtype):
+        """Buffer(s) of `numel` elements in registered symmetric memory (zero-copy collectives, fused kernels).
+        Device transport: torch tensor(s) of torch dtype `dtype`; host transport: numpy array(s).  Returns (handle, buffers),
+        one buffer per local rank; free with mem_free(handle) after dropping the buffers."""
+        import numpy as np
+        if self.device:
+            import torch
+            itemsize = torch.empty(0, dtype=dtype).element_size()
+        else:
+            itemsize = np.dtype(dtype).itemsize
+        nbytes = (numel * itemsize + 255) // 256 * 256
+        handle, ptrs = self.mem_alloc(nbytes)
+        bufs = []
+        for ptr in ptrs:
+            if self.device:
+                import torch
+
+                class _P:
+                    pass
+                o = _P()
+                o.__cuda_array_interface__ = {"shape": (numel * itemsize,), "typestr": "|u1", "data": (int(ptr), False), "version": 3}
+                bufs.append(torch.as_tensor(o, device="cuda").view(dtype))
+            else:
+                raw = (C.c_uint8 * (numel * itemsize)).from_address(ptr)
+                bufs.append(np.frombuffer(raw, dtype=dtype, count=numel))
+        return handle, bufs
+
     def mem_query(self, handle):
         """Returns (peer pointer table [local][rank], multicast pointers [local], bytes)."""
         peers = (C.c_void_p * (self.nlocal * self.nranks))()

@@ -85,6 +85,23 @@ def scenario_collectives(c, p, r, args):
                     idx = bad.nonzero().flatten()
                     raise AssertionError("allreduce n=%d algo=%s dtype=%s op=%d: %d bad elements, first %d last %d\n%s" % (
                         n, L.ALGO_NAMES[algo], dtype, op, int(bad.sum()), int(idx[0]), int(idx[-1]), str(e)[:300]))
+    if nvls:  # zero-copy on registered symmetric memory
+        n = 1_000_000
+        hin, (zin,) = c.symmetric_empty(n, torch.float32)
+        hout, (zout,) = c.symmetric_empty(n, torch.float32)
+        xs = [inp(q, n, torch.float32, seed=21) for q in range(p)]
+        zin.copy_(xs[r])
+        zout.zero_()
+        c.all_reduce(zin, zout)
+        ok(c)
+        assert c.trace()[-1]["algo"] == "nvls_zerocopy", c.trace()[-1]
+        close(zout, red(xs, L.SUM), torch.float32, p)
+        c.all_reduce(zin, zin)  # in place
+        ok(c)
+        close(zin, red(xs, L.SUM), torch.float32, p)
+        del zin, zout
+        c.mem_free(hin)
+        c.mem_free(hout)
     for algo in [L.ALGO_MESH, L.ALGO_RING, L.ALGO_RHD] + ([L.ALGO_NVLS] if nvls else []):
         n = 40_000
         xs = [inp(q, n * p, torch.float32, seed=3) for q in range(p)]
@@ -184,6 +201,14 @@ def scenario_perf(c, p, r, args):
                     if tr:
                         print("  launch %s" % c.last_launch)
                         print("  trace %s size %d: " % (L.ALGO_NAMES[algo], size) + " ".join("s%d[w%.0f m%.0f g%.0f]" % (i, w, m, g or 0) for i, w, m, g in tr[:14]))
+        if nv and size >= (1 << 20) and os.environ.get("PERF_ZC", "1") == "1":
+            hz, (zb,) = c.symmetric_empty(n * nwin, torch.float32)
+            zb.uniform_(-1, 1)
+            c.repeat(L.ALLREDUCE, zb, zb, n, L.FP32, nwin, size, nwin)  # first touch of every window (agreement over the hub)
+            t = _time_repeat(c, lambda it: c.repeat(L.ALLREDUCE, zb, zb, n, L.FP32, it, size, nwin), iters)
+            rows.append(("zero_copy", 0, t))
+            del zb
+            c.mem_free(hz)
         ok(c)
         if r == 0:
             for name, nchan, t in rows:

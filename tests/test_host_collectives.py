@@ -285,3 +285,28 @@ def test_auto_selection_runs(comms):
         np.testing.assert_allclose(outs[3], np_reduce(ins, L.SUM), **tol(np.float32, 8))
     tr = c.trace()
     assert tr and tr[-1]["op"] == "AllReduce" and tr[-1]["algo"] in L.ALGO_NAMES
+
+
+@pytest.mark.parametrize("p", [2, 5, 8])
+def test_zero_copy_allreduce_on_registered_memory(comms, p):
+    """Buffers in registered symmetric memory: the zero-copy plan reduces straight from the send buffers into the receive
+    buffers of every rank (host executor emulates the multicast accesses)."""
+    c = comms(p)
+    n = 300_000  # 1.2 MB: above the zero-copy threshold
+    hin, ins = c.symmetric_empty(n, np.float32)
+    hout, outs = c.symmetric_empty(n, np.float32)
+    src = make_inputs(p, n, np.float32)
+    for r in range(p):
+        ins[r][:] = src[r]
+        outs[r][:] = 0
+    c.all_reduce(ins, outs)
+    assert c.trace()[-1]["algo"] == "nvls_zerocopy"
+    ref = np_reduce(src, L.SUM)
+    for o in outs:
+        np.testing.assert_allclose(o, ref, **tol(np.float32, p))
+    c.all_reduce(ins, ins)  # in place
+    for o in ins:
+        np.testing.assert_allclose(o, ref, **tol(np.float32, p))
+    del ins, outs
+    c.mem_free(hin)
+    c.mem_free(hout)
