@@ -556,7 +556,13 @@ HcclResult Communicator::run_collective_once(const OpRequest &rq)
         }
         use_zc = zit->second == 1;
         CHK_RET_LOG(rq.algo == ALGO_NVLS_ZC && !use_zc, HCCL_E_PARA, "zero-copy AllReduce needs both buffers in registered symmetric memory at the same offsets on every rank");
-        if (use_zc) sel.algo = ALGO_NVLS_ZC;
+        if (use_zc) {
+            sel.algo = ALGO_NVLS_ZC;
+            // nothing but the switch is busy in this path: more CTAs keep more multimem requests in flight
+            int zch = all_local_ ? sel.nchan : 64;
+            if (const char *e = getenv("HCCL_ZC_CHANNELS")) zch = std::max(1, std::min(atoi(e), kMaxChannels));
+            if (rq.nchan <= 0 && rq.count * es >= (8u << 20)) sel.nchan = zch;
+        }
     } else {
         CHK_RET_LOG(rq.algo == ALGO_NVLS_ZC, HCCL_E_NOT_SUPPORT, "zero-copy AllReduce needs NVLS, registered buffers, a reducible dtype/op pair and a multiple of 16 bytes");
     }
