@@ -79,6 +79,37 @@ HcclResult Communicator::tp_all_gather_matmul(const void *const *x_shard, const 
     CHK_RET(tp_workspace(key.str(), (size_t)M * K * 2, M, &wsp));
     TpWorkspace &ws = *(TpWorkspace *)wsp;
     ++ws.epoch;
+    // zero-copy source: when every rank's shard lies in registered symmetric memory at one common offset the peers pull it
+    // from where it is; agreed once per (buffer, shape) so that all ranks take the same path
+    std::vector<int> zh(nl, 0);
+    std::vector<size_t> zo(nl, 0);
+    bool zc = false;
+    if (nranks_ > 1 && !user_segs_.empty()) {
+        const size_t shard_bytes = (size_t)(M / nranks_) * K * 2;
+        bool mine = true;
+        for (int li = 0; li < nl && mine; ++li) {
+            zh[li] = find_user_seg(li, x_shard[li], shard_bytes, &zo[li]);
+            mine = zh[li] != 0 && (zo[li] & 15) == 0 && zh[li] == zh[0] && zo[li] == zo[0];
+        }
+        std::ostringstream zk;
+        zk << "ag:" << x_shard[0] << ':' << M << ':' << K;
+        auto zit = zc_agreed_.find(zk.str());
+        if (zit == zc_agreed_.end()) {
+            struct { uint32_t ok; int32_t h; uint64_t off; } me_v{mine ? 1u : 0u, zh[0], zo[0]};
+            int agreed = mine ? 1 : 0;
+            if (!all_local_) {
+                std::vector<std::string> all;
+                CHK_RET(exchange("zc/" + std::to_string(zc_agreed_.size()), std::string((const char *)&me_v, sizeof(me_v)), &all));
+                for (auto &blob : all) {
+                    decltype(me_v) o;
+                    memcpy(&o, blob.data(), sizeof(o));
+                    if (!o.ok || o.h != me_v.h || o.off != me_v.off) agreed = 0;
+                }
+            }
+            zit = zc_agreed_.emplace(zk.str(), agreed).first;
+        }
+        zc = zit->second == 1;
+    }
     StateGuard guard(state_, CS_INUSE);
     std::vector<TpGemmParams> P(nl);
     std::vector<const void *> A(nl), B(nl);
@@ -90,13 +121,14 @@ HcclResult Communicator::tp_all_gather_matmul(const void *const *x_shard, const 
         for (int q = 0; q < nranks_; ++q) {
             P[li].flags[q] = (uint64_t *)ws.segs[li].peer[q];
             P[li].xfull[q] = (__nv_bfloat16 *)(ws.segs[li].peer[q] + ws.flag_bytes);
+            if (zc) P[li].x_peer[q] = (const __nv_bfloat16 *)(user_segs_[zh[li]][li].peer[q] + zo[li]);
         }
         A[li] = P[li].xfull[ctx_[li].rank];
         B[li] = w[li];
     }
     stats_.launches++;
     stats_.ops[COLL_ALLGATHER]++;
-    int ncomm = nranks_ > 1 ? 8 : 1;
+    int ncomm = nranks_ > 4 ? 12 : (nranks_ > 1 ? 8 : 1);
     if (const char *e = getenv("HCCL_TP_COMM_CTAS")) ncomm = std::max(1, atoi(e));
     return launch_tp_gemm(P.data(), A.data(), B.data(), nl, ncomm, stream);
 }

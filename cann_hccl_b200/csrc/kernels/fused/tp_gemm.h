@@ -17,6 +17,7 @@ struct alignas(64) TpGemmParams {
     uint64_t epoch;                   // call count on this workspace, from 1
     uint64_t timeout_ns;
     const __nv_bfloat16 *x_shard;     // AG: this rank's rows [M/p, K]
+    const __nv_bfloat16 *x_peer[kMaxRanks]; // AG, optional: rank q's x_shard as mapped here (registered symmetric memory): peers pull from it, nothing is staged
     __nv_bfloat16 *xfull[kMaxRanks];  // AG: gathered X [M,K] of rank q (symmetric); A's tensor map covers xfull[rank]
     __nv_bfloat16 *partial[kMaxRanks];// RS: receive area of rank q: p slots of [M/p, N]
     __nv_bfloat16 *out;               // RS: this rank's reduced rows [M/p, N]

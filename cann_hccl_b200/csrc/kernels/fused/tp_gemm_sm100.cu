@@ -41,6 +41,7 @@ namespace {
 
 constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16;
 constexpr int kStages = 4;
+constexpr int kMaxPanels = 60;
 constexpr int kThreads = 256;  // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue, warps 6-7 move data between GPUs (AG)
 constexpr uint32_t kABytes = BM * BK * 2, kBBytes = BN * BK * 2, kStageBytes = kABytes + kBBytes;
 constexpr uint32_t kTmemCols = 512;
@@ -58,6 +59,9 @@ struct SharedStorage {
     uint64_t comm_bar[kCommDepth];
     uint32_t tmem_base;
     uint32_t fail;
+    uint32_t gemm_done;      // RS: the epilogue has published this CTA's last tile
+    uint32_t early_go[2];    // RS: decision of the early reducer's leader for its next item (by item parity)
+    uint32_t early_count;    // RS: items this CTA's early reducer finished before the GEMM ended
 };
 
 // ---------------------------------------------------------------------------------------------- PTX wrappers
@@ -211,6 +215,16 @@ __device__ __forceinline__ void report(const TpGemmParams &P, uint32_t code, int
 __device__ __forceinline__ int panel_width(const TpGemmParams &P, int n_tiles)
 {
     long long w = (40ll << 20) / ((long long)BN * P.K * 2);
+    if (P.mode == TP_MODE_RS) {
+        // A panel's receive slots are summed while the next panel is computed, so only the last panel is left for the tail:
+        // narrower panels shorten that tail.  Every panel streams A once more, hence no more than about N / 1024 of them.
+        int target = P.N / 1024;
+        target = target < 1 ? 1 : (target > 8 ? 8 : target);
+        const long long wr = (n_tiles + target - 1) / target;
+        if (wr < w) w = wr;
+    }
+    const long long wmin = (n_tiles + kMaxPanels - 1) / kMaxPanels;  // the flag area holds kMaxPanels counters per row block
+    if (w < wmin) w = wmin;
     if (w < 1) w = 1;
     if (w > n_tiles) w = n_tiles;
     return (int)w;
@@ -219,7 +233,10 @@ __device__ __forceinline__ void tile_coords(const TpGemmParams &P, int t, int n_
 {
     // rows are handled shard by shard (one rank's row blocks at a time, all panels), so that the transfer of the next
     // shard has the whole compute time of the current one; without communication there is a single "shard"
-    const bool comm = P.mode == TP_MODE_AG && P.nranks > 1;  // RS pushes asynchronously and keeps the L2-friendliest order
+    // RS pushes asynchronously and keeps the L2-friendliest order.  AG goes shard by shard only when a shard holds at least
+    // two waves of tiles; smaller shards would cost a whole tile time each (a partial wave per shard), so they are walked in
+    // the global panel order and every row block simply waits for its own arrival flag.
+    const bool comm = P.mode == TP_MODE_AG && P.nranks > 1 && (m_tiles / P.nranks) * n_tiles >= 2 * P.n_gemm_ctas;
     const int per = comm ? m_tiles / P.nranks : m_tiles;  // m tiles per shard
     const int tiles_per_shard = per * n_tiles;
     const int sidx = t / tiles_per_shard, r1 = t - sidx * tiles_per_shard;
@@ -236,7 +253,8 @@ __device__ __forceinline__ void tile_coords(const TpGemmParams &P, int t, int n_
         return;
     }
     // AG: own shard first (read straight from the caller's buffer), then the ranks after me in fetch order
-    mt = ((sidx + P.rank) % P.nranks) * per + ml;
+    if (comm) mt = ((sidx + P.rank) % P.nranks) * per + ml;
+    else mt = (ml + P.rank * (m_tiles / P.nranks)) % m_tiles;
 }
 
 // ---------------------------------------------------------------------------------------------- comm CTAs
@@ -281,19 +299,29 @@ __device__ void comm_role_ag(const TpGemmParams &P, SharedStorage &S, int c, int
     volatile uint32_t *fail = &S.fail;
     if (threadIdx.x != 0) return;  // one thread drives the bulk copies
     uint32_t g = 0;
-    // the peers' pulls of the previous call from my slot must be over before I overwrite it
-    for (int q = 0; q < p; ++q)
-        if (q != me && !wait_word_ge(myflags + p + q, (P.epoch - 1) * (uint64_t)nc, true, deadline, fail)) { report(P, *fail, 100 + q); return; }
-    // stage my shard into my slot of the gathered buffer: m tiles [me*per, (me+1)*per), split over the comm CTAs
-    for (int j = c; j < per; j += nc) {
-        int mt = me * per + j;
-        if (!bulk_copy(S, (uint8_t *)P.xfull[me] + (uint64_t)mt * tile_bytes, (const uint8_t *)P.x_shard + (uint64_t)j * tile_bytes, tile_bytes, g, fail)) { report(P, *fail, 200); return; }
-        bulk_wait_all<0>();
-        fence_proxy_async();
-        st_release_gpu(myflags + 2 * p + mt, P.epoch);                // the GEMM may load it
-        __threadfence_system();
+    // zero-copy source: every rank's shard sits in registered symmetric memory, so the peers read it where it is
+    const bool zc = P.x_peer[(me + 1) % p] != nullptr;
+    if (zc) {
+        // stream order made my shard valid before this kernel began: tell the peers at once
+        if (c == 0) {
+            __threadfence_system();
+            for (int q = 0; q < p; ++q)
+                if (q != me) red_add_release_sys(P.flags[q] + me, (uint64_t)per);
+        }
+    } else {
+        // the peers' pulls of the previous call from my slot must be over before I overwrite it
         for (int q = 0; q < p; ++q)
-            if (q != me) red_add_release_sys(P.flags[q] + me, 1);     // and the peers may pull it
+            if (q != me && !wait_word_ge(myflags + p + q, (P.epoch - 1) * (uint64_t)nc, true, deadline, fail)) { report(P, *fail, 100 + q); return; }
+        // stage my shard into my slot of the gathered buffer: m tiles [me*per, (me+1)*per), split over the comm CTAs
+        for (int j = c; j < per; j += nc) {
+            int mt = me * per + j;
+            if (!bulk_copy(S, (uint8_t *)P.xfull[me] + (uint64_t)mt * tile_bytes, (const uint8_t *)P.x_shard + (uint64_t)j * tile_bytes, tile_bytes, g, fail)) { report(P, *fail, 200); return; }
+            bulk_wait_all<0>();
+            fence_proxy_async();
+            __threadfence_system();
+            for (int q = 0; q < p; ++q)
+                if (q != me) red_add_release_sys(P.flags[q] + me, 1);     // the peers may pull it
+        }
     }
     // pull the peers' shards in the order in which the GEMM consumes them
     for (int i = 1; i < p; ++i) {
@@ -301,16 +329,21 @@ __device__ void comm_role_ag(const TpGemmParams &P, SharedStorage &S, int c, int
         if (!wait_word_ge(myflags + q, P.epoch * (uint64_t)per, true, deadline, fail)) { report(P, *fail, 300 + q); return; }
         for (int j = c; j < per; j += nc) {
             int mt = q * per + j;
-            if (!bulk_copy(S, (uint8_t *)P.xfull[me] + (uint64_t)mt * tile_bytes, (const uint8_t *)P.xfull[q] + (uint64_t)mt * tile_bytes, tile_bytes, g, fail)) { report(P, *fail, 400 + q); return; }
+            const uint8_t *src = zc ? (const uint8_t *)P.x_peer[q] + (uint64_t)j * tile_bytes : (const uint8_t *)P.xfull[q] + (uint64_t)mt * tile_bytes;
+            if (!bulk_copy(S, (uint8_t *)P.xfull[me] + (uint64_t)mt * tile_bytes, src, tile_bytes, g, fail)) { report(P, *fail, 400 + q); return; }
             bulk_wait_all<0>();
             fence_proxy_async();
             st_release_gpu(myflags + 2 * p + mt, P.epoch);
         }
     }
-    // this CTA no longer reads any peer's slot
+    // this CTA no longer reads any peer's memory
     __threadfence_system();
     for (int q = 0; q < p; ++q)
         if (q != me) red_add_release_sys(P.flags[q] + p + me, 1);
+    // zero-copy: the caller may overwrite its shard once this kernel is over, so the peers' pulls have to be over by then
+    if (zc && c == 0)
+        for (int q = 0; q < p; ++q)
+            if (q != me && !wait_word_ge(myflags + p + q, P.epoch * (uint64_t)nc, true, deadline, fail)) { report(P, *fail, 700 + q); return; }
 }
 
 __device__ __forceinline__ uint64_t rs_done_index(const TpGemmParams &P, int per, int npanels) { return (uint64_t)P.nranks * per * npanels; }
@@ -318,8 +351,111 @@ __device__ __forceinline__ uint64_t rs_done_index(const TpGemmParams &P, int per
 // Flag words of a rank in RS mode (uint64):
 //   [(src * per + j) * panels + panel]  n tiles of panel `panel` of this rank's row block j delivered by src
 //   [p * per * panels + o]  CTAs of owner o that finished reducing (epoch * G when complete): o's slots may be rewritten
-// After its GEMM tiles every CTA turns into a reducer: item = (panel, my row block j, n tile) -> 128 x 256 outputs, summed
-// over the p receive slots in fp32 in rank order as soon as all sources have delivered that panel of block j.
+// Reduce item = (panel, my row block j, n tile) -> 128 x 256 outputs, summed over the p receive slots in fp32 in rank
+// order once all sources have delivered that panel of block j.  Items are ordered like the GEMM's production (panel major,
+// then row block, then n tile) and dealt round-robin to the CTAs.  While the GEMM runs, the CTA's two spare warps reduce
+// the items whose inputs are complete (everything but the last panel, as a rule); after its GEMM tiles the whole CTA
+// finishes the rest.
+struct RsItem { int panel, j, nt, w; };
+__device__ __forceinline__ RsItem rs_item(int item, int per, int n_tiles, int pw)
+{
+    RsItem it;
+    int rem = item;
+    it.panel = 0;
+    for (;; ++it.panel) {
+        int n0p = it.panel * pw, wp = (n_tiles - n0p < pw) ? n_tiles - n0p : pw;
+        if (rem < per * wp) break;
+        rem -= per * wp;
+    }
+    const int n0 = it.panel * pw;
+    it.w = (n_tiles - n0 < pw) ? n_tiles - n0 : pw;
+    it.j = rem / it.w;
+    it.nt = n0 + rem % it.w;
+    return it;
+}
+
+// Sums one item with `nthr` threads (lid = this thread's index among them).  Every thread sums four 16-byte vectors at a
+// time, two slots per round: eight loads are in flight before the first add whatever the rank count (one load at a time
+// would leave the reduction latency-bound).
+__device__ __forceinline__ void rs_reduce_item(const TpGemmParams &P, const RsItem &it, int lid, int nthr)
+{
+    const int p = P.nranks, me = P.rank;
+    const uint64_t slot_elems = (uint64_t)(P.M / p) * P.N;  // one source's partial rows for me
+    constexpr int vec_per_row = BN / 8, kVec = 4;
+    for (int v0 = lid; v0 < BM * vec_per_row; v0 += kVec * nthr) {
+        uint64_t eoff[kVec];
+        float acc[kVec][8];
+#pragma unroll
+        for (int i = 0; i < kVec; ++i) {
+            const int v = v0 + i * nthr;  // BM * vec_per_row is a multiple of kVec * nthr
+            eoff[i] = ((uint64_t)it.j * BM + v / vec_per_row) * P.N + (uint64_t)it.nt * BN + (uint64_t)(v % vec_per_row) * 8;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[i][k] = 0.f;
+        }
+        for (int q0 = 0; q0 < p; q0 += 2) {
+            uint4 x[kVec][2];
+            const bool two = q0 + 1 < p;
+#pragma unroll
+            for (int i = 0; i < kVec; ++i) {
+                x[i][0] = ld_stream((const uint4 *)(P.partial[me] + (uint64_t)q0 * slot_elems + eoff[i]));
+                x[i][1] = two ? ld_stream((const uint4 *)(P.partial[me] + (uint64_t)(q0 + 1) * slot_elems + eoff[i])) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int i = 0; i < kVec; ++i)
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const __nv_bfloat162 *h = (const __nv_bfloat162 *)&x[i][u];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        float2 f = __bfloat1622float2(h[k]);
+                        acc[i][2 * k] += f.x;
+                        acc[i][2 * k + 1] += f.y;
+                    }
+                }
+        }
+#pragma unroll
+        for (int i = 0; i < kVec; ++i) {
+            uint4 o;
+            o.x = pack_bf16(__float_as_uint(acc[i][0]), __float_as_uint(acc[i][1]));
+            o.y = pack_bf16(__float_as_uint(acc[i][2]), __float_as_uint(acc[i][3]));
+            o.z = pack_bf16(__float_as_uint(acc[i][4]), __float_as_uint(acc[i][5]));
+            o.w = pack_bf16(__float_as_uint(acc[i][6]), __float_as_uint(acc[i][7]));
+            *(uint4 *)(P.out + eoff[i]) = o;
+        }
+    }
+}
+
+// The two spare warps (64 threads) while the GEMM runs.  Their leader polls the p delivery counters of the next item; it
+// gives up as soon as the CTA's GEMM is over (the whole CTA is faster from there) or a failure is flagged.
+__device__ void reduce_early_rs(const TpGemmParams &P, SharedStorage &S, int pw, int npanels)
+{
+    const int p = P.nranks, me = P.rank;
+    const int m_tiles = P.M / BM, per = m_tiles / p, n_tiles = P.N / BN;
+    const uint64_t *myflags = P.flags[me];
+    const int lid = threadIdx.x - (kThreads - 64);
+    const int items = per * n_tiles;
+    uint32_t done = 0;
+    for (int item = blockIdx.x; item < items; item += gridDim.x, ++done) {
+        const RsItem it = rs_item(item, per, n_tiles, pw);
+        if (lid == 0) {
+            uint32_t go = 0;
+            for (;;) {
+                if (*(volatile uint32_t *)&S.gemm_done || *(volatile uint32_t *)&S.fail) break;
+                int q = 0;
+                for (; q < p; ++q)
+                    if (ld_acquire_sys(myflags + ((uint64_t)q * per + it.j) * npanels + it.panel) < P.epoch * (uint64_t)it.w) break;
+                if (q == p) { go = 1; break; }
+                __nanosleep(200);
+            }
+            *(volatile uint32_t *)&S.early_go[done & 1] = go;
+        }
+        asm volatile("bar.sync 2, 64;" ::: "memory");
+        if (!*(volatile uint32_t *)&S.early_go[done & 1]) break;
+        rs_reduce_item(P, it, lid, 64);
+    }
+    if (lid == 0) S.early_count = done;
+}
+
 __device__ void reduce_tail_rs(const TpGemmParams &P, SharedStorage &S, int pw, int npanels)
 {
     const int p = P.nranks, me = P.rank;
@@ -327,45 +463,14 @@ __device__ void reduce_tail_rs(const TpGemmParams &P, SharedStorage &S, int pw, 
     uint64_t *myflags = P.flags[me];
     const uint64_t deadline = global_timer_ns() + P.timeout_ns;
     volatile uint32_t *fail = &S.fail;
-    const uint64_t slot_elems = (uint64_t)(P.M / p) * P.N;  // one source's partial rows for me
     const int items = per * n_tiles;
-    for (int item = blockIdx.x; item < items; item += gridDim.x) {
-        // items are ordered like the GEMM's production: panel major, then row block, then n tile
-        int panel = 0, rem = item;
-        for (;; ++panel) {
-            int n0p = panel * pw, wp = (n_tiles - n0p < pw) ? n_tiles - n0p : pw;
-            if (rem < per * wp) break;
-            rem -= per * wp;
-        }
-        const int n0 = panel * pw, w = (n_tiles - n0 < pw) ? n_tiles - n0 : pw;
-        const int j = rem / w, nt = n0 + rem % w;
+    for (int item = blockIdx.x + (int)S.early_count * gridDim.x; item < items; item += gridDim.x) {
+        const RsItem it = rs_item(item, per, n_tiles, pw);
         if (threadIdx.x < p) {
-            if (!wait_word_ge(myflags + ((uint64_t)threadIdx.x * per + j) * npanels + panel, P.epoch * (uint64_t)w, true, deadline, fail)) report(P, *fail, 500 + threadIdx.x);
+            if (!wait_word_ge(myflags + ((uint64_t)threadIdx.x * per + it.j) * npanels + it.panel, P.epoch * (uint64_t)it.w, true, deadline, fail)) report(P, *fail, 500 + threadIdx.x);
         }
         if (__syncthreads_or((int)*fail)) return;
-        constexpr int vec_per_row = BN / 8;
-        for (int v = threadIdx.x; v < BM * vec_per_row; v += blockDim.x) {
-            const uint64_t eoff = ((uint64_t)j * BM + v / vec_per_row) * P.N + (uint64_t)nt * BN + (uint64_t)(v % vec_per_row) * 8;
-            float acc[8];
-#pragma unroll
-            for (int k = 0; k < 8; ++k) acc[k] = 0.f;
-            for (int q = 0; q < p; ++q) {
-                uint4 x = ld_stream((const uint4 *)(P.partial[me] + (uint64_t)q * slot_elems + eoff));
-                const __nv_bfloat162 *h = (const __nv_bfloat162 *)&x;
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    float2 f = __bfloat1622float2(h[k]);
-                    acc[2 * k] += f.x;
-                    acc[2 * k + 1] += f.y;
-                }
-            }
-            uint4 o;
-            o.x = pack_bf16(__float_as_uint(acc[0]), __float_as_uint(acc[1]));
-            o.y = pack_bf16(__float_as_uint(acc[2]), __float_as_uint(acc[3]));
-            o.z = pack_bf16(__float_as_uint(acc[4]), __float_as_uint(acc[5]));
-            o.w = pack_bf16(__float_as_uint(acc[6]), __float_as_uint(acc[7]));
-            *(uint4 *)(P.out + eoff) = o;
-        }
+        rs_reduce_item(P, it, threadIdx.x, blockDim.x);
         __syncthreads();
     }
     // this CTA is done reading my receive slots: sources may overwrite them in the next call once every CTA said so
@@ -389,6 +494,8 @@ __global__ void __launch_bounds__(kThreads, 1) tp_gemm_kernel(const __grid_const
 
     if (threadIdx.x == 0) {
         S.fail = 0;
+        S.gemm_done = 0;
+        S.early_count = 0;
         for (int i = 0; i < kStages; ++i) { mbar_init(&S.full_bar[i], 1); mbar_init(&S.empty_bar[i], 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(&S.tmem_full[i], 1); mbar_init(&S.tmem_empty[i], 128); }
         for (int i = 0; i < kCommDepth; ++i) mbar_init(&S.comm_bar[i], 1);
@@ -529,17 +636,24 @@ __global__ void __launch_bounds__(kThreads, 1) tp_gemm_kernel(const __grid_const
             mbar_arrive(&S.tmem_empty[buf]);  // 128 arrivals free the accumulator for the tile after next
             if (P.mode == TP_MODE_RS) {
                 // the four epilogue warps finished their rows: one of them publishes the tile to the owner
+                // (no fence per thread: 128 system-scope fences per tile cost more than the whole transfer; the completed
+                // bulk stores are ordered before the barrier, and the one release below publishes them)
                 bulk_wait_all<0>();  // this thread's row pieces are written
-                __threadfence_system();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (warp == 2 && lane == 0) {
-                    __threadfence_system();
                     red_add_release_sys(P.flags[owner] + ((uint64_t)P.rank * per + (mt - owner * per)) * npanels + panel, 1);
                 }
             }
         }
     }
-    if (warp >= 2 && warp < 6) bulk_wait_all<0>();  // every row piece of this thread has been written
+    else if (P.mode == TP_MODE_RS) {
+        // ------------------------------------------------------------------ spare warps: reduce what has already arrived
+        reduce_early_rs(P, S, pw, npanels);
+    }
+    if (warp >= 2 && warp < 6) {
+        bulk_wait_all<0>();  // every row piece of this thread has been written
+        if (P.mode == TP_MODE_RS && warp == 2 && lane == 0) *(volatile uint32_t *)&S.gemm_done = 1;
+    }
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {

@@ -229,6 +229,16 @@ def scenario_fused_tp(c, p, r, args):
     ref = torch.cat([x.float() for x in xs]) @ w.float().t()
     err = float((y.float() - ref).norm() / ref.norm())
     assert err < 1e-2, err
+    # the same with the shard in registered symmetric memory: peers pull it in place, and it may be rewritten after the call
+    handle, bufs = c.symmetric_empty(Ms * K, torch.bfloat16)
+    xz = bufs[0].view(Ms, K)
+    for _ in range(3):
+        xz.copy_(xs[r])
+        y = fused_tp.all_gather_matmul(c, xz, w)
+        xz.zero_()
+        ok(c)
+        err = float((y.float() - ref).norm() / ref.norm())
+        assert err < 1e-2, err
     M = Ms * p
     hs = [g(q, (M, K), 3) for q in range(p)]
     ws = [g(q, (N, K), 4, 0.05) for q in range(p)]
@@ -239,6 +249,41 @@ def scenario_fused_tp(c, p, r, args):
     err = float((o.float() - full[r * Ms:(r + 1) * Ms]).norm() / full.norm())
     assert err < 2e-2, err
     print("rank %d fused_tp ok" % r)
+
+
+def scenario_tp_shapes(c, p, r, args):
+    """Fused AG+GEMM / GEMM+RS against the plain tcgen05 GEMM of the same per-rank shape (device-timed)."""
+    from cann_hccl_b200.parallel import fused_tp
+    M, N, K = [int(a) for a in args[:3]]
+
+    def t(fn, iters=10):
+        for _ in range(3):
+            fn()
+        c.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / iters
+    xs = torch.randn(M // p, K, device="cuda").to(torch.bfloat16)
+    xf = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    w = torch.randn(N, K, device="cuda").to(torch.bfloat16)
+    y = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    o = torch.empty(M // p, N, device="cuda", dtype=torch.bfloat16)
+    t_plain = t(lambda: fused_tp.gemm(xf, w, out=y))
+    t_ag = t(lambda: fused_tp.all_gather_matmul(c, xs, w, out=y))
+    t_rs = t(lambda: fused_tp.matmul_reduce_scatter(c, xf, w, out=o))
+    handle, bufs = c.symmetric_empty(xs.numel(), torch.bfloat16)
+    xz = bufs[0].view_as(xs)
+    xz.copy_(xs)
+    t_agz = t(lambda: fused_tp.all_gather_matmul(c, xz, w, out=y))
+    torch.cuda.synchronize()
+    ok(c)
+    if r == 0:
+        print("TPSHAPE M%d N%d K%d p%d: plain %.3f ms, ag+gemm %.3f ms (registered shard %.3f ms), gemm+rs %.3f ms" % (M, N, K, p, t_plain, t_ag, t_agz, t_rs))
 
 
 def scenario_extras(c, p, r, args):

@@ -76,6 +76,36 @@ def test_all_gather_matmul(comms, p):
         assert rel_err(ys[r], xfull @ ws[r].float().t()) < 1e-2
 
 
+@pytest.mark.parametrize("p", [2, 4])
+def test_all_gather_matmul_registered_source(comms, p):
+    """Shards in registered symmetric memory are pulled by the peers where they lie (no staging copy); the caller may
+    rewrite its shard right after the call, and an unregistered call on the same workspace may follow."""
+    c = comms(p)
+    Ms, K, N = 256, 512, 512
+    g = torch.Generator(device="cuda").manual_seed(40 + p)
+    handle, bufs = c.symmetric_empty(Ms * K, torch.bfloat16)
+    xs = [b.view(Ms, K) for b in bufs]
+    ws = [(torch.randn(N, K, device="cuda", generator=g) * 0.05).to(torch.bfloat16) for _ in range(p)]
+    for it in range(3):
+        vals = [torch.randn(Ms, K, device="cuda", generator=g).to(torch.bfloat16) for _ in range(p)]
+        for x, v in zip(xs, vals):
+            x.copy_(v)
+        ys = fused_tp.all_gather_matmul(c, xs, ws)
+        for x in xs:
+            x.zero_()  # stream order: the kernel has let go of the shards by the time it ends
+        assert c.sync() == 0, c.describe_status()
+        xfull = torch.cat([v.float() for v in vals])
+        for r in range(p):
+            assert rel_err(ys[r], xfull @ ws[r].float().t()) < 1e-2
+    plain = [v.clone() for v in vals]
+    ys = fused_tp.all_gather_matmul(c, plain, ws)
+    assert c.sync() == 0, c.describe_status()
+    for r in range(p):
+        assert rel_err(ys[r], xfull @ ws[r].float().t()) < 1e-2
+    del xs, bufs
+    c.mem_free(handle)
+
+
 @pytest.mark.parametrize("p", [1, 2, 4])
 def test_matmul_reduce_scatter(comms, p):
     c = comms(p)
