@@ -418,12 +418,11 @@ __global__ void __launch_bounds__(kExecThreads, 1) exec_plan_kernel(const RankCt
         }
         // ---- signal
         if (s.sig_rank != RANK_NONE) {
-            __syncthreads();  // every thread's stores of this step precede the fence of the signalling threads
+            __syncthreads();  // every thread's stores of this step precede the release (a system-scope fence in itself) of the signalling threads
             const uint64_t val = flag_value(a, s, s.sig_val);
             if (s.sig_rank == RANK_ALL) {
-                if (tid < p && (tid != me || (s.flags & SF_INCLUDE_SELF))) { fence_sys(); st_release_sys(c.flags[tid] + flag_index(s.sig_bank, me, chan), val); }
+                if (tid < p && (tid != me || (s.flags & SF_INCLUDE_SELF))) { st_release_sys(c.flags[tid] + flag_index(s.sig_bank, me, chan), val); }
             } else if (tid == 0 && s.sig_rank != me) {
-                fence_sys();
                 st_release_sys(c.flags[s.sig_rank] + flag_index(s.sig_bank, me, chan), val);
             }
         }
@@ -442,7 +441,7 @@ __global__ void __launch_bounds__(kExecThreads, 1) exec_plan_kernel(const RankCt
         }
         __syncthreads();
         if (s_last && !s_fail) {
-            if (tid < p && tid != me) { fence_sys(); st_release_sys(c.flags[tid] + done_index(me), a.seq); }
+            if (tid < p && tid != me) { st_release_sys(c.flags[tid] + done_index(me), a.seq); }
             if (tid == 0) *c.dev_tail = a.seq;  // read by the heartbeat thread with an asynchronous copy
         }
     }
