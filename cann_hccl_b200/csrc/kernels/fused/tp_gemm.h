@@ -28,9 +28,9 @@ struct alignas(64) TpGemmParams {
 struct TpGemmParamsArray {
     TpGemmParams r[kTpMaxLocal];
 };
-// Flag words a rank needs for AG ( ready[p], done[p], chunk_ready[M/128] ) and RS ( count[M/128 row blocks x panels], done[p] );
-// up to 64 panels.
-inline size_t tp_flag_words(int M, int nranks) { return (size_t)4 * nranks + (size_t)(M / 128) * 64 + 64; }
+// Flag words a rank needs for AG ( 2 x [p], chunk_ready[M/128], ready[p x 32 data-movement CTAs] ) and RS ( count[M/128 row
+// blocks x panels], done[p] ); up to 64 panels.
+inline size_t tp_flag_words(int M, int nranks) { return (size_t)4 * nranks + (size_t)(M / 128) * 64 + 64 + (size_t)nranks * 32; }
 // Fills the tensor maps and launches.  `A` / `B` per local rank.  n_comm_ctas data-movement CTAs per rank.
 HcclResult launch_tp_gemm(TpGemmParams *P, const void *const *A, const void *const *B, int nlocal, int n_comm_ctas, void *stream);
 size_t tp_gemm_smem_bytes();

@@ -42,6 +42,7 @@ namespace {
 constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16;
 constexpr int kStages = 4;
 constexpr int kMaxPanels = 60;
+constexpr int kMaxCommCtas = 32;  // data-movement CTAs per rank (AG), bound of the per-CTA ready words
 constexpr int kThreads = 256;  // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue, warps 6-7 move data between GPUs (AG)
 constexpr uint32_t kABytes = BM * BK * 2, kBBytes = BN * BK * 2, kStageBytes = kABytes + kBBytes;
 constexpr uint32_t kTmemCols = 512;
@@ -285,9 +286,12 @@ __device__ bool bulk_copy(SharedStorage &S, uint8_t *dst, const uint8_t *src, ui
 }
 
 // Flag words of a rank in AG mode (uint64):
-//   [src]          ready: m tiles of src's shard staged in src's own slot, counted by src (epoch * per when complete)
+//   [src]          (unused)
 //   [p + src]      done : comm CTAs of src that finished pulling from this rank (epoch * nc when complete)
 //   [2p + m tile]  local: epoch once the rows of that m tile are in this rank's gathered X
+//   [2p + m_tiles + src * kMaxCommCtas + c]  ready: m tiles of src's shard that src's comm CTA c has made available, counted
+//                  over all calls.  Comm CTA c of every rank handles the tiles c, c + nc, ... of each shard, so the puller of
+//                  a tile and its provider talk through one word and a pull starts as soon as that one tile is there.
 __device__ void comm_role_ag(const TpGemmParams &P, SharedStorage &S, int c, int nc)
 {
     const int p = P.nranks, me = P.rank;
@@ -298,15 +302,15 @@ __device__ void comm_role_ag(const TpGemmParams &P, SharedStorage &S, int c, int
     volatile uint32_t *fail = &S.fail;
     if (threadIdx.x != 0) return;  // one thread drives the bulk copies
     uint32_t g = 0;
+    const uint64_t mine_per_call = c < per ? (uint64_t)(per - c + nc - 1) / nc : 0;  // tiles of a shard that comm CTA c handles
+    const uint64_t ready_base = 2 * (uint64_t)p + m_tiles + c;
     // zero-copy source: every rank's shard sits in registered symmetric memory, so the peers read it where it is
     const bool zc = P.x_peer[(me + 1) % p] != nullptr;
     if (zc) {
         // stream order made my shard valid before this kernel began: tell the peers at once
-        if (c == 0) {
-            __threadfence_system();
+        if (mine_per_call)
             for (int q = 0; q < p; ++q)
-                if (q != me) red_add_release_sys(P.flags[q] + me, (uint64_t)per);
-        }
+                if (q != me) red_add_release_sys(P.flags[q] + ready_base + (uint64_t)me * kMaxCommCtas, mine_per_call);
     } else {
         // the peers' pulls of the previous call from my slot must be over before I overwrite it
         for (int q = 0; q < p; ++q)
@@ -317,17 +321,17 @@ __device__ void comm_role_ag(const TpGemmParams &P, SharedStorage &S, int c, int
             if (!bulk_copy(S, (uint8_t *)P.xfull[me] + (uint64_t)mt * tile_bytes, (const uint8_t *)P.x_shard + (uint64_t)j * tile_bytes, tile_bytes, g, fail)) { report(P, *fail, 200); return; }
             bulk_wait_all<0>();
             fence_proxy_async();
-            __threadfence_system();
             for (int q = 0; q < p; ++q)
-                if (q != me) red_add_release_sys(P.flags[q] + me, 1);     // the peers may pull it
+                if (q != me) red_add_release_sys(P.flags[q] + ready_base + (uint64_t)me * kMaxCommCtas, 1);  // the peers may pull it
         }
     }
     // pull the peers' shards in the order in which the GEMM consumes them
     for (int i = 1; i < p; ++i) {
         int q = (me + i) % p;
-        if (!wait_word_ge(myflags + q, P.epoch * (uint64_t)per, true, deadline, fail)) { report(P, *fail, 300 + q); return; }
-        for (int j = c; j < per; j += nc) {
+        uint64_t k = 0;
+        for (int j = c; j < per; j += nc, ++k) {
             int mt = q * per + j;
+            if (!wait_word_ge(myflags + ready_base + (uint64_t)q * kMaxCommCtas, (P.epoch - 1) * mine_per_call + k + 1, true, deadline, fail)) { report(P, *fail, 300 + q); return; }
             const uint8_t *src = zc ? (const uint8_t *)P.x_peer[q] + (uint64_t)j * tile_bytes : (const uint8_t *)P.xfull[q] + (uint64_t)mt * tile_bytes;
             if (!bulk_copy(S, (uint8_t *)P.xfull[me] + (uint64_t)mt * tile_bytes, src, tile_bytes, g, fail)) { report(P, *fail, 400 + q); return; }
             bulk_wait_all<0>();
@@ -336,7 +340,6 @@ __device__ void comm_role_ag(const TpGemmParams &P, SharedStorage &S, int c, int
         }
     }
     // this CTA no longer reads any peer's memory
-    __threadfence_system();
     for (int q = 0; q < p; ++q)
         if (q != me) red_add_release_sys(P.flags[q] + p + me, 1);
     // zero-copy: the caller may overwrite its shard once this kernel is over, so the peers' pulls have to be over by then
@@ -704,6 +707,7 @@ HcclResult launch_tp_gemm(TpGemmParams *P, const void *const *A, const void *con
     else if (n_comm_ctas < 1) n_comm_ctas = 1;
     int per_rank = sms / nlocal;  // all CTAs of all local ranks must be resident together
     if (n_comm_ctas > per_rank / 4) n_comm_ctas = std::max(1, per_rank / 4);
+    if (n_comm_ctas > kMaxCommCtas) n_comm_ctas = kMaxCommCtas;
     // with communication every rank must run the same grid (completion counters count CTAs)
     int total = (P0.M / BM) * (P0.N / BN);
     int n_gemm = P0.mode == TP_MODE_PLAIN ? std::min(total, per_rank) : per_rank - n_comm_ctas;
