@@ -33,6 +33,14 @@ class RootInfo(C.Structure):
     _fields_ = [("internal", C.c_char * HCCL_ROOT_INFO_BYTES)]
 
 
+class TopoDescs(C.Structure):
+    _fields_ = [("algSets", C.c_uint64), ("rankSize", C.c_uint32)]
+
+
+ALG_MESH, ALG_RING, ALG_SWITCH = 1, 2, 4
+TOPO_L0, TOPO_L1, TOPO_MAX = 0, 1, 2
+
+
 class CommConfig(C.Structure):
     _fields_ = [("reserved", C.c_char * 24), ("hcclBufferSize", C.c_uint32), ("hcclDeterministic", C.c_uint32),
                 ("hcclCommName", C.c_char * 128), ("hcclUdi", C.c_char * 128), ("hcclOpExpansionMode", C.c_uint32),
@@ -169,6 +177,26 @@ def lib():
         "HcclB200Exchange": [vp, C.c_char_p, vp, C.c_size_t, vp],
         "HcclB200GetDeviceContext": [vp, P(vp), P(u64)],
         "HcclB200ReloadEnv": [],
+        "HcclB200Put": [vp, u32, i32, u32, C.c_size_t, vp, C.c_size_t, vp],
+        "HcclB200Get": [vp, u32, i32, u32, C.c_size_t, vp, C.c_size_t, vp],
+        "HcclB200GetTopoJson": [vp, C.c_char_p, C.c_size_t],
+        "HcclB200GetOverflowCount": [vp, P(u64)],
+        "HcclGetTopoDesc": [vp, P(TopoDescs), u32],
+        "HcomInitByFile": [C.c_char_p, C.c_char_p],
+        "HcomInitByComm": [vp],
+        "HcomDestroy": [],
+        "HcomCreateGroup": [C.c_char_p, u32, P(u32)],
+        "HcomDestroyGroup": [C.c_char_p],
+        "HcomGetRankSize": [C.c_char_p, P(u32)],
+        "HcomGetRankId": [C.c_char_p, P(u32)],
+        "HcomGetWorldRankFromGroupRank": [C.c_char_p, u32, P(u32)],
+        "HcomGetGroupRankFromWorldRank": [u32, C.c_char_p, P(u32)],
+        "HcomGetCommHandleByGroup": [C.c_char_p, P(vp)],
+        "HcomGetTopoDesc": [C.c_char_p, P(TopoDescs), u32],
+        "HcomSetGradFusionByIndex": [C.c_char_p, u32, P(u32)],
+        "HcomSetGradFusionBySize": [C.c_char_p, u32, P(C.c_float)],
+        "HcomGetGradFusionByIndex": [C.c_char_p, P(u32), P(u32)],
+        "HcomGetGradFusionBySize": [C.c_char_p, P(u32), P(C.c_float)],
     }
     for name, args in sigs.items():
         fn = getattr(L, name)

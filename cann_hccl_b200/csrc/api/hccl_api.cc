@@ -831,6 +831,48 @@ HcclResult HcclB200MemQuery(HcclComm comm, int32_t handle, void **peerPtrs, void
     CHK_RET_LOG(!peerPtrs, HCCL_E_PTR, "[EI0003] HcclB200MemQuery: peerPtrs is null");
     return c->sym_query(handle, peerPtrs, mcPtrs, bytes);
 }
+HcclResult HcclB200Put(HcclComm comm, uint32_t localRank, int32_t handle, uint32_t peer, size_t offset, const void *src, size_t bytes,
+                       aclrtStream stream)
+{
+    GET_COMM("HcclB200Put");
+    CHK_RET_LOG(!src && bytes, HCCL_E_PTR, "[EI0003] HcclB200Put: src is null");
+    return c->sym_put((int)localRank, handle, (int)peer, offset, src, bytes, stream);
+}
+HcclResult HcclB200Get(HcclComm comm, uint32_t localRank, int32_t handle, uint32_t peer, size_t offset, void *dst, size_t bytes,
+                       aclrtStream stream)
+{
+    GET_COMM("HcclB200Get");
+    CHK_RET_LOG(!dst && bytes, HCCL_E_PTR, "[EI0003] HcclB200Get: dst is null");
+    return c->sym_get((int)localRank, handle, (int)peer, offset, dst, bytes, stream);
+}
+HcclResult HcclB200GetTopoJson(HcclComm comm, char *json, size_t cap)
+{
+    GET_COMM("HcclB200GetTopoJson");
+    CHK_RET_LOG(!json || cap == 0, HCCL_E_PTR, "[EI0003] HcclB200GetTopoJson: json is null");
+    std::string s = c->topo_json();
+    CHK_RET_LOG(s.size() + 1 > cap, HCCL_E_MEMORY, "HcclB200GetTopoJson: %zu bytes needed, %zu given", s.size() + 1, cap);
+    memcpy(json, s.c_str(), s.size() + 1);
+    return HCCL_SUCCESS;
+}
+HcclResult HcclB200GetOverflowCount(HcclComm comm, uint64_t *count)
+{
+    GET_COMM("HcclB200GetOverflowCount");
+    CHK_RET_LOG(!count, HCCL_E_PTR, "[EI0003] HcclB200GetOverflowCount: count is null");
+    *count = c->overflow_count();
+    return HCCL_SUCCESS;
+}
+HcclResult HcclGetTopoDesc(HcclComm comm, HcclTopoDescs *topoDescs, uint32_t topoSize)
+{
+    // reference: op_base.cc:3523 and hccl_communicator.cc:7236-7257 (L0 = the server's link type and rank count, L1 empty)
+    GET_COMM("HcclGetTopoDesc");
+    CHK_RET_LOG(!topoDescs, HCCL_E_PTR, "[EI0003] HcclGetTopoDesc: topoDescs is null");
+    CHK_RET_LOG(topoSize < (uint32_t)HCCL_TOPO_MAX, HCCL_E_PARA, "HcclGetTopoDesc: topoSize %u is below %d", topoSize, (int)HCCL_TOPO_MAX);
+    topoDescs[HCCL_TOPO_L0].algSets = HCCL_ALG_MESH | HCCL_ALG_RING | (c->has_nvls() ? HCCL_ALG_SWITCH : 0u);
+    topoDescs[HCCL_TOPO_L0].rankSize = (uint32_t)c->nranks();
+    topoDescs[HCCL_TOPO_L1].algSets = 0;
+    topoDescs[HCCL_TOPO_L1].rankSize = 0;
+    return HCCL_SUCCESS;
+}
 HcclResult HcclB200Exchange(HcclComm comm, const char *tag, const void *mine, size_t len, void *all)
 {
     GET_COMM("HcclB200Exchange");

@@ -16,6 +16,9 @@
 #include "health/consistency.h"
 #include "health/fault_inject.h"
 #include "kernels/ar_ll.h"
+#include "kernels/overflow.h"
+#include <nvtx3/nvToolsExt.h>
+#include <fstream>
 #include "p2p/p2p_backend.h"
 #include "transport/host_exec.h"
 
@@ -102,6 +105,7 @@ HcclResult Communicator::create(uint32_t nranks, const RootHandle &root, uint32_
         CHK_RET_LOG(e.rank != r, HCCL_E_PARA, "rank table entry %u carries rank %u", r, e.rank);
         CHK_RET_LOG(e.transport != me.transport, HCCL_E_PARA, "rank %u uses a different transport", r);
         CHK_RET_LOG(strcmp(e.host, me.host) != 0, HCCL_E_NOT_SUPPORT, "rank %u is on host %s: one NVSwitch domain per communicator", r, e.host);
+        c->topo_.push_back(TopoEntry{(int)r, e.pid, (int)e.device, std::string(e.host)});
     }
     if (st.transport == TR_HOST) c->alloc_.reset(make_host_shm_allocator(c->hub_.get(), c->ident_, (int)rank, (int)nranks, tmo));
     else {
@@ -271,7 +275,11 @@ Communicator::~Communicator()
         if (dev_exit_) cudaFree(dev_exit_);
         if (dev_trace_) cudaFree(dev_trace_);
         if (pinned_) cudaFreeHost(pinned_);
-    } else free(pinned_);
+        if (overflow_word_) cudaFreeHost(overflow_word_);
+    } else {
+        free(pinned_);
+        free(overflow_word_);
+    }
     alloc_.reset();
     if (hb_conn_) hb_conn_->bye();
     if (p2p_conn_) p2p_conn_->bye();
@@ -287,6 +295,11 @@ HcclResult Communicator::destroy()
         // leave together so that no rank unmaps memory a peer's kernel may still touch; bounded wait
         if (settings_.transport == TR_DEVICE) { cudaSetDevice(settings_.device); cudaDeviceSynchronize(); }
         hub_->barrier(key_prefix_ + "/destroy", nranks_, rank(), 10000);
+    }
+    if (!env_config().stats_dump.empty()) {
+        // one JSON object per line and communicator; ranks of a job append to the same file
+        std::ofstream f(env_config().stats_dump, std::ios::app);
+        if (f) f << stats_json() << "\n";
     }
     delete this;
     return HCCL_SUCCESS;
@@ -482,11 +495,15 @@ HcclResult Communicator::collective(const OpRequest &rq)
     bool peer_failed = ready != HCCL_SUCCESS && remote_error_.load() == (uint32_t)ready && env_config().retry_enable;
     if (ready != HCCL_SUCCESS && !peer_failed) return ready;
     StateGuard guard(state_, CS_INUSE);
+    const bool nvtx = env_config().nvtx;
+    if (nvtx) nvtxRangePushA(coll_name(rq.coll));
     HcclResult rc = peer_failed ? ready : run_collective_once(rq);
     if (rc != HCCL_SUCCESS && (rc == HCCL_E_TIMEOUT || rc == HCCL_E_REMOTE)) {
         stats_.timeouts++;
         rc = maybe_retry(rq, rc);
     }
+    if (rc == HCCL_SUCCESS && env_config().overflow_check) rc = overflow_scan(rq);
+    if (nvtx) nvtxRangePop();
     if (env_config().entry_log)
         HLOG_RUN("%s count=%llu dtype=%d op=%d root=%d -> %d, took %.1f us", coll_name(rq.coll), (unsigned long long)rq.count,
                  rq.dtype, rq.redop, rq.root, (int)rc, now_us() - t0);
@@ -1132,6 +1149,143 @@ HcclResult Communicator::maybe_retry(const OpRequest &rq, HcclResult failure)
         rc = run_collective_once(rq);
     }
     return rc;
+}
+
+// ------------------------------------------------------------------------------------------------ overflow check, topology
+static bool float_dtype(int dt)
+{
+    return dt == HCCL_DATA_TYPE_FP32 || dt == HCCL_DATA_TYPE_FP64 || dt == HCCL_DATA_TYPE_FP16 || dt == HCCL_DATA_TYPE_BFP16;
+}
+
+HcclResult Communicator::overflow_scan(const OpRequest &rq)
+{
+    const bool reduces = rq.coll == COLL_ALLREDUCE || rq.coll == COLL_REDUCE || rq.coll == COLL_REDUCE_SCATTER || rq.coll == COLL_REDUCE_SCATTER_V;
+    if (!reduces || !float_dtype(rq.dtype)) return HCCL_SUCCESS;
+    const bool dev = settings_.transport == TR_DEVICE;
+    if (!overflow_word_) {
+        if (dev) {
+            CHK_RET_LOG(cudaHostAlloc((void **)&overflow_word_, 64, cudaHostAllocMapped) != cudaSuccess, HCCL_E_MEMORY, "cudaHostAlloc(overflow word) failed");
+        } else {
+            overflow_word_ = (unsigned long long *)malloc(64);
+            CHK_RET_LOG(!overflow_word_, HCCL_E_MEMORY, "malloc failed");
+        }
+        *overflow_word_ = 0;
+    }
+    for (int li = 0; li < nlocal(); ++li) {
+        const int r = local_ranks_[li];
+        uint64_t n = rq.count;  // AllReduce: count; ReduceScatter: recvCount
+        if (rq.coll == COLL_REDUCE && r != rq.root) continue;  // only the root holds a result
+        if (rq.coll == COLL_REDUCE_SCATTER_V) n = rq.counts[r];
+        if (dev) {
+            unsigned long long *dptr = nullptr;
+            CHK_RET_LOG(cudaHostGetDevicePointer((void **)&dptr, overflow_word_, 0) != cudaSuccess, HCCL_E_RUNTIME, "cudaHostGetDevicePointer failed");
+            CHK_RET(launch_overflow_scan(rq.out[li], n, rq.dtype, dptr, rq.stream));
+        } else {
+            unsigned long long bad = 0;
+            for (uint64_t i = 0; i < n; ++i) {
+                double v = 0;
+                switch (rq.dtype) {
+                    case HCCL_DATA_TYPE_FP32: v = ((const float *)rq.out[li])[i]; break;
+                    case HCCL_DATA_TYPE_FP64: v = ((const double *)rq.out[li])[i]; break;
+                    case HCCL_DATA_TYPE_FP16: v = fp16_to_float(((const uint16_t *)rq.out[li])[i]); break;
+                    default: v = bf16_to_float(((const uint16_t *)rq.out[li])[i]); break;
+                }
+                bad += std::isfinite(v) ? 0 : 1;
+            }
+            __atomic_fetch_add(overflow_word_, bad, __ATOMIC_RELAXED);
+        }
+    }
+    return HCCL_SUCCESS;
+}
+
+uint64_t Communicator::overflow_count()
+{
+    if (!overflow_word_) return 0;
+    return __atomic_load_n(overflow_word_, __ATOMIC_RELAXED);
+}
+
+std::string Communicator::topo_json()
+{
+    std::ostringstream o;
+    const bool dev = settings_.transport == TR_DEVICE;
+    o << "{\"identifier\":\"" << ident_ << "\",\"ranks\":" << nranks_ << ",\"transport\":\"" << (dev ? "device" : "host") << "\""
+      << ",\"fabric\":\"" << (dev ? (nranks_ > 1 ? "nvlink-nvswitch" : "local") : "shared-memory") << "\",\"nvls\":" << (nvls_ ? "true" : "false")
+      << ",\"levels\":[{\"level\":0,\"ranks\":" << nranks_ << ",\"algorithms\":[\"mesh\",\"ring\"" << (nvls_ ? ",\"switch\"" : "") << "]},{\"level\":1,\"ranks\":0,\"algorithms\":[]}]"
+      << ",\"all_local\":" << (all_local_ ? "true" : "false") << ",\"rank_table\":[";
+    char host[64] = {0};
+    gethostname(host, sizeof(host) - 1);
+    for (int r = 0; r < nranks_; ++r) {
+        TopoEntry e{r, (uint32_t)getpid(), settings_.device, host};
+        if (r < (int)topo_.size()) e = topo_[r];
+        o << (r ? "," : "") << "{\"rank\":" << e.rank << ",\"host\":\"" << e.host << "\",\"pid\":" << e.pid << ",\"device\":" << (dev ? e.device : -1) << "}";
+    }
+    o << "]";
+    if (dev) {
+        // peer-access matrix over the devices that appear in the rank table (1 = this pair can map each other's memory)
+        std::vector<int> devs;
+        for (int r = 0; r < nranks_; ++r) {
+            int d = r < (int)topo_.size() ? topo_[r].device : settings_.device;
+            if (std::find(devs.begin(), devs.end(), d) == devs.end()) devs.push_back(d);
+        }
+        int ndev = 0;
+        cudaGetDeviceCount(&ndev);
+        o << ",\"devices\":[";
+        for (size_t i = 0; i < devs.size(); ++i) o << (i ? "," : "") << devs[i];
+        o << "],\"peer_access\":[";
+        for (size_t i = 0; i < devs.size(); ++i) {
+            o << (i ? "," : "") << "[";
+            for (size_t j = 0; j < devs.size(); ++j) {
+                int can = devs[i] == devs[j] ? 1 : 0;
+                if (!can && devs[i] < ndev && devs[j] < ndev) cudaDeviceCanAccessPeer(&can, devs[i], devs[j]);
+                o << (j ? "," : "") << can;
+            }
+            o << "]";
+        }
+        o << "]";
+    }
+    o << "}";
+    return o.str();
+}
+
+// ------------------------------------------------------------------------------------------------ one-sided put / get
+HcclResult Communicator::sym_put(int local, int handle, int peer, size_t offset, const void *src, size_t bytes, void *stream)
+{
+    std::lock_guard<std::mutex> lk(op_mu_);
+    CHK_RET(check_ready());
+    auto it = user_segs_.find(handle);
+    CHK_RET_LOG(it == user_segs_.end(), HCCL_E_NOT_FOUND, "put: unknown symmetric allocation %d", handle);
+    CHK_RET_LOG(local < 0 || local >= nlocal() || peer < 0 || peer >= nranks_, HCCL_E_PARA, "put: bad rank (local %d, peer %d)", local, peer);
+    const SymSegment &sg = it->second[local];
+    CHK_RET_LOG(offset > sg.bytes || bytes > sg.bytes - offset, HCCL_E_PARA, "put: [%zu, %zu) outside the allocation of %zu bytes", offset, offset + bytes, sg.bytes);
+    if (bytes == 0) return HCCL_SUCCESS;
+    StateGuard guard(state_, CS_INUSE);
+    if (settings_.transport == TR_DEVICE) {
+        CHK_RET_LOG(cudaMemcpyAsync(sg.peer[peer] + offset, src, bytes, cudaMemcpyDefault, (cudaStream_t)stream) != cudaSuccess, HCCL_E_RUNTIME, "put: cudaMemcpyAsync failed");
+    } else {
+        memcpy(sg.peer[peer] + offset, src, bytes);
+        __atomic_thread_fence(__ATOMIC_SEQ_CST);
+    }
+    return HCCL_SUCCESS;
+}
+
+HcclResult Communicator::sym_get(int local, int handle, int peer, size_t offset, void *dst, size_t bytes, void *stream)
+{
+    std::lock_guard<std::mutex> lk(op_mu_);
+    CHK_RET(check_ready());
+    auto it = user_segs_.find(handle);
+    CHK_RET_LOG(it == user_segs_.end(), HCCL_E_NOT_FOUND, "get: unknown symmetric allocation %d", handle);
+    CHK_RET_LOG(local < 0 || local >= nlocal() || peer < 0 || peer >= nranks_, HCCL_E_PARA, "get: bad rank (local %d, peer %d)", local, peer);
+    const SymSegment &sg = it->second[local];
+    CHK_RET_LOG(offset > sg.bytes || bytes > sg.bytes - offset, HCCL_E_PARA, "get: [%zu, %zu) outside the allocation of %zu bytes", offset, offset + bytes, sg.bytes);
+    if (bytes == 0) return HCCL_SUCCESS;
+    StateGuard guard(state_, CS_INUSE);
+    if (settings_.transport == TR_DEVICE) {
+        CHK_RET_LOG(cudaMemcpyAsync(dst, sg.peer[peer] + offset, bytes, cudaMemcpyDefault, (cudaStream_t)stream) != cudaSuccess, HCCL_E_RUNTIME, "get: cudaMemcpyAsync failed");
+    } else {
+        __atomic_thread_fence(__ATOMIC_SEQ_CST);
+        memcpy(dst, sg.peer[peer] + offset, bytes);
+    }
+    return HCCL_SUCCESS;
 }
 
 // ------------------------------------------------------------------------------------------------ symmetric user memory

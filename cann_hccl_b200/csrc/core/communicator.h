@@ -126,6 +126,15 @@ public:
     // Peer pointer table of a symmetric allocation: ptrs[local][rank]; mc[local]
     HcclResult sym_query(int handle, void **peer_ptrs, void **mc_ptrs, size_t *bytes);
 
+    // One-sided copy between a local buffer and rank `peer`'s copy of a symmetric allocation (stream-ordered on the device
+    // transport, immediate on the host transport).  Only the caller takes part.
+    HcclResult sym_put(int local, int handle, int peer, size_t offset, const void *src, size_t bytes, void *stream);
+    HcclResult sym_get(int local, int handle, int peer, size_t offset, void *dst, size_t bytes, void *stream);
+    // Ranks (host, pid, device), transport, NVLS and the peer-access matrix of the local devices, as JSON.
+    std::string topo_json();
+    // Outputs of floating-point reductions that were Inf or NaN (counted only with HCCL_OVERFLOW_CHECK=1).
+    uint64_t overflow_count();
+
     // Fused tensor-parallel operators (kernels/fused/tp_gemm_sm100.cu).  Pointers per local rank; bf16; weights [N, K].
     //   all_gather_matmul:     y[M,N]     = all_gather(x_shard[M/p,K]) * w[N,K]^T
     //   matmul_reduce_scatter: out[M/p,N] = reduce_scatter_rows(h[M,K] * w[N,K]^T)
@@ -170,6 +179,7 @@ private:
     HcclResult maybe_retry(const OpRequest &rq, HcclResult failure);
     void heartbeat_loop();
     void record_trace(const OpRequest &rq, int algo, int nchan, uint64_t bytes, double us);
+    HcclResult overflow_scan(const OpRequest &rq);
     HcclResult p2p_plan_exec(bool is_send, int peer, const void *sbuf, void *rbuf, uint64_t count, int dtype, void *stream);
 
     CommSettings settings_;
@@ -235,6 +245,9 @@ private:
     uint64_t op_index_ = 0;                  // API-level op counter (one per collective call)
     std::function<void(uint64_t)> fault_hook_;
     std::unique_ptr<P2pBackend> p2p_;
+    struct TopoEntry { int rank; uint32_t pid; int device; std::string host; };
+    std::vector<TopoEntry> topo_;            // one entry per rank (filled at creation)
+    unsigned long long *overflow_word_ = nullptr;  // host-mapped (device transport) or heap counter of non-finite outputs
     friend class P2pBackend;
 };
 

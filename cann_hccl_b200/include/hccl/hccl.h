@@ -126,6 +126,10 @@ extern HcclResult HcclCommActivateCommMemory(HcclComm comm, void *virPtr, size_t
                                              aclrtDrvMemHandle handle, uint64_t flags);
 extern HcclResult HcclCommDeactivateCommMemory(HcclComm comm, void *virPtr);
 
+/* ---- topology ----------------------------------------------------------- */
+/* topoSize = entries in topoDescs, at least HCCL_TOPO_MAX. */
+extern HcclResult HcclGetTopoDesc(HcclComm comm, HcclTopoDescs *topoDescs, uint32_t topoSize);
+
 #ifdef __cplusplus
 }
 #endif

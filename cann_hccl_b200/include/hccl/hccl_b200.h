@@ -113,6 +113,19 @@ extern HcclResult HcclB200MemAlloc(HcclComm comm, size_t bytes, void **localPtrs
 extern HcclResult HcclB200MemFree(HcclComm comm, int32_t handle);
 /* peerPtrs[local * nRanks + q] = rank q's copy as mapped for the local rank; mcPtrs[local] = multicast mapping or NULL. */
 extern HcclResult HcclB200MemQuery(HcclComm comm, int32_t handle, void **peerPtrs, void **mcPtrs, size_t *bytes);
+/* One-sided transfers on symmetric memory (role of the reference's one_sided_service interface,
+ * communicator/impl/one_sided_service/): stream-ordered copy between a local buffer and `bytes` at `offset` inside rank
+ * `peer`'s copy of allocation `handle`.  Only the calling rank takes part; pair with HcclBarrier (or any collective) to
+ * order against the peer's own accesses.  `localRank` selects the virtual rank on an all-local communicator, else 0. */
+extern HcclResult HcclB200Put(HcclComm comm, uint32_t localRank, int32_t handle, uint32_t peer, size_t offset, const void *src,
+                              size_t bytes, aclrtStream stream);
+extern HcclResult HcclB200Get(HcclComm comm, uint32_t localRank, int32_t handle, uint32_t peer, size_t offset, void *dst,
+                              size_t bytes, aclrtStream stream);
+/* Topology of the communicator as JSON: ranks (host, pid, device), transport, NVLS, peer-access matrix of local devices. */
+extern HcclResult HcclB200GetTopoJson(HcclComm comm, char *json, size_t cap);
+/* Overflow check (role of the reference's TaskOverflow hookup): with HCCL_OVERFLOW_CHECK=1 every floating-point reduction
+ * is followed by a scan of its output; *count = outputs that were Inf or NaN since the communicator was made. */
+extern HcclResult HcclB200GetOverflowCount(HcclComm comm, uint64_t *count);
 /* All-gather `len` bytes per rank over the bootstrap hub (control plane; not for bulk data). */
 extern HcclResult HcclB200Exchange(HcclComm comm, const char *tag, const void *mine, size_t len, void *all);
 /* Context handed to custom kernels (role of the reference's MC2 resource export, op_base.cc:3137-3284):

@@ -150,6 +150,23 @@ typedef struct HcclSendRecvItemDef {
     uint32_t remoteRank;
 } HcclSendRecvItem;
 
+/* Topology description per level (HcclGetTopoDesc; the reference declares these in a closed header and fills them in
+ * hccl_communicator.cc:7236-7257).  One NVSwitch domain is a single level: L0 holds every rank, L1 is empty. */
+typedef enum {
+    HCCL_TOPO_L0 = 0,
+    HCCL_TOPO_L1 = 1,
+    HCCL_TOPO_MAX
+} HcclTopoLevel;
+
+#define HCCL_ALG_MESH 0x1u   /* every rank reaches every peer directly */
+#define HCCL_ALG_RING 0x2u
+#define HCCL_ALG_SWITCH 0x4u /* in-switch reduction / multicast (NVLS) is available */
+
+typedef struct HcclTopoDescsDef {
+    uint64_t algSets;  /* HCCL_ALG_* bits usable at this level */
+    uint32_t rankSize; /* ranks at this level */
+} HcclTopoDescs;
+
 #ifdef __cplusplus
 }
 #endif

@@ -82,7 +82,21 @@ class Communicator:
                 "HcclCreateSubCommConfig")
         return Communicator(sub.value, self.device) if sub.value else None
 
+    @classmethod
+    def from_handle(cls, handle, device=None, owned=True):
+        """Wrap an HcclComm made elsewhere (for instance by the group-name front end).  With owned=False destroy() only
+        forgets the handle."""
+        if device is None:
+            import os
+            device = _have_gpu() and os.environ.get("HCCL_TRANSPORT", "") != "host"
+        c = cls(handle, device)
+        c._owned = owned
+        return c
+
     def destroy(self):
+        if not getattr(self, "_owned", True):
+            self._h = C.c_void_p()
+            return L.SUCCESS
         if self._h and self._h.value:
             code = L.lib().HcclCommDestroy(self._h)
             if code == L.SUCCESS:
@@ -348,6 +362,31 @@ class Communicator:
 
     def mem_free(self, handle):
         L.check(L.lib().HcclB200MemFree(self._h, handle), "HcclB200MemFree")
+
+    def put(self, handle, peer, offset, src_ptr, nbytes, local=0, stream=None):
+        """One-sided: copy nbytes from src_ptr into rank `peer`'s copy of allocation `handle` at byte `offset`."""
+        L.check(L.lib().HcclB200Put(self._h, local, handle, peer, offset, src_ptr, nbytes, self._stream(stream)), "HcclB200Put")
+
+    def get(self, handle, peer, offset, dst_ptr, nbytes, local=0, stream=None):
+        """One-sided: copy nbytes at byte `offset` of rank `peer`'s copy of allocation `handle` to dst_ptr."""
+        L.check(L.lib().HcclB200Get(self._h, local, handle, peer, offset, dst_ptr, nbytes, self._stream(stream)), "HcclB200Get")
+
+    def topology(self):
+        """Ranks, transport, NVLS and peer-access matrix as a dict."""
+        buf = C.create_string_buffer(1 << 16)
+        L.check(L.lib().HcclB200GetTopoJson(self._h, buf, 1 << 16), "HcclB200GetTopoJson")
+        return json.loads(buf.value.decode())
+
+    def topo_desc(self):
+        """HcclGetTopoDesc: [(algSets, rankSize)] per level."""
+        d = (L.TopoDescs * L.TOPO_MAX)()
+        L.check(L.lib().HcclGetTopoDesc(self._h, d, L.TOPO_MAX), "HcclGetTopoDesc")
+        return [(int(x.algSets), int(x.rankSize)) for x in d]
+
+    def overflow_count(self):
+        v = C.c_uint64()
+        L.check(L.lib().HcclB200GetOverflowCount(self._h, C.byref(v)), "HcclB200GetOverflowCount")
+        return v.value
 
     def device_context(self):
         p, s = C.c_void_p(), C.c_uint64()

@@ -69,6 +69,18 @@ def run(comm, world, rank, dist, max_over_ranks, sync, time_steps):
     tb = max_over_ranks(_time(base_ag, iters, sync))
     row["cublas_nccl_ms"] = round(tb, 4)
     row["speedup_vs_cublas_nccl"] = round(tb / t, 3)
+    if world > 1:
+        # the same with the shard in registered symmetric memory: the peers pull it in place, no staging copy
+        handle, bufs = comm.symmetric_empty(x_shard.numel(), torch.bfloat16)
+        xz = bufs[0].view_as(x_shard)
+        xz.copy_(x_shard)
+        tz = max_over_ranks(_time(lambda: fused_tp.all_gather_matmul(comm, xz, w_up, out=y), iters, sync))
+        assert comm.sync() == 0, comm.describe_status()
+        row["registered_shard_ms"] = round(tz, 4)
+        row["registered_shard_speedup_vs_cublas_nccl"] = round(tb / tz, 3)
+        row["registered_shard_roofline_fraction"] = round(roof_ms / tz, 3)
+        del xz, bufs
+        comm.mem_free(handle)
     out["ag_gemm"] = row
     # ---- H W_down^T -> reduce-scatter
     t = max_over_ranks(_time(lambda: fused_tp.matmul_reduce_scatter(comm, h, w_down, out=o), iters, sync))

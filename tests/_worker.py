@@ -149,6 +149,98 @@ def scenario_subcomm(c, p, r, args):
     print("subcomm ok")
 
 
+def scenario_hcom(c, p, r, args):
+    """Group-name front end: world group adopted from a communicator, a group over the odd ranks, rank translation,
+    gradient fusion settings and the bucketed data-parallel AllReduce that reads them."""
+    from cann_hccl_b200.ops import hcom
+    from cann_hccl_b200.parallel import grad_bucket
+    hcom.init_by_comm(c)
+    assert hcom.rank_size() == p and hcom.rank_id() == r
+    members = list(range(1, p, 2))
+    hcom.create_group("odd", members)
+    assert hcom.rank_size("odd") == len(members)
+    assert hcom.world_rank_from_group_rank("odd", 0) == 1
+    assert hcom.group_rank_from_world_rank(members[-1], "odd") == len(members) - 1
+    sub = hcom.group_comm("odd")
+    if r in members:
+        assert sub is not None and sub.rank == members.index(r) and hcom.rank_id("odd") == sub.rank
+        x = np.full(64, r, np.float32)
+        out = np.zeros_like(x)
+        sub.all_reduce(x, out)
+        np.testing.assert_array_equal(out, np.full(64, sum(members), np.float32))
+    else:
+        assert sub is None
+    lib = L.lib()
+    bad = (L.C.c_uint32 * 2)(3, 3)
+    assert lib.HcomSetGradFusionByIndex(None, 2, bad) == L.E_PARA            # not ascending
+    shares = (L.C.c_float * 2)(30.0, 60.0)
+    assert lib.HcomSetGradFusionBySize(None, 2, shares) == L.E_PARA         # does not sum to 100
+    assert hcom.grad_fusion_by_index() is None
+    # three segments by index over seven gradients: [0..1], [2..4], [5..6]
+    hcom.set_grad_fusion_by_index(None, [1, 4, 6])
+    shapes = [(5,), (3, 4), (7,), (2, 2), (9,), (1,), (6,)]
+    grads = [np.random.default_rng(100 * q + r).uniform(-1, 1, sh).astype(np.float32) for q, sh in enumerate(shapes)]
+    want = [sum(np.random.default_rng(100 * q + rr).uniform(-1, 1, sh).astype(np.float32) for rr in range(p)) / p for q, sh in enumerate(shapes)]
+    calls = lambda: c.stats()["ops"].get("AllReduce", {"calls": 0})["calls"]
+    before = calls()
+    segs = grad_bucket.all_reduce_gradients(c, grads)
+    assert segs == [(0, 2), (2, 5), (5, 7)], segs
+    assert calls() - before == 3
+    for g, w in zip(grads, want):
+        np.testing.assert_allclose(g, w, rtol=1e-5, atol=1e-6)
+    # by size on a named group setting: 50 / 50 of the element count
+    hcom.set_grad_fusion_by_size("odd", [50.0, 50.0])
+    cuts = grad_bucket.plan_segments([10, 10, 10, 10], group="odd")
+    assert cuts == [(0, 2), (2, 4)], cuts
+    td = c.topo_desc()
+    assert td[0][1] == p and td[0][0] & L.ALG_MESH and td[1] == (0, 0)
+    hcom.destroy_group("odd")
+    hcom.destroy()
+    x = np.ones(8, np.float32)
+    out = np.zeros_like(x)
+    c.all_reduce(x, out)        # the adopted world communicator outlives the front end
+    np.testing.assert_array_equal(out, np.full(8, p, np.float32))
+    print("hcom ok")
+
+
+def scenario_onesided(c, p, r, args):
+    """Put / get on symmetric memory, topology JSON, overflow counter."""
+    n = 256
+    handle, (buf,) = c.symmetric_empty(n * p, np.float32)
+    buf[:] = -1
+    c.barrier()
+    mine = np.full(n, r + 1, np.float32)
+    for q in range(p):      # everyone writes its block into slot r of every rank's copy
+        c.put(handle, q, r * n * 4, mine.ctypes.data, n * 4)
+    c.barrier()
+    np.testing.assert_array_equal(buf.reshape(p, n), np.repeat(np.arange(1, p + 1, dtype=np.float32)[:, None], n, 1))
+    got = np.zeros(n, np.float32)
+    c.get(handle, (r + 1) % p, ((r + 1) % p) * n * 4, got.ctypes.data, n * 4)
+    np.testing.assert_array_equal(got, np.full(n, (r + 1) % p + 1, np.float32))
+    try:
+        c.put(handle, 0, n * p * 4 - 8, mine.ctypes.data, 64)
+        raise AssertionError("out-of-range put accepted")
+    except H.HcclError as e:
+        assert e.code == L.E_PARA
+    c.barrier()
+    del buf
+    c.mem_free(handle)
+    topo = c.topology()
+    assert topo["ranks"] == p and topo["transport"] == "host" and len(topo["rank_table"]) == p
+    assert [e["rank"] for e in topo["rank_table"]] == list(range(p)) and topo["rank_table"][r]["pid"] == os.getpid()
+    # overflow: rank 0 contributes an Inf to the second AllReduce only
+    assert c.overflow_count() == 0
+    x = np.ones(32, np.float32)
+    out = np.zeros_like(x)
+    c.all_reduce(x, out)
+    assert c.overflow_count() == 0
+    if r == 0:
+        x[3] = np.inf
+    c.all_reduce(x, out)
+    assert c.overflow_count() == 1, c.overflow_count()
+    print("onesided ok")
+
+
 def scenario_mismatch(c, p, r, args):
     """rank 1 passes a different count: the consistency check must fail the call on every rank."""
     n = 100 if r != 1 else 101

@@ -294,3 +294,50 @@ def test_single_rank_c_api_and_stats():
     st = c.stats()
     assert st["launches"] >= 2 and st["ops"]["AllReduce"]["calls"] == 1
     c.destroy()
+
+
+def test_one_sided_topology_overflow_device(comms, monkeypatch):
+    """Put / get through peer mappings (copy engine), topology description, and the Inf / NaN scan after a reduction."""
+    p = 4
+    c = comms(p)
+    n = 1024
+    handle, bufs = c.symmetric_empty(n * p, torch.float32)
+    for b in bufs:
+        b.fill_(-1)
+    torch.cuda.synchronize()
+    srcs = [torch.full((n,), float(r + 1), device="cuda") for r in range(p)]
+    for r in range(p):          # virtual rank r writes its block into slot r of every rank's copy
+        for q in range(p):
+            c.put(handle, q, r * n * 4, srcs[r].data_ptr(), n * 4, local=r)
+    torch.cuda.synchronize()
+    want = torch.arange(1, p + 1, device="cuda", dtype=torch.float32).repeat_interleave(n)
+    for b in bufs:
+        assert torch.equal(b, want)
+    got = torch.zeros(n, device="cuda")
+    c.get(handle, 2, 2 * n * 4, got.data_ptr(), n * 4, local=1)
+    torch.cuda.synchronize()
+    assert torch.equal(got, torch.full((n,), 3.0, device="cuda"))
+    with pytest.raises(H.HcclError):
+        c.put(handle, 0, n * p * 4, srcs[0].data_ptr(), 16)
+    del bufs, b
+    c.mem_free(handle)
+    topo = c.topology()
+    assert topo["ranks"] == p and topo["transport"] == "device" and topo["all_local"] and topo["peer_access"] == [[1]]
+    td = c.topo_desc()
+    assert td[0][1] == p and td[0][0] & L.ALG_MESH and td[1] == (0, 0)
+    monkeypatch.setenv("HCCL_OVERFLOW_CHECK", "1")
+    L.lib().HcclB200ReloadEnv()
+    try:
+        xs = [torch.ones(5000, device="cuda", dtype=torch.bfloat16) for _ in range(p)]
+        ys = [torch.empty_like(x) for x in xs]
+        c.all_reduce(xs, ys)
+        ok(c)
+        assert c.overflow_count() == 0
+        xs[1][17] = float("inf")
+        xs[2][99] = float("nan")
+        c.all_reduce(xs, ys)
+        ok(c)
+        assert c.overflow_count() == 2 * p      # two bad outputs on each of the p virtual ranks
+    finally:
+        monkeypatch.delenv("HCCL_OVERFLOW_CHECK")
+        L.lib().HcclB200ReloadEnv()

@@ -27,6 +27,20 @@ def test_sub_communicator():
     assert all("subcomm ok" in out for _, out in res)
 
 
+def test_hcom_groups_and_grad_fusion():
+    res = run_ranks(4, "hcom")
+    assert all("hcom ok" in out for _, out in res)
+
+
+def test_one_sided_topology_overflow(tmp_path):
+    dump = str(tmp_path / "stats.jsonl")
+    res = run_ranks(3, "onesided", env={"HCCL_OVERFLOW_CHECK": "1", "HCCL_NVTX": "1", "HCCL_STATS_DUMP": dump})
+    assert all("onesided ok" in out for _, out in res)
+    import json
+    lines = [json.loads(x) for x in open(dump).read().splitlines() if x.strip()]
+    assert len(lines) == 3 and all(d["ops"]["AllReduce"]["calls"] >= 2 for d in lines)
+
+
 def test_param_mismatch_detected():
     res = run_ranks(3, "mismatch")
     assert all("mismatch detected" in out for _, out in res)
