@@ -172,6 +172,7 @@ def lib():
         "HcclB200HasNvls": [vp, P(i32)],
         "HcclB200GetLocalRankNum": [vp, P(u32)],
         "HcclB200MemAlloc": [vp, C.c_size_t, P(vp), P(i32)],
+        "HcclB200MemAdopt": [vp, P(vp), C.c_size_t, P(u64), C.c_size_t, P(i32)],
         "HcclB200MemFree": [vp, i32],
         "HcclB200MemQuery": [vp, i32, P(vp), P(vp), P(C.c_size_t)],
         "HcclB200Exchange": [vp, C.c_char_p, vp, C.c_size_t, vp],

@@ -905,12 +905,18 @@ HcclResult HcclCommResume(HcclComm comm)
     return c->resume();
 }
 
-// Zero-copy registration.  A range reserved with HcclCommSetMemoryRange is backed by symmetric memory when it is
-// activated; collectives whose buffers lie inside an activated range skip the staging copy.
+// Zero-copy registration (reference: zero_copy_memory_agent.cc, request types SET_MEMORY_RANGE .. DEACTIVATE_COMM_MEMORY).
+// HcclCommSetMemoryRange reserves an address range; HcclCommActivateCommMemory, called by every rank of the communicator
+// in the same order, registers memory inside it as a symmetric allocation: peers map it, and collectives whose buffers lie
+// in registered memory at the same offsets on all ranks take the zero-copy path.  With one rank per GPU `handle` is the
+// driver allocation handle behind virPtr (created exportable as a POSIX file descriptor; the whole allocation, offset 0);
+// a communicator that cannot map foreign memory (CPU ranks in separate processes) keeps the record and stages as before.
 namespace {
-struct Range { Communicator *c; void *base; size_t size; int handle; };
+struct Range { Communicator *c; void *base; size_t size; };
+struct Activation { Communicator *c; void *ptr; size_t size; int handle; };
 std::mutex g_range_mu;
 std::vector<Range> g_ranges;
+std::vector<Activation> g_acts;
 }  // namespace
 HcclResult HcclCommSetMemoryRange(HcclComm comm, void *baseVirPtr, size_t size, size_t alignment, uint64_t flags)
 {
@@ -921,7 +927,7 @@ HcclResult HcclCommSetMemoryRange(HcclComm comm, void *baseVirPtr, size_t size, 
     for (auto &r : g_ranges)
         CHK_RET_LOG(r.c == c && (char *)baseVirPtr < (char *)r.base + r.size && (char *)r.base < (char *)baseVirPtr + size, HCCL_E_PARA,
                     "HcclCommSetMemoryRange: range overlaps a registered range");
-    g_ranges.push_back({c, baseVirPtr, size, 0});
+    g_ranges.push_back({c, baseVirPtr, size});
     return HCCL_SUCCESS;
 }
 HcclResult HcclCommUnsetMemoryRange(HcclComm comm, void *baseVirPtr)
@@ -930,7 +936,9 @@ HcclResult HcclCommUnsetMemoryRange(HcclComm comm, void *baseVirPtr)
     std::lock_guard<std::mutex> lk(g_range_mu);
     for (size_t i = 0; i < g_ranges.size(); ++i)
         if (g_ranges[i].c == c && g_ranges[i].base == baseVirPtr) {
-            CHK_RET_LOG(g_ranges[i].handle != 0, HCCL_E_PARA, "HcclCommUnsetMemoryRange: range still has activated memory");
+            for (auto &a : g_acts)
+                CHK_RET_LOG(a.c == c && (char *)a.ptr >= (char *)g_ranges[i].base && (char *)a.ptr < (char *)g_ranges[i].base + g_ranges[i].size,
+                            HCCL_E_PARA, "HcclCommUnsetMemoryRange: range still has activated memory");
             g_ranges.erase(g_ranges.begin() + i);
             return HCCL_SUCCESS;
         }
@@ -939,26 +947,59 @@ HcclResult HcclCommUnsetMemoryRange(HcclComm comm, void *baseVirPtr)
 HcclResult HcclCommActivateCommMemory(HcclComm comm, void *virPtr, size_t size, size_t offset, aclrtDrvMemHandle handle, uint64_t flags)
 {
     GET_COMM("HcclCommActivateCommMemory");
-    (void)offset; (void)handle; (void)flags;
+    (void)flags;
+    CHK_RET_LOG(!virPtr || size == 0, HCCL_E_PARA, "HcclCommActivateCommMemory: empty region");
+    {
+        std::lock_guard<std::mutex> lk(g_range_mu);
+        bool inside = false;
+        for (auto &r : g_ranges)
+            inside |= r.c == c && (char *)virPtr >= (char *)r.base && (char *)virPtr + size <= (char *)r.base + r.size;
+        CHK_RET_LOG(!inside, HCCL_E_PARA, "HcclCommActivateCommMemory: address not inside a range set with HcclCommSetMemoryRange");
+        for (auto &a : g_acts)
+            CHK_RET_LOG(a.c == c && (char *)virPtr < (char *)a.ptr + a.size && (char *)a.ptr < (char *)virPtr + size, HCCL_E_PARA,
+                        "HcclCommActivateCommMemory: region overlaps activated memory");
+    }
+    int h = 0;
+    if (c->nlocal() == 1) {
+        void *ptrs[1] = {virPtr};
+        unsigned long long dh[1] = {(unsigned long long)(uintptr_t)handle};
+        HcclResult rc = c->sym_adopt(ptrs, size, handle ? dh : nullptr, offset, &h);
+        if (rc == HCCL_E_NOT_SUPPORT) h = 0;  // recorded only: this transport cannot map foreign memory
+        else CHK_RET(rc);
+    }
     std::lock_guard<std::mutex> lk(g_range_mu);
-    for (auto &r : g_ranges)
-        if (r.c == c && (char *)virPtr >= (char *)r.base && (char *)virPtr + size <= (char *)r.base + r.size) {
-            r.handle = 1;  // marks the range active; peers exchange the mapping on first use
-            return HCCL_SUCCESS;
-        }
-    HLOG_ERROR("HcclCommActivateCommMemory: address not inside a range set with HcclCommSetMemoryRange");
-    return HCCL_E_PARA;
+    g_acts.push_back({c, virPtr, size, h});
+    return HCCL_SUCCESS;
 }
 HcclResult HcclCommDeactivateCommMemory(HcclComm comm, void *virPtr)
 {
     GET_COMM("HcclCommDeactivateCommMemory");
-    std::lock_guard<std::mutex> lk(g_range_mu);
-    for (auto &r : g_ranges)
-        if (r.c == c && (char *)virPtr >= (char *)r.base && (char *)virPtr < (char *)r.base + r.size) {
-            r.handle = 0;
-            return HCCL_SUCCESS;
-        }
-    return HCCL_E_NOT_FOUND;
+    Activation act{nullptr, nullptr, 0, 0};
+    {
+        std::lock_guard<std::mutex> lk(g_range_mu);
+        for (size_t i = 0; i < g_acts.size(); ++i)
+            if (g_acts[i].c == c && (char *)virPtr >= (char *)g_acts[i].ptr && (char *)virPtr < (char *)g_acts[i].ptr + g_acts[i].size) {
+                act = g_acts[i];
+                g_acts.erase(g_acts.begin() + i);
+                break;
+            }
+    }
+    if (!act.c) return HCCL_E_NOT_FOUND;
+    if (act.handle) return c->sym_free(act.handle);
+    return HCCL_SUCCESS;
+}
+HcclResult HcclB200MemAdopt(HcclComm comm, void *const *localPtrs, size_t bytes, const uint64_t *drvHandles, size_t handleOffset, int32_t *handle)
+{
+    GET_COMM("HcclB200MemAdopt");
+    CHK_RET_LOG(!localPtrs || !handle, HCCL_E_PTR, "[EI0003] HcclB200MemAdopt: null pointer");
+    CHK_RET_LOG(bytes == 0, HCCL_E_PARA, "HcclB200MemAdopt: empty region");
+    for (int li = 0; li < c->nlocal(); ++li) CHK_RET_LOG(!localPtrs[li], HCCL_E_PTR, "[EI0003] HcclB200MemAdopt: localPtrs[%d] is null", li);
+    std::vector<unsigned long long> dh;
+    if (drvHandles) dh.assign(drvHandles, drvHandles + c->nlocal());
+    int h = 0;
+    CHK_RET(c->sym_adopt(localPtrs, bytes, drvHandles ? dh.data() : nullptr, handleOffset, &h));
+    *handle = h;
+    return HCCL_SUCCESS;
 }
 
 }  // extern "C"

@@ -1296,6 +1296,21 @@ HcclResult Communicator::sym_alloc(size_t bytes, void **local_ptrs, int *handle)
     std::vector<SymSegment> segs;
     CHK_RET(alloc_->alloc(bytes, true, &segs));
     for (int li = 0; li < nlocal(); ++li) local_ptrs[li] = segs[li].peer[local_ranks_[li]];
+    return register_user_segs(std::move(segs), handle);
+}
+
+HcclResult Communicator::sym_adopt(void *const *local_ptrs, size_t bytes, const unsigned long long *drv_handles, size_t handle_offset, int *handle)
+{
+    std::lock_guard<std::mutex> lk(op_mu_);
+    StateGuard guard(state_, CS_BUILDING);
+    std::vector<SymSegment> segs;
+    CHK_RET(alloc_->adopt(local_ptrs, bytes, drv_handles, handle_offset, true, &segs));
+    CHK_RET_LOG((int)segs.size() != nlocal(), HCCL_E_INTERNAL, "allocator returned %zu segments for %d local ranks", segs.size(), nlocal());
+    return register_user_segs(std::move(segs), handle);
+}
+
+HcclResult Communicator::register_user_segs(std::vector<SymSegment> segs, int *handle)
+{
     *handle = next_handle_++;
     std::vector<void *> tabs(nlocal(), nullptr);
     for (int li = 0; li < nlocal(); ++li) {

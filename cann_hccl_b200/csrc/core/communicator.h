@@ -122,6 +122,9 @@ public:
 
     // Symmetric user memory (zero-copy paths, fused kernels).  Collective over the communicator.
     HcclResult sym_alloc(size_t bytes, void **local_ptrs /*nlocal*/, int *handle);
+    // Registers caller-owned memory (one pointer per local rank) as a symmetric allocation; sym_free() undoes it and leaves
+    // the memory alone.  drv_handles: driver allocation handles behind the pointers (one rank per GPU only), else null.
+    HcclResult sym_adopt(void *const *local_ptrs, size_t bytes, const unsigned long long *drv_handles, size_t handle_offset, int *handle);
     HcclResult sym_free(int handle);
     // Peer pointer table of a symmetric allocation: ptrs[local][rank]; mc[local]
     HcclResult sym_query(int handle, void **peer_ptrs, void **mc_ptrs, size_t *bytes);
@@ -232,6 +235,7 @@ private:
     std::map<std::string, int> zc_agreed_;                 // (buffers, count) -> 1 when every rank can run the op zero-copy, 0 otherwise
     // Finds the registered allocation that holds [ptr, ptr+bytes) of local rank li; returns its handle or 0.
     int find_user_seg(int li, const void *ptr, size_t bytes, size_t *offset);
+    HcclResult register_user_segs(std::vector<SymSegment> segs, int *handle);
     int next_handle_ = 1;
     struct ZcArgs { uint8_t *const *in_tab; uint8_t *const *out_tab; uint8_t *in_mc; uint8_t *out_mc; size_t oin, oout; };
     std::vector<ZcArgs> zc_args_;   // zero-copy pointers of the op being launched (per local rank)

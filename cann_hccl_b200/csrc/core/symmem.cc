@@ -36,9 +36,19 @@ public:
         }
         return HCCL_SUCCESS;
     }
+    HcclResult adopt(void *const *local_ptrs, size_t bytes, const unsigned long long *, size_t, bool, std::vector<SymSegment> *out) override
+    {
+        out->assign(n_, SymSegment());
+        for (int r = 0; r < n_; ++r) {
+            (*out)[r].bytes = bytes;
+            (*out)[r].kind = kSegAdoptedLocal;
+            for (int q = 0; q < n_; ++q) (*out)[r].peer[q] = (uint8_t *)local_ptrs[q];
+        }
+        return HCCL_SUCCESS;
+    }
     void release(std::vector<SymSegment> *segs) override
     {
-        if (!segs->empty())
+        if (!segs->empty() && (*segs)[0].kind != kSegAdoptedLocal)
             for (int q = 0; q < n_; ++q) free((*segs)[0].peer[q]);
         segs->clear();
     }
@@ -132,9 +142,19 @@ public:
         }
         return HCCL_SUCCESS;
     }
+    HcclResult adopt(void *const *local_ptrs, size_t bytes, const unsigned long long *, size_t, bool, std::vector<SymSegment> *out) override
+    {
+        out->assign(n_, SymSegment());
+        for (int r = 0; r < n_; ++r) {
+            (*out)[r].bytes = bytes;
+            (*out)[r].kind = kSegAdoptedLocal;
+            for (int q = 0; q < n_; ++q) (*out)[r].peer[q] = (uint8_t *)local_ptrs[q];
+        }
+        return HCCL_SUCCESS;
+    }
     void release(std::vector<SymSegment> *segs) override
     {
-        if (!segs->empty())
+        if (!segs->empty() && (*segs)[0].kind != kSegAdoptedLocal)
             for (int q = 0; q < n_; ++q) cudaFree((*segs)[0].peer[q]);
         segs->clear();
     }
@@ -186,13 +206,51 @@ public:
         return rc;
     }
 
+    HcclResult adopt(void *const *local_ptrs, size_t bytes, const unsigned long long *drv_handles, size_t handle_offset, bool want_mc,
+                     std::vector<SymSegment> *out) override
+    {
+        if (cudaSetDevice(dev_) != cudaSuccess) return HCCL_E_RUNTIME;
+        uint64_t seq = seq_++;
+        // every rank states whether it can take part (exportable handle given, size on the allocation granularity) and its
+        // size, so that all ranks return the same verdict instead of some waiting for a peer that gave up
+        const DriverApi &d = driver_api();
+        size_t gran = 2u << 20;
+        if (d.ok) {
+            CUmemAllocationProp prop;
+            memset(&prop, 0, sizeof(prop));
+            prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+            prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+            prop.location.id = dev_;
+            prop.requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+            d.MemGetAllocationGranularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_MINIMUM);
+        }
+        struct { uint32_t ok, mc; uint64_t bytes; } me_v{0, 0, bytes};
+        me_v.ok = vmm_ok_ && drv_handles && drv_handles[0] && local_ptrs && local_ptrs[0] && bytes && bytes % gran == 0 && handle_offset == 0;
+        me_v.mc = mc_ok_ && want_nvls_ && want_mc;
+        std::vector<std::string> all;
+        CHK_RET(hub_->rendezvous(ident_ + "/adoptcaps/" + std::to_string(seq), n_, rank_, std::string((const char *)&me_v, sizeof(me_v)), &all, tmo_));
+        bool ok = true, use_mc = n_ > 1;
+        for (auto &blob : all) {
+            decltype(me_v) o;
+            memcpy(&o, blob.data(), sizeof(o));
+            ok &= o.ok != 0 && o.bytes == bytes;
+            use_mc &= o.mc != 0;
+        }
+        CHK_RET_LOG(!ok, HCCL_E_PARA, "registering user memory needs, on every rank, a whole allocation (offset 0) whose handle is exportable as a file "
+                    "descriptor, and one common size that is a multiple of %zu bytes", gran);
+        out->assign(1, SymSegment());
+        HcclResult rc = alloc_vmm(bytes, use_mc, seq, &(*out)[0], (CUmemGenericAllocationHandle)drv_handles[0], (uint8_t *)local_ptrs[0], handle_offset);
+        if (rc != HCCL_SUCCESS) out->clear();
+        return rc;
+    }
+
     void release(std::vector<SymSegment> *segs) override
     {
         const DriverApi &d = driver_api();
         cudaSetDevice(dev_);
         cudaDeviceSynchronize();
         for (auto &s : *segs) {
-            if (s.kind == 1) {
+            if (s.kind == 1 || s.kind == kSegAdoptedVmm) {
                 if (s.mc) {
                     d.MemUnmap((CUdeviceptr)s.mc, s.map_bytes);
                     d.MemAddressFree((CUdeviceptr)s.mc, s.map_bytes);
@@ -203,6 +261,7 @@ public:
                 }
                 for (int q = 0; q < n_; ++q) {
                     if (!s.peer[q]) continue;
+                    if (s.kind == kSegAdoptedVmm && q == rank_) continue;  // the caller's own mapping and handle stay
                     d.MemUnmap((CUdeviceptr)s.peer[q], s.map_bytes);
                     d.MemAddressFree((CUdeviceptr)s.peer[q], s.map_bytes);
                     d.MemRelease((CUmemGenericAllocationHandle)s.handles[q]);
@@ -258,8 +317,12 @@ private:
         return HCCL_SUCCESS;
     }
 
-    HcclResult alloc_vmm(size_t bytes, bool use_mc, uint64_t seq, SymSegment *s)
+    // ext_handle != 0: the memory is the caller's allocation `ext_handle` (from byte ext_off on), already mapped at ext_va;
+    // nothing is created, cleared or mapped for this rank itself, only exported for the peers.
+    HcclResult alloc_vmm(size_t bytes, bool use_mc, uint64_t seq, SymSegment *s, CUmemGenericAllocationHandle ext_handle = 0,
+                         uint8_t *ext_va = nullptr, size_t ext_off = 0)
     {
+        (void)ext_off;  // cuMemMap only maps whole allocations from offset 0; adopt() has checked that
         const DriverApi &d = driver_api();
         CUdevice cd;
         d.DeviceGet(&cd, dev_);
@@ -280,11 +343,14 @@ private:
             size_t mg = gran;
             if (d.MulticastGetGranularity(&mg, &mprop, CU_MULTICAST_GRANULARITY_RECOMMENDED) == CUDA_SUCCESS && mg > gran) gran = mg;
         }
-        size_t sz = (bytes + gran - 1) / gran * gran;
+        size_t sz = ext_handle ? bytes : (bytes + gran - 1) / gran * gran;
         mprop.size = sz;
-        CUmemGenericAllocationHandle mine = 0, mch = 0;
-        CUresult cr = d.MemCreate(&mine, sz, &prop, 0);
-        CHK_RET_LOG(cr != CUDA_SUCCESS, HCCL_E_MEMORY, "cuMemCreate(%zu) failed: %s", sz, cu_err(cr));
+        CUmemGenericAllocationHandle mine = ext_handle, mch = 0;
+        CUresult cr = CUDA_SUCCESS;
+        if (!ext_handle) {
+            cr = d.MemCreate(&mine, sz, &prop, 0);
+            CHK_RET_LOG(cr != CUDA_SUCCESS, HCCL_E_MEMORY, "cuMemCreate(%zu) failed: %s", sz, cu_err(cr));
+        }
         std::vector<int> myfds;
         int fd = -1;
         cr = d.MemExportToShareableHandle(&fd, mine, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0);
@@ -306,7 +372,7 @@ private:
         bool mc_on = use_mc && all[0].size() >= 2;
         s->bytes = bytes;
         s->map_bytes = sz;
-        s->kind = 1;
+        s->kind = ext_handle ? kSegAdoptedVmm : 1;
         CUmemAccessDesc acc;
         memset(&acc, 0, sizeof(acc));
         acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
@@ -315,6 +381,11 @@ private:
         HcclResult rc = HCCL_SUCCESS;
         for (int q = 0; q < n_ && rc == HCCL_SUCCESS; ++q) {
             CUmemGenericAllocationHandle h = mine;
+            if (q == rank_ && ext_handle) {  // the caller's own mapping serves
+                s->peer[q] = ext_va;
+                s->handles[q] = 0;
+                continue;
+            }
             if (q != rank_) {
                 cr = d.MemImportFromShareableHandle(&h, (void *)(uintptr_t)all[q][0], CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
                 if (cr != CUDA_SUCCESS) { HLOG_ERROR("import of rank %d memory failed: %s", q, cu_err(cr)); rc = HCCL_E_DRV; break; }
@@ -366,7 +437,7 @@ private:
         for (auto &v : all)
             for (int x : v) close(x);
         if (rc == HCCL_SUCCESS) {
-            cudaMemset(s->peer[rank_], 0, bytes);
+            if (!ext_handle) cudaMemset(s->peer[rank_], 0, bytes);
             cudaDeviceSynchronize();
         }
         HcclResult rb2 = hub_->barrier(ident_ + "/vmm-ready/" + std::to_string(seq), n_, rank_, tmo_);

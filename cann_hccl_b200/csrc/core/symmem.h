@@ -26,15 +26,29 @@ struct SymSegment {
     unsigned long long handles[kMaxRanks] = {0};
     unsigned long long mc_handle = 0;
     size_t map_bytes = 0;
-    int kind = 0;
+    int kind = 0;                          // back-end specific; kSegAdopted* = caller-owned memory
     std::string shm_name;
 };
+
+constexpr int kSegAdoptedLocal = 9;  // caller-owned, peers in the same process: nothing to undo
+constexpr int kSegAdoptedVmm = 3;    // caller-owned VMM allocation mapped by the peers
 
 class SymAllocator {
 public:
     virtual ~SymAllocator() {}
     // Collective over all ranks of the communicator.  out->size() == number of local ranks.
     virtual HcclResult alloc(size_t bytes, bool want_mc, std::vector<SymSegment> *out) = 0;
+    // Registers memory that the caller owns and keeps (one pointer per local rank, `bytes` each) as a symmetric segment, so
+    // that peers can reach it like memory from alloc().  Collective.  Back ends whose ranks share a process record the
+    // pointers; the one-rank-per-GPU back end needs the driver allocation handle behind the pointer (created exportable as a
+    // POSIX file descriptor; the registered memory is the whole allocation: `handle_offset` 0 and `bytes` its size, because the
+    // driver maps allocations only as a whole) and maps it on every peer.  release() undoes the registration and leaves the memory alone.
+    virtual HcclResult adopt(void *const *local_ptrs, size_t bytes, const unsigned long long *drv_handles, size_t handle_offset,
+                             bool want_mc, std::vector<SymSegment> *out)
+    {
+        (void)local_ptrs; (void)bytes; (void)drv_handles; (void)handle_offset; (void)want_mc; (void)out;
+        return HCCL_E_NOT_SUPPORT;
+    }
     virtual void release(std::vector<SymSegment> *segs) = 0;
     virtual bool is_device() const = 0;
     virtual bool has_multicast() const { return false; }

@@ -110,6 +110,13 @@ extern HcclResult HcclB200GetLocalRankNum(HcclComm comm, uint32_t *n);
 
 /* Symmetric memory: same-size allocation on every rank, peers mapped.  localPtrs gets one pointer per local rank. */
 extern HcclResult HcclB200MemAlloc(HcclComm comm, size_t bytes, void **localPtrs, int32_t *handle);
+/* Registers memory the caller owns (one pointer per local rank, `bytes` each) as a symmetric allocation: peers map it and
+ * zero-copy collectives, put/get and the fused kernels accept it like memory from HcclB200MemAlloc.  Collective.  With one
+ * rank per GPU, drvHandles[0] is the driver allocation handle behind the pointer (created exportable as a POSIX file
+ * descriptor; whole allocation, handleOffset 0); with virtual ranks in one process drvHandles may be NULL.
+ * HcclB200MemFree ends the registration and leaves the memory alone.  This is what HcclCommActivateCommMemory calls. */
+extern HcclResult HcclB200MemAdopt(HcclComm comm, void *const *localPtrs, size_t bytes, const uint64_t *drvHandles, size_t handleOffset,
+                                   int32_t *handle);
 extern HcclResult HcclB200MemFree(HcclComm comm, int32_t handle);
 /* peerPtrs[local * nRanks + q] = rank q's copy as mapped for the local rank; mcPtrs[local] = multicast mapping or NULL. */
 extern HcclResult HcclB200MemQuery(HcclComm comm, int32_t handle, void **peerPtrs, void **mcPtrs, size_t *bytes);

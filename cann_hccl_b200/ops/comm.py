@@ -351,6 +351,23 @@ class Communicator:
                 bufs.append(np.frombuffer(raw, dtype=dtype, count=numel))
         return handle, bufs
 
+    def mem_adopt(self, bufs, drv_handles=None):
+        """Register caller-owned buffers (one per local rank; numpy arrays or torch tensors of equal byte size) as a symmetric
+        allocation.  drv_handles: driver allocation handles behind the buffers (one rank per GPU).  Returns the handle for
+        mem_free(), which leaves the memory alone."""
+        bufs = list(bufs) if isinstance(bufs, (list, tuple)) else [bufs]
+        assert len(bufs) == self.nlocal
+        ptrs = (C.c_void_p * self.nlocal)(*[b.data_ptr() if hasattr(b, "data_ptr") else b.ctypes.data for b in bufs])
+        b0 = bufs[0]
+        nbytes = b0.numel() * b0.element_size() if hasattr(b0, "data_ptr") else b0.nbytes
+        dh = None
+        if drv_handles is not None:
+            dh = (C.c_uint64 * self.nlocal)(*[int(h) for h in drv_handles])
+        h = C.c_int32()
+        L.check(L.lib().HcclB200MemAdopt(self._h, ptrs, nbytes, dh, 0, C.byref(h)), "HcclB200MemAdopt")
+        self._keep.append(bufs)
+        return h.value
+
     def mem_query(self, handle):
         """Returns (peer pointer table [local][rank], multicast pointers [local], bytes)."""
         peers = (C.c_void_p * (self.nlocal * self.nranks))()

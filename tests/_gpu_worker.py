@@ -102,6 +102,7 @@ def scenario_collectives(c, p, r, args):
         del zin, zout
         c.mem_free(hin)
         c.mem_free(hout)
+    _adopted_vmm_memory(c, p, r, nvls)
     for algo in [L.ALGO_MESH, L.ALGO_RING, L.ALGO_RHD] + ([L.ALGO_NVLS] if nvls else []):
         n = 40_000
         xs = [inp(q, n * p, torch.float32, seed=3) for q in range(p)]
@@ -151,6 +152,81 @@ def scenario_collectives(c, p, r, args):
         assert torch.equal(y, inp(r - 1, 100_000, torch.float32, seed=8))
     ok(c)
     print("rank %d collectives ok; stats %s" % (r, c.stats()["algos"]))
+
+
+def _adopted_vmm_memory(c, p, r, nvls):
+    """User memory made with the driver's virtual-memory calls, registered through HcclCommSetMemoryRange /
+    HcclCommActivateCommMemory: peers map it, put/get reach it, and AllReduce on it runs zero-copy."""
+    try:
+        from cuda.bindings import driver as drv
+    except ImportError:
+        print("rank %d: cuda-python missing, adopted-memory case skipped" % r)
+        return
+    import ctypes as C
+
+    def chk(res):
+        err, rest = res[0], res[1:]
+        assert int(err) == 0, "driver call failed: %s" % err
+        return rest[0] if len(rest) == 1 else rest
+
+    dev = torch.cuda.current_device()
+    prop = drv.CUmemAllocationProp()
+    prop.type = drv.CUmemAllocationType.CU_MEM_ALLOCATION_TYPE_PINNED
+    prop.location.type = drv.CUmemLocationType.CU_MEM_LOCATION_TYPE_DEVICE
+    prop.location.id = dev
+    prop.requestedHandleTypes = drv.CUmemAllocationHandleType.CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR
+    size = 8 << 20
+    acc = drv.CUmemAccessDesc()
+    acc.location.type = drv.CUmemLocationType.CU_MEM_LOCATION_TYPE_DEVICE
+    acc.location.id = dev
+    acc.flags = drv.CUmemAccess_flags.CU_MEM_ACCESS_FLAGS_PROT_READWRITE
+    regions = []
+    for _ in range(2):  # send and receive buffer, one allocation each
+        h = chk(drv.cuMemCreate(size, prop, 0))
+        va = chk(drv.cuMemAddressReserve(size, 2 << 20, 0, 0))
+        chk(drv.cuMemMap(va, size, 0, h, 0))
+        chk(drv.cuMemSetAccess(va, size, [acc], 1))
+        regions.append((int(h), int(va)))
+
+    def view(va, n):
+        class _P:
+            pass
+        o = _P()
+        o.__cuda_array_interface__ = {"shape": (n,), "typestr": "<f4", "data": (va, False), "version": 3}
+        return torch.as_tensor(o, device="cuda")
+
+    lib = L.lib()
+    n = size // 4
+    for h, va in regions:
+        L.check(lib.HcclCommSetMemoryRange(c.handle, va, size, 0, 0), "HcclCommSetMemoryRange")
+        L.check(lib.HcclCommActivateCommMemory(c.handle, va, size, 0, C.c_void_p(h), 0), "HcclCommActivateCommMemory")
+    zin, zout = view(regions[0][1], n), view(regions[1][1], n)
+    xs = [inp(q, n, torch.float32, seed=33) for q in range(p)]
+    zin.copy_(xs[r])
+    zout.zero_()
+    c.all_reduce(zin, zout)
+    ok(c)
+    if nvls:
+        assert c.trace()[-1]["algo"] == "nvls_zerocopy", c.trace()[-1]
+    close(zout, red(xs, L.SUM), torch.float32, p)
+    torch.cuda.synchronize()
+    c.barrier()
+    ok(c)
+    for h, va in regions:
+        L.check(lib.HcclCommDeactivateCommMemory(c.handle, va), "HcclCommDeactivateCommMemory")
+        L.check(lib.HcclCommUnsetMemoryRange(c.handle, va), "HcclCommUnsetMemoryRange")
+    zout.zero_()
+    c.all_reduce(zin, zout)     # registration gone: staged path on the same memory
+    ok(c)
+    assert c.trace()[-1]["algo"] != "nvls_zerocopy"
+    close(zout, red(xs, L.SUM), torch.float32, p)
+    torch.cuda.synchronize()
+    del zin, zout
+    for h, va in regions:
+        chk(drv.cuMemUnmap(va, size))
+        chk(drv.cuMemAddressFree(va, size))
+        chk(drv.cuMemRelease(h))
+    print("rank %d adopted vmm memory ok" % r)
 
 
 def _time_repeat(c, fn, iters):

@@ -106,6 +106,30 @@ def test_all_gather_matmul_registered_source(comms, p):
     c.mem_free(handle)
 
 
+def test_all_gather_matmul_adopted_source(comms):
+    """Ordinary tensors registered with mem_adopt are pulled in place like library-allocated symmetric memory."""
+    p = 2
+    c = comms(p)
+    Ms, K, N = 256, 512, 512
+    g = torch.Generator(device="cuda").manual_seed(77)
+    xs = [torch.randn(Ms, K, device="cuda", generator=g).to(torch.bfloat16) for _ in range(p)]
+    ws = [(torch.randn(N, K, device="cuda", generator=g) * 0.05).to(torch.bfloat16) for _ in range(p)]
+    handle = c.mem_adopt(xs)
+    table, _, nbytes = c.mem_query(handle)
+    assert nbytes == Ms * K * 2 and table[0][1] == xs[1].data_ptr() and table[1][0] == xs[0].data_ptr()
+    for _ in range(2):
+        ys = fused_tp.all_gather_matmul(c, xs, ws)
+        assert c.sync() == 0, c.describe_status()
+    xfull = torch.cat([x.float() for x in xs])
+    for r in range(p):
+        assert rel_err(ys[r], xfull @ ws[r].float().t()) < 1e-2
+    c.mem_free(handle)
+    ys = fused_tp.all_gather_matmul(c, xs, ws)  # staged again
+    assert c.sync() == 0, c.describe_status()
+    for r in range(p):
+        assert rel_err(ys[r], xfull @ ws[r].float().t()) < 1e-2
+
+
 @pytest.mark.parametrize("p", [1, 2, 4])
 def test_matmul_reduce_scatter(comms, p):
     c = comms(p)

@@ -310,3 +310,29 @@ def test_zero_copy_allreduce_on_registered_memory(comms, p):
     del ins, outs
     c.mem_free(hin)
     c.mem_free(hout)
+
+
+def test_zero_copy_allreduce_on_adopted_user_memory(comms):
+    """Caller-owned buffers registered with mem_adopt behave like library-allocated symmetric memory: the zero-copy plan
+    runs on them, and mem_free ends the registration without touching the buffers."""
+    p = 4
+    c = comms(p)
+    n = 300_000
+    src = make_inputs(p, n, np.float32)
+    ins = [s_.copy() for s_ in src]
+    outs = [np.zeros(n, np.float32) for _ in range(p)]
+    hin, hout = c.mem_adopt(ins), c.mem_adopt(outs)
+    c.all_reduce(ins, outs)
+    assert c.trace()[-1]["algo"] == "nvls_zerocopy"
+    ref = np_reduce(src, L.SUM)
+    for o in outs:
+        np.testing.assert_allclose(o, ref, **tol(np.float32, p))
+    c.mem_free(hin)
+    c.mem_free(hout)
+    outs2 = [np.zeros(n, np.float32) for _ in range(p)]
+    c.all_reduce(ins, outs2)  # registration gone: staged path, same values
+    assert c.trace()[-1]["algo"] != "nvls_zerocopy"
+    for o in outs2:
+        np.testing.assert_allclose(o, ref, **tol(np.float32, p))
+    for a, b in zip(ins, src):
+        np.testing.assert_array_equal(a, b)

@@ -48,6 +48,11 @@ def test_collectives_multi_gpu(p):
         pytest.skip("needs %d GPUs" % p)
     outs = run_gpu_ranks(p, "collectives")
     assert all("collectives ok" in o for _, o in outs)
+    try:
+        from cuda.bindings import driver  # noqa: F401
+        assert all("adopted vmm memory ok" in o for _, o in outs)  # user memory registered through the memory-range calls
+    except ImportError:
+        pass
 
 
 def test_collectives_multi_gpu_p2p_only():
