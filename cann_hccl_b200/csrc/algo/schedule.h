@@ -68,4 +68,9 @@ HcclResult build_plan(const OpDesc &d, const std::vector<int> &local, Plan *plan
 // Staging bytes per rank that `chunk_count` elements need under this algorithm (to size the staging loop).
 uint64_t plan_stage_bytes(const OpDesc &d);
 
+// Static bounds check of a plan built from `d` for the ranks `local`: operand ranges against the declared staging need
+// (and one staging half when stage_half != 0), the mailbox area and the caller's buffer sizes that the API contract implies;
+// channel, bank and rank fields against their ranges.  HCCL_E_INTERNAL and a description in *why on the first violation.
+HcclResult verify_plan(const OpDesc &d, const std::vector<int> &local, const Plan &plan, uint64_t stage_half, std::string *why);
+
 }  // namespace hcclb

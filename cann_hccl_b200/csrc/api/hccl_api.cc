@@ -873,6 +873,22 @@ HcclResult HcclGetTopoDesc(HcclComm comm, HcclTopoDescs *topoDescs, uint32_t top
     topoDescs[HCCL_TOPO_L1].rankSize = 0;
     return HCCL_SUCCESS;
 }
+HcclResult HcclB200PlanCheck(int32_t coll, int32_t algo, uint32_t nRanks, uint64_t count, HcclDataType dataType, uint32_t nChannels,
+                             uint64_t stageHalfBytes, int32_t skewStep, int64_t skewBytes, char *message, size_t cap)
+{
+    OpDesc d;
+    d.coll = coll; d.algo = algo; d.nranks = (int)nRanks; d.dtype = dataType; d.nchan = (int)nChannels;
+    d.count = count; d.chunk_off = 0; d.chunk_count = count;
+    std::vector<int> local;
+    for (uint32_t r = 0; r < nRanks; ++r) local.push_back((int)r);
+    Plan plan;
+    CHK_RET(build_plan(d, local, &plan));
+    if (skewStep >= 0 && !plan.steps.empty() && skewStep < (int)plan.steps[0].size()) plan.steps[0][skewStep].d_off += (uint64_t)skewBytes;
+    std::string why;
+    HcclResult rc = verify_plan(d, local, plan, stageHalfBytes, &why);
+    if (message && cap) snprintf(message, cap, "%s", rc == HCCL_SUCCESS ? plan.name.c_str() : why.c_str());
+    return rc;
+}
 HcclResult HcclB200Exchange(HcclComm comm, const char *tag, const void *mine, size_t len, void *all)
 {
     GET_COMM("HcclB200Exchange");

@@ -320,6 +320,11 @@ HcclResult Communicator::get_plan(const OpDesc &d, const std::string &key, Cache
     }
     CachedPlan cp;
     CHK_RET(build_plan(d, local_ranks_, &cp.plan));
+    {
+        std::string why;
+        HcclResult vrc = verify_plan(d, local_ranks_, cp.plan, d.coll == COLL_SEND || d.coll == COLL_RECV ? 0 : settings_.stage_half_bytes, &why);
+        CHK_RET_LOG(vrc != HCCL_SUCCESS, vrc, "plan verification failed: %s", why.c_str());
+    }
     if (settings_.transport == TR_DEVICE) {
         for (auto &steps : cp.plan.steps) {
             Step *ds = nullptr;

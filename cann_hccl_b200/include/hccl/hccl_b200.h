@@ -133,6 +133,12 @@ extern HcclResult HcclB200GetTopoJson(HcclComm comm, char *json, size_t cap);
 /* Overflow check (role of the reference's TaskOverflow hookup): with HCCL_OVERFLOW_CHECK=1 every floating-point reduction
  * is followed by a scan of its output; *count = outputs that were Inf or NaN since the communicator was made. */
 extern HcclResult HcclB200GetOverflowCount(HcclComm comm, uint64_t *count);
+/* Offline lint of a schedule: lowers (coll, algo) for nRanks ranks and `count` elements and runs the static bounds check
+ * that every plan passes before its first execution (operand ranges against staging / mailbox / caller buffer sizes, channel,
+ * bank and rank fields).  skewStep >= 0 adds skewBytes to the destination offset of that step of rank 0 first, to show the
+ * check firing.  message receives the plan name, or the first violation.  No communicator and no GPU needed. */
+extern HcclResult HcclB200PlanCheck(int32_t coll, int32_t algo, uint32_t nRanks, uint64_t count, HcclDataType dataType, uint32_t nChannels,
+                                    uint64_t stageHalfBytes, int32_t skewStep, int64_t skewBytes, char *message, size_t cap);
 /* All-gather `len` bytes per rank over the bootstrap hub (control plane; not for bulk data). */
 extern HcclResult HcclB200Exchange(HcclComm comm, const char *tag, const void *mine, size_t len, void *all);
 /* Context handed to custom kernels (role of the reference's MC2 resource export, op_base.cc:3137-3284):

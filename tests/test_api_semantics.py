@@ -235,3 +235,28 @@ print('INITALL OK')
     env = dict(os.environ, HCCL_TRANSPORT="host")
     out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, cwd=os.path.dirname(os.path.dirname(__file__)), timeout=60)
     assert "INITALL OK" in out.stdout, out.stdout + out.stderr
+
+
+def test_plan_verifier_accepts_schedules_and_catches_a_skewed_step():
+    """Every plan passes a static bounds check before its first run; a destination offset pushed past the staging area
+    (or the caller's buffer) is reported with the step, at plan build time."""
+    lib = L.lib()
+    msg = C.create_string_buffer(512)
+    n = 100_003
+    for coll, algos in ((L.ALLREDUCE, (L.ALGO_MESH, L.ALGO_RING, L.ALGO_RHD, L.ALGO_MESH_ONESHOT)), (L.ALLGATHER, (L.ALGO_MESH, L.ALGO_RING)),
+                        (L.REDUCE_SCATTER, (L.ALGO_MESH, L.ALGO_RING, L.ALGO_RHD)), (L.BROADCAST, (L.ALGO_STAR, L.ALGO_RING, L.ALGO_TREE))):
+        for algo in algos:
+            for p in (2, 3, 5, 8):
+                rc = lib.HcclB200PlanCheck(coll, algo, p, n, L.FP32, 4, 64 << 20, -1, 0, msg, 512)
+                assert rc == L.SUCCESS, msg.value
+    # staging half too small for the declared need
+    assert lib.HcclB200PlanCheck(L.ALLREDUCE, L.ALGO_MESH, 4, n, L.FP32, 4, 4096, -1, 0, msg, 512) == L.E_INTERNAL
+    assert b"staging" in msg.value
+    # a step whose destination runs 1 GiB past its buffer
+    bad = 0
+    for step in range(6):
+        rc = lib.HcclB200PlanCheck(L.ALLREDUCE, L.ALGO_RING, 4, n, L.FP32, 4, 64 << 20, step, 1 << 30, msg, 512)
+        if rc == L.E_INTERNAL:
+            bad += 1
+            assert b"step %d" % step in msg.value and b"reaches byte" in msg.value, msg.value
+    assert bad >= 4
