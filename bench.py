@@ -123,13 +123,17 @@ def main():
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
 
+    # staging of 640 MB per direction (HCCL_BUFFSIZE semantics; the default is 200): every message of the sweep and the
+    # 8 x 64 MiB AllGather / ReduceScatter of the side table then run as one launch instead of a staging loop
+    cfg = L.CommConfig.default()
+    cfg.hcclBufferSize = int(os.environ.get("HCCL_BUFFSIZE", "640"))
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
         blob = [H.Communicator.get_root_info() if rank == 0 else None]
         dist.broadcast_object_list(blob, src=0)
-        comm = H.Communicator.init_root(world, blob[0], rank, device=True)
+        comm = H.Communicator.init_root(world, blob[0], rank, config=cfg, device=True)
     else:
-        comm = H.Communicator.init_root(1, H.Communicator.get_root_info(), 0, device=True)
+        comm = H.Communicator.init_root(1, H.Communicator.get_root_info(), 0, config=cfg, device=True)
 
     def sync():
         torch.cuda.synchronize()
@@ -294,7 +298,7 @@ def main():
         "dtype": "fp32", "data": "synthetic (uniform[-1,1) seeded 1234+rank)",
         "config": {"model": "hccl_test all_reduce_test -d fp32 -o sum", "global_batch": world, "seq_len": n,
                    "message_bytes_per_rank": HEADLINE_BYTES, "parallelism": "allreduce%d" % world, "algorithm": algo,
-                   "nvls": comm.has_nvls(), "l2_policy": "4 rotating buffer sets, 512 MiB total > 126 MB L2"},
+                   "nvls": comm.has_nvls(), "l2_policy": "4 rotating buffer sets, 512 MiB total > 126 MB L2", "staging_mb": int(cfg.hcclBufferSize)},
         "check_result": "success" if check else "failed",
         "clocks": clocks,
         "e2e": {"value": round(e2e_value, 3), "unit": "GB/s", "h2d_bytes_per_step": HEADLINE_BYTES, "d2h_bytes_per_step": HEADLINE_BYTES,

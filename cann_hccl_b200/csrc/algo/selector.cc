@@ -95,7 +95,7 @@ double estimate_us(int coll, int algo, uint64_t bytes, int p, const CostModel &m
             break;
         case COLL_BROADCAST:
             switch (algo) {
-                case ALGO_STAR: return L + a + n / G + n / B * 1.0 + 2 * s;  // every non-root pulls n from the root: root egress (p-1)n
+                case ALGO_STAR: return L + a + n / G + (p - 1) * n / B + 2 * s;  // every non-root pulls n from the root: root egress (p-1)n
                 case ALGO_RING: return L + (p - 1 + 3) * (a + s) + (1.0 + (p - 2) / 4.0) * n / B;
                 case ALGO_TREE: return L + lg * (a + s) + lg * n / B;
                 case ALGO_NVLS: return L + a + n / Bn + n / G;

@@ -87,7 +87,7 @@ HcclResult Communicator::calibrate(void *stream)
     if (avg[3] > 0) model_.nvls_gbps = avg[3];
     // ---- measured AllReduce table: every candidate algorithm at a ladder of sizes, agreed over all ranks
     {
-        static const int cands[] = {ALGO_LL, ALGO_MESH_ONESHOT, ALGO_NVLS_ONESHOT, ALGO_MESH, ALGO_NVLS, ALGO_RING};
+        static const int cands[] = {ALGO_LL, ALGO_MESH_ONESHOT, ALGO_NVLS_ONESHOT, ALGO_MESH, ALGO_NVLS, ALGO_RING, ALGO_MESH_PIPE, ALGO_NVLS_PIPE};
         std::vector<uint64_t> sizes;
         for (uint64_t sz = 16u << 10; sz <= (256u << 20) && sz <= settings_.stage_half_bytes / 2; sz *= 4) sizes.push_back(sz);
         size_t maxb = sizes.empty() ? 0 : sizes.back();
@@ -100,10 +100,12 @@ HcclResult Communicator::calibrate(void *stream)
             std::vector<double> mine(sizes.size() * ALGO_COUNT, 0.0);
             for (size_t b = 0; b < sizes.size(); ++b) {
                 for (int algo : cands) {
-                    bool is_nvls = algo == ALGO_NVLS || algo == ALGO_NVLS_ONESHOT;
+                    bool is_nvls = algo == ALGO_NVLS || algo == ALGO_NVLS_ONESHOT || algo == ALGO_NVLS_PIPE;
+                    if ((algo == ALGO_MESH_PIPE || algo == ALGO_NVLS_PIPE) && sizes[b] < (16u << 20)) continue;
                     if (is_nvls && !nvls_) continue;
                     if (algo == ALGO_LL && (!ll_ok_ || sizes[b] > si_ll_max())) continue;
-                    if ((algo == ALGO_MESH_ONESHOT || algo == ALGO_NVLS_ONESHOT) && sizes[b] > (8u << 20)) continue;
+                    // with two ranks one-shot moves no more bytes than two-shot and saves a phase: a candidate at every size
+                    if ((algo == ALGO_MESH_ONESHOT || algo == ALGO_NVLS_ONESHOT) && sizes[b] > (8u << 20) && nranks_ > 2) continue;
                     if (algo == ALGO_RING && sizes[b] < (1u << 20)) continue;
                     int iters = sizes[b] <= (1u << 20) ? 12 : (sizes[b] <= (16u << 20) ? 6 : 3);
                     OpRequest rq;

@@ -36,6 +36,53 @@ def _time(fn, iters, sync):
     return ms
 
 
+def other_collectives(comm, world, rank, dist, max_over_ranks, sync):
+    """AllGather / ReduceScatter / Broadcast and AllReduce in bf16 and with max, 64 MiB per rank, next to NCCL
+    (torch.distributed on the same stream).  Ours is issued by the C loop; both are device-timed, max over ranks."""
+    from .. import _lib as L
+    rows = {}
+    mib = 64
+    iters = 8
+
+    def t_ours(coll, send, recv, count, dtype, **kw):
+        comm.repeat(coll, send, recv, count, dtype, 3, **kw)
+        sync()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        comm.repeat(coll, send, recv, count, dtype, iters, **kw)
+        b.record()
+        torch.cuda.synchronize()
+        assert comm.sync() == 0, comm.describe_status()
+        return max_over_ranks(a.elapsed_time(b) / iters)
+
+    def t_nccl(fn):
+        return max_over_ranks(_time(fn, iters, sync))
+
+    def row(name, ours_ms, nccl_ms, nbytes):
+        rows[name] = {"bytes_per_rank": nbytes, "ours_us": round(ours_ms * 1e3, 1), "nccl_us": round(nccl_ms * 1e3, 1),
+                      "ours_GBps": round(nbytes / ours_ms / 1e6, 1), "nccl_GBps": round(nbytes / nccl_ms / 1e6, 1),
+                      "speedup_vs_nccl": round(nccl_ms / ours_ms, 3)}
+
+    for dt, hd, name in ((torch.bfloat16, L.BFP16, "bf16"), (torch.float32, L.FP32, "fp32")):
+        es = 2 if dt == torch.bfloat16 else 4
+        n = (mib << 20) // es
+        small = torch.randn(n, device="cuda").to(dt)
+        big = torch.randn(n * world, device="cuda").to(dt)
+        big2 = torch.empty_like(big)
+        small2 = torch.empty_like(small)
+        # AllGather: 64 MiB sent by each rank; bandwidth counted on the gathered bytes per rank as hccl_test does for the send size
+        row("allgather_%s" % name, t_ours(L.ALLGATHER, small, big2, n, hd), t_nccl(lambda: dist.all_gather_into_tensor(big2, small)), n * es)
+        row("reducescatter_sum_%s" % name, t_ours(L.REDUCE_SCATTER, big, small2, n, hd), t_nccl(lambda: dist.reduce_scatter_tensor(small2, big)), n * es)
+        if name == "bf16":
+            row("allreduce_sum_bf16", t_ours(L.ALLREDUCE, small, small2, n, hd), t_nccl(lambda: dist.all_reduce(small2)), n * es)
+        else:
+            row("allreduce_max_fp32", t_ours(L.ALLREDUCE, small, small2, n, hd, op=L.MAX),
+                t_nccl(lambda: dist.all_reduce(small2, op=dist.ReduceOp.MAX)), n * es)
+            row("broadcast_fp32", t_ours(L.BROADCAST, small, small, n, hd, root=0), t_nccl(lambda: dist.broadcast(small2, src=0)), n * es)
+        del small, big, big2, small2
+    return rows
+
+
 def run(comm, world, rank, dist, max_over_ranks, sync, time_steps):
     out = {}
     peak_tflops, peak_kind = _peaks()
@@ -99,6 +146,12 @@ def run(comm, world, rank, dist, max_over_ranks, sync, time_steps):
     row["speedup_vs_cublas_nccl"] = round(tb / t, 3)
     out["gemm_rs"] = row
     out["shape"] = {"tokens": TOKENS, "hidden": HIDDEN, "ffn_per_gpu": fl, "dtype": "bf16"}
+    del x_shard, w_up, w_down, h, y, o, xfull, part
+    if dist is not None:
+        try:
+            out["collectives_vs_nccl"] = other_collectives(comm, world, rank, dist, max_over_ranks, sync)
+        except Exception as e:  # a side table never takes the rest down
+            out["collectives_vs_nccl"] = {"error": repr(e)[:300]}
     try:
         from . import moe
         out["moe"] = moe.bench(comm, world, rank, dist, max_over_ranks, sync)

@@ -262,7 +262,7 @@ def scenario_perf(c, p, r, args):
         if os.environ.get("PERF_ALGOS"):
             algos = [L.ALGO_NAMES.index(x) for x in os.environ["PERF_ALGOS"].split(",") if x in L.ALGO_NAMES and (nv or "nvls" not in x)]
         for algo in algos:
-            if algo in (L.ALGO_MESH_ONESHOT, L.ALGO_NVLS_ONESHOT) and size > (4 << 20):
+            if algo in (L.ALGO_MESH_ONESHOT, L.ALGO_NVLS_ONESHOT) and size > (4 << 20) and p > 2:
                 continue
             if algo in (L.ALGO_MESH_PIPE, L.ALGO_NVLS_PIPE) and size < (4 << 20):
                 continue
