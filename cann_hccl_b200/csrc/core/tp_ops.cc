@@ -128,7 +128,7 @@ HcclResult Communicator::tp_all_gather_matmul(const void *const *x_shard, const 
     }
     stats_.launches++;
     stats_.ops[COLL_ALLGATHER]++;
-    int ncomm = nranks_ > 1 ? 8 : 1;
+    int ncomm = 8;  // the launcher drops them for a single rank
     if (const char *e = getenv("HCCL_TP_COMM_CTAS")) ncomm = std::max(1, atoi(e));
     return launch_tp_gemm(P.data(), A.data(), B.data(), nl, ncomm, stream);
 }

@@ -301,6 +301,7 @@ __device__ void comm_role_ag(const TpGemmParams &P, SharedStorage &S, int c, int
     const uint64_t deadline = global_timer_ns() + P.timeout_ns;
     volatile uint32_t *fail = &S.fail;
     if (threadIdx.x != 0) return;  // one thread drives the bulk copies
+    if (p == 1) return;            // nobody to serve and nothing to fetch: the GEMM reads the caller's rows directly
     uint32_t g = 0;
     const uint64_t mine_per_call = c < per ? (uint64_t)(per - c + nc - 1) / nc : 0;  // tiles of a shard that comm CTA c handles
     const uint64_t ready_base = 2 * (uint64_t)p + m_tiles + c;
@@ -703,10 +704,10 @@ HcclResult launch_tp_gemm(TpGemmParams *P, const void *const *A, const void *con
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     // AG: a few CTAs only move data (bulk asynchronous copies); RS needs none (reduce tail on every CTA)
-    if (P0.mode != TP_MODE_AG) n_comm_ctas = 0;
+    if (P0.mode != TP_MODE_AG || P0.nranks == 1) n_comm_ctas = 0;  // a single rank has nothing to move: every CTA computes
     else if (n_comm_ctas < 1) n_comm_ctas = 1;
     int per_rank = sms / nlocal;  // all CTAs of all local ranks must be resident together
-    if (n_comm_ctas > per_rank / 4) n_comm_ctas = std::max(1, per_rank / 4);
+    if (n_comm_ctas > per_rank / 4) n_comm_ctas = n_comm_ctas ? std::max(1, per_rank / 4) : 0;
     if (n_comm_ctas > kMaxCommCtas) n_comm_ctas = kMaxCommCtas;
     // with communication every rank must run the same grid (completion counters count CTAs)
     int total = (P0.M / BM) * (P0.N / BN);

@@ -116,6 +116,12 @@ def run(comm, world, rank, dist, max_over_ranks, sync, time_steps):
     tb = max_over_ranks(_time(base_ag, iters, sync))
     row["cublas_nccl_ms"] = round(tb, 4)
     row["speedup_vs_cublas_nccl"] = round(tb / t, 3)
+    # numerics of the fused kernel against the cuBLAS + NCCL result of the same operands (both bf16 outputs)
+    y_ref = y.clone()
+    fused_tp.all_gather_matmul(comm, x_shard, w_up, out=y)
+    assert comm.sync() == 0, comm.describe_status()
+    err = float((y.float() - y_ref.float()).norm() / (y_ref.float().norm() + 1e-12))
+    row["rel_err_vs_cublas_nccl"] = round(max_over_ranks(err), 6)
     if world > 1:
         # the same with the shard in registered symmetric memory: the peers pull it in place, no staging copy
         handle, bufs = comm.symmetric_empty(x_shard.numel(), torch.bfloat16)
@@ -126,8 +132,11 @@ def run(comm, world, rank, dist, max_over_ranks, sync, time_steps):
         row["registered_shard_ms"] = round(tz, 4)
         row["registered_shard_speedup_vs_cublas_nccl"] = round(tb / tz, 3)
         row["registered_shard_roofline_fraction"] = round(roof_ms / tz, 3)
+        err = float((y.float() - y_ref.float()).norm() / (y_ref.float().norm() + 1e-12))
+        row["registered_shard_rel_err"] = round(max_over_ranks(err), 6)
         del xz, bufs
         comm.mem_free(handle)
+    del y_ref
     out["ag_gemm"] = row
     # ---- H W_down^T -> reduce-scatter
     t = max_over_ranks(_time(lambda: fused_tp.matmul_reduce_scatter(comm, h, w_down, out=o), iters, sync))
@@ -144,6 +153,12 @@ def run(comm, world, rank, dist, max_over_ranks, sync, time_steps):
     tb = max_over_ranks(_time(base_rs, iters, sync))
     row["cublas_nccl_ms"] = round(tb, 4)
     row["speedup_vs_cublas_nccl"] = round(tb / t, 3)
+    o_ref = o.clone()
+    fused_tp.matmul_reduce_scatter(comm, h, w_down, out=o)
+    assert comm.sync() == 0, comm.describe_status()
+    err = float((o.float() - o_ref.float()).norm() / (o_ref.float().norm() + 1e-12))
+    row["rel_err_vs_cublas_nccl"] = round(max_over_ranks(err), 6)
+    del o_ref
     out["gemm_rs"] = row
     out["shape"] = {"tokens": TOKENS, "hidden": HIDDEN, "ffn_per_gpu": fl, "dtype": "bf16"}
     del x_shard, w_up, w_down, h, y, o, xfull, part
