@@ -552,6 +552,29 @@ void ag_mesh(Prog &P, const Slots &S, uint64_t in_off, bool uniform, uint64_t d_
         }
     }
 }
+// Push variant of the mesh AllGather (role of the reference's AllGatherMeshDirect, all_gather_mesh_direct.cc, and of its
+// AIV all-to-all push kernels): step i of rank r stores r's block straight into the staging slot r of rank (r+i)%p and
+// signals that one rank; receivers copy each slot out as its flag arrives.  One remote store pass instead of a local staging
+// copy followed by remote loads: the sender's input is read once and nothing waits for a round trip.
+void ag_push(Prog &P, const Slots &S, uint64_t in_off)
+{
+    const int p = P.p;
+    for (int r = 0; r < p; ++r) {
+        P.add(r, P.copy(BUF_IN, RANK_SELF, in_off, BUF_OUT, RANK_SELF, S.out_off[r], S.len[r]));  // step 0: own block
+        for (int i = 1; i < p; ++i) {  // step i: push to the i-th rank after me
+            int q = (r + i) % p;
+            Step c = P.copy(BUF_IN, RANK_SELF, in_off, BUF_STAGE, q, S.st_off[r], S.len[r]);
+            c.sig_rank = (int16_t)q;
+            P.add(r, c);
+        }
+        for (int i = 1; i < p; ++i) {  // the i-th rank before me pushed its block in its step i
+            int src = (r - i + p) % p;
+            Step c = P.copy(BUF_STAGE, RANK_SELF, S.st_off[src], BUF_OUT, RANK_SELF, S.out_off[src], S.len[src]);
+            P.wait_lane(c, src, i);
+            P.add(r, c);
+        }
+    }
+}
 void ag_ring(Prog &P, const Slots &S, uint64_t in_off)
 {
     for (int r = 0; r < P.p; ++r) {
@@ -1041,6 +1064,7 @@ HcclResult build_plan(const OpDesc &d, const std::vector<int> &local, Plan *plan
                 if (d.algo == ALGO_MESH) ag_mesh(P, S, io, uni, d.count * es, false);
                 else if (d.algo == ALGO_NVLS) ag_mesh(P, S, io, uni, d.count * es, true);
                 else if (d.algo == ALGO_RING) ag_ring(P, S, io);
+                else if (d.algo == ALGO_PAIRWISE) ag_push(P, S, io);
                 else if (d.algo == ALGO_RHD) ag_rhd(P, S, io);
                 else ok = false;
                 break;

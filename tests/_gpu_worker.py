@@ -115,6 +115,11 @@ def scenario_collectives(c, p, r, args):
         c.all_gather(gs[r], g, algo=algo)
         ok(c)
         assert torch.equal(g, torch.cat(gs))
+        if algo == L.ALGO_MESH:  # push variant
+            g.zero_()
+            c.all_gather(gs[r], g, algo=L.ALGO_PAIRWISE)
+            ok(c)
+            assert torch.equal(g, torch.cat(gs))
     for root in (0, p - 1):
         for algo in [L.ALGO_STAR, L.ALGO_RING, L.ALGO_TREE] + ([L.ALGO_NVLS] if nvls else []):
             b = inp(r, 50_000, torch.float32, seed=5)

@@ -152,6 +152,12 @@ def test_reduce_scatter_all_gather(comms, p, algo):
     ok(c)
     for o in gouts:
         assert torch.equal(o, torch.cat(gins))
+    if algo == L.ALGO_MESH:  # push variant: remote stores into the peers' staging slots
+        gouts = [torch.zeros(n * p, device="cuda", dtype=torch.int32) for _ in range(p)]
+        c.all_gather(gins, gouts, algo=L.ALGO_PAIRWISE)
+        ok(c)
+        for o in gouts:
+            assert torch.equal(o, torch.cat(gins))
 
 
 @pytest.mark.parametrize("p", [2, 5, 8])

@@ -115,7 +115,7 @@ def test_reduce_scatter(comms, p, algo, n):
 
 
 @pytest.mark.parametrize("p", RANKS)
-@pytest.mark.parametrize("algo", [L.ALGO_MESH, L.ALGO_RING, L.ALGO_RHD])
+@pytest.mark.parametrize("algo", [L.ALGO_MESH, L.ALGO_RING, L.ALGO_RHD, L.ALGO_PAIRWISE])
 @pytest.mark.parametrize("n", [1, 33, 1025])
 def test_all_gather(comms, p, algo, n):
     c = comms(p)
@@ -130,7 +130,7 @@ def test_all_gather(comms, p, algo, n):
 def test_all_gather_in_place_large(comms):
     p, n = 4, 300_000
     c = comms(p)
-    for algo in [L.ALGO_MESH, L.ALGO_RING, L.ALGO_RHD]:
+    for algo in [L.ALGO_MESH, L.ALGO_RING, L.ALGO_RHD, L.ALGO_PAIRWISE]:
         ins = make_inputs(p, n, np.float32)
         outs = [np.zeros(n * p, np.float32) for _ in range(p)]
         for r in range(p):
@@ -161,6 +161,12 @@ def test_v_variants(comms, p, algo):
     for o in outs:
         for j in range(p):
             np.testing.assert_array_equal(o[int(displs[j]):int(displs[j] + counts[j])], ins[j])
+    if algo == L.ALGO_MESH:  # the push variant exists for the gather side only
+        outs = [np.full(total, -7, np.float32) for _ in range(p)]
+        c.all_gather_v(ins, outs, counts, displs, algo=L.ALGO_PAIRWISE)
+        for o in outs:
+            for j in range(p):
+                np.testing.assert_array_equal(o[int(displs[j]):int(displs[j] + counts[j])], ins[j])
     # ReduceScatterV
     ins = [rng.standard_normal(total).astype(np.float32) for _ in range(p)]
     outs = [np.zeros(max(1, int(counts[r])), np.float32) for r in range(p)]
