@@ -1,0 +1,242 @@
+"""hccl_test-shaped command line: sweep one collective over message sizes and print, per size, the columns of the
+reference's external HCCL-Test tool (its README: `mpirun -n 8 ./bin/all_reduce_test -b 8K -e 64M -f 2 -d fp32 -o sum -p 8`,
+output `data_size`, `aveg_time` us, `alg_bandwidth` GB/s, `check_result`).
+
+    python -m cann_hccl_b200.utils.hccl_test all_reduce_test -b 8K -e 64M -f 2 -d fp32 -o sum -p 8
+    python -m cann_hccl_b200.utils.hccl_test all_gather_test -b 1K -e 1M -f 4 -d int32 -p 4 --host     # CPU ranks
+
+One process per rank is started by this program itself (no mpirun): rank 0 writes the root info to a temporary file, the
+others read it.  On GPUs rank r uses device r; the timed calls are issued back to back from C and timed with CUDA events
+(host transport: wall clock), `aveg_time` is the maximum over ranks.  `check_result` compares every rank's output with the
+numpy reference built from the seeded inputs of all ranks (uniform[-1,1) floats / small integers, seed 1234 + rank).
+
+Tests: all_reduce_test, all_gather_test, reduce_scatter_test, broadcast_test, reduce_test, scatter_test, gather_test,
+alltoall_test.  `-b/-e` are bytes per rank of the collective's `count` argument times the element size (the send count for
+all_gather / gather / alltoall, the receive count for reduce_scatter / scatter).
+"""
+import argparse
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+TESTS = ("all_reduce_test", "all_gather_test", "reduce_scatter_test", "broadcast_test", "reduce_test", "scatter_test", "gather_test",
+         "alltoall_test")
+NP_DTYPES = {"int8": np.int8, "uint8": np.uint8, "int16": np.int16, "uint16": np.uint16, "int32": np.int32, "uint32": np.uint32,
+             "int64": np.int64, "uint64": np.uint64, "fp16": np.float16, "fp32": np.float32, "fp64": np.float64, "bfp16": None}
+OPS = {"sum": 0, "prod": 1, "max": 2, "min": 3}
+
+
+def parse_size(s):
+    s = s.strip().upper()
+    mult = 1
+    if s[-1] in "KMG":
+        mult = {"K": 1 << 10, "M": 1 << 20, "G": 1 << 30}[s[-1]]
+        s = s[:-1]
+    return int(float(s) * mult)
+
+
+def make_input(rank, n, dtype_name, seed_base=1234):
+    """Seeded input of one rank as a numpy array (bfp16 is produced as float32 values that are exact in bfloat16)."""
+    rng = np.random.default_rng(seed_base + rank)
+    if dtype_name in ("fp16", "fp32", "fp64", "bfp16"):
+        x = rng.uniform(-1, 1, n).astype(np.float32)
+        if dtype_name == "bfp16":
+            x = (x.view(np.uint32) & np.uint32(0xFFFF0000)).view(np.float32)
+            return x
+        return x.astype(NP_DTYPES[dtype_name])
+    return rng.integers(0, 3, n).astype(NP_DTYPES[dtype_name])
+
+
+def reference(test, ins, op, p, rank, root, count):
+    """numpy result of rank `rank` (None when the rank receives nothing)."""
+    def red(arrs):
+        acc = arrs[0].astype(np.float64) if arrs[0].dtype.kind == "f" else arrs[0].copy()
+        for a in arrs[1:]:
+            b = a.astype(np.float64) if a.dtype.kind == "f" else a
+            acc = {0: acc + b, 1: acc * b, 2: np.maximum(acc, b), 3: np.minimum(acc, b)}[op]
+        return acc
+    if test == "all_reduce_test":
+        return red(ins)
+    if test == "reduce_test":
+        return red(ins) if rank == root else None
+    if test == "all_gather_test":
+        return np.concatenate(ins)
+    if test == "gather_test":
+        return np.concatenate(ins) if rank == root else None
+    if test == "reduce_scatter_test":
+        return red(ins)[rank * count:(rank + 1) * count]
+    if test == "broadcast_test":
+        return ins[root]
+    if test == "scatter_test":
+        return ins[root][rank * count:(rank + 1) * count]
+    if test == "alltoall_test":
+        return np.concatenate([ins[q][rank * count:(rank + 1) * count] for q in range(p)])
+    raise ValueError(test)
+
+
+def in_elems(test, count, p):
+    return count * p if test in ("reduce_scatter_test", "scatter_test", "alltoall_test") else count
+
+
+def out_elems(test, count, p):
+    return count * p if test in ("all_gather_test", "gather_test", "alltoall_test") else count
+
+
+def worker(a):
+    rank, p = a.rank, a.nranks
+    if a.host:
+        os.environ["HCCL_TRANSPORT"] = "host"
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+    import cann_hccl_b200 as H
+    from cann_hccl_b200 import _lib as L
+    device = not a.host
+    torch = None
+    if device:
+        import torch
+        torch.cuda.set_device(rank % torch.cuda.device_count())
+    # rendezvous through a file
+    if rank == 0:
+        info = H.Communicator.get_root_info()
+        with open(a.root_file + ".tmp", "wb") as f:
+            f.write(info)
+        os.rename(a.root_file + ".tmp", a.root_file)
+    else:
+        t0 = time.time()
+        while not os.path.exists(a.root_file):
+            if time.time() - t0 > 60:
+                raise RuntimeError("root info never appeared")
+            time.sleep(0.01)
+        info = open(a.root_file, "rb").read()
+    cfg = L.CommConfig.default()
+    cfg.hcclBufferSize = a.buffsize
+    comm = H.Communicator.init_root(p, info, rank, config=cfg, device=device)
+    coll = {"all_reduce_test": L.ALLREDUCE, "all_gather_test": L.ALLGATHER, "reduce_scatter_test": L.REDUCE_SCATTER, "broadcast_test": L.BROADCAST,
+            "reduce_test": L.REDUCE, "scatter_test": L.SCATTER, "gather_test": L.GATHER, "alltoall_test": L.ALLTOALL}[a.test]
+    hd = {"int8": L.INT8, "uint8": L.UINT8, "int16": L.INT16, "uint16": L.UINT16, "int32": L.INT32, "uint32": L.UINT32, "int64": L.INT64,
+          "uint64": L.UINT64, "fp16": L.FP16, "fp32": L.FP32, "fp64": L.FP64, "bfp16": L.BFP16}[a.dtype]
+    es = 2 if a.dtype == "bfp16" else np.dtype(NP_DTYPES[a.dtype]).itemsize
+    op = OPS[a.op]
+    algo = L.ALGO_NAMES.index(a.algo) if a.algo else L.ALGO_AUTO
+    if rank == 0:
+        print("the minbytes is %d, maxbytes is %d, iters is %d, warmup_iters is %d" % (a.minbytes, a.maxbytes, a.iters, a.warmup))
+        print("%-16s %-16s %-22s %s" % ("data_size(Bytes):", "aveg_time(us):", "alg_bandwidth(GB/s):", "check_result:"))
+    size = a.minbytes
+    failed = False
+    while size <= a.maxbytes:
+        count = max(1, size // es)
+        n_in, n_out = in_elems(a.test, count, p), out_elems(a.test, count, p)
+        mine = make_input(rank, n_in, a.dtype)
+        if device:
+            tdt = {"bfp16": torch.bfloat16}.get(a.dtype)
+            send = torch.from_numpy(mine).cuda().to(tdt) if tdt else torch.from_numpy(mine).cuda()
+            recv = send if a.test == "broadcast_test" else torch.zeros(n_out, device="cuda", dtype=send.dtype)
+        else:
+            if a.dtype == "bfp16":
+                send = (mine.view(np.uint32) >> 16).astype(np.uint16)  # bf16 bit patterns
+            else:
+                send = mine
+            recv = send if a.test == "broadcast_test" else np.zeros(n_out, send.dtype)
+        kw = dict(op=op, root=a.root, algo=algo)
+
+        def call(k):
+            if k > 0:
+                comm.repeat(coll, send, recv, count, hd, k, **kw)
+
+        # one checked call, then warm-up and the timed loop
+        call(1)
+        if device:
+            assert comm.sync() == 0, comm.describe_status()
+        ok = True
+        if a.check:
+            ins = [make_input(q, n_in, a.dtype) for q in range(p)]
+            ref = reference(a.test, ins, op, p, rank, a.root, count)
+            if ref is not None:
+                if device:
+                    got = recv.float().cpu().numpy() if a.dtype in ("bfp16", "fp16") else recv.cpu().numpy()
+                elif a.dtype == "bfp16":
+                    got = (recv.astype(np.uint32) << 16).view(np.float32)
+                else:
+                    got = recv
+                if np.asarray(ref).dtype.kind == "f" or got.dtype.kind == "f":
+                    tol = {"fp64": 1e-12, "fp32": 1e-5, "fp16": 4e-3, "bfp16": 2e-2}.get(a.dtype, 1e-5) * max(1, p // 2)
+                    ok = bool(np.allclose(got.astype(np.float64), np.asarray(ref, np.float64), rtol=tol, atol=tol))
+                else:
+                    ok = bool(np.array_equal(got, ref.astype(got.dtype)))
+        call(a.warmup)
+        comm.barrier()
+        if device:
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            call(a.iters)
+            e1.record()
+            torch.cuda.synchronize()
+            assert comm.sync() == 0, comm.describe_status()
+            us = e0.elapsed_time(e1) * 1e3 / a.iters
+        else:
+            t0 = time.perf_counter()
+            call(a.iters)
+            us = (time.perf_counter() - t0) * 1e6 / a.iters
+        # maximum over ranks and the conjunction of the checks, gathered over the control plane
+        import struct
+        blob = comm.exchange("t%d" % size, struct.pack("<dI", us, 1 if ok else 0))
+        vals = [struct.unpack("<dI", b) for b in blob]
+        us = max(v[0] for v in vals)
+        ok = all(v[1] for v in vals)
+        failed |= not ok
+        if rank == 0:
+            print("%-16d %-16.2f %-22.5f %s" % (count * es, us, count * es / us / 1e3, "success" if ok else "failed"), flush=True)
+        del send, recv
+        size = size * a.factor if a.factor > 1 else size + max(1, a.step)
+    code = comm.destroy()
+    return 1 if failed or code != 0 else 0
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(prog="hccl_test", description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("test", choices=TESTS)
+    ap.add_argument("-b", "--minbytes", default="8K")
+    ap.add_argument("-e", "--maxbytes", default="64M")
+    ap.add_argument("-f", "--factor", type=int, default=2, help="multiply the size by this each step (0/1: use -i)")
+    ap.add_argument("-i", "--step", type=int, default=0, help="size increment in bytes when -f is 0 or 1")
+    ap.add_argument("-d", "--dtype", default="fp32", choices=sorted(NP_DTYPES))
+    ap.add_argument("-o", "--op", default="sum", choices=sorted(OPS))
+    ap.add_argument("-p", "--nranks", type=int, default=0, help="ranks (default: visible GPUs, or 2 with --host)")
+    ap.add_argument("-n", "--iters", type=int, default=20)
+    ap.add_argument("-w", "--warmup", type=int, default=5)
+    ap.add_argument("-c", "--check", type=int, default=1)
+    ap.add_argument("-r", "--root", type=int, default=0)
+    ap.add_argument("--algo", default="", help="force an algorithm (mesh, ring, rhd, nvls, ...)")
+    ap.add_argument("--host", action="store_true", help="CPU ranks over the host-memory transport")
+    ap.add_argument("--buffsize", type=int, default=640, help="staging MB per direction (HCCL_BUFFSIZE)")
+    ap.add_argument("--rank", type=int, default=-1, help=argparse.SUPPRESS)
+    ap.add_argument("--root-file", default="", help=argparse.SUPPRESS)
+    a = ap.parse_args(argv)
+    a.minbytes, a.maxbytes = parse_size(a.minbytes), parse_size(a.maxbytes)
+    if a.rank >= 0:
+        return worker(a)
+    if a.nranks <= 0:
+        if a.host:
+            a.nranks = 2
+        else:
+            import torch
+            a.nranks = max(1, torch.cuda.device_count())
+    tmp = tempfile.mkdtemp(prefix="hccl_test_")
+    root_file = os.path.join(tmp, "root.bin")
+    base = [sys.executable, "-m", "cann_hccl_b200.utils.hccl_test"] + [x for x in (argv if argv is not None else sys.argv[1:])]
+    if "-p" not in base and "--nranks" not in base:
+        base += ["-p", str(a.nranks)]
+    env = dict(os.environ)
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    env["PYTHONPATH"] = root + os.pathsep + env.get("PYTHONPATH", "")
+    procs = [subprocess.Popen(base + ["--rank", str(r), "--root-file", root_file], env=env) for r in range(a.nranks)]
+    codes = [p.wait() for p in procs]
+    return 0 if all(c == 0 for c in codes) else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

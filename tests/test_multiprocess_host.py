@@ -77,3 +77,23 @@ def test_stuck_detection_via_heartbeat():
            "HCCL_CONSISTENCY_CHECK": "0"}
     res = run_ranks(2, "stuck", env=env)
     assert "stuck peer reported" in res[1][1]
+
+
+@pytest.mark.parametrize("argv", [
+    ["all_reduce_test", "-b", "8K", "-e", "128K", "-f", "4", "-d", "fp32", "-o", "sum", "-p", "3"],
+    ["reduce_scatter_test", "-b", "1K", "-e", "16K", "-f", "4", "-d", "bfp16", "-o", "max", "-p", "2"],
+    ["all_gather_test", "-b", "1000", "-e", "3000", "-f", "0", "-i", "1000", "-d", "int8", "-p", "4", "--algo", "ring"],
+    ["broadcast_test", "-b", "4K", "-e", "4K", "-d", "int64", "-p", "3", "-r", "1"],
+])
+def test_hccl_test_command_line(argv):
+    """The hccl_test-shaped CLI prints the reference tool's columns and reports success for every size (CPU ranks)."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "cann_hccl_b200.utils.hccl_test"] + argv + ["--host", "-n", "3", "-w", "1"]
+    r = subprocess.run(cmd, cwd=root, capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stdout + r.stderr
+    lines = [ln.split() for ln in r.stdout.splitlines() if ln and ln[0].isdigit()]
+    assert "aveg_time(us):" in r.stdout and "alg_bandwidth(GB/s):" in r.stdout and "check_result:" in r.stdout
+    assert lines and all(ln[3] == "success" and float(ln[1]) > 0 for ln in lines), r.stdout
