@@ -3,7 +3,12 @@
 #include <time.h>
 #include <unistd.h>
 #include <cstring>
+#include <algorithm>
+#include <fstream>
+#include <sstream>
 #include "bootstrap/socket.h"
+#include "common/env.h"
+#include "common/json.h"
 #include "common/log.h"
 
 namespace hcclb {
@@ -30,6 +35,25 @@ Hub *Hub::start(const std::string &ip, int port, int family, std::string *err)
         if (err) *err = "cannot listen on port " + std::to_string(port);
         delete h;
         return nullptr;
+    }
+    // connection whitelist (reference: framework/common/src/topo/hccl_whitelist.cc: JSON file with a "host_ip" array, enabled
+    // by HCCL_WHITELIST_DISABLE=0): a hub that cannot load its list refuses to start rather than run open
+    const EnvConfig &env = env_config();
+    if (env.whitelist_enable) {
+        std::ifstream f(env.whitelist_file);
+        std::stringstream ss;
+        ss << f.rdbuf();
+        JsonValue v;
+        std::string jerr;
+        const JsonValue *ips = nullptr;
+        if (!f || !json_parse(ss.str(), &v, &jerr) || !(ips = v.get("host_ip")) || ips->type != JsonValue::ARR) {
+            if (err) *err = "whitelist file " + env.whitelist_file + " cannot be read as {\"host_ip\": [...]}" + (jerr.empty() ? "" : ": " + jerr);
+            delete h;
+            return nullptr;
+        }
+        for (const JsonValue &ipv : ips->arr)
+            if (ipv.type == JsonValue::STR) h->whitelist_.push_back(ipv.str);
+        h->whitelist_on_ = true;
     }
     h->th_ = std::thread([h] { h->run(); });
     return h;
@@ -141,6 +165,14 @@ void Hub::run()
         if (pf[1].revents) break;
         if (pf[0].revents & POLLIN) {
             int fd = net::accept_timeout(lfd_, 0);
+            if (fd >= 0 && whitelist_on_) {
+                std::string peer = net::peer_address(fd);
+                if (std::find(whitelist_.begin(), whitelist_.end(), peer) == whitelist_.end()) {
+                    HLOG_ERROR("connection from %s refused: address not in the whitelist", peer.c_str());
+                    net::close_fd(fd);
+                    fd = -1;
+                }
+            }
             if (fd >= 0) clients_.push_back(fd);
         }
         for (size_t i = 2; i < pf.size(); ++i) {

@@ -62,6 +62,8 @@ private:
     std::thread th_;
     std::atomic<bool> stop_{false};
     std::vector<int> clients_;
+    bool whitelist_on_ = false;              // HCCL_WHITELIST_DISABLE=0: only the listed addresses may connect
+    std::vector<std::string> whitelist_;     // numeric addresses from HCCL_WHITELIST_FILE ("host_ip")
     std::map<std::string, Pending> pending_;
     std::map<std::string, std::map<uint32_t, Beat>> beats_;
 };

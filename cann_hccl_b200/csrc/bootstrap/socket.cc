@@ -96,6 +96,19 @@ int accept_timeout(int lfd, int timeout_ms)
     return fd;
 }
 
+std::string peer_address(int fd)
+{
+    sockaddr_storage ss;
+    socklen_t len = sizeof(ss);
+    if (getpeername(fd, (sockaddr *)&ss, &len) != 0) return "";
+    char buf[INET6_ADDRSTRLEN] = {0};
+    if (ss.ss_family == AF_INET) inet_ntop(AF_INET, &((sockaddr_in *)&ss)->sin_addr, buf, sizeof(buf));
+    else if (ss.ss_family == AF_INET6) inet_ntop(AF_INET6, &((sockaddr_in6 *)&ss)->sin6_addr, buf, sizeof(buf));
+    std::string a(buf);
+    if (a.rfind("::ffff:", 0) == 0) a = a.substr(7);
+    return a;
+}
+
 bool send_all(int fd, const void *buf, size_t len)
 {
     const char *p = (const char *)buf;

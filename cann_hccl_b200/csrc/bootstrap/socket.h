@@ -11,6 +11,8 @@ int tcp_listen(const std::string &ip, int *port, int family = 4);
 int tcp_connect(const std::string &ip, int port, int timeout_ms, int family = 4);
 // Accept with a bound; returns fd, -1 on error, -2 on timeout.
 int accept_timeout(int lfd, int timeout_ms);
+// Numeric address of the peer of a connected TCP socket ("" when unknown); IPv4-mapped IPv6 addresses come back as IPv4.
+std::string peer_address(int fd);
 bool send_all(int fd, const void *buf, size_t len);
 // Receive exactly len bytes; timeout_ms < 0 waits forever. Returns false on error / EOF / timeout.
 bool recv_all(int fd, void *buf, size_t len, int timeout_ms = -1);

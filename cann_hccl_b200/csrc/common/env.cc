@@ -144,6 +144,9 @@ EnvConfig parse_env(const std::map<std::string, std::string> &v)
     if (auto s = get("HCCL_CHANNELS")) { if (parse_int(*s, n) && n >= 0 && n <= 128) c.channels = (int)n; }
     if (auto s = get("HCCL_PIPE_CHUNK_KB")) { if (parse_int(*s, n) && n >= 16) c.pipe_chunk_bytes = (uint64_t)n << 10; }
     if (auto s = get("HCCL_NCCL_LIB")) c.ncc_lib = *s;
+    if (auto s = get("HCCL_WHITELIST_DISABLE")) c.whitelist_enable = *s == "0";
+    if (auto s = get("HCCL_WHITELIST_FILE")) c.whitelist_file = *s;
+    if (c.whitelist_enable && c.whitelist_file.empty()) fail(c, "HCCL_WHITELIST_DISABLE=0 needs HCCL_WHITELIST_FILE");
     if (auto s = get("HCCL_NVTX")) c.nvtx = *s == "1" || lower(*s) == "true";
     if (auto s = get("HCCL_OVERFLOW_CHECK")) c.overflow_check = *s == "1" || lower(*s) == "true";
     if (auto s = get("HCCL_STATS_DUMP")) c.stats_dump = *s;

@@ -37,6 +37,8 @@ struct EnvConfig {
     int channels = 0;              // HCCL_CHANNELS: force CTAs per op (0 = selector decides)
     uint64_t pipe_chunk_bytes = 0; // HCCL_PIPE_CHUNK_KB: chunk of the pipelined large-message algorithms (0 = default)
     std::string ncc_lib;           // HCCL_NCCL_LIB: path of libnccl.so.2 for Send/Recv
+    bool whitelist_enable = false; // HCCL_WHITELIST_DISABLE=0 switches the connection whitelist on (HCCL convention: 1 = off, the default)
+    std::string whitelist_file;    // HCCL_WHITELIST_FILE: JSON {"host_ip": ["a.b.c.d", ...]} of addresses that may connect to the bootstrap hub
     bool nvtx = false;             // HCCL_NVTX: NVTX range around every API-level operation
     bool overflow_check = false;   // HCCL_OVERFLOW_CHECK: scan the output of floating-point reductions for Inf / NaN
     std::string stats_dump;        // HCCL_STATS_DUMP: file that receives the statistics JSON when a communicator is destroyed

@@ -89,7 +89,7 @@ HcclResult Communicator::calibrate(void *stream)
     {
         static const int cands[] = {ALGO_LL, ALGO_MESH_ONESHOT, ALGO_NVLS_ONESHOT, ALGO_MESH, ALGO_NVLS, ALGO_RING, ALGO_MESH_PIPE, ALGO_NVLS_PIPE};
         std::vector<uint64_t> sizes;
-        for (uint64_t sz = 16u << 10; sz <= (256u << 20) && sz <= settings_.stage_half_bytes / 2; sz *= 4) sizes.push_back(sz);
+        for (uint64_t sz = 16u << 10; sz <= (256u << 20) && sz <= settings_.stage_half_bytes / 2; sz *= 2) sizes.push_back(sz);
         size_t maxb = sizes.empty() ? 0 : sizes.back();
         std::vector<void *> tin(nl), tout(nl);
         bool okalloc = maxb > 0;
@@ -110,8 +110,20 @@ HcclResult Communicator::calibrate(void *stream)
                     int iters = sizes[b] <= (1u << 20) ? 12 : (sizes[b] <= (16u << 20) ? 6 : 3);
                     OpRequest rq;
                     rq.coll = COLL_ALLREDUCE; rq.algo = algo; rq.count = sizes[b] / 4; rq.dtype = HCCL_DATA_TYPE_FP32; rq.redop = HCCL_REDUCE_SUM;
-                    rq.in = (const void *const *)tin.data(); rq.out = tout.data(); rq.stream = stream;
-                    mine[b * ALGO_COUNT + algo] = t.us(iters, [&] { HcclResult r = collective(rq); if (r != HCCL_SUCCESS) rc = r; });
+                    rq.stream = stream;
+                    // successive calls walk through disjoint windows of the buffers, as an application's tensors would: a
+                    // table measured on one L2-resident buffer favours the algorithms that re-read their input most
+                    const uint64_t nwin = std::max<uint64_t>(1, std::min<uint64_t>(8, maxb / sizes[b]));
+                    uint64_t call = 0;
+                    std::vector<const void *> win_in(nl);
+                    std::vector<void *> win_out(nl);
+                    mine[b * ALGO_COUNT + algo] = t.us(iters, [&] {
+                        const size_t off = (size_t)((call++ % nwin) * sizes[b]);
+                        for (int li = 0; li < nl; ++li) { win_in[li] = (const uint8_t *)tin[li] + off; win_out[li] = (uint8_t *)tout[li] + off; }
+                        rq.in = win_in.data(); rq.out = win_out.data();
+                        HcclResult r = collective(rq);
+                        if (r != HCCL_SUCCESS) rc = r;
+                    });
                 }
             }
             for (int li = 0; li < nl; ++li) { cudaFree(tin[li]); cudaFree(tout[li]); }

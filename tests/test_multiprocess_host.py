@@ -41,6 +41,26 @@ def test_one_sided_topology_overflow(tmp_path):
     assert len(lines) == 3 and all(d["ops"]["AllReduce"]["calls"] >= 2 for d in lines)
 
 
+def test_connection_whitelist(tmp_path):
+    """HCCL_WHITELIST_DISABLE=0: the bootstrap hub only serves addresses listed under "host_ip" in HCCL_WHITELIST_FILE."""
+    good = tmp_path / "wl_ok.json"
+    good.write_text('{"host_ip": ["10.1.2.3", "127.0.0.1"]}')
+    env = {"HCCL_WHITELIST_DISABLE": "0", "HCCL_WHITELIST_FILE": str(good), "HCCL_IF_IP": "127.0.0.1"}
+    res = run_ranks(2, "sweep", env=env)
+    assert all(code == 0 for code, _ in res)
+    bad = tmp_path / "wl_other.json"
+    bad.write_text('{"host_ip": ["10.1.2.3"]}')
+    env["HCCL_WHITELIST_FILE"] = str(bad)
+    env["HCCL_CONNECT_TIMEOUT"] = "5"
+    res = run_ranks(2, "sweep", env=env, expect_fail_ranks=(0, 1), timeout=60)
+    assert all(code != 0 for code, _ in res)
+    assert "not in the whitelist" in res[0][1]
+    # a hub that cannot load its list refuses to start
+    env["HCCL_WHITELIST_FILE"] = str(tmp_path / "missing.json")
+    res = run_ranks(1, "sweep", env=env, expect_fail_ranks=(0,), timeout=60)
+    assert res[0][0] != 0 and "whitelist file" in res[0][1]
+
+
 def test_param_mismatch_detected():
     res = run_ranks(3, "mismatch")
     assert all("mismatch detected" in out for _, out in res)
