@@ -107,7 +107,7 @@ def main():
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "yzh1703456/cann-hccl needs the CANN toolkit, Ascend NPUs and the closed "
-                          "libhccl_plf.so; the tree has no setup.py/pyproject.toml, so pip cannot install it (see DESIGN.md)"}))
+                          "libhccl_plf.so; the tree has no setup.py/pyproject.toml, so pip cannot install it"}))
         return 0
 
     import torch
