@@ -280,3 +280,35 @@ def test_headers_compile_as_c99_and_library_runs_from_c(tmp_path):
     env = dict(os.environ, HCCL_TRANSPORT="host")
     r = subprocess.run([exe], capture_output=True, text=True, env=env, timeout=120)
     assert r.returncode == 0 and "c consumer ok" in r.stdout, r.stdout + r.stderr
+
+
+def test_plan_verifier_property_sweep():
+    """Random (collective, algorithm, ranks, count, dtype, channels): every schedule the generators emit stays inside its
+    buffers (hypothesis drives the static verifier; no communicator involved)."""
+    hyp = pytest.importorskip("hypothesis")
+    from hypothesis import given, settings, strategies as st
+    lib = L.lib()
+    table = {
+        L.ALLREDUCE: [L.ALGO_MESH, L.ALGO_MESH_ONESHOT, L.ALGO_RING, L.ALGO_RHD, L.ALGO_MESH_PIPE],
+        L.ALLGATHER: [L.ALGO_MESH, L.ALGO_RING, L.ALGO_RHD, L.ALGO_PAIRWISE],
+        L.REDUCE_SCATTER: [L.ALGO_MESH, L.ALGO_RING, L.ALGO_RHD],
+        L.BROADCAST: [L.ALGO_STAR, L.ALGO_RING, L.ALGO_TREE],
+        L.REDUCE: [L.ALGO_STAR, L.ALGO_RING, L.ALGO_TREE, L.ALGO_RHD],
+        L.SCATTER: [L.ALGO_STAR, L.ALGO_RING],
+        L.GATHER: [L.ALGO_STAR, L.ALGO_RING],
+        L.ALLTOALL: [L.ALGO_MESH, L.ALGO_PAIRWISE],
+    }
+    pairs = [(c, a) for c, algos in table.items() for a in algos]
+    msg = C.create_string_buffer(512)
+
+    @settings(max_examples=400, deadline=None)
+    @given(st.sampled_from(pairs), st.integers(2, 16), st.integers(1, 200_000), st.sampled_from([L.INT8, L.FP16, L.FP32, L.FP64]),
+           st.integers(1, 16))
+    def run(pair, p, count, dtype, nchan):
+        coll, algo = pair
+        if algo == L.ALGO_MESH_PIPE and nchan < 3:
+            nchan = 3
+        rc = lib.HcclB200PlanCheck(coll, algo, p, count, dtype, nchan, 1 << 30, -1, 0, msg, 512)
+        assert rc == L.SUCCESS, (coll, L.ALGO_NAMES[algo], p, count, dtype, nchan, msg.value)
+
+    run()
