@@ -70,6 +70,22 @@ struct Prog {
         st.wait_clo = 0;
         st.wait_cn = (uint16_t)nchan;
     }
+    // Every channel of rank r stops here until all of the rank's own channels have arrived.  Needed where later steps write
+    // the caller's receive buffer in pieces that do not line up with the pieces in which earlier steps read the send buffer:
+    // when both are the same memory (in place), one channel would otherwise overwrite input that a slower channel of the same
+    // rank has yet to read.  Two steps: signal my own flag words, then wait for all of them (and tell the peers).
+    void own_channels_barrier(int r)
+    {
+        Step sig = mk(ST_NOP);
+        sig.sig_rank = (int16_t)r;
+        sig.flags |= SF_INCLUDE_SELF;
+        int i = add(r, sig);
+        Step w = mk(ST_NOP);
+        wait_allch(w, r, i);
+        w.flags |= SF_INCLUDE_SELF;
+        w.sig_rank = RANK_ALL;  // generators chain on "the last step of rank r": it has to be one that peers can wait for
+        add(r, w);
+    }
     Step copy(uint8_t ab, int ar, uint64_t aoff, uint8_t db, int dr, uint64_t doff, uint64_t count) const
     {
         Step st = mk(ST_COPY);
@@ -155,12 +171,14 @@ void ar_mesh_twoshot(Prog &P, const OpDesc &d, bool nvls)
     // writes an element after having read it
     uint64_t region2 = 0;
     for (int r = 0; r < P.p; ++r) {
-        int last = 0;
-        for (int j = 0; j < P.p; ++j) {  // per-slice copies keep channel lanes aligned with the consumers
-            Step c = P.copy(BUF_IN, RANK_SELF, uoff + S.off(j) * P.es, BUF_STAGE, RANK_SELF, S.off(j) * P.es, S.len(j));
-            if (j == P.p - 1) c.sig_rank = RANK_ALL;
-            last = P.add(r, c);
-        }
+        // one step copies all p slices, each split over the channels on its own: channel c of every rank stages piece c of
+        // every slice, so the consumers' lanes line up with the producers' (a gather from this rank's own input)
+        Step cin = P.mk(ST_GATHER_ALL);
+        cin.a_buf = BUF_IN; cin.a_rank = RANK_SELF; cin.a_off = uoff; cin.a_stride = S.sl * P.es;
+        cin.d_buf = BUF_STAGE; cin.d_off = 0; cin.d_stride = S.sl * P.es;
+        cin.count = S.sl; cin.limit = n;
+        cin.sig_rank = RANK_ALL;
+        int last = P.add(r, cin);
         Step red = P.mk(nvls ? ST_MC_REDUCE : ST_REDUCE_ALL);
         red.a_buf = BUF_STAGE; red.a_rank = RANK_ALL; red.a_off = S.off(r) * P.es;
         red.count = S.len(r);
@@ -382,6 +400,8 @@ void ar_rhd(Prog &P, const OpDesc &d)
         st.sig_rank = RANK_ALL;
         P.add(r, st);
     }
+    // the halving steps write the receive buffer in ranges unrelated to the lanes of the input reads above
+    for (int r = 0; r < P.p; ++r) P.own_channels_barrier(r);
     auto off = [&](int b) { return S.off(b) * P.es; };
     hd_reduce_scatter(P, H, off, [&](int b) { return uoff + S.off(b) * P.es; });
     // doubling (all-gather) inside the block
@@ -498,6 +518,7 @@ void rs_rhd(Prog &P, const Slots &S, uint64_t out_off)
             P.add(r, st);
         }
     }
+    for (int r = 0; r < p; ++r) P.own_channels_barrier(r);  // in place: all input reads before the first output write
     auto off = [&](int b) -> uint64_t {
         if (b >= H.B) return S.total_stage;
         int lo, hi;
@@ -777,6 +798,7 @@ void reduce_rhd(Prog &P, const OpDesc &d)
         st.sig_rank = RANK_ALL;
         P.add(r, st);
     }
+    P.own_channels_barrier(d.root);  // in place at the root: all of its input reads before its first output write
     auto off = [&](int b) { return S.off(b) * P.es; };
     hd_reduce_scatter(P, H, off, [](int) { return ~0ull; });
     std::vector<int> lastidx(P.p);

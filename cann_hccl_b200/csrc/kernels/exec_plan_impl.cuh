@@ -89,6 +89,22 @@ __device__ __forceinline__ void copy_range(const uint8_t *a, uint8_t *d, uint8_t
     }
 }
 
+// Up to p blocks of at most one 16-byte vector per thread each: the loads of eight blocks are in flight before the first
+// store.  Not inlined: its 32 data registers stay out of the executor's main loop.
+static __device__ __noinline__ void gather_small_blocks(const uint8_t *const *src, uint8_t *const *dst, const uint64_t *bytes, int p)
+{
+    const uint64_t mine = (uint64_t)threadIdx.x * 16;
+    for (int i0 = 0; i0 < p; i0 += 8) {
+        uint4 v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            if (i0 + k < p && mine < bytes[i0 + k]) v[k] = ld_stream((const uint4 *)src[i0 + k] + threadIdx.x);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            if (i0 + k < p && mine < bytes[i0 + k]) ((uint4 *)dst[i0 + k])[threadIdx.x] = v[k];
+    }
+}
+
 // multicast store of a local range: d_mc = a on every rank
 __device__ __forceinline__ void copy_range_mc(const uint8_t *a, uint8_t *d_mc, uint64_t bytes)
 {
@@ -298,6 +314,9 @@ __global__ void __launch_bounds__(kExecThreads, 1) exec_plan_kernel(const RankCt
     const int es = dtype_size(a.dtype);
     __shared__ int s_fail;
     __shared__ const uint8_t *s_src[kMaxRanks];
+    __shared__ const uint8_t *s_gsrc[kMaxRanks];  // ST_GATHER_ALL: source, destination and bytes of every block of this channel
+    __shared__ uint8_t *s_gdst[kMaxRanks];
+    __shared__ uint64_t s_gbytes[kMaxRanks];
     if (tid == 0) s_fail = 0;
     __syncthreads();
     const int me = c.rank, p = c.nranks;
@@ -393,21 +412,34 @@ __global__ void __launch_bounds__(kExecThreads, 1) exec_plan_kernel(const RankCt
                 break;
             }
             case ST_GATHER_ALL: {
-                for (int i = 0; i < p; ++i) {
-                    int q = (me + i) % p;
-                    if (q == me && (s.flags & SF_SKIP_SELF)) continue;
+                // Small blocks (at most one 16-byte vector per thread and block): the loads of all blocks are issued before
+                // the first store, so the step costs one memory round trip instead of one per block (p NVLink latencies in
+                // the gather phase of a two-shot AllReduce of a few MiB).  Threads tid < p describe the blocks.
+                if (tid < p) {
+                    const int q = (me + tid) % p;
                     uint64_t cnt = s.count;
                     if (s.limit) {
                         uint64_t start = (uint64_t)q * s.count;
                         cnt = start >= s.limit ? 0 : (s.limit - start < s.count ? s.limit - start : s.count);
                     }
+                    if (q == me && (s.flags & SF_SKIP_SELF)) cnt = 0;
                     chan_range(cnt, es, s.chan_n, ci, lo, hi);
-                    if (hi <= lo) continue;
-                    int src_rank = s.a_rank == RANK_ALL ? q : RANK_SELF;
-                    copy_range(resolve_addr(c, a, s.a_buf, src_rank, s.a_off + (uint64_t)q * s.a_stride, half_off) + lo * es,
-                               resolve_addr(c, a, s.d_buf, RANK_SELF, s.d_off + (uint64_t)q * s.d_stride, half_off) + lo * es, nullptr,
-                               (hi - lo) * es, es);
+                    const int src_rank = s.a_rank == RANK_ALL ? q : RANK_SELF;
+                    s_gsrc[tid] = resolve_addr(c, a, s.a_buf, src_rank, s.a_off + (uint64_t)q * s.a_stride, half_off) + lo * es;
+                    s_gdst[tid] = resolve_addr(c, a, s.d_buf, RANK_SELF, s.d_off + (uint64_t)q * s.d_stride, half_off) + lo * es;
+                    s_gbytes[tid] = hi > lo ? (hi - lo) * es : 0;
                 }
+                __syncthreads();
+                bool small = true;
+                for (int i = 0; i < p; ++i)
+                    small = small && s_gbytes[i] <= (uint64_t)16 * blockDim.x && (s_gbytes[i] & 15) == 0 && aligned16(s_gsrc[i]) && aligned16(s_gdst[i]);
+                if (small) {
+                    gather_small_blocks(s_gsrc, s_gdst, s_gbytes, p);
+                } else {
+                    for (int i = 0; i < p; ++i)
+                        if (s_gbytes[i]) copy_range(s_gsrc[i], s_gdst[i], nullptr, s_gbytes[i], es);
+                }
+                __syncthreads();  // the block descriptions are rewritten by the next gather step
                 break;
             }
             default: break;
@@ -422,7 +454,7 @@ __global__ void __launch_bounds__(kExecThreads, 1) exec_plan_kernel(const RankCt
             const uint64_t val = flag_value(a, s, s.sig_val);
             if (s.sig_rank == RANK_ALL) {
                 if (tid < p && (tid != me || (s.flags & SF_INCLUDE_SELF))) { st_release_sys(c.flags[tid] + flag_index(s.sig_bank, me, chan), val); }
-            } else if (tid == 0 && s.sig_rank != me) {
+            } else if (tid == 0 && (s.sig_rank != me || (s.flags & SF_INCLUDE_SELF))) {
                 st_release_sys(c.flags[s.sig_rank] + flag_index(s.sig_bank, me, chan), val);
             }
         }
