@@ -71,6 +71,7 @@ struct RankCtx {
     uint32_t *exit_counter;      // local counter used to find the last CTA of an op; [1] = first failure code of this rank
     uint64_t *dev_tail;          // device word: sequence number of the newest completed op
     uint64_t *trace;             // optional in-kernel timestamps (HCCL_KERNEL_TRACE=1): [0] kernel start, then 3 per step
+    uint32_t *pipe_cnt;          // arrival counters of the pipelined kernels: [stage][ring slot], zero between ops
     uint64_t stage_half;         // bytes per staging half
     uint64_t timeout_ns;         // bound of every wait
 };

@@ -249,66 +249,6 @@ void ring_ag(Prog &P, const SliceIo &io, int h, int first_idx)
     }
 }
 
-// Pipelined mesh AllReduce for large messages: three CTA groups of one kernel work on successive chunks at the same
-// time.  Group A copies the caller's input into staging (HBM traffic only), group B reduces this rank's slice of a
-// chunk across all peers (peer loads over NVLink, or one multimem.ld_reduce), group C gathers the reduced slices of
-// the other ranks (peer loads, or local reads of what the peers multicast).  Counterpart of the reference's big-data
-// AIV kernels with progress flags (aiv_all_reduce_910b_bigdata.h: producer and consumer blocks).
-void pipe_groups(int nchan, int &nA, int &nB, int &nC)
-{
-    // copy-in and copy-out are HBM-bound and need few CTAs; the reduce group is link-bound and gets the rest
-    nA = std::max(1, nchan / 5);
-    nC = std::max(1, nchan / 5);
-    nB = std::max(1, nchan - nA - nC);
-}
-void ar_mesh_pipelined(Prog &P, const OpDesc &d, bool nvls)
-{
-    uint64_t n = d.chunk_count, uoff = d.chunk_off * P.es;
-    int nA, nB, nC;
-    pipe_groups(P.nchan, nA, nB, nC);
-    uint64_t unit = P.vec * (uint64_t)P.p;
-    uint64_t ce = std::max<uint64_t>(unit, (d.pipe_chunk_bytes ? d.pipe_chunk_bytes : (4u << 20)) / P.es / unit * unit);
-    uint64_t region2 = 0;  // NVLS multicasts the reduced slice over the raw one in place (only its owner reads the raw slice)
-    for (int r = 0; r < P.p; ++r) {
-        uint32_t k = 0;
-        for (uint64_t c0 = 0; c0 < n; c0 += ce, ++k) {
-            uint64_t len = std::min(ce, n - c0);
-            Step a = P.copy(BUF_IN, RANK_SELF, uoff + c0 * P.es, BUF_STAGE, RANK_SELF, c0 * P.es, len);
-            a.chan_lo = 0; a.chan_n = (uint16_t)nA;
-            a.sig_rank = RANK_ALL; a.sig_val = k + 1; a.flags |= SF_INCLUDE_SELF;  // this rank's own reduce group waits on it too
-            P.add(r, a, true);
-        }
-        k = 0;
-        for (uint64_t c0 = 0; c0 < n; c0 += ce, ++k) {
-            uint64_t len = std::min(ce, n - c0);
-            Slices S = make_slices(len, P.p, P.vec);
-            uint64_t so = (c0 + S.off(r)) * P.es;
-            Step b = P.mk(nvls ? ST_MC_REDUCE : ST_REDUCE_ALL);
-            b.a_buf = BUF_STAGE; b.a_rank = RANK_ALL; b.a_off = so; b.count = S.len(r);
-            b.d_buf = BUF_STAGE;
-            if (nvls) { b.d_rank = RANK_ALL; b.d_off = region2 + so; }
-            else { b.d_rank = RANK_SELF; b.d_off = so; }
-            b.d2_buf = BUF_OUT; b.d2_off = uoff + so;
-            b.chan_lo = (uint16_t)nA; b.chan_n = (uint16_t)nB;
-            b.wait_rank = RANK_ALL; b.wait_val = k + 1; b.flags |= SF_WAIT_ALLCH | SF_INCLUDE_SELF; b.wait_clo = 0; b.wait_cn = (uint16_t)nA;
-            b.sig_rank = RANK_ALL; b.sig_val = k + 1;
-            P.add(r, b, true);
-        }
-        k = 0;
-        for (uint64_t c0 = 0; c0 < n; c0 += ce, ++k) {
-            uint64_t len = std::min(ce, n - c0);
-            Slices S = make_slices(len, P.p, P.vec);
-            Step g = P.mk(ST_GATHER_ALL);
-            g.a_buf = BUF_STAGE; g.a_rank = nvls ? RANK_SELF : RANK_ALL; g.a_off = (nvls ? region2 : 0) + c0 * P.es; g.a_stride = S.sl * P.es;
-            g.d_buf = BUF_OUT; g.d_off = uoff + c0 * P.es; g.d_stride = S.sl * P.es;
-            g.count = S.sl; g.limit = len; g.flags |= SF_SKIP_SELF;
-            g.chan_lo = (uint16_t)(nA + nB); g.chan_n = (uint16_t)nC;
-            g.wait_rank = RANK_ALL; g.wait_val = k + 1; g.flags |= SF_WAIT_ALLCH; g.wait_clo = (uint16_t)nA; g.wait_cn = (uint16_t)nB;
-            P.add(r, g, true);
-        }
-    }
-}
-
 // Zero-copy NVLS AllReduce: both user buffers live in registered symmetric memory with a multicast mapping, so the
 // switch reduces straight from the send buffers and multicasts straight into the receive buffers
 // (role of the reference's zero-copy path for registered memory, hccl_communicator.cc:400-423 PrepareZeroCopy).
@@ -1008,8 +948,6 @@ uint64_t plan_stage_bytes(const OpDesc &d)
             uint64_t sl = std::max<uint64_t>(round_up_u64(ceil_div_u64(n, (uint64_t)m), vec), vec);
             uint64_t region = round_up_u64(sl * m * es, 256);
             if (d.algo == ALGO_NVLS_ZC) return 0;
-            if (d.algo == ALGO_MESH_PIPE) return round_up_u64(nA, 256);
-            if (d.algo == ALGO_NVLS_PIPE) return round_up_u64(nA, 256);
             return std::max<uint64_t>(region, nA);
         }
         case COLL_REDUCE_SCATTER: case COLL_ALLGATHER: case COLL_SCATTER: case COLL_GATHER: case COLL_ALLTOALL:
@@ -1059,10 +997,6 @@ HcclResult build_plan(const OpDesc &d, const std::vector<int> &local, Plan *plan
                 else if (d.algo == ALGO_NVLS_ONESHOT) ar_mesh_oneshot(P, d, true);
                 else if (d.algo == ALGO_MESH) ar_mesh_twoshot(P, d, false);
                 else if (d.algo == ALGO_NVLS) ar_mesh_twoshot(P, d, true);
-                else if (d.algo == ALGO_MESH_PIPE || d.algo == ALGO_NVLS_PIPE) {
-                    if (d.nchan < 3) return HCCL_E_PARA;
-                    ar_mesh_pipelined(P, d, d.algo == ALGO_NVLS_PIPE);
-                }
                 else if (d.algo == ALGO_NVLS_ZC) ar_nvls_zerocopy(P, d);
                 else if (d.algo == ALGO_RING) ar_ring(P, d);
                 else if (d.algo == ALGO_RHD) ar_rhd(P, d);

@@ -29,8 +29,9 @@ enum AlgoId : int {
     ALGO_NVLS,          // in-switch reduction / multicast (two-shot for AllReduce)
     ALGO_NVLS_ONESHOT,  // AllReduce: multimem.ld_reduce of the whole message on every rank
     ALGO_SINGLE,        // one rank: local copy
-    ALGO_MESH_PIPE,     // AllReduce / ReduceScatter / AllGather: mesh with CTA groups pipelining copy-in, reduce and gather over chunks
-    ALGO_NVLS_PIPE,     // same with in-switch reduction / multicast stores
+    ALGO_MESH_PIPE,     // AllReduce / ReduceScatter / AllGather / Broadcast: pipelined kernel (kernels/pipe_coll.*), CTA stages over a ring of
+                        // staging slots, peer loads and stores; no step list (device only; CPU ranks run the plain mesh / ring schedule)
+    ALGO_NVLS_PIPE,     // same with in-switch reduction (multimem.ld_reduce) and multicast stores
     ALGO_NVLS_ZC,       // AllReduce on registered symmetric buffers: multimem.ld_reduce from the send buffers, multimem.st into the receive buffers, no staging
     ALGO_LL,            // AllReduce, small messages: data and flag travel together in 16-byte lines (device only)
     ALGO_COUNT
@@ -50,7 +51,6 @@ struct OpDesc {
     uint64_t chunk_off = 0;    // window of `count` this plan covers (staging loop)
     uint64_t chunk_count = 0;
     uint64_t slot_bytes = 0;   // AlltoAllV: bytes of one per-sender staging slot
-    uint64_t pipe_chunk_bytes = 0;  // pipelined algorithms: bytes per pipeline chunk (0 = default)
     // V variants (arrays of nranks entries, elements).  AllGatherV: counts/displs describe the receive
     // layout; ReduceScatterV: the send layout.  AlltoAllV: this rank's four rows, only valid for
     // plans built for a single local rank; AlltoAllVC and emulated ranks pass the full matrix instead.

@@ -43,11 +43,11 @@ static bool algo_exists(int coll, int algo)
 {
     switch (coll) {
         case COLL_ALLREDUCE: return algo == ALGO_MESH || algo == ALGO_MESH_ONESHOT || algo == ALGO_RING || algo == ALGO_RHD || algo == ALGO_NVLS || algo == ALGO_NVLS_ONESHOT || algo == ALGO_MESH_PIPE || algo == ALGO_NVLS_PIPE || algo == ALGO_LL || algo == ALGO_NVLS_ZC;
-        case COLL_REDUCE_SCATTER: return algo == ALGO_MESH || algo == ALGO_RING || algo == ALGO_RHD || algo == ALGO_NVLS;
-        case COLL_ALLGATHER: return algo == ALGO_MESH || algo == ALGO_RING || algo == ALGO_RHD || algo == ALGO_NVLS || algo == ALGO_PAIRWISE;
+        case COLL_REDUCE_SCATTER: return algo == ALGO_MESH || algo == ALGO_RING || algo == ALGO_RHD || algo == ALGO_NVLS || algo == ALGO_MESH_PIPE || algo == ALGO_NVLS_PIPE;
+        case COLL_ALLGATHER: return algo == ALGO_MESH || algo == ALGO_RING || algo == ALGO_RHD || algo == ALGO_NVLS || algo == ALGO_PAIRWISE || algo == ALGO_MESH_PIPE;
         case COLL_REDUCE_SCATTER_V: return algo == ALGO_MESH || algo == ALGO_RING || algo == ALGO_NVLS;
         case COLL_ALLGATHER_V: return algo == ALGO_MESH || algo == ALGO_RING || algo == ALGO_NVLS || algo == ALGO_PAIRWISE;
-        case COLL_BROADCAST: return algo == ALGO_STAR || algo == ALGO_RING || algo == ALGO_TREE || algo == ALGO_NVLS;
+        case COLL_BROADCAST: return algo == ALGO_STAR || algo == ALGO_RING || algo == ALGO_TREE || algo == ALGO_NVLS || algo == ALGO_MESH_PIPE || algo == ALGO_NVLS_PIPE;
         case COLL_REDUCE: return algo == ALGO_STAR || algo == ALGO_RING || algo == ALGO_TREE || algo == ALGO_RHD;
         case COLL_SCATTER: case COLL_GATHER: return algo == ALGO_STAR || algo == ALGO_RING;
         case COLL_ALLTOALL: case COLL_ALLTOALLV: case COLL_ALLTOALLVC: return algo == ALGO_MESH || algo == ALGO_PAIRWISE;
@@ -63,6 +63,9 @@ double estimate_us(int coll, int algo, uint64_t bytes, int p, const CostModel &m
     const double lg = std::ceil(std::log2((double)p));
     const bool pow2 = (p & (p - 1)) == 0;
     const double f = (double)(p - 1) / p;
+    // link bytes per chunk of the pipelined kernels (Communicator::run_pipe): 1/16 of what crosses the links, 1 to 8 MiB
+    const double fan = (coll == COLL_REDUCE_SCATTER || coll == COLL_ALLGATHER) ? p : 1.0;
+    const double chunk = std::min(n * fan, std::min(8.0 * (1 << 20), std::max(1.0 * (1 << 20), n * fan / 16)));
     switch (coll) {
         case COLL_ALLREDUCE:
             switch (algo) {
@@ -74,9 +77,9 @@ double estimate_us(int coll, int algo, uint64_t bytes, int p, const CostModel &m
                 case ALGO_RHD: return L + (2 * lg + (pow2 ? 0 : 2)) * (a + s) + (pow2 ? 2 * f : 2.0 * (2 * p - 1) / p) * n / B + n / G;
                 case ALGO_NVLS_ONESHOT: return L + a + p * n / Bn + n / G + 2 * s;
                 case ALGO_NVLS: return L + 2 * a + (1.0 + 1.0 / p) * n / Bn + 2 * n / G + (p + 2) * s;
-                // pipelined: local copies hide behind the transfers; costs a pipeline fill of roughly one chunk per phase
-                case ALGO_MESH_PIPE: return L + 4 * a + std::max(2 * f * n / B, 2 * n / G) + 3 * std::min(n, 4.0 * (1 << 20)) / B + 6 * s + std::ceil(n / (4.0 * (1 << 20))) * 3 * (2 * a + 4);
-                case ALGO_NVLS_PIPE: return L + 4 * a + std::max((1.0 + 1.0 / p) * n / Bn, 2 * n / G) + 3 * std::min(n, 4.0 * (1 << 20)) / Bn + 6 * s + std::ceil(n / (4.0 * (1 << 20))) * 3 * (2 * a + 4);
+                // pipelined kernels: the local copies hide behind the transfer; the price is a pipeline fill of one chunk per stage
+                case ALGO_MESH_PIPE: return L + (p == 2 ? 2 : 3) * a + (p == 2 ? 1.0 : 2 * f) * n / B + 3 * chunk / B;
+                case ALGO_NVLS_PIPE: return L + (p == 2 ? 2 : 3) * a + (p == 2 ? 1.0 : 1.0 + 1.0 / p) * n / Bn + 3 * chunk / Bn;
             }
             break;
         case COLL_REDUCE_SCATTER: case COLL_REDUCE_SCATTER_V:  // bytes = one rank's result
@@ -85,6 +88,8 @@ double estimate_us(int coll, int algo, uint64_t bytes, int p, const CostModel &m
                 case ALGO_RING: return L + (p - 1) * (a + s) + (p - 1) * n / B;
                 case ALGO_RHD: return L + (lg + (pow2 ? 0 : 1)) * (a + s) + (pow2 ? (p - 1) : (2 * p - 1)) * n / B + p * n / G;
                 case ALGO_NVLS: return L + a + n * (double)p / Bn / p * (p - 1) + p * n / G + (p + 1) * s;
+                case ALGO_MESH_PIPE: return L + 2 * a + (p - 1) * n / B + 2 * chunk / B;
+                case ALGO_NVLS_PIPE: return L + 2 * a + (p - 1) * n / Bn + 2 * chunk / Bn;
             }
             break;
         case COLL_ALLGATHER: case COLL_ALLGATHER_V:  // bytes = one rank's contribution
@@ -94,6 +99,7 @@ double estimate_us(int coll, int algo, uint64_t bytes, int p, const CostModel &m
                 case ALGO_PAIRWISE: return L + a + (p - 1) * n / B + (p - 1) * n / G + (p + 1) * s;  // push: no staging copy, copy-out per slot
                 case ALGO_RHD: return L + (lg + (pow2 ? 0 : 2)) * (a + s) + (pow2 ? (p - 1) : (2 * p - 1)) * n / B;
                 case ALGO_NVLS: return L + a + (p - 1) * n / Bn + p * n / G + 2 * s;
+                case ALGO_MESH_PIPE: return L + 2 * a + (p - 1) * n / B + 2 * chunk / B;
             }
             break;
         case COLL_BROADCAST:
@@ -102,6 +108,8 @@ double estimate_us(int coll, int algo, uint64_t bytes, int p, const CostModel &m
                 case ALGO_RING: return L + (p - 1 + 3) * (a + s) + (1.0 + (p - 2) / 4.0) * n / B;
                 case ALGO_TREE: return L + lg * (a + s) + lg * n / B;
                 case ALGO_NVLS: return L + a + n / Bn + n / G;
+                case ALGO_MESH_PIPE: return L + n / B + (p - 1) * (a + chunk / B);  // chain: every hop adds one chunk
+                case ALGO_NVLS_PIPE: return L + 2 * a + n / Bn + 2 * chunk / Bn;
             }
             break;
         case COLL_REDUCE:
@@ -156,7 +164,7 @@ Selection select_algo(const SelectInput &in, const CostModel &m)
         if (algo == ALGO_NVLS || algo == ALGO_NVLS_ONESHOT || algo == ALGO_NVLS_PIPE) return nvls_ok;
         if (algo == ALGO_NVLS_ZC) return false;  // chosen by the communicator when the buffers are registered, never by the model
         if (algo == ALGO_LL) return in.device && in.expansion_mode != 1 && in.ll_max_bytes > 0 && in.bytes <= in.ll_max_bytes;
-        if ((algo == ALGO_MESH_PIPE || algo == ALGO_NVLS_PIPE) && (!in.device || sel.nchan < 6)) return false;
+        if ((algo == ALGO_MESH_PIPE || algo == ALGO_NVLS_PIPE) && (!in.device || in.expansion_mode == 1)) return false;  // device kernels only
         return true;
     };
     if (!in.forced.empty()) {

@@ -143,6 +143,12 @@ EnvConfig parse_env(const std::map<std::string, std::string> &v)
     if (auto s = get("HCCL_STUCK_DETECT_MS")) { if (parse_int(*s, n) && n >= 1) c.stuck_ms = (int)n; }
     if (auto s = get("HCCL_CHANNELS")) { if (parse_int(*s, n) && n >= 0 && n <= 128) c.channels = (int)n; }
     if (auto s = get("HCCL_PIPE_CHUNK_KB")) { if (parse_int(*s, n) && n >= 16) c.pipe_chunk_bytes = (uint64_t)n << 10; }
+    if (auto s = get("HCCL_PIPE_SLOTS")) { if (parse_int(*s, n) && n >= 1 && n <= 16) c.pipe_slots = (int)n; }
+    if (auto s = get("HCCL_PIPE_CTAS")) {
+        int a = 0, b = 0, d = 0;
+        if (sscanf(s->c_str(), "%d,%d,%d", &a, &b, &d) >= 2 && a >= 1 && b >= 1 && d >= 0 && a + b + d <= 128) { c.pipe_ctas[0] = a; c.pipe_ctas[1] = b; c.pipe_ctas[2] = d > 0 ? d : 1; }
+        else fail(c, "HCCL_PIPE_CTAS must be a,b[,c] with a + b + c <= 128");
+    }
     if (auto s = get("HCCL_NCCL_LIB")) c.ncc_lib = *s;
     if (auto s = get("HCCL_WHITELIST_DISABLE")) c.whitelist_enable = *s == "0";
     if (auto s = get("HCCL_WHITELIST_FILE")) c.whitelist_file = *s;

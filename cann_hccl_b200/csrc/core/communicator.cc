@@ -17,6 +17,7 @@
 #include "health/fault_inject.h"
 #include "kernels/ar_ll.h"
 #include "kernels/overflow.h"
+#include "kernels/pipe_coll.h"
 #include <nvtx3/nvToolsExt.h>
 #include <fstream>
 #include "p2p/p2p_backend.h"
@@ -214,6 +215,10 @@ HcclResult Communicator::init_common()
         CHK_RET_LOG(cudaMalloc(&dev_exit_, sizeof(uint32_t) * 4 * nl) != cudaSuccess, HCCL_E_MEMORY, "cudaMalloc failed");
         cudaMemset(dev_exit_, 0, sizeof(uint32_t) * 4 * nl);
     }
+    if (dev) {
+        CHK_RET_LOG(cudaMalloc(&dev_pipe_cnt_, sizeof(uint32_t) * kPipeCounterWords * nl) != cudaSuccess, HCCL_E_MEMORY, "cudaMalloc failed");
+        cudaMemset(dev_pipe_cnt_, 0, sizeof(uint32_t) * kPipeCounterWords * nl);
+    }
     if (dev && getenv("HCCL_KERNEL_TRACE") && atoi(getenv("HCCL_KERNEL_TRACE")) > 0) {
         CHK_RET_LOG(cudaMalloc(&dev_trace_, sizeof(uint64_t) * kTraceWords * nl) != cudaSuccess, HCCL_E_MEMORY, "cudaMalloc failed");
         cudaMemset(dev_trace_, 0, sizeof(uint64_t) * kTraceWords * nl);
@@ -238,6 +243,7 @@ HcclResult Communicator::init_common()
         x.abort = abort_[li];
         x.exit_counter = dev ? (uint32_t *)dev_exit_ + 4 * li : nullptr;
         x.dev_tail = dev ? (uint64_t *)((uint32_t *)dev_exit_ + 4 * li + 2) : nullptr;
+        x.pipe_cnt = dev ? (uint32_t *)dev_pipe_cnt_ + (size_t)li * kPipeCounterWords : nullptr;
         x.stage_half = half;
         x.trace = dev_trace_ ? (uint64_t *)dev_trace_ + (size_t)li * kTraceWords : nullptr;
         x.timeout_ns = (uint64_t)(tmo_ms * 1e6);
@@ -273,6 +279,7 @@ Communicator::~Communicator()
     if (dev) {
         if (dev_ctx_) cudaFree(dev_ctx_);
         if (dev_exit_) cudaFree(dev_exit_);
+        if (dev_pipe_cnt_) cudaFree(dev_pipe_cnt_);
         if (dev_trace_) cudaFree(dev_trace_);
         if (pinned_) cudaFreeHost(pinned_);
         if (overflow_word_) cudaFreeHost(overflow_word_);
@@ -431,7 +438,6 @@ Selection Communicator::select(int coll, uint64_t count, int dtype, int redop) c
             if (t <= 0) continue;
             if ((a == ALGO_NVLS || a == ALGO_NVLS_ONESHOT || a == ALGO_NVLS_PIPE) && !nvls_ok) continue;
             if (a == ALGO_LL && (si.bytes > si.ll_max_bytes || si.expansion_mode == 1)) continue;
-            if ((a == ALGO_MESH_PIPE || a == ALGO_NVLS_PIPE) && s.nchan < 6) continue;
             if (bt < 0 || t < bt) { bt = t; s.algo = a; }
         }
         if (bt > 0) s.est_us = bt;
@@ -608,10 +614,24 @@ HcclResult Communicator::run_collective_once(const OpRequest &rq)
         sel.algo = ALGO_MESH_ONESHOT;  // unaligned or oversized: the plan executor handles every layout
     }
 
+    if (sel.algo == ALGO_MESH_PIPE || sel.algo == ALGO_NVLS_PIPE) {
+        if (settings_.transport == TR_DEVICE && pipe_mode_for(rq.coll) >= 0) {
+            HcclResult prc = run_pipe(rq, sel.algo == ALGO_NVLS_PIPE);
+            uint64_t pbytes = sel_count * es;
+            stats_.ops[rq.coll]++;
+            stats_.bytes[rq.coll] += pbytes;
+            stats_.algo_hist[sel.algo]++;
+            record_trace(rq, sel.algo, 0, pbytes, now_us() - t0);
+            return prc;
+        }
+        // CPU ranks have no pipelined executor: the plain schedule of the same family moves the same bytes
+        const bool mc = sel.algo == ALGO_NVLS_PIPE;
+        sel.algo = rq.coll == COLL_BROADCAST ? (mc ? ALGO_NVLS : ALGO_RING) : (mc ? ALGO_NVLS : ALGO_MESH);
+    }
+
     OpDesc d;
     d.coll = rq.coll; d.algo = sel.algo; d.nranks = p; d.root = rq.root; d.dtype = rq.dtype; d.redop = rq.redop;
     d.nchan = sel.nchan; d.count = rq.count;
-    d.pipe_chunk_bytes = env_config().pipe_chunk_bytes;
     if (is_v) { d.counts.assign(rq.counts, rq.counts + p); d.displs.assign(rq.displs, rq.displs + p); }
     if (is_a2av) {
         d.send_counts.assign(rq.send_counts, rq.send_counts + (size_t)nl * p);
@@ -648,7 +668,7 @@ HcclResult Communicator::run_collective_once(const OpRequest &rq)
         uint64_t n = std::min(max_chunk, window - off);
         d.chunk_off = off; d.chunk_count = n;
         std::ostringstream key;
-        key << rq.coll << ':' << d.algo << ':' << d.nchan << ':' << d.pipe_chunk_bytes << ':' << rq.dtype << ':' << rq.root << ':' << rq.count << ':' << off << ':' << n;
+        key << rq.coll << ':' << d.algo << ':' << d.nchan << ':' << rq.dtype << ':' << rq.root << ':' << rq.count << ':' << off << ':' << n;
         if (is_v) for (int j = 0; j < p; ++j) key << ',' << d.counts[j] << '@' << d.displs[j];
         if (is_a2av) {
             uint32_t crc = crc32(d.send_counts.data(), d.send_counts.size() * 8, 0);
@@ -676,6 +696,81 @@ HcclResult Communicator::run_collective_once(const OpRequest &rq)
     stats_.bytes[rq.coll] += bytes;
     stats_.algo_hist[sel.algo]++;
     record_trace(rq, sel.algo, sel.nchan, bytes, now_us() - t0);
+    return rc;
+}
+
+int Communicator::pipe_mode_for(int coll) const
+{
+    switch (coll) {
+        case COLL_ALLREDUCE: return nranks_ == 2 ? PM_ALLREDUCE_ONESHOT : PM_ALLREDUCE;  // two ranks: one-shot moves the same bytes and saves a stage
+        case COLL_REDUCE_SCATTER: return PM_REDUCE_SCATTER;
+        case COLL_ALLGATHER: return PM_ALLGATHER;
+        case COLL_BROADCAST: return PM_BROADCAST_CHAIN;
+        default: return -1;
+    }
+}
+
+// Pipelined large-message path: one launch for a message of any size (the ring of staging slots replaces the staging
+// loop).  Geometry: a chunk moves about 1/16 of the message over the links, between 1 and 8 MiB, so that the pipeline
+// fill stays small against the transfer and a stage's per-chunk bookkeeping (a few microseconds) stays small against
+// the chunk's transfer time.
+HcclResult Communicator::run_pipe(const OpRequest &rq, bool want_mc)
+{
+    const EnvConfig &env = env_config();
+    const int p = nranks_, nl = nlocal(), es = dtype_size(rq.dtype);
+    int mode = pipe_mode_for(rq.coll);
+    const uint64_t block_bytes = rq.count * (uint64_t)es;
+    const bool reducing = mode == PM_ALLREDUCE || mode == PM_ALLREDUCE_ONESHOT || mode == PM_REDUCE_SCATTER;
+    bool use_mc = want_mc && nvls_ && block_bytes % 16 == 0 && (!reducing || nvls_reduce_supported(rq.dtype, rq.redop, block_bytes)) && !deterministic();
+    if (mode == PM_ALLGATHER) use_mc = false;  // blocks are pulled from the peers' slots
+    if (mode == PM_BROADCAST_CHAIN && use_mc) mode = PM_BROADCAST_MC;
+    // bytes that one chunk moves over the links, per element of a block
+    const uint64_t fan = (mode == PM_REDUCE_SCATTER || mode == PM_ALLGATHER) ? (uint64_t)p : 1;
+    uint64_t link_total = block_bytes * fan;
+    uint64_t lc = env.pipe_chunk_bytes ? env.pipe_chunk_bytes : std::min<uint64_t>(8u << 20, std::max<uint64_t>(1u << 20, link_total / 16));
+    int nslots = env.pipe_slots > 0 ? std::min(env.pipe_slots, kPipeMaxSlots) : 4;
+    const uint64_t unit = (uint64_t)p * (256 / es);  // elements: slices of a chunk stay 256-byte aligned
+    auto slot_of = [&](uint64_t ce) { return pipe_slot_bytes(mode, ce, es, p); };
+    uint64_t ce = std::max<uint64_t>(unit, lc / fan / es / unit * unit);
+    while (ce > unit && slot_of(ce) * nslots > settings_.stage_half_bytes) ce = std::max<uint64_t>(unit, ce / 2 / unit * unit);
+    while (nslots > 1 && slot_of(ce) * nslots > settings_.stage_half_bytes) --nslots;
+    CHK_RET_LOG(slot_of(ce) * nslots > settings_.stage_half_bytes, HCCL_E_MEMORY, "staging buffer too small for the pipelined kernels");
+    while (ceil_div_u64(rq.count, ce) >= (1ull << kSeqShift) - 1) ce *= 2;  // chunk index travels in the low flag bits
+    CHK_RET_LOG(slot_of(ce) * nslots > settings_.stage_half_bytes, HCCL_E_MEMORY, "message needs more pipeline chunks than a flag can count");
+    // CTAs per stage: enough to keep the links busy, no more than 16 KiB-per-CTA pieces justify
+    int budget = all_local_ ? std::max(3, 128 / nl) : 64;
+    int n1, n2, n3 = 0;
+    switch (mode) {
+        case PM_ALLREDUCE: n1 = budget / 4; n2 = budget / 2; n3 = budget / 4; break;
+        case PM_ALLGATHER: n1 = std::max(1, budget / 8); n2 = budget - n1; break;
+        case PM_BROADCAST_MC: case PM_BROADCAST_CHAIN: n1 = budget / 2; n2 = 0; break;
+        default: n1 = budget * 3 / 8; n2 = budget - n1; break;
+    }
+    if (env.pipe_ctas[0] > 0) { n1 = env.pipe_ctas[0]; n2 = env.pipe_ctas[1]; n3 = env.pipe_ctas[2]; }
+    const uint64_t chunk_bytes = std::min(ce, rq.count) * (uint64_t)es;
+    auto cap = [&](int n, uint64_t bytes) { return (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)std::max(1, n), bytes / (16u << 10))); };
+    if (mode == PM_ALLREDUCE) { n1 = cap(n1, chunk_bytes); n2 = cap(n2, chunk_bytes / p); n3 = cap(n3, chunk_bytes); }
+    else if (mode == PM_BROADCAST_MC || mode == PM_BROADCAST_CHAIN) { n1 = cap(n1, chunk_bytes); n2 = 0; }
+    else { n1 = cap(n1, chunk_bytes * (mode == PM_REDUCE_SCATTER ? p : 1)); n2 = cap(n2, chunk_bytes * (mode == PM_ALLGATHER ? p - 1 : 1)); }
+    std::vector<PipeArgs> args(nl);
+    for (int li = 0; li < nl; ++li) {
+        PipeArgs &a = args[li];
+        memset(&a, 0, sizeof(a));
+        a.in = (const uint8_t *)rq.in[li];
+        a.out = (uint8_t *)rq.out[li];
+        a.count = rq.count; a.chunk_elems = ce; a.seq = seq_;
+        a.mode = mode; a.dtype = rq.dtype; a.root = rq.root; a.nslots = nslots;
+        a.n1 = n1; a.n2 = n2; a.n3 = n3; a.use_mc = use_mc ? 1 : 0;
+        status_[li]->head = seq_;
+    }
+    stats_.launches++;
+    if (dev_trace_)
+        for (int li = 0; li < nl; ++li) {
+            cudaMemsetAsync((uint64_t *)dev_trace_ + (size_t)li * kTraceWords, 0, sizeof(uint64_t) * (kTraceWords - 2), (cudaStream_t)rq.stream);
+            cudaMemsetAsync((uint64_t *)dev_trace_ + (size_t)li * kTraceWords, 0xff, 8, (cudaStream_t)rq.stream);
+        }
+    HcclResult rc = launch_pipe_coll((const RankCtx *)dev_ctx_, args.data(), nl, rq.redop, rq.stream);
+    ++seq_;
     return rc;
 }
 
@@ -978,6 +1073,7 @@ HcclResult Communicator::resume_locked()
     }
     if (dev && dev_exit_)
         for (int li = 0; li < nlocal(); ++li) cudaMemset((uint32_t *)dev_exit_ + 4 * li, 0, sizeof(uint32_t) * 2);  // counter + failure code
+    if (dev && dev_pipe_cnt_) cudaMemset(dev_pipe_cnt_, 0, sizeof(uint32_t) * kPipeCounterWords * nlocal());  // an abandoned pipelined op leaves arrivals behind
     // order matters for the heartbeat thread: own status is clean, then the epoch moves (peers' older error reports
     // become stale), then what it may have recorded from those reports is dropped
     resume_gen_.store(gen);

@@ -176,6 +176,8 @@ private:
     HcclResult get_plan(const OpDesc &d, const std::string &key, CachedPlan **out);
     HcclResult run_collective_once(const OpRequest &rq);
     HcclResult run_ll_allreduce(const OpRequest &rq);
+    HcclResult run_pipe(const OpRequest &rq, bool want_mc);
+    int pipe_mode_for(int coll) const;  // PipeMode of a collective, -1 when it has no pipelined kernel
     HcclResult tp_workspace(const std::string &key, size_t data_bytes, int M, void **ws_out);
     void tp_release_workspaces();
     HcclResult consistency_check(const OpRequest &rq, int algo);
@@ -206,6 +208,7 @@ private:
     std::vector<volatile uint32_t *> abort_;
     void *dev_ctx_ = nullptr;              // device array of RankCtx
     void *dev_exit_ = nullptr;
+    void *dev_pipe_cnt_ = nullptr;         // arrival counters of the pipelined kernels (kPipeCounterWords per local rank)
     void *hb_stream_ = nullptr;            // stream of the heartbeat thread (device counter read-back)
     void *dev_trace_ = nullptr;            // in-kernel timestamp buffers (kTraceWords per local rank) when enabled
     void *pinned_ = nullptr;               // host-mapped block holding status + abort words

@@ -65,8 +65,6 @@ def scenario_collectives(c, p, r, args):
         for algo in ar_algos:
             if algo in (L.ALGO_NVLS, L.ALGO_NVLS_ONESHOT, L.ALGO_NVLS_PIPE) and (n * 4) % 16:
                 continue
-            if algo in (L.ALGO_MESH_PIPE, L.ALGO_NVLS_PIPE) and n < 1000:
-                continue
             if algo == L.ALGO_LL and n > 60000:
                 continue
             for dtype, op in ((torch.float32, L.SUM), (torch.bfloat16, L.SUM), (torch.bfloat16, L.MAX), (torch.int32, L.MIN)):
@@ -76,7 +74,7 @@ def scenario_collectives(c, p, r, args):
                     continue
                 xs = [inp(q, n, dtype, seed=n % 97) for q in range(p)]
                 out = torch.zeros(n, device="cuda", dtype=dtype)
-                c.all_reduce(xs[r], out, op=op, algo=algo, nchan=12 if algo in (L.ALGO_MESH_PIPE, L.ALGO_NVLS_PIPE) else 0)
+                c.all_reduce(xs[r], out, op=op, algo=algo)
                 ok(c)
                 try:
                     close(out, red(xs, op), dtype, p)
@@ -120,6 +118,38 @@ def scenario_collectives(c, p, r, args):
             c.all_gather(gs[r], g, algo=L.ALGO_PAIRWISE)
             ok(c)
             assert torch.equal(g, torch.cat(gs))
+    # pipelined kernels on messages that go around the ring of staging slots several times (16 MB halves)
+    pipes = [L.ALGO_MESH_PIPE] + ([L.ALGO_NVLS_PIPE] if nvls else [])
+    for algo in pipes:
+        for dtype in (torch.float32, torch.bfloat16):
+            n = 1_500_000
+            xs = [inp(q, n * p, dtype, seed=13) for q in range(p)]
+            out = torch.zeros(n, device="cuda", dtype=dtype)
+            c.reduce_scatter(xs[r], out, algo=algo)
+            ok(c)
+            close(out, red(xs, L.SUM)[r * n:(r + 1) * n], dtype, p)
+            del xs
+            gs = [inp(q, n, dtype, seed=14) for q in range(p)]
+            g = torch.zeros(n * p, device="cuda", dtype=dtype)
+            c.all_gather(gs[r], g, algo=algo)
+            ok(c)
+            assert torch.equal(g, torch.cat(gs))
+            del gs, g
+        for root in (0, p - 1):
+            n = 9_000_000
+            b = inp(r, n, torch.float32, seed=15)
+            c.broadcast(b, root, algo=algo)
+            ok(c)
+            assert torch.equal(b, inp(root, n, torch.float32, seed=15))
+        xs = [inp(q, 12_000_000, torch.float32, seed=16) for q in range(p)]
+        want = red(xs, L.SUM)
+        mine = xs[r].clone()
+        for _ in range(3):  # back to back: staging halves alternate, counters are reused
+            mine.copy_(xs[r])
+            c.all_reduce(mine, mine, algo=algo)
+        ok(c)
+        close(mine, want, torch.float32, p)
+        del xs, want, mine
     for root in (0, p - 1):
         for algo in [L.ALGO_STAR, L.ALGO_RING, L.ALGO_TREE] + ([L.ALGO_NVLS] if nvls else []):
             b = inp(r, 50_000, torch.float32, seed=5)

@@ -106,18 +106,86 @@ def test_allreduce_low_latency_protocol(comms, p, dtype, op):
     assert c.stats()["algos"].get("ll", 0) >= 12
 
 
-@pytest.mark.parametrize("p", [2, 4, 8])
-def test_allreduce_pipelined_groups(comms, p):
-    """Large-message algorithm: copy-in, reduce and gather CTA groups of one kernel pipelined over chunks."""
+PIPE_SIZES = (5, 70_001, 3_000_000)  # part of a chunk; one chunk; twelve chunks through a four-slot ring (4 MB staging halves)
+
+
+@pytest.mark.parametrize("p", [2, 3, 4, 8])
+@pytest.mark.parametrize("dtype,op", [(torch.float32, L.SUM), (torch.bfloat16, L.MAX), (torch.int32, L.MIN), (torch.float64, L.PROD)])
+def test_pipelined_allreduce(comms, p, dtype, op):
+    """Pipelined kernel: copy-in, reduce and copy-out stages of one launch over a ring of staging slots (two ranks: one-shot)."""
     c = comms(p)
-    n = 900_001
-    ins = rnd(p, n, torch.float32, seed=11)
-    outs = [torch.zeros(n, device="cuda") for _ in range(p)]
-    c.all_reduce(ins, outs, algo=L.ALGO_MESH_PIPE, nchan=9)
-    ok(c)
+    for n in PIPE_SIZES:
+        ins = rnd(p, n, dtype, seed=n % 89)
+        outs = [torch.zeros(n, device="cuda", dtype=dtype) for _ in range(p)]
+        c.all_reduce(ins, outs, op=op, algo=L.ALGO_MESH_PIPE)
+        ok(c)
+        assert c.trace()[-1]["algo"] == "mesh_pipe"
+        ref = ref_reduce(ins, op)
+        for o in outs:
+            close(o, ref, dtype, p)
+
+
+def test_pipelined_allreduce_in_place_unaligned_back_to_back(comms):
+    p = 4
+    c = comms(p)
+    n = 2_500_001
+    base = rnd(p, n + 1, torch.float32, seed=5)
+    ins = [b[1:] for b in base]  # 4-byte aligned only: the scalar paths of the copy and reduce loops
     ref = ref_reduce(ins, L.SUM)
-    for o in outs:
+    c.all_reduce(ins, ins, algo=L.ALGO_MESH_PIPE)
+    ok(c)
+    for o in ins:
         close(o, ref, torch.float32, p)
+    # consecutive ops alternate staging halves and reuse the arrival counters
+    xs = rnd(p, 1_200_000, torch.float32, seed=6)
+    outs = [torch.zeros_like(x) for x in xs]
+    for _ in range(5):
+        c.all_reduce(xs, outs, algo=L.ALGO_MESH_PIPE)
+    ok(c)
+    for o in outs:
+        close(o, ref_reduce(xs, L.SUM), torch.float32, p)
+
+
+@pytest.mark.parametrize("p", [2, 3, 8])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_pipelined_reduce_scatter_allgather(comms, p, dtype):
+    c = comms(p)
+    for n in (3, 40_001, 700_000):  # per-rank block; the largest runs the ring several times over
+        ins = rnd(p, n * p, dtype, seed=n % 83)
+        outs = [torch.zeros(n, device="cuda", dtype=dtype) for _ in range(p)]
+        c.reduce_scatter(ins, outs, algo=L.ALGO_MESH_PIPE)
+        ok(c)
+        ref = ref_reduce(ins, L.SUM)
+        for r, o in enumerate(outs):
+            close(o, ref[r * n:(r + 1) * n], dtype, p)
+        gs = rnd(p, n, dtype, seed=n % 79)
+        gout = [torch.zeros(n * p, device="cuda", dtype=dtype) for _ in range(p)]
+        c.all_gather(gs, gout, algo=L.ALGO_MESH_PIPE)
+        ok(c)
+        for o in gout:
+            assert torch.equal(o, torch.cat(gs))
+    # AllGather in place: every rank's block already sits at its position of the receive buffer
+    n = 300_001
+    full = [torch.zeros(n * p, device="cuda") for _ in range(p)]
+    gs = rnd(p, n, torch.float32, seed=2)
+    for r in range(p):
+        full[r][r * n:(r + 1) * n] = gs[r]
+    c.all_gather([full[r][r * n:(r + 1) * n] for r in range(p)], full, algo=L.ALGO_MESH_PIPE)
+    ok(c)
+    for o in full:
+        assert torch.equal(o, torch.cat(gs))
+
+
+@pytest.mark.parametrize("p", [2, 3, 8])
+def test_pipelined_broadcast_chain(comms, p):
+    c = comms(p)
+    for n, root in ((7, 0), (100_003, p - 1), (2_000_000, 1)):
+        bufs = rnd(p, n, torch.float32, seed=n % 71)
+        want = bufs[root].clone()
+        c.broadcast(bufs, root, algo=L.ALGO_MESH_PIPE)
+        ok(c)
+        for b in bufs:
+            assert torch.equal(b, want)
 
 
 def test_allreduce_staging_loop_in_place_unaligned(comms):
