@@ -702,10 +702,10 @@ HcclResult Communicator::run_collective_once(const OpRequest &rq)
 int Communicator::pipe_mode_for(int coll) const
 {
     switch (coll) {
-        case COLL_ALLREDUCE: return nranks_ == 2 ? PM_ALLREDUCE_ONESHOT : PM_ALLREDUCE;  // two ranks: one-shot moves the same bytes and saves a stage
-        case COLL_REDUCE_SCATTER: return PM_REDUCE_SCATTER;
-        case COLL_ALLGATHER: return PM_ALLGATHER;
-        case COLL_BROADCAST: return PM_BROADCAST_CHAIN;
+        case COLL_ALLREDUCE: return nranks_ == 2 ? PM_AR1_PUSH : PM_AR2_PUSH;  // two ranks: one-shot moves the same bytes and saves a stage
+        case COLL_REDUCE_SCATTER: return PM_RS_PUSH;
+        case COLL_ALLGATHER: return PM_AG_PULL;
+        case COLL_BROADCAST: return PM_BC_PUSH;
         default: return -1;
     }
 }
@@ -713,19 +713,24 @@ int Communicator::pipe_mode_for(int coll) const
 // Pipelined large-message path: one launch for a message of any size (the ring of staging slots replaces the staging
 // loop).  Geometry: a chunk moves about 1/16 of the message over the links, between 1 and 8 MiB, so that the pipeline
 // fill stays small against the transfer and a stage's per-chunk bookkeeping (a few microseconds) stays small against
-// the chunk's transfer time.
+// the chunk's transfer time.  Every choice below depends only on facts that all ranks share (sizes, type, operator,
+// environment), never on a rank's own pointers: the kernels take unaligned buffers on slower paths instead.
 HcclResult Communicator::run_pipe(const OpRequest &rq, bool want_mc)
 {
     const EnvConfig &env = env_config();
     const int p = nranks_, nl = nlocal(), es = dtype_size(rq.dtype);
     int mode = pipe_mode_for(rq.coll);
     const uint64_t block_bytes = rq.count * (uint64_t)es;
-    const bool reducing = mode == PM_ALLREDUCE || mode == PM_ALLREDUCE_ONESHOT || mode == PM_REDUCE_SCATTER;
-    bool use_mc = want_mc && nvls_ && block_bytes % 16 == 0 && (!reducing || nvls_reduce_supported(rq.dtype, rq.redop, block_bytes)) && !deterministic();
-    if (mode == PM_ALLGATHER) use_mc = false;  // blocks are pulled from the peers' slots
-    if (mode == PM_BROADCAST_CHAIN && use_mc) mode = PM_BROADCAST_MC;
-    // bytes that one chunk moves over the links, per element of a block
-    const uint64_t fan = (mode == PM_REDUCE_SCATTER || mode == PM_ALLGATHER) ? (uint64_t)p : 1;
+    const bool reducing = rq.coll == COLL_ALLREDUCE || rq.coll == COLL_REDUCE_SCATTER;
+    const bool use_mc = want_mc && nvls_ && block_bytes % 16 == 0 && (!reducing || nvls_reduce_supported(rq.dtype, rq.redop, block_bytes)) && !deterministic();
+    if (use_mc) {
+        if (mode == PM_AR2_PUSH) mode = PM_AR2_MC;
+        else if (mode == PM_AR1_PUSH) mode = PM_AR1_MC;
+        else if (mode == PM_RS_PUSH) mode = PM_RS_MC;
+        else if (mode == PM_BC_PUSH) mode = PM_BC_MC;
+    }
+    // a chunk of ce elements per block moves about fan * ce elements over a rank's links
+    const uint64_t fan = (mode == PM_AR2_MC || mode == PM_AR2_PUSH || pipe_mode_is_bcast(mode)) ? 1 : (uint64_t)(p - 1);
     uint64_t link_total = block_bytes * fan;
     uint64_t lc = env.pipe_chunk_bytes ? env.pipe_chunk_bytes : std::min<uint64_t>(8u << 20, std::max<uint64_t>(1u << 20, link_total / 16));
     int nslots = env.pipe_slots > 0 ? std::min(env.pipe_slots, kPipeMaxSlots) : 4;
@@ -741,17 +746,22 @@ HcclResult Communicator::run_pipe(const OpRequest &rq, bool want_mc)
     int budget = all_local_ ? std::max(3, 128 / nl) : 64;
     int n1, n2, n3 = 0;
     switch (mode) {
-        case PM_ALLREDUCE: n1 = budget / 4; n2 = budget / 2; n3 = budget / 4; break;
-        case PM_ALLGATHER: n1 = std::max(1, budget / 8); n2 = budget - n1; break;
-        case PM_BROADCAST_MC: case PM_BROADCAST_CHAIN: n1 = budget / 2; n2 = 0; break;
+        case PM_AR2_MC: case PM_AR2_PUSH: n1 = budget / 4; n2 = budget / 2; n3 = budget / 4; break;
+        case PM_AG_PULL: n1 = std::max(1, budget / 8); n2 = budget - n1; break;
+        case PM_BC_MC: case PM_BC_PUSH: n1 = budget / 2; n2 = 0; break;
+        case PM_RS_PUSH: n1 = budget / 2; n2 = budget - n1; break;
         default: n1 = budget * 3 / 8; n2 = budget - n1; break;
     }
     if (env.pipe_ctas[0] > 0) { n1 = env.pipe_ctas[0]; n2 = env.pipe_ctas[1]; n3 = env.pipe_ctas[2]; }
     const uint64_t chunk_bytes = std::min(ce, rq.count) * (uint64_t)es;
     auto cap = [&](int n, uint64_t bytes) { return (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)std::max(1, n), bytes / (16u << 10))); };
-    if (mode == PM_ALLREDUCE) { n1 = cap(n1, chunk_bytes); n2 = cap(n2, chunk_bytes / p); n3 = cap(n3, chunk_bytes); }
-    else if (mode == PM_BROADCAST_MC || mode == PM_BROADCAST_CHAIN) { n1 = cap(n1, chunk_bytes); n2 = 0; }
-    else { n1 = cap(n1, chunk_bytes * (mode == PM_REDUCE_SCATTER ? p : 1)); n2 = cap(n2, chunk_bytes * (mode == PM_ALLGATHER ? p - 1 : 1)); }
+    if (pipe_mode_has_copy_out(mode)) { n1 = cap(n1, chunk_bytes); n2 = cap(n2, chunk_bytes / p); n3 = cap(n3, chunk_bytes); }
+    else if (pipe_mode_is_bcast(mode)) { n1 = cap(n1, chunk_bytes); n2 = 0; }
+    else {
+        const bool rs = mode == PM_RS_MC || mode == PM_RS_PUSH;
+        n1 = cap(n1, chunk_bytes * (rs ? p : 1));
+        n2 = cap(n2, chunk_bytes * (mode == PM_AG_PULL ? p - 1 : 1));
+    }
     std::vector<PipeArgs> args(nl);
     for (int li = 0; li < nl; ++li) {
         PipeArgs &a = args[li];
@@ -760,7 +770,7 @@ HcclResult Communicator::run_pipe(const OpRequest &rq, bool want_mc)
         a.out = (uint8_t *)rq.out[li];
         a.count = rq.count; a.chunk_elems = ce; a.seq = seq_;
         a.mode = mode; a.dtype = rq.dtype; a.root = rq.root; a.nslots = nslots;
-        a.n1 = n1; a.n2 = n2; a.n3 = n3; a.use_mc = use_mc ? 1 : 0;
+        a.n1 = n1; a.n2 = n2; a.n3 = n3;
         status_[li]->head = seq_;
     }
     stats_.launches++;

@@ -44,10 +44,11 @@ HcclResult launch_pipe_coll(const RankCtx *dev_ctx, const PipeArgs *args, int nl
 {
     if (nlocal < 1 || nlocal > kMaxRanks) return HCCL_E_PARA;
     const PipeArgs &a0 = args[0];
-    const bool bcast = a0.mode == PM_BROADCAST_MC || a0.mode == PM_BROADCAST_CHAIN;
-    const int nb = a0.n1 + a0.n2 + (a0.mode == PM_ALLREDUCE ? a0.n3 : 0);
+    if (a0.mode < 0 || a0.mode >= PM_COUNT) return HCCL_E_PARA;
+    const bool bcast = pipe_mode_is_bcast(a0.mode), three = pipe_mode_has_copy_out(a0.mode);
+    const int nb = bcast ? a0.n1 : a0.n1 + a0.n2 + (three ? a0.n3 : 0);
     if (nb < 1 || nb > kMaxChannels || a0.nslots < 1 || a0.nslots > kPipeMaxSlots || a0.chunk_elems == 0) return HCCL_E_PARA;
-    if (!bcast && (a0.n1 < 1 || a0.n2 < 1 || (a0.mode == PM_ALLREDUCE && a0.n3 < 1))) return HCCL_E_PARA;
+    if (a0.n1 < 1 || (!bcast && a0.n2 < 1) || (three && a0.n3 < 1)) return HCCL_E_PARA;
     PipeArgsArray arr;
     for (int i = 0; i < nlocal; ++i) arr.a[i] = args[i];
     const void *fn = pipe_kernel_for(a0.dtype, redop);

@@ -1,53 +1,69 @@
 // Launch interface of the pipelined large-message kernels (kernels/pipe_coll.cuh, pipe_coll.cu).
 //
 // One launch runs a whole collective of any size through a small ring of staging slots: the message is cut into
-// chunks, and the CTAs of a rank are split into groups that each own one stage of the pipeline (copy-in, transfer /
-// reduce over NVLink, copy-out), so that the local copies of chunk c+1 and c-1 run while chunk c crosses the links.
+// chunks, and the CTAs of a rank are split into groups that each own one stage of the pipeline (stage-in or push,
+// reduce / pull, copy-out), so that the local copies of chunk c+1 and c-1 run while chunk c crosses the links.
 // Role of the reference's big-data AIV kernels (algorithm/base/alg_aiv_template/aiv_all_reduce_910b_bigdata.h:19-127
 // ReduceWithFlagWrap, aiv_all_gather_910b_bigdata.h:74-154 MemcpyWithFlagWrap, aiv_reduce_scatter_910b_bigdata.h),
 // which overlap producer and consumer blocks with progress flags.
+//
+// Two families.  "mc": every rank copies its chunk into its own slot, the in-switch reduction (multimem.ld_reduce)
+// reads all slots at once and multimem.st writes all of them at once.  "push": a rank stores its contribution straight
+// into the slots of the ranks that need it (peer stores only, no peer loads: a store needs no round trip), and every
+// reduction reads local memory.
 #pragma once
 #include "algo/plan.h"
 
 namespace hcclb {
 
 enum PipeMode : int32_t {
-    PM_ALLREDUCE = 0,      // two-shot: copy-in | reduce my slice of the chunk over all ranks, write it back to all | copy-out
-    PM_ALLREDUCE_ONESHOT,  // copy-in | every rank reduces the whole chunk from all slots straight into its receive buffer
-    PM_REDUCE_SCATTER,     // copy-in of the p blocks of a chunk | reduce my block over all ranks into the receive buffer
-    PM_ALLGATHER,          // copy-in of my block | pull the peers' blocks straight into the receive buffer
-    PM_BROADCAST_MC,       // root: multicast store of the chunk into every rank's slot | others: copy-out
-    PM_BROADCAST_CHAIN,    // root -> root+1 -> ... : every rank pulls the chunk from its predecessor's slot
+    PM_AR2_MC = 0,  // AllReduce two-shot: copy-in | ld_reduce my slice of the chunk, multimem.st it back into every slot | copy-out
+    PM_AR2_PUSH,    // AllReduce two-shot: push slice q to rank q | reduce my slice locally, store the result to every rank | copy-out
+    PM_AR1_MC,      // AllReduce one-shot: copy-in | ld_reduce the whole chunk into the receive buffer
+    PM_AR1_PUSH,    // AllReduce one-shot: push the chunk to every peer | reduce the p copies locally into the receive buffer
+    PM_RS_MC,       // ReduceScatter: copy-in of the p blocks of a chunk | ld_reduce my block into the receive buffer
+    PM_RS_PUSH,     // ReduceScatter: push block q to rank q | reduce the p copies of my block locally into the receive buffer
+    PM_AG_PULL,     // AllGather: copy-in of my block | pull the peers' blocks straight into the receive buffer
+    PM_BC_MC,       // Broadcast: root multicasts the chunk into every slot | the others copy out
+    PM_BC_PUSH,     // Broadcast chain root -> root+1 -> ...: every rank copies its slot out and on into its successor's slot
+    PM_COUNT
 };
 
 constexpr int kPipeMaxSlots = 16;
 constexpr int kPipeRoles = 3;
 constexpr size_t kPipeCounterWords = (size_t)kPipeRoles * kPipeMaxSlots;  // per local rank, device memory, zero between ops
 // Flag words of the pipeline inside bank 0 of the flag page (channel index): values are (seq << kSeqShift) + chunk + 1.
-constexpr int kPipeWordReady = 0;  // source rank finished staging the chunk
-constexpr int kPipeWordDone = 1;   // source rank finished its transfer stage on the chunk
-constexpr int kPipeWordOut = 2;    // (own page only) copy-out of the chunk finished
-constexpr int kPipeTraceWords = 16;
+constexpr int kPipeWordReady = 0;  // source rank finished its first stage on the chunk (slot staged, or contribution pushed)
+constexpr int kPipeWordDone = 1;   // source rank finished its second stage on the chunk
+constexpr int kPipeWordOut = 2;    // source rank finished copying the chunk out
 
 struct PipeArgs {
     const uint8_t *in;
     uint8_t *out;
     uint64_t count;        // elements: AllReduce / Broadcast message, AllGather send count, ReduceScatter receive count
-    uint64_t chunk_elems;  // elements of one block that a chunk covers
+    uint64_t chunk_elems;  // elements of one block that a chunk covers; a multiple of nranks * 256 bytes
     uint64_t seq;
     int32_t mode, dtype, root, nslots;
-    int32_t n1, n2, n3;    // CTAs per stage (AllReduce uses all three, the other modes the first two; Broadcast: all CTAs do one job)
-    int32_t use_mc;        // 1: multimem.ld_reduce / multimem.st through the NVLS mapping of the staging buffer
+    int32_t n1, n2, n3;    // CTAs per stage (two-shot AllReduce uses all three, Broadcast only n1, the other modes the first two)
+    int32_t pad;
 };
 struct PipeArgsArray {
     PipeArgs a[kMaxRanks];
 };
 
-// Bytes of one ring slot for the given mode.
+// Bytes of one ring slot.
 HCCLB_HD uint64_t pipe_slot_bytes(int mode, uint64_t chunk_elems, int es, int p)
 {
-    return (mode == PM_REDUCE_SCATTER ? (uint64_t)p : 1ull) * chunk_elems * (uint64_t)es;
+    const uint64_t c = chunk_elems * (uint64_t)es;
+    switch (mode) {
+        case PM_AR2_PUSH: return 2 * c;  // the p pushed slices, then the p reduced slices
+        case PM_AR1_PUSH: case PM_RS_MC: case PM_RS_PUSH: return (uint64_t)p * c;
+        default: return c;
+    }
 }
+HCCLB_HD bool pipe_mode_is_mc(int mode) { return mode == PM_AR2_MC || mode == PM_AR1_MC || mode == PM_RS_MC || mode == PM_BC_MC; }
+HCCLB_HD bool pipe_mode_is_bcast(int mode) { return mode == PM_BC_MC || mode == PM_BC_PUSH; }
+HCCLB_HD bool pipe_mode_has_copy_out(int mode) { return mode == PM_AR2_MC || mode == PM_AR2_PUSH; }
 
 // One launch runs the listed local ranks (more than one: virtual ranks of one GPU).  Always a cooperative launch: the
 // stages of a rank wait on one another, so all CTAs have to be resident together.
