@@ -733,34 +733,40 @@ HcclResult Communicator::run_pipe(const OpRequest &rq, bool want_mc)
     const uint64_t fan = (mode == PM_AR2_MC || mode == PM_AR2_PUSH || pipe_mode_is_bcast(mode)) ? 1 : (uint64_t)(p - 1);
     uint64_t link_total = block_bytes * fan;
     uint64_t lc = env.pipe_chunk_bytes ? env.pipe_chunk_bytes : std::min<uint64_t>(8u << 20, std::max<uint64_t>(1u << 20, link_total / 16));
-    int nslots = env.pipe_slots > 0 ? std::min(env.pipe_slots, kPipeMaxSlots) : 4;
+    int nslots = env.pipe_slots > 0 ? std::min(env.pipe_slots, kPipeMaxSlots) : 8;
     const uint64_t unit = (uint64_t)p * (256 / es);  // elements: slices of a chunk stay 256-byte aligned
     auto slot_of = [&](uint64_t ce) { return pipe_slot_bytes(mode, ce, es, p); };
     uint64_t ce = std::max<uint64_t>(unit, lc / fan / es / unit * unit);
+    while (nslots > 4 && slot_of(ce) * nslots > settings_.stage_half_bytes) --nslots;
     while (ce > unit && slot_of(ce) * nslots > settings_.stage_half_bytes) ce = std::max<uint64_t>(unit, ce / 2 / unit * unit);
     while (nslots > 1 && slot_of(ce) * nslots > settings_.stage_half_bytes) --nslots;
     CHK_RET_LOG(slot_of(ce) * nslots > settings_.stage_half_bytes, HCCL_E_MEMORY, "staging buffer too small for the pipelined kernels");
     while (ceil_div_u64(rq.count, ce) >= (1ull << kSeqShift) - 1) ce *= 2;  // chunk index travels in the low flag bits
     CHK_RET_LOG(slot_of(ce) * nslots > settings_.stage_half_bytes, HCCL_E_MEMORY, "message needs more pipeline chunks than a flag can count");
-    // CTAs per stage: enough to keep the links busy, no more than 16 KiB-per-CTA pieces justify
-    int budget = all_local_ ? std::max(3, 128 / nl) : 64;
-    int n1, n2, n3 = 0;
-    switch (mode) {
-        case PM_AR2_MC: case PM_AR2_PUSH: n1 = budget / 4; n2 = budget / 2; n3 = budget / 4; break;
-        case PM_AG_PULL: n1 = std::max(1, budget / 8); n2 = budget - n1; break;
-        case PM_BC_MC: case PM_BC_PUSH: n1 = budget / 2; n2 = 0; break;
-        case PM_RS_PUSH: n1 = budget / 2; n2 = budget - n1; break;
-        default: n1 = budget * 3 / 8; n2 = budget - n1; break;
-    }
-    if (env.pipe_ctas[0] > 0) { n1 = env.pipe_ctas[0]; n2 = env.pipe_ctas[1]; n3 = env.pipe_ctas[2]; }
+    // CTAs per stage.  The copy stages are driven by the copy engine (one thread per CTA, about 160 KB in flight each) and
+    // need few CTAs; the reduce stage runs register loops and gets the rest.  No more CTAs than 16 KiB pieces justify.
+    const int budget = all_local_ ? std::max(3, 128 / nl) : 64;
+    const bool three = pipe_mode_has_copy_out(mode), bc = pipe_mode_is_bcast(mode);
+    int n[3] = {0, 0, 0}, g[3] = {1, 1, 1};
+    if (three) { n[0] = std::max(1, budget / 8); n[2] = std::max(1, budget / 8); n[1] = budget - n[0] - n[2]; }
+    else if (bc) { n[0] = std::max(1, budget / 4); }
+    else if (mode == PM_AG_PULL) { n[0] = std::max(1, budget / 16); n[1] = std::max(1, budget / 4); }
+    else { n[0] = std::max(1, budget / (mode == PM_RS_MC ? 4 : 8)); n[1] = budget - n[0]; }
+    if (env.pipe_ctas[0] > 0) { n[0] = env.pipe_ctas[0]; n[1] = env.pipe_ctas[1]; n[2] = env.pipe_ctas[2]; }
+    if (bc) n[1] = n[2] = 0;
+    if (!three) n[2] = 0;
     const uint64_t chunk_bytes = std::min(ce, rq.count) * (uint64_t)es;
-    auto cap = [&](int n, uint64_t bytes) { return (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)std::max(1, n), bytes / (16u << 10))); };
-    if (pipe_mode_has_copy_out(mode)) { n1 = cap(n1, chunk_bytes); n2 = cap(n2, chunk_bytes / p); n3 = cap(n3, chunk_bytes); }
-    else if (pipe_mode_is_bcast(mode)) { n1 = cap(n1, chunk_bytes); n2 = 0; }
-    else {
-        const bool rs = mode == PM_RS_MC || mode == PM_RS_PUSH;
-        n1 = cap(n1, chunk_bytes * (rs ? p : 1));
-        n2 = cap(n2, chunk_bytes * (mode == PM_AG_PULL ? p - 1 : 1));
+    auto cap = [&](int v, uint64_t bytes) { return (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)std::max(1, v), bytes / (16u << 10))); };
+    const bool rs = mode == PM_RS_MC || mode == PM_RS_PUSH;
+    n[0] = cap(n[0], chunk_bytes * (rs ? p : 1));
+    if (three) { n[1] = cap(n[1], chunk_bytes / p); n[2] = cap(n[2], chunk_bytes); }
+    else if (!bc) n[1] = cap(n[1], chunk_bytes * (mode == PM_AG_PULL ? p - 1 : 1));
+    // groups: two or three chunks in flight per stage hide a stage's flag traffic behind its transfers
+    const uint64_t nchunks = ceil_div_u64(rq.count, ce);
+    for (int i = 0; i < 3; ++i) {
+        int want = env.pipe_groups[i] > 0 ? env.pipe_groups[i] : (i == 1 && !bc ? 3 : 2);
+        while (want > 1 && (n[i] % want != 0 || (uint64_t)want > nchunks)) --want;
+        g[i] = std::max(1, want);
     }
     std::vector<PipeArgs> args(nl);
     for (int li = 0; li < nl; ++li) {
@@ -770,7 +776,7 @@ HcclResult Communicator::run_pipe(const OpRequest &rq, bool want_mc)
         a.out = (uint8_t *)rq.out[li];
         a.count = rq.count; a.chunk_elems = ce; a.seq = seq_;
         a.mode = mode; a.dtype = rq.dtype; a.root = rq.root; a.nslots = nslots;
-        a.n1 = n1; a.n2 = n2; a.n3 = n3;
+        a.n1 = n[0]; a.n2 = n[1]; a.n3 = n[2]; a.g1 = g[0]; a.g2 = g[1]; a.g3 = g[2];
         status_[li]->head = seq_;
     }
     stats_.launches++;

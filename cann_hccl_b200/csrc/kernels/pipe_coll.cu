@@ -1,6 +1,9 @@
 // Launcher of the pipelined large-message kernels (pipe_coll.cuh); the kernels themselves are instantiated per element
 // type in exec_plan_<type>.cu.
 #include <cuda_runtime.h>
+#include <mutex>
+#include <set>
+#include <utility>
 #include "common/log.h"
 #include "kernels/pipe_coll.h"
 
@@ -49,12 +52,29 @@ HcclResult launch_pipe_coll(const RankCtx *dev_ctx, const PipeArgs *args, int nl
     const int nb = bcast ? a0.n1 : a0.n1 + a0.n2 + (three ? a0.n3 : 0);
     if (nb < 1 || nb > kMaxChannels || a0.nslots < 1 || a0.nslots > kPipeMaxSlots || a0.chunk_elems == 0) return HCCL_E_PARA;
     if (a0.n1 < 1 || (!bcast && a0.n2 < 1) || (three && a0.n3 < 1)) return HCCL_E_PARA;
+    if (a0.g1 < 1 || a0.g2 < 1 || a0.g3 < 1) return HCCL_E_PARA;
     PipeArgsArray arr;
     for (int i = 0; i < nlocal; ++i) arr.a[i] = args[i];
     const void *fn = pipe_kernel_for(a0.dtype, redop);
+    {
+        // the opt-in to more than 48 KB of dynamic shared memory is a property of (device, function): once for each pair
+        static std::mutex mu;
+        static std::set<std::pair<int, const void *>> done;
+        int dev = 0;
+        cudaGetDevice(&dev);
+        std::lock_guard<std::mutex> lk(mu);
+        if (!done.count({dev, fn})) {
+            cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPipeDynSmem);
+            if (e != cudaSuccess) {
+                HLOG_ERROR("cudaFuncSetAttribute(pipelined kernel, %zu bytes of shared memory) failed: %s", kPipeDynSmem, cudaGetErrorString(e));
+                return HCCL_E_RUNTIME;
+            }
+            done.insert({dev, fn});
+        }
+    }
     dim3 grid((unsigned)nb, (unsigned)nlocal), block(kPipeThreads);
     void *kargs[] = {(void *)&dev_ctx, (void *)&arr};
-    cudaError_t e = cudaLaunchCooperativeKernel(fn, grid, block, kargs, 0, (cudaStream_t)stream);
+    cudaError_t e = cudaLaunchCooperativeKernel(fn, grid, block, kargs, kPipeDynSmem, (cudaStream_t)stream);
     if (e != cudaSuccess) {
         HLOG_ERROR("pipelined kernel launch failed (mode %d, grid %dx%d): %s", a0.mode, nb, nlocal, cudaGetErrorString(e));
         return HCCL_E_RUNTIME;

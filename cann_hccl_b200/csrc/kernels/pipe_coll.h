@@ -29,13 +29,19 @@ enum PipeMode : int32_t {
     PM_COUNT
 };
 
+constexpr uint32_t kTmaBuf = 32 * 1024;  // piece of a bulk asynchronous copy
+constexpr int kTmaDepth = 6;             // pieces of a CTA's shared-memory ring
+constexpr size_t kPipeDynSmem = (size_t)kTmaBuf * kTmaDepth;  // dynamic shared memory of the kernels
 constexpr int kPipeMaxSlots = 16;
 constexpr int kPipeRoles = 3;
 constexpr size_t kPipeCounterWords = (size_t)kPipeRoles * kPipeMaxSlots;  // per local rank, device memory, zero between ops
-// Flag words of the pipeline inside bank 0 of the flag page (channel index): values are (seq << kSeqShift) + chunk + 1.
+// Progress words of the pipeline: one per (stage, source rank, ring slot) inside bank 0 of the flag page; the value is
+// (seq << kSeqShift) + chunk + 1 of the newest chunk of that slot the stage has finished (per slot the chunks come in order).
 constexpr int kPipeWordReady = 0;  // source rank finished its first stage on the chunk (slot staged, or contribution pushed)
 constexpr int kPipeWordDone = 1;   // source rank finished its second stage on the chunk
 constexpr int kPipeWordOut = 2;    // source rank finished copying the chunk out
+HCCLB_HD size_t pipe_flag_index(int word, int src, int slot) { return flag_index(0, src, word * kPipeMaxSlots + slot); }
+static_assert(kPipeRoles * kPipeMaxSlots <= kMaxChannels, "progress words must fit one bank of the flag page");
 
 struct PipeArgs {
     const uint8_t *in;
@@ -45,6 +51,7 @@ struct PipeArgs {
     uint64_t seq;
     int32_t mode, dtype, root, nslots;
     int32_t n1, n2, n3;    // CTAs per stage (two-shot AllReduce uses all three, Broadcast only n1, the other modes the first two)
+    int32_t g1, g2, g3;    // groups per stage: group g of G takes the chunks c with c % G == g (CTAs of a stage divisible by G)
     int32_t pad;
 };
 struct PipeArgsArray {
