@@ -546,8 +546,11 @@ HcclResult Communicator::run_collective_once(const OpRequest &rq)
     if (rq.nchan > 0) sel.nchan = rq.nchan;
     if (p == 1) sel.algo = ALGO_SINGLE;
     if (rq.coll == COLL_BARRIER) { sel.algo = p == 1 ? ALGO_SINGLE : ALGO_MESH; sel.nchan = 1; }
-    // zero-copy: both buffers of every local rank inside registered symmetric memory with a multicast mapping, at offsets
-    // that all ranks share; agreed once per (buffers, count) over the hub so that every rank takes the same path
+    // zero-copy: both buffers of every local rank inside registered symmetric memory with a multicast mapping.  The decision
+    // is made from this rank's own lookup and nothing else: registration is collective, and a collective whose buffers lie in
+    // registered memory has to be called with the same (allocation, offset) pair on every rank (the contract of symmetric
+    // memory).  No agreement round per call, so no rank can wait alone in one; a caller that breaks the contract is caught
+    // by the consistency check below, whose frame carries the algorithm and the offsets.
     struct ZcInfo { int hin = 0, hout = 0; size_t oin = 0, oout = 0; };
     std::vector<ZcInfo> zc(nl);
     bool use_zc = false;
@@ -561,28 +564,10 @@ HcclResult Communicator::run_collective_once(const OpRequest &rq)
             zc[li].hout = find_user_seg(li, rq.out[li], rq.count * es, &zc[li].oout);
             mine = zc[li].hin && zc[li].hout && (host_tr || (user_segs_[zc[li].hin][li].mc && user_segs_[zc[li].hout][li].mc)) &&
                    ((zc[li].oin | zc[li].oout) & 15) == 0;
+            // virtual ranks of one process: the same pair on every local rank
+            mine = mine && zc[li].hin == zc[0].hin && zc[li].hout == zc[0].hout && zc[li].oin == zc[0].oin && zc[li].oout == zc[0].oout;
         }
-        std::ostringstream zk;
-        zk << rq.in[0] << ':' << rq.out[0] << ':' << rq.count << ':' << rq.dtype << ':' << rq.redop;
-        auto zit = zc_agreed_.find(zk.str());
-        if (zit == zc_agreed_.end()) {
-            struct { uint32_t ok; int32_t hin, hout; uint64_t oin, oout; } me_v{mine ? 1u : 0u, zc[0].hin, zc[0].hout, zc[0].oin, zc[0].oout};
-            std::vector<std::string> all;
-            int agreed = mine ? 1 : 0;
-            if (!all_local_) {
-                CHK_RET(exchange("zc/" + std::to_string(zc_agreed_.size()), std::string((const char *)&me_v, sizeof(me_v)), &all));
-                for (auto &sblob : all) {
-                    decltype(me_v) o;
-                    memcpy(&o, sblob.data(), sizeof(o));
-                    if (!o.ok || o.hin != me_v.hin || o.hout != me_v.hout || o.oin != me_v.oin || o.oout != me_v.oout) agreed = 0;
-                }
-            } else {
-                for (int li = 1; li < nl; ++li)
-                    if (zc[li].hin != zc[0].hin || zc[li].hout != zc[0].hout || zc[li].oin != zc[0].oin || zc[li].oout != zc[0].oout) agreed = 0;
-            }
-            zit = zc_agreed_.emplace(zk.str(), agreed).first;
-        }
-        use_zc = zit->second == 1;
+        use_zc = mine;
         CHK_RET_LOG(rq.algo == ALGO_NVLS_ZC && !use_zc, HCCL_E_PARA, "zero-copy AllReduce needs both buffers in registered symmetric memory at the same offsets on every rank");
         if (use_zc) {
             sel.algo = ALGO_NVLS_ZC;
@@ -598,7 +583,7 @@ HcclResult Communicator::run_collective_once(const OpRequest &rq)
         HLOG_ERROR("NVLS algorithm requested but no multicast mapping exists on this communicator");
         return HCCL_E_NOT_SUPPORT;
     }
-    CHK_RET(consistency_check(rq, sel.algo));
+    CHK_RET(consistency_check(rq, sel.algo, use_zc ? ((uint64_t)zc[0].hin << 48) ^ zc[0].oin : 0, use_zc ? ((uint64_t)zc[0].hout << 48) ^ zc[0].oout : 0));
     if (sel.algo == ALGO_LL) {
         bool fits = rq.coll == COLL_ALLREDUCE && ll_ok_ && rq.count * es <= kLlMaxPayload;
         for (int li = 0; li < nl && fits; ++li) fits = (((uintptr_t)rq.in[li] | (uintptr_t)rq.out[li]) & 7) == 0;
@@ -819,7 +804,7 @@ HcclResult Communicator::run_ll_allreduce(const OpRequest &rq)
     return launch_ar_ll(args.data(), nl, rq.dtype, rq.redop, rq.stream);
 }
 
-HcclResult Communicator::consistency_check(const OpRequest &rq, int algo)
+HcclResult Communicator::consistency_check(const OpRequest &rq, int algo, uint64_t zc_in, uint64_t zc_out)
 {
     if (all_local_ || nranks_ == 1 || !consistency_enabled()) return HCCL_SUCCESS;
     // one check per distinct op shape: the parameter frame of every rank must hash identically
@@ -830,6 +815,7 @@ HcclResult Communicator::consistency_check(const OpRequest &rq, int algo)
     bool uniform = !(rq.coll == COLL_ALLTOALLV || rq.coll == COLL_ALLTOALLVC);
     f.count = uniform ? rq.count : 0;
     f.stage_half = settings_.stage_half_bytes;
+    f.zc_in = zc_in; f.zc_out = zc_out;
     if (rq.counts) f.counts_crc = crc32(rq.counts, 8 * (size_t)nranks_, 0);
     if (rq.displs) f.displs_crc = crc32(rq.displs, 8 * (size_t)nranks_, 0);
     std::string key((const char *)&f, sizeof(f));
@@ -1455,7 +1441,6 @@ HcclResult Communicator::sym_free(int handle)
     user_segs_.erase(it);
     for (void *t : user_peer_tabs_[handle]) { if (settings_.transport == TR_DEVICE) cudaFree(t); else free(t); }
     user_peer_tabs_.erase(handle);
-    zc_agreed_.clear();
     return HCCL_SUCCESS;
 }
 int Communicator::find_user_seg(int li, const void *ptr, size_t bytes, size_t *offset)

@@ -180,7 +180,7 @@ private:
     int pipe_mode_for(int coll) const;  // PipeMode of a collective, -1 when it has no pipelined kernel
     HcclResult tp_workspace(const std::string &key, size_t data_bytes, int M, void **ws_out);
     void tp_release_workspaces();
-    HcclResult consistency_check(const OpRequest &rq, int algo);
+    HcclResult consistency_check(const OpRequest &rq, int algo, uint64_t zc_in = 0, uint64_t zc_out = 0);
     HcclResult maybe_retry(const OpRequest &rq, HcclResult failure);
     void heartbeat_loop();
     void record_trace(const OpRequest &rq, int algo, int nchan, uint64_t bytes, double us);
@@ -235,7 +235,6 @@ private:
 
     std::map<int, std::vector<SymSegment>> user_segs_;
     std::map<int, std::vector<void *>> user_peer_tabs_;   // per allocation and local rank: array of nranks peer pointers (device or host memory)
-    std::map<std::string, int> zc_agreed_;                 // (buffers, count) -> 1 when every rank can run the op zero-copy, 0 otherwise
     // Finds the registered allocation that holds [ptr, ptr+bytes) of local rank li; returns its handle or 0.
     int find_user_seg(int li, const void *ptr, size_t bytes, size_t *offset);
     HcclResult register_user_segs(std::vector<SymSegment> segs, int *handle);

@@ -17,6 +17,14 @@ struct TpWorkspace {
     uint64_t epoch = 0;
 };
 
+// Workspaces of all communicators of the process.  Communicators of different GPUs run on different threads
+// (HcclCommInitAll): every access to the outer map holds ws_mu(); a communicator's own entries are only touched under its
+// operation lock, so references into the inner map stay valid outside ws_mu().
+static std::mutex &ws_mu()
+{
+    static std::mutex m;
+    return m;
+}
 static std::map<Communicator *, std::map<std::string, TpWorkspace>> &workspaces()
 {
     static std::map<Communicator *, std::map<std::string, TpWorkspace>> w;
@@ -25,15 +33,25 @@ static std::map<Communicator *, std::map<std::string, TpWorkspace>> &workspaces(
 
 void Communicator::tp_release_workspaces()
 {
-    auto it = workspaces().find(this);
-    if (it == workspaces().end()) return;
-    for (auto &kv : it->second) alloc_->release(&kv.second.segs);
-    workspaces().erase(it);
+    std::map<std::string, TpWorkspace> mine;
+    {
+        std::lock_guard<std::mutex> lk(ws_mu());
+        auto it = workspaces().find(this);
+        if (it == workspaces().end()) return;
+        mine = std::move(it->second);
+        workspaces().erase(it);
+    }
+    for (auto &kv : mine) alloc_->release(&kv.second.segs);
 }
 
 HcclResult Communicator::tp_workspace(const std::string &key, size_t data_bytes, int M, void **ws_out)
 {
-    auto &mine = workspaces()[this];
+    std::map<std::string, TpWorkspace> *minep;
+    {
+        std::lock_guard<std::mutex> lk(ws_mu());
+        minep = &workspaces()[this];  // std::map: the inner map's address survives insertions of other communicators
+    }
+    auto &mine = *minep;
     auto it = mine.find(key);
     if (it == mine.end()) {
         TpWorkspace w;
@@ -79,36 +97,19 @@ HcclResult Communicator::tp_all_gather_matmul(const void *const *x_shard, const 
     CHK_RET(tp_workspace(key.str(), (size_t)M * K * 2, M, &wsp));
     TpWorkspace &ws = *(TpWorkspace *)wsp;
     ++ws.epoch;
-    // zero-copy source: when every rank's shard lies in registered symmetric memory at one common offset the peers pull it
-    // from where it is; agreed once per (buffer, shape) so that all ranks take the same path
+    // zero-copy source: a shard that lies in registered symmetric memory is pulled by the peers from where it is.  Decided
+    // from this rank's own lookup: symmetric memory is used with the same (allocation, offset) on every rank by contract,
+    // so no per-call agreement round (in which a rank could wait alone) is needed.
     std::vector<int> zh(nl, 0);
     std::vector<size_t> zo(nl, 0);
     bool zc = false;
     if (nranks_ > 1 && !user_segs_.empty()) {
         const size_t shard_bytes = (size_t)(M / nranks_) * K * 2;
-        bool mine = true;
-        for (int li = 0; li < nl && mine; ++li) {
+        zc = true;
+        for (int li = 0; li < nl && zc; ++li) {
             zh[li] = find_user_seg(li, x_shard[li], shard_bytes, &zo[li]);
-            mine = zh[li] != 0 && (zo[li] & 15) == 0 && zh[li] == zh[0] && zo[li] == zo[0];
+            zc = zh[li] != 0 && (zo[li] & 15) == 0 && zh[li] == zh[0] && zo[li] == zo[0];
         }
-        std::ostringstream zk;
-        zk << "ag:" << x_shard[0] << ':' << M << ':' << K;
-        auto zit = zc_agreed_.find(zk.str());
-        if (zit == zc_agreed_.end()) {
-            struct { uint32_t ok; int32_t h; uint64_t off; } me_v{mine ? 1u : 0u, zh[0], zo[0]};
-            int agreed = mine ? 1 : 0;
-            if (!all_local_) {
-                std::vector<std::string> all;
-                CHK_RET(exchange("zc/" + std::to_string(zc_agreed_.size()), std::string((const char *)&me_v, sizeof(me_v)), &all));
-                for (auto &blob : all) {
-                    decltype(me_v) o;
-                    memcpy(&o, blob.data(), sizeof(o));
-                    if (!o.ok || o.h != me_v.h || o.off != me_v.off) agreed = 0;
-                }
-            }
-            zit = zc_agreed_.emplace(zk.str(), agreed).first;
-        }
-        zc = zit->second == 1;
     }
     StateGuard guard(state_, CS_INUSE);
     std::vector<TpGemmParams> P(nl);
@@ -130,7 +131,9 @@ HcclResult Communicator::tp_all_gather_matmul(const void *const *x_shard, const 
     stats_.ops[COLL_ALLGATHER]++;
     int ncomm = 8;  // the launcher drops them for a single rank
     if (const char *e = getenv("HCCL_TP_COMM_CTAS")) ncomm = std::max(1, atoi(e));
-    return launch_tp_gemm(P.data(), A.data(), B.data(), nl, ncomm, stream);
+    HcclResult rc = launch_tp_gemm(P.data(), A.data(), B.data(), nl, ncomm, stream);
+    if (rc != HCCL_SUCCESS) --ws.epoch;  // rejected before any kernel ran: the counters still stand at the previous call
+    return rc;
 }
 
 HcclResult Communicator::tp_matmul_reduce_scatter(const void *const *h, const void *const *w, void *const *out, int M, int N, int K, void *stream)
@@ -142,7 +145,7 @@ HcclResult Communicator::tp_matmul_reduce_scatter(const void *const *h, const vo
     CHK_RET_LOG(nl > kTpMaxLocal, HCCL_E_NOT_SUPPORT, "at most %d virtual ranks per GPU for the fused kernels", kTpMaxLocal);
     CHK_RET_LOG(M % (128 * nranks_) != 0, HCCL_E_PARA, "M (%d) must be a multiple of 128 x ranks (%d)", M, 128 * nranks_);
     std::ostringstream key;
-    key << "rs:" << M << ':' << N;
+    key << "rs:" << M << ':' << N << ':' << K;  // the panel layout of the completion counters depends on K as well
     void *wsp = nullptr;
     CHK_RET(tp_workspace(key.str(), (size_t)M * N * 2, M, &wsp));
     TpWorkspace &ws = *(TpWorkspace *)wsp;
@@ -162,7 +165,9 @@ HcclResult Communicator::tp_matmul_reduce_scatter(const void *const *h, const vo
     }
     stats_.launches++;
     stats_.ops[COLL_REDUCE_SCATTER]++;
-    return launch_tp_gemm(P.data(), A.data(), B.data(), nl, 0, stream);
+    HcclResult rc = launch_tp_gemm(P.data(), A.data(), B.data(), nl, 0, stream);
+    if (rc != HCCL_SUCCESS) --ws.epoch;  // rejected before any kernel ran: the counters still stand at the previous call
+    return rc;
 }
 
 }  // namespace hcclb

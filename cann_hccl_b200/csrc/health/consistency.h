@@ -12,6 +12,7 @@ struct OpFrame {
     int32_t coll, dtype, redop, root, algo, pad;
     uint64_t count;
     uint64_t stage_half;
+    uint64_t zc_in, zc_out;  // (allocation << 48) ^ offset of the buffers of a zero-copy op, else 0
     uint32_t counts_crc, displs_crc;
 };
 }  // namespace hcclb

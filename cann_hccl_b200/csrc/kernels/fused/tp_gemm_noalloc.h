@@ -27,7 +27,12 @@
  *     because it is fully rewritten before it is read.  Two calls that overlap on the GPU (different streams, no ordering
  *     between them) race on the array: keep the calls of one device in stream order.
  *
- * Returns an HcclResult value as int (0 = success).
+ * Returns an HcclResult value as int (0 = success).  That value covers argument checks and the launch only.  The kernel's
+ * own waits are bounded; if one runs out, `out` is incomplete and the kernel leaves its code (HCCL_E_TIMEOUT) in a word
+ * inside the same static array.  hcclb200_matmul_reduce_noalloc_status(stream) waits for `stream`, reads that word with a
+ * 4-byte copy into a stack variable (no allocation either) and returns it: 0 when the newest call on this device ran to
+ * the end.  The word is cleared together with the counters at the start of the next call.
+ * First calls on a device may come from several threads at once: the set-up is serialised inside the library.
  */
 #ifndef HCCLB200_TP_GEMM_NOALLOC_H_
 #define HCCLB200_TP_GEMM_NOALLOC_H_
@@ -38,6 +43,7 @@
 extern "C" {
 #endif
 int hcclb200_matmul_reduce_noalloc(const void *h, const void *w, void *out, int M, int N, int K, void *stream);
+int hcclb200_matmul_reduce_noalloc_status(void *stream);
 #ifdef __cplusplus
 }
 #endif

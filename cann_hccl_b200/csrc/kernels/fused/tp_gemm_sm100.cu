@@ -27,6 +27,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <mutex>
 #include <algorithm>
 #include <cstring>
 #include "common/log.h"
@@ -199,8 +200,9 @@ __device__ __forceinline__ bool wait_word_ge(const uint64_t *p, uint64_t want, b
 
 __device__ __forceinline__ void report(const TpGemmParams &P, uint32_t code, int where)
 {
-    if (!P.status) return;
+    if (!P.fail_word) return;
     if (atomicCAS(P.fail_word, 0u, code) != 0u) return;
+    if (!P.status) return;  // no host-mapped status block (allocation-free entry): the failure word is the record
     DevStatus *s = P.status;
     s->step = (uint32_t)where;
     s->peer = -1;
@@ -725,12 +727,18 @@ HcclResult launch_tp_gemm(TpGemmParams *P, const void *const *A, const void *con
         CHK_RET(encode_2d(&P[i].tmB, B[i], (uint64_t)P[i].N, (uint64_t)P[i].K, BN));
         arr.r[i] = P[i];
     }
-    static bool attr_set = false;
+    // the opt-in to large dynamic shared memory belongs to the (device, function) pair: once per device, not per process
+    // (a process may drive several GPUs, one thread each)
+    static std::mutex attr_mu;
+    static bool attr_set[64] = {false};
     size_t smem = tp_gemm_smem_bytes();
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(tp_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) { HLOG_ERROR("cannot raise dynamic shared memory to %zu: %s", smem, cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
-        attr_set = true;
+    {
+        std::lock_guard<std::mutex> lk(attr_mu);
+        if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+            cudaError_t e = cudaFuncSetAttribute(tp_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) { HLOG_ERROR("cannot raise dynamic shared memory to %zu: %s", smem, cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
+            if (dev >= 0 && dev < 64) attr_set[dev] = true;
+        }
     }
     dim3 grid((unsigned)(n_gemm + n_comm_ctas), (unsigned)nlocal), block(kThreads);
     cudaError_t e;
@@ -755,10 +763,14 @@ constexpr size_t kNoAllocFlagBytes = 64 * 1024;
 constexpr size_t kNoAllocScratchBytes = kNoAllocFlagBytes + HCCLB200_NOALLOC_MAX_OUT_ELEMS * 2;
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
 
+// The last 64 bytes of the counter area hold the failure word: the first bounded wait of a call that runs out leaves its
+// code there (cleared with the counters at the next call).
+constexpr size_t kNoAllocFailOffset = kNoAllocFlagBytes - 64;
 struct NoAllocDeviceState {
     unsigned char *scratch = nullptr;  // device address of g_noalloc_scratch on that device
 };
 NoAllocDeviceState g_noalloc_state[64];
+std::mutex g_noalloc_mu;  // first calls from several threads set the table up one at a time
 }  // namespace
 
 extern "C" int hcclb200_matmul_reduce_noalloc(const void *h, const void *w, void *out, int M, int N, int K, void *stream)
@@ -771,10 +783,11 @@ extern "C" int hcclb200_matmul_reduce_noalloc(const void *h, const void *w, void
                    (unsigned long long)M * N, (unsigned long long)HCCLB200_NOALLOC_MAX_OUT_ELEMS);
         return HCCL_E_MEMORY;
     }
-    if (tp_flag_words(M, 1) * 8 > kNoAllocFlagBytes) return HCCL_E_MEMORY;
+    if (tp_flag_words(M, 1) * 8 > kNoAllocFailOffset) return HCCL_E_MEMORY;
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return HCCL_E_RUNTIME;
     NoAllocDeviceState &st = g_noalloc_state[dev];
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
     if (!st.scratch) {
         // first call on this device: in host code the array's name is only a stand-in, the kernel needs the device address
         void *p = nullptr;
@@ -796,6 +809,25 @@ extern "C" int hcclb200_matmul_reduce_noalloc(const void *h, const void *w, void
     P.out = (__nv_bfloat16 *)out;
     P.flags[0] = (uint64_t *)st.scratch;
     P.partial[0] = (__nv_bfloat16 *)(st.scratch + kNoAllocFlagBytes);
+    P.fail_word = (uint32_t *)(st.scratch + kNoAllocFailOffset);
     const void *a[1] = {h}, *b[1] = {w};
     return launch_tp_gemm(&P, a, b, 1, 0, stream);
+}
+
+extern "C" int hcclb200_matmul_reduce_noalloc_status(void *stream)
+{
+    using namespace hcclb;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return HCCL_E_RUNTIME;
+    unsigned char *scratch;
+    {
+        std::lock_guard<std::mutex> lk(g_noalloc_mu);
+        scratch = g_noalloc_state[dev].scratch;
+    }
+    if (!scratch) return HCCL_SUCCESS;  // nothing has run on this device yet
+    uint32_t code = 0;
+    if (cudaMemcpyAsync(&code, scratch + kNoAllocFailOffset, sizeof(code), cudaMemcpyDeviceToHost, (cudaStream_t)stream) != cudaSuccess ||
+        cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess)
+        return HCCL_E_RUNTIME;
+    return (int)code;
 }

@@ -17,8 +17,10 @@
 // Data movement.  Plain copies (stage-in, push to the peers' slots, pull from the peers' slots, copy-out) are driven
 // by one thread per CTA with bulk asynchronous copies (cp.async.bulk global -> shared -> global, never multicast)
 // through a 6 x 32 KB shared-memory ring: 160 KB in flight per SM without a register, which is what a microsecond-scale
-// NVLink round trip needs.  Buffers that are not 16-byte aligned take register loops instead.  Reductions run in
-// registers: multimem.ld_reduce / multimem.st for the in-switch modes, local vector loads for the push modes.
+// NVLink round trip needs.  The reductions of the push modes are fed the same way: thread 0 streams tiles of the p
+// sources into the ring, all threads reduce a stage from shared memory in registers and store the result straight to
+// its destinations.  The in-switch modes reduce with multimem.ld_reduce / multimem.st in registers.  Buffers that are
+// not 16-byte aligned take plain register loops instead.
 #pragma once
 #include "kernels/exec_plan_impl.cuh"
 #include "kernels/pipe_coll.h"
@@ -249,6 +251,75 @@ static __device__ __noinline__ void pipe_reduce(const uint8_t *const *src, int p
     }
 }
 
+// Same reduction fed by the copy engine: thread 0 streams tiles of the p sources into the shared-memory ring with bulk
+// asynchronous copies (kStages - 1 stages ahead, about 160 KB in flight), all threads reduce a stage from shared memory in
+// registers and store the result straight to the nd destinations.  All addresses 16-byte aligned, `bytes` a multiple of 16,
+// p <= NP.  `g` counts stages over the kernel's lifetime (as in tma_copy_segments; a CTA uses one of the two, never both).
+// False: an mbarrier poll ran out.
+template <class T, int OP, int NP>
+__device__ __forceinline__ bool tma_reduce_np(uint8_t *ring, uint64_t *bar, uint32_t &g, const uint8_t *const *src, int p, uint8_t *const *dst,
+                                             int nd, uint64_t bytes)
+{
+    using namespace pipe_detail;
+    using N = DNum<T>;
+    using Acc = typename N::Acc;
+    constexpr int E = 16 / sizeof(T);
+    constexpr uint32_t kStageBytes = NP == 8 ? 2 * kTmaBuf : kTmaBuf;       // p tiles per stage
+    constexpr int kStages = (int)(kPipeDynSmem / kStageBytes);
+    constexpr uint32_t kTile = kStageBytes / NP;
+    const int tid = threadIdx.x, nt = blockDim.x;
+    const uint64_t ntiles = (bytes + kTile - 1) / kTile;
+    auto issue = [&](uint64_t t) {
+        const uint64_t off = t * kTile;
+        const uint32_t len = bytes - off < kTile ? (uint32_t)(bytes - off) : kTile, st = (uint32_t)((g + t) % kStages);
+        mbar_expect_tx(&bar[st], len * (uint32_t)p);
+        for (int q = 0; q < p; ++q) bulk_g2s(ring + (size_t)st * kStageBytes + (size_t)q * kTile, src[q] + off, len, &bar[st]);
+    };
+    if (tid == 0) {
+        fence_proxy_async();
+        for (uint64_t t = 0; t < ntiles && t < (uint64_t)(kStages - 1); ++t) issue(t);
+    }
+    bool ok = true;
+    for (uint64_t t = 0; t < ntiles; ++t) {
+        if (tid == 0 && t + kStages - 1 < ntiles) issue(t + kStages - 1);  // into the stage that tile t - 1 left at the barrier below
+        const uint32_t st = (uint32_t)((g + t) % kStages);
+        if (!mbar_wait(&bar[st], (uint32_t)(((g + t) / kStages) & 1))) { ok = false; break; }
+        const uint64_t off = t * kTile;
+        const uint32_t nv = (uint32_t)((bytes - off < kTile ? bytes - off : kTile) >> 4);
+        const uint4 *tile = (const uint4 *)(ring + (size_t)st * kStageBytes);
+        for (uint32_t i = tid; i < nv; i += nt) {
+            Pack16<T> x;
+            x.u = tile[i];
+            Acc acc[E];
+#pragma unroll
+            for (int k = 0; k < E; ++k) acc[k] = N::up(x.e[k]);
+#pragma unroll
+            for (int q = 1; q < NP; ++q)
+                if (q < p) {
+                    Pack16<T> y;
+                    y.u = tile[(size_t)q * (kTile >> 4) + i];
+#pragma unroll
+                    for (int k = 0; k < E; ++k) acc[k] = red_op<OP>(acc[k], N::up(y.e[k]));
+                }
+            Pack16<T> z;
+#pragma unroll
+            for (int k = 0; k < E; ++k) z.e[k] = N::down(acc[k]);
+            for (int q = 0; q < nd; ++q) ((uint4 *)(dst[q] + off))[i] = z.u;
+        }
+        __syncthreads();  // every thread has read the stage: it may be loaded again
+    }
+    g += (uint32_t)ntiles;
+    return ok;
+}
+template <class T, int OP>
+static __device__ __noinline__ bool tma_reduce(uint8_t *ring, uint64_t *bar, uint32_t &g, const uint8_t *const *src, int p, uint8_t *const *dst, int nd,
+                                               uint64_t bytes)
+{
+    if (p <= 2) return tma_reduce_np<T, OP, 2>(ring, bar, g, src, p, dst, nd, bytes);
+    if (p <= 4) return tma_reduce_np<T, OP, 4>(ring, bar, g, src, p, dst, nd, bytes);
+    return tma_reduce_np<T, OP, 8>(ring, bar, g, src, p, dst, nd, bytes);
+}
+
 // in-switch reduction of `bytes` (a multiple of 16) at mc into d: the multicast mapping itself, or local memory of any alignment
 template <class T, int OP>
 static __device__ __noinline__ void pipe_mc_reduce(const uint8_t *mc, uint8_t *d, bool d_is_mc, uint64_t bytes)
@@ -337,6 +408,18 @@ __global__ void __launch_bounds__(kExecThreads, 1) pipe_coll_kernel(const RankCt
         if (!tma) { pipe_copy_segments(s_src, s_dst, s_bytes, nseg, es); return; }
         if (tid == 0 && !tma_copy_segments(pipe_ring, s_bar, tma_g, nseg, s_src, s_dst, s_bytes)) {
             report_failure(c, a.seq, HCCL_E_TIMEOUT, -2, me, b, 0, 0);
+            s_fail = HCCL_E_TIMEOUT;
+        }
+    };
+
+    // dst[0..nd) = reduction of n elements over the p sources in s_src: fed by the copy engine when everything is aligned
+    auto reduce_sources = [&](int nd, uint64_t n) {
+        bool tma = p <= 8 && ((n * es) & 15) == 0;
+        for (int q = 0; q < p; ++q) tma = tma && aligned16(s_src[q]);
+        for (int q = 0; q < nd; ++q) tma = tma && aligned16(s_dst[q]);
+        if (!tma) { if (n) pipe_reduce<T, OP>(s_src, p, s_dst, nd, n); return; }
+        if (!tma_reduce<T, OP>(pipe_ring, s_bar, tma_g, s_src, p, s_dst, nd, n * es) && tid == 0) {
+            report_failure(c, a.seq, HCCL_E_TIMEOUT, -3, me, b, 0, 0);
             s_fail = HCCL_E_TIMEOUT;
         }
     };
@@ -479,7 +562,7 @@ __global__ void __launch_bounds__(kExecThreads, 1) pipe_coll_kernel(const RankCt
                         s_dst[tid] = tid == me ? a.out + mo : c.stage[tid] + soff + (ce + slo(me) + lo) * es;
                     }
                     __syncthreads();
-                    if (hi > lo) pipe_reduce<T, OP>(s_src, p, s_dst, p, hi - lo);
+                    reduce_sources(p, hi > lo ? hi - lo : 0);
                     break;
                 }
                 case PM_AR1_MC: case PM_RS_MC: {
@@ -498,7 +581,7 @@ __global__ void __launch_bounds__(kExecThreads, 1) pipe_coll_kernel(const RankCt
                         if (tid == 0) s_dst[0] = a.out + (e0 + lo) * es;
                     }
                     __syncthreads();
-                    if (hi > lo) pipe_reduce<T, OP>(s_src, p, s_dst, 1, hi - lo);
+                    reduce_sources(1, hi > lo ? hi - lo : 0);
                     break;
                 }
                 case PM_AG_PULL: {

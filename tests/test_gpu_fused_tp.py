@@ -35,6 +35,24 @@ def test_gemm_bf16(M, N, K):
     assert torch.equal(c, c2)
 
 
+def test_gemm_bf16_every_tile_multi_wave():
+    """2048 x 3584 x 8192: 224 output tiles of 128 x 256 on 148 SMs (more than one wave).  A global norm would hide one wrong
+    tile, so every tile is held to a max-abs bound of its own against the fp32 product of the same bf16 operands."""
+    _need_gpu()
+    M, N, K = 2048, 3584, 8192
+    g = torch.Generator(device="cuda").manual_seed(5)
+    a = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    b = (torch.randn(N, K, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    c = fused_tp.gemm(a, b)
+    torch.cuda.synchronize()
+    ref = a.float() @ b.float().t()
+    err = (c.float() - ref).abs().view(M // 128, 128, N // 256, 256).amax(dim=(1, 3))      # [m tiles, n tiles]
+    scale = ref.abs().view(M // 128, 128, N // 256, 256).amax(dim=(1, 3))
+    # bf16 output rounding is 2^-8 relative; fp32 accumulation over K = 8192 adds far less
+    bad = (err > scale * 2 ** -7).nonzero()
+    assert bad.numel() == 0, "tiles off: %s (err %s)" % (bad[:8].tolist(), err[err > scale * 2 ** -7][:8].tolist())
+
+
 def test_gemm_rejects_bad_shapes():
     _need_gpu()
     a = torch.zeros(100, 64, device="cuda", dtype=torch.bfloat16)
@@ -145,6 +163,34 @@ def test_matmul_reduce_scatter(comms, p):
     rows = M // p
     for r in range(p):
         assert rel_err(outs[r], full[r * rows:(r + 1) * rows]) < 2e-2
+
+
+def test_matmul_reduce_scatter_same_shape_other_depth_and_after_rejected_call(comms):
+    """The completion-counter layout depends on K (wide K makes the panels narrower), so calls that share M and N but not K
+    must not share counters; and a call rejected for its arguments must leave the workspace's call count alone."""
+    p = 2
+    c = comms(p)
+    M, N = 512, 512
+    g = torch.Generator(device="cuda").manual_seed(90)
+    ws_small = None
+    for K in (256, 20480, 256):
+        hs = [torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16) for _ in range(p)]
+        ws = [(torch.randn(N, K, device="cuda", generator=g) * 0.02).to(torch.bfloat16) for _ in range(p)]
+        outs = fused_tp.matmul_reduce_scatter(c, hs, ws)
+        assert c.sync() == 0, c.describe_status()
+        full = sum(h.float() @ w.float().t() for h, w in zip(hs, ws))
+        for r in range(p):
+            assert rel_err(outs[r], full[r * (M // p):(r + 1) * (M // p)]) < 2e-2
+        if K == 256:
+            ws_small = (hs, ws, full)
+    hs, ws, full = ws_small
+    bad = [h[:, :200].contiguous() for h in hs]          # K = 200 is not a multiple of 64: refused before any launch
+    with pytest.raises(H.HcclError):
+        fused_tp.matmul_reduce_scatter(c, bad, [w[:, :200].contiguous() for w in ws])
+    outs = fused_tp.matmul_reduce_scatter(c, hs, ws)     # the same workspace right after the refused call
+    assert c.sync() == 0, c.describe_status()
+    for r in range(p):
+        assert rel_err(outs[r], full[r * (M // p):(r + 1) * (M // p)]) < 2e-2
 
 
 def test_tensor_parallel_mlp_forward(comms):

@@ -26,6 +26,9 @@ def test_no_alloc_entry_matches_regular_entry_twice():
     fn = lib.hcclb200_matmul_reduce_noalloc
     fn.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
     fn.restype = C.c_int
+    status = lib.hcclb200_matmul_reduce_noalloc_status
+    status.argtypes = [C.c_void_p]
+    status.restype = C.c_int
     comm = H.Communicator.init_root(1, H.Communicator.get_root_info(), 0, device=True)
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
     for call, (M, N, K) in enumerate([(512, 1024, 256), (1024, 2048, 512)]):
@@ -38,6 +41,7 @@ def test_no_alloc_entry_matches_regular_entry_twice():
         free_before = torch.cuda.mem_get_info()[0]
         rc = fn(h.data_ptr(), w.data_ptr(), got.data_ptr(), M, N, K, stream)
         assert rc == 0, rc
+        assert status(stream) == 0                                     # no bounded wait of the kernel ran out (also waits for the stream)
         torch.cuda.synchronize()
         assert torch.cuda.mem_get_info()[0] == free_before            # nothing was allocated on the device
         # same kernel, same arithmetic: the tolerance of the fused-kernel tests (relative Frobenius error)
