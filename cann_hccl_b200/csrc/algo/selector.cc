@@ -63,9 +63,9 @@ double estimate_us(int coll, int algo, uint64_t bytes, int p, const CostModel &m
     const double lg = std::ceil(std::log2((double)p));
     const bool pow2 = (p & (p - 1)) == 0;
     const double f = (double)(p - 1) / p;
-    // link bytes per chunk of the pipelined kernels (Communicator::run_pipe): 1/16 of what crosses the links, 1 to 8 MiB
+    // link bytes per chunk of the pipelined kernels (Communicator::run_pipe): 1/16 of what crosses the links, 4 to 8 MiB
     const double fan = (coll == COLL_REDUCE_SCATTER || coll == COLL_ALLGATHER) ? p : 1.0;
-    const double chunk = std::min(n * fan, std::min(8.0 * (1 << 20), std::max(1.0 * (1 << 20), n * fan / 16)));
+    const double chunk = std::min(n * fan, std::min(8.0 * (1 << 20), std::max(4.0 * (1 << 20), n * fan / 16)));
     switch (coll) {
         case COLL_ALLREDUCE:
             switch (algo) {

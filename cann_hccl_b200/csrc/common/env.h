@@ -34,6 +34,8 @@ struct EnvConfig {
     int heartbeat_ms = 50;         // HCCL_HEARTBEAT_INTERVAL_MS (reference BROADCAST_INTERVAL 50 ms)
     int stuck_ms = 300000;         // HCCL_STUCK_DETECT_TIME (seconds in env; reference STUCK_INTERVAL 300 s)
     int heartbeat_lost_ms = 3000;  // HCCL_HEARTBEAT_LOST_MS: silence after which a peer counts as lost
+    bool calibrate = true;         // HCCL_CALIBRATE=0: device communicators skip the measurement pass at creation
+    int calibrate_max_mb = 0;      // HCCL_CALIBRATE_MAX_MB: largest message of the calibration ladder (0 = 64)
     int channels = 0;              // HCCL_CHANNELS: force CTAs per op (0 = selector decides)
     uint64_t pipe_chunk_bytes = 0; // HCCL_PIPE_CHUNK_KB: bytes a chunk of the pipelined large-message kernels moves over the links (0 = by message size)
     int pipe_slots = 0;            // HCCL_PIPE_SLOTS: ring depth of the pipelined kernels (0 = default, at most 16)

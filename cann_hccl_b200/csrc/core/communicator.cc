@@ -124,6 +124,11 @@ HcclResult Communicator::create(uint32_t nranks, const RootHandle &root, uint32_
         c->p2p_conn_.reset(new HubClient());
         if (c->p2p_conn_->connect(root.ip, (int)root.port, (int)root.family, tmo) == HCCL_SUCCESS) P2pBackend::create(c.get(), &c->p2p_);
     }
+    if (st.transport == TR_DEVICE && nranks > 1 && env.calibrate) {
+        // every rank runs it (the decision depends on the shared environment only); a failure leaves the default model
+        HcclResult crc = c->calibrate(nullptr);
+        if (crc != HCCL_SUCCESS) { HLOG_WARN("calibration failed (%d): selecting from the default cost model", (int)crc); CHK_RET(c->resume()); }
+    }
     *out = c.release();
     return HCCL_SUCCESS;
 }
@@ -177,6 +182,10 @@ HcclResult Communicator::create_sub(uint32_t rank_num, const uint32_t *rank_ids,
     if (settings_.transport == TR_HOST) c->alloc_.reset(make_host_shm_allocator(c->hub_.get(), c->ident_, (int)sub_rank, (int)rank_num, tmo));
     else c->alloc_.reset(make_device_vmm_allocator(c->hub_.get(), c->ident_, (int)sub_rank, (int)rank_num, settings_.device, env.nvls_enable != 0, tmo));
     CHK_RET(c->init_common());
+    if (c->settings_.transport == TR_DEVICE && rank_num > 1 && env.calibrate) {
+        HcclResult crc = c->calibrate(nullptr);
+        if (crc != HCCL_SUCCESS) { HLOG_WARN("calibration failed (%d): selecting from the default cost model", (int)crc); CHK_RET(c->resume()); }
+    }
     *out = c.release();
     return HCCL_SUCCESS;
 }
@@ -423,21 +432,29 @@ Selection Communicator::select(int coll, uint64_t count, int dtype, int redop) c
     si.forced = forced_algo_for(env, coll);
     si.ll_max_bytes = ll_ok_ ? kLlMaxPayload : 0;
     Selection s = select_algo(si, model_);
-    if (coll == COLL_ALLREDUCE && !tuned_sizes_.empty() && si.forced.empty() && nranks_ > 1) {
+    const int table_coll = coll == COLL_ALLGATHER_V ? COLL_ALLGATHER : (coll == COLL_REDUCE_SCATTER_V ? COLL_REDUCE_SCATTER : coll);
+    auto tt = tuned_.find(table_coll);
+    if (tt != tuned_.end() && !tt->second.sizes.empty() && si.forced.empty() && nranks_ > 1 && si.device) {
         // nearest bucket on a log scale; candidates must be legal for this dtype / op / determinism setting
+        const TunedTable &tb = tt->second;
         size_t best_b = 0;
         double best_d = 1e300;
-        for (size_t b = 0; b < tuned_sizes_.size(); ++b) {
-            double d = std::fabs(std::log2((double)std::max<uint64_t>(si.bytes, 1)) - std::log2((double)tuned_sizes_[b]));
+        for (size_t b = 0; b < tb.sizes.size(); ++b) {
+            double d = std::fabs(std::log2((double)std::max<uint64_t>(si.bytes, 1)) - std::log2((double)tb.sizes[b]));
             if (d < best_d) { best_d = d; best_b = b; }
         }
-        bool nvls_ok = nvls_ && !si.deterministic && si.expansion_mode != 1 && nvls_reduce_supported(dtype, redop, si.bytes);
+        const bool reducing = table_coll == COLL_ALLREDUCE || table_coll == COLL_REDUCE_SCATTER;
+        const bool nvls_ok = nvls_ && !si.deterministic && si.expansion_mode != 1 &&
+                             (reducing ? nvls_reduce_supported(dtype, redop, si.bytes) : si.bytes % 16 == 0);
+        const bool is_v = coll != table_coll;  // the V variants have plain schedules only
         double bt = -1;
         for (int a = 0; a < ALGO_COUNT; ++a) {
-            double t = tuned_us_[best_b][a];
+            double t = tb.us[best_b][a];
             if (t <= 0) continue;
             if ((a == ALGO_NVLS || a == ALGO_NVLS_ONESHOT || a == ALGO_NVLS_PIPE) && !nvls_ok) continue;
             if (a == ALGO_LL && (si.bytes > si.ll_max_bytes || si.expansion_mode == 1)) continue;
+            if ((a == ALGO_MESH_PIPE || a == ALGO_NVLS_PIPE) && (is_v || si.expansion_mode == 1)) continue;
+            if (is_v && (a == ALGO_RHD || a == ALGO_PAIRWISE) && coll == COLL_REDUCE_SCATTER_V) continue;
             if (bt < 0 || t < bt) { bt = t; s.algo = a; }
         }
         if (bt > 0) s.est_us = bt;
@@ -488,7 +505,28 @@ std::string Communicator::stats_json()
         first = false;
     }
     o << "},\"model\":{\"alpha_us\":" << model_.alpha_us << ",\"beta_gbps\":" << model_.beta_gbps << ",\"nvls_gbps\":" << model_.nvls_gbps
-      << ",\"gamma_gbps\":" << model_.gamma_gbps << ",\"launch_us\":" << model_.launch_us << "}}";
+      << ",\"gamma_gbps\":" << model_.gamma_gbps << ",\"launch_us\":" << model_.launch_us << ",\"measured\":" << (tuned_.empty() ? "false" : "true") << "}";
+    // measured selection tables: per collective the size ladder and, per algorithm that was timed, microseconds per size
+    o << ",\"tuned\":{";
+    first = true;
+    for (auto &kv : tuned_) {
+        o << (first ? "" : ",") << "\"" << coll_name(kv.first) << "\":{\"sizes\":[";
+        for (size_t b = 0; b < kv.second.sizes.size(); ++b) o << (b ? "," : "") << kv.second.sizes[b];
+        o << "],\"us\":{";
+        bool fa = true;
+        for (int a = 0; a < ALGO_COUNT; ++a) {
+            bool any = false;
+            for (auto &row : kv.second.us) any = any || row[a] > 0;
+            if (!any) continue;
+            o << (fa ? "" : ",") << "\"" << algo_name(a) << "\":[";
+            for (size_t b = 0; b < kv.second.us.size(); ++b) o << (b ? "," : "") << (double)((long long)(kv.second.us[b][a] * 10 + 0.5)) / 10.0;
+            o << "]";
+            fa = false;
+        }
+        o << "}}";
+        first = false;
+    }
+    o << "}}";
     return o.str();
 }
 
@@ -498,8 +536,10 @@ HcclResult Communicator::collective(const OpRequest &rq)
     std::lock_guard<std::mutex> lk(op_mu_);
     double t0 = now_us();
     ++op_index_;
-    fault::before_op(rank(), op_index_);
-    if (fault_hook_) fault_hook_(op_index_);
+    if (!calibrating_) {
+        fault::before_op(rank(), op_index_);
+        if (fault_hook_) fault_hook_(op_index_);
+    }
     HcclResult ready = check_ready();
     // a failure reported by a peer while this rank was between ops counts as a failure of this op: with operator
     // retry enabled the rank joins the peers' retry round instead of giving up
@@ -696,9 +736,9 @@ int Communicator::pipe_mode_for(int coll) const
 }
 
 // Pipelined large-message path: one launch for a message of any size (the ring of staging slots replaces the staging
-// loop).  Geometry: a chunk moves about 1/16 of the message over the links, between 1 and 8 MiB, so that the pipeline
-// fill stays small against the transfer and a stage's per-chunk bookkeeping (a few microseconds) stays small against
-// the chunk's transfer time.  Every choice below depends only on facts that all ranks share (sizes, type, operator,
+// loop).  Geometry: a chunk moves about 1/16 of the message over the links, between 4 and 8 MiB: a stage's per-chunk
+// bookkeeping (completion of the bulk copies, fence, flag: several microseconds) has to stay small against the chunk's
+// transfer time, and the pipeline fill (one chunk per stage) small against the whole transfer.  Every choice below depends only on facts that all ranks share (sizes, type, operator,
 // environment), never on a rank's own pointers: the kernels take unaligned buffers on slower paths instead.
 HcclResult Communicator::run_pipe(const OpRequest &rq, bool want_mc)
 {
@@ -717,8 +757,8 @@ HcclResult Communicator::run_pipe(const OpRequest &rq, bool want_mc)
     // a chunk of ce elements per block moves about fan * ce elements over a rank's links
     const uint64_t fan = (mode == PM_AR2_MC || mode == PM_AR2_PUSH || pipe_mode_is_bcast(mode)) ? 1 : (uint64_t)(p - 1);
     uint64_t link_total = block_bytes * fan;
-    uint64_t lc = env.pipe_chunk_bytes ? env.pipe_chunk_bytes : std::min<uint64_t>(8u << 20, std::max<uint64_t>(1u << 20, link_total / 16));
-    int nslots = env.pipe_slots > 0 ? std::min(env.pipe_slots, kPipeMaxSlots) : 8;
+    uint64_t lc = env.pipe_chunk_bytes ? env.pipe_chunk_bytes : std::min<uint64_t>(8u << 20, std::max<uint64_t>(4u << 20, link_total / 16));
+    int nslots = env.pipe_slots > 0 ? std::min(env.pipe_slots, kPipeMaxSlots) : kPipeMaxSlots;
     const uint64_t unit = (uint64_t)p * (256 / es);  // elements: slices of a chunk stay 256-byte aligned
     auto slot_of = [&](uint64_t ce) { return pipe_slot_bytes(mode, ce, es, p); };
     uint64_t ce = std::max<uint64_t>(unit, lc / fan / es / unit * unit);
@@ -728,15 +768,16 @@ HcclResult Communicator::run_pipe(const OpRequest &rq, bool want_mc)
     CHK_RET_LOG(slot_of(ce) * nslots > settings_.stage_half_bytes, HCCL_E_MEMORY, "staging buffer too small for the pipelined kernels");
     while (ceil_div_u64(rq.count, ce) >= (1ull << kSeqShift) - 1) ce *= 2;  // chunk index travels in the low flag bits
     CHK_RET_LOG(slot_of(ce) * nslots > settings_.stage_half_bytes, HCCL_E_MEMORY, "message needs more pipeline chunks than a flag can count");
-    // CTAs per stage.  The copy stages are driven by the copy engine (one thread per CTA, about 160 KB in flight each) and
-    // need few CTAs; the reduce stage runs register loops and gets the rest.  No more CTAs than 16 KiB pieces justify.
-    const int budget = all_local_ ? std::max(3, 128 / nl) : 64;
+    // CTAs per stage.  A copy-engine driven CTA moves about 45 GB/s whatever the direction, so a stage that has to carry
+    // the full link rate needs 16 to 32 of them; the reduce stage gets what is left of the 128.  No more CTAs than 16 KiB
+    // pieces justify.
+    const int budget = all_local_ ? std::max(3, 128 / nl) : 128;
     const bool three = pipe_mode_has_copy_out(mode), bc = pipe_mode_is_bcast(mode);
     int n[3] = {0, 0, 0}, g[3] = {1, 1, 1};
-    if (three) { n[0] = std::max(1, budget / 8); n[2] = std::max(1, budget / 8); n[1] = budget - n[0] - n[2]; }
+    if (three) { n[0] = std::max(1, budget / 4); n[2] = std::max(1, budget / 4); n[1] = budget - n[0] - n[2]; }
     else if (bc) { n[0] = std::max(1, budget / 4); }
-    else if (mode == PM_AG_PULL) { n[0] = std::max(1, budget / 16); n[1] = std::max(1, budget / 4); }
-    else { n[0] = std::max(1, budget / (mode == PM_RS_MC ? 4 : 8)); n[1] = budget - n[0]; }
+    else if (mode == PM_AG_PULL) { n[0] = std::max(1, budget / 8); n[1] = std::max(1, budget / 2); }
+    else { n[0] = std::max(1, budget / (mode == PM_RS_MC || mode == PM_RS_PUSH ? 4 : 8)); n[1] = budget - n[0]; }
     if (env.pipe_ctas[0] > 0) { n[0] = env.pipe_ctas[0]; n[1] = env.pipe_ctas[1]; n[2] = env.pipe_ctas[2]; }
     if (bc) n[1] = n[2] = 0;
     if (!three) n[2] = 0;
@@ -749,7 +790,7 @@ HcclResult Communicator::run_pipe(const OpRequest &rq, bool want_mc)
     // groups: two or three chunks in flight per stage hide a stage's flag traffic behind its transfers
     const uint64_t nchunks = ceil_div_u64(rq.count, ce);
     for (int i = 0; i < 3; ++i) {
-        int want = env.pipe_groups[i] > 0 ? env.pipe_groups[i] : (i == 1 && !bc ? 3 : 2);
+        int want = env.pipe_groups[i] > 0 ? env.pipe_groups[i] : (i == 1 && !bc ? 4 : 2);
         while (want > 1 && (n[i] % want != 0 || (uint64_t)want > nchunks)) --want;
         g[i] = std::max(1, want);
     }
@@ -806,7 +847,7 @@ HcclResult Communicator::run_ll_allreduce(const OpRequest &rq)
 
 HcclResult Communicator::consistency_check(const OpRequest &rq, int algo, uint64_t zc_in, uint64_t zc_out)
 {
-    if (all_local_ || nranks_ == 1 || !consistency_enabled()) return HCCL_SUCCESS;
+    if (all_local_ || nranks_ == 1 || calibrating_ || !consistency_enabled()) return HCCL_SUCCESS;
     // one check per distinct op shape: the parameter frame of every rank must hash identically
     // (reference: RankConsistentcyChecker, common/health/rank_consistentcy_checker.cc)
     OpFrame f;

@@ -224,10 +224,14 @@ private:
     std::map<std::string, bool> checked_;
     std::map<std::pair<int, int>, uint32_t> p2p_rounds_;  // (src,dst) -> rounds exchanged
     CostModel model_;
-    // Measured AllReduce times per (size bucket, algorithm) from calibrate(); empty until calibrated.  When present the
-    // selector picks the fastest measured algorithm that is allowed for the (dtype, op) at hand instead of the model's guess.
-    std::vector<uint64_t> tuned_sizes_;
-    std::vector<std::vector<double>> tuned_us_;  // [bucket][algo], <= 0 = not measured
+    // Measured times per collective, (size bucket, algorithm), from calibrate(); empty until calibrated.  Where a table exists
+    // the selector picks the fastest measured algorithm that is allowed for the (dtype, op) at hand instead of the model's guess.
+    struct TunedTable {
+        std::vector<uint64_t> sizes;            // bytes per rank in the sense of the API count
+        std::vector<std::vector<double>> us;    // [bucket][algo], <= 0 = not measured
+    };
+    std::map<int, TunedTable> tuned_;           // by collective
+    bool calibrating_ = false;                  // calibration traffic: no parameter exchange, no fault hooks
     CommStats stats_;
     std::vector<TraceRecord> trace_;
     size_t trace_pos_ = 0;
