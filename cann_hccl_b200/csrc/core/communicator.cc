@@ -736,9 +736,10 @@ int Communicator::pipe_mode_for(int coll) const
 }
 
 // Pipelined large-message path: one launch for a message of any size (the ring of staging slots replaces the staging
-// loop).  Geometry: a chunk moves about 1/16 of the message over the links, between 4 and 8 MiB: a stage's per-chunk
-// bookkeeping (completion of the bulk copies, fence, flag: several microseconds) has to stay small against the chunk's
-// transfer time, and the pipeline fill (one chunk per stage) small against the whole transfer.  Every choice below depends only on facts that all ranks share (sizes, type, operator,
+// loop).  Geometry: a chunk moves 8 MiB over the links (half the message below 16 MiB): a stage's per-chunk bookkeeping
+// (completion of the bulk copies, fence, flag hop: several microseconds) has to stay small against the chunk's transfer
+// time.  (Shorter chunks at both ends of the message, to fill and drain the pipeline sooner, measured slower: the flag
+// hops of the extra chunks cost more than the fill saves.)  Every choice below depends only on facts that all ranks share (sizes, type, operator,
 // environment), never on a rank's own pointers: the kernels take unaligned buffers on slower paths instead.
 HcclResult Communicator::run_pipe(const OpRequest &rq, bool want_mc)
 {
@@ -757,7 +758,7 @@ HcclResult Communicator::run_pipe(const OpRequest &rq, bool want_mc)
     // a chunk of ce elements per block moves about fan * ce elements over a rank's links
     const uint64_t fan = (mode == PM_AR2_MC || mode == PM_AR2_PUSH || pipe_mode_is_bcast(mode)) ? 1 : (uint64_t)(p - 1);
     uint64_t link_total = block_bytes * fan;
-    uint64_t lc = env.pipe_chunk_bytes ? env.pipe_chunk_bytes : std::min<uint64_t>(8u << 20, std::max<uint64_t>(4u << 20, link_total / 16));
+    uint64_t lc = env.pipe_chunk_bytes ? env.pipe_chunk_bytes : std::min<uint64_t>(8u << 20, std::max<uint64_t>(1u << 20, link_total / 2));
     int nslots = env.pipe_slots > 0 ? std::min(env.pipe_slots, kPipeMaxSlots) : kPipeMaxSlots;
     const uint64_t unit = (uint64_t)p * (256 / es);  // elements: slices of a chunk stay 256-byte aligned
     auto slot_of = [&](uint64_t ce) { return pipe_slot_bytes(mode, ce, es, p); };
@@ -777,7 +778,7 @@ HcclResult Communicator::run_pipe(const OpRequest &rq, bool want_mc)
     if (three) { n[0] = std::max(1, budget / 4); n[2] = std::max(1, budget / 4); n[1] = budget - n[0] - n[2]; }
     else if (bc) { n[0] = std::max(1, budget / 4); }
     else if (mode == PM_AG_PULL) { n[0] = std::max(1, budget / 8); n[1] = std::max(1, budget / 2); }
-    else { n[0] = std::max(1, budget / (mode == PM_RS_MC || mode == PM_RS_PUSH ? 4 : 8)); n[1] = budget - n[0]; }
+    else { n[0] = std::max(1, budget / 4); n[1] = budget - n[0]; }
     if (env.pipe_ctas[0] > 0) { n[0] = env.pipe_ctas[0]; n[1] = env.pipe_ctas[1]; n[2] = env.pipe_ctas[2]; }
     if (bc) n[1] = n[2] = 0;
     if (!three) n[2] = 0;
