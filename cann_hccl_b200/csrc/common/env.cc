@@ -141,6 +141,7 @@ EnvConfig parse_env(const std::map<std::string, std::string> &v)
     if (auto s = get("HCCL_HEARTBEAT_LOST_MS")) { if (parse_int(*s, n) && n >= 1) c.heartbeat_lost_ms = (int)n; }
     if (auto s = get("HCCL_STUCK_DETECT_TIME")) { if (parse_int(*s, n) && n >= 1) c.stuck_ms = (int)n * 1000; }
     if (auto s = get("HCCL_STUCK_DETECT_MS")) { if (parse_int(*s, n) && n >= 1) c.stuck_ms = (int)n; }
+    if (auto s = get("HCCL_ALLTOALLV_CHECK")) { if (parse_int(*s, n) && (n == 0 || n == 1)) c.a2av_check = (int)n; else fail(c, "HCCL_ALLTOALLV_CHECK must be 0 or 1"); }
     if (auto s = get("HCCL_CALIBRATE")) c.calibrate = !(*s == "0" || lower(*s) == "false");
     if (auto s = get("HCCL_CALIBRATE_MAX_MB")) { if (parse_int(*s, n) && n >= 1 && n <= 1024) c.calibrate_max_mb = (int)n; }
     if (auto s = get("HCCL_CHANNELS")) { if (parse_int(*s, n) && n >= 0 && n <= 128) c.channels = (int)n; }

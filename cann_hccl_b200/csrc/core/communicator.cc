@@ -530,6 +530,60 @@ std::string Communicator::stats_json()
     return o.str();
 }
 
+// ------------------------------------------------------------------------------------------------ buffer overlap
+// Byte ranges that a collective reads and writes on one rank, from the semantics of its count argument (reference:
+// IsHcclOpInplace, algorithm/impl/coll_alg_utils.cc:253-307: AllGather writes p * count, ReduceScatter reads p * count,
+// rooted ops touch the large side on the root only).
+static void op_byte_ranges(const OpRequest &rq, int p, int rank, uint64_t *in_bytes, uint64_t *out_bytes)
+{
+    const uint64_t n = rq.count * (uint64_t)dtype_size(rq.dtype);
+    uint64_t vin = 0, vout = 0;
+    auto span = [&](const uint64_t *counts, const uint64_t *displs) {
+        uint64_t hi = 0;
+        for (int j = 0; j < p; ++j) hi = std::max(hi, displs[j] + counts[j]);
+        return hi * (uint64_t)dtype_size(rq.dtype);
+    };
+    switch (rq.coll) {
+        case COLL_ALLREDUCE: vin = vout = n; break;
+        case COLL_BROADCAST: vin = rank == rq.root ? n : 0; vout = rank == rq.root ? 0 : n; break;  // one buffer: never "overlapping"
+        case COLL_REDUCE: vin = n; vout = rank == rq.root ? n : 0; break;
+        case COLL_ALLGATHER: vin = n; vout = n * p; break;
+        case COLL_REDUCE_SCATTER: vin = n * p; vout = n; break;
+        case COLL_GATHER: vin = n; vout = rank == rq.root ? n * p : 0; break;
+        case COLL_SCATTER: vin = rank == rq.root ? n * p : 0; vout = n; break;
+        case COLL_ALLTOALL: vin = vout = n * p; break;
+        case COLL_ALLGATHER_V: vin = rq.counts[rank] * (uint64_t)dtype_size(rq.dtype); vout = span(rq.counts, rq.displs); break;
+        case COLL_REDUCE_SCATTER_V: vin = span(rq.counts, rq.displs); vout = rq.counts[rank] * (uint64_t)dtype_size(rq.dtype); break;
+        default: break;  // AlltoAllV / VC: checked against their own displacement tables by the API layer
+    }
+    *in_bytes = vin;
+    *out_bytes = vout;
+}
+
+// 0: the buffers of local rank li are disjoint; 1: they overlap in the one form the op defines as "in place" (same
+// pointer, or the rank's own block at its position inside the larger buffer); 2: any other overlap.
+int Communicator::overlap_kind(const OpRequest &rq, int li) const
+{
+    if (!rq.in || !rq.out || !rq.in[li] || !rq.out[li]) return 0;
+    const int p = nranks_, r = local_ranks_[li];
+    uint64_t ib = 0, ob = 0;
+    op_byte_ranges(rq, p, r, &ib, &ob);
+    if (ib == 0 || ob == 0) return 0;
+    const uint8_t *a = (const uint8_t *)rq.in[li], *b = (const uint8_t *)rq.out[li];
+    if (a + ib <= b || b + ob <= a) return 0;
+    const uint64_t n = rq.count * (uint64_t)dtype_size(rq.dtype);
+    switch (rq.coll) {
+        case COLL_ALLREDUCE: case COLL_REDUCE: return a == b ? 1 : 2;
+        case COLL_ALLGATHER: return a == b + (uint64_t)r * n ? 1 : 2;
+        case COLL_REDUCE_SCATTER: return b == a + (uint64_t)r * n ? 1 : 2;
+        case COLL_GATHER: return a == b + (uint64_t)r * n ? 1 : 2;
+        case COLL_SCATTER: return b == a + (uint64_t)r * n ? 1 : 2;
+        case COLL_ALLGATHER_V: return a == b + rq.displs[r] * (uint64_t)dtype_size(rq.dtype) ? 1 : 2;
+        case COLL_REDUCE_SCATTER_V: return b == a + rq.displs[r] * (uint64_t)dtype_size(rq.dtype) ? 1 : 2;
+        default: return 2;
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ collectives
 HcclResult Communicator::collective(const OpRequest &rq)
 {
@@ -545,6 +599,10 @@ HcclResult Communicator::collective(const OpRequest &rq)
     // retry enabled the rank joins the peers' retry round instead of giving up
     bool peer_failed = ready != HCCL_SUCCESS && remote_error_.load() == (uint32_t)ready && env_config().retry_enable;
     if (ready != HCCL_SUCCESS && !peer_failed) return ready;
+    for (int li = 0; li < nlocal(); ++li)
+        CHK_RET_LOG(overlap_kind(rq, li) == 2, HCCL_E_PARA,
+                    "%s: send and receive buffers of rank %d overlap in a way the operation does not define (in place means the same "
+                    "pointer, or the rank's own block at its position of the larger buffer)", coll_name(rq.coll), local_ranks_[li]);
     StateGuard guard(state_, CS_INUSE);
     const bool nvtx = env_config().nvtx;
     if (nvtx) nvtxRangePushA(coll_name(rq.coll));
@@ -623,6 +681,7 @@ HcclResult Communicator::run_collective_once(const OpRequest &rq)
         HLOG_ERROR("NVLS algorithm requested but no multicast mapping exists on this communicator");
         return HCCL_E_NOT_SUPPORT;
     }
+    if (is_a2av) CHK_RET(a2av_check(rq));
     CHK_RET(consistency_check(rq, sel.algo, use_zc ? ((uint64_t)zc[0].hin << 48) ^ zc[0].oin : 0, use_zc ? ((uint64_t)zc[0].hout << 48) ^ zc[0].oout : 0));
     if (sel.algo == ALGO_LL) {
         bool fits = rq.coll == COLL_ALLREDUCE && ll_ok_ && rq.count * es <= kLlMaxPayload;
@@ -881,6 +940,51 @@ HcclResult Communicator::consistency_check(const OpRequest &rq, int algo, uint64
     }
     checked_[key] = true;
     return HCCL_SUCCESS;
+}
+
+// AlltoAllV / VC: what rank i sends to rank j must be what j expects from i (reference: alltoall_operator.cc:49-72 checks
+// the exchanged count matrix).  Virtual ranks hold the whole matrix; processes publish their two rows over the hub.  The
+// exchange costs a control-plane round trip, so by default only the first calls of a communicator are checked (the call
+// count is the same on every rank, so all ranks agree on which calls those are); HCCL_ALLTOALLV_CHECK=1 checks every
+// call, =0 none.
+HcclResult Communicator::a2av_check(const OpRequest &rq)
+{
+    const int p = nranks_, nl = nlocal();
+    const EnvConfig &env = env_config();
+    if (p == 1 || calibrating_ || env.a2av_check == 0) return HCCL_SUCCESS;
+    const uint64_t call = a2av_calls_++;
+    if (env.a2av_check < 0 && call >= 16) return HCCL_SUCCESS;
+    if (all_local_) {
+        for (int i = 0; i < nl; ++i)
+            for (int j = 0; j < nl; ++j) {
+                const uint64_t sij = rq.send_counts[(size_t)i * p + j], rji = rq.recv_counts[(size_t)j * p + i];
+                CHK_RET_LOG(sij != rji, HCCL_E_PARA, "%s: rank %d sends %llu elements to rank %d, which expects %llu", coll_name(rq.coll), i,
+                            (unsigned long long)sij, j, (unsigned long long)rji);
+            }
+        return HCCL_SUCCESS;
+    }
+    std::string mine((const char *)rq.send_counts, (size_t)p * 8);
+    mine.append((const char *)rq.recv_counts, (size_t)p * 8);
+    std::vector<std::string> all;
+    CHK_RET(hub_->rendezvous(key_prefix_ + "/a2av/" + std::to_string(call), nranks_, rank(), mine, &all, env.connect_timeout_s * 1000));
+    const int me = rank();
+    HcclResult rc = HCCL_SUCCESS;
+    for (int j = 0; j < p; ++j) {
+        if (all[j].size() != (size_t)p * 16) return HCCL_E_INTERNAL;
+        const uint64_t *sj = (const uint64_t *)all[j].data(), *rj = sj + p;
+        // every rank checks the whole matrix, so that all of them return the same verdict
+        for (int i = 0; i < p; ++i) {
+            const uint64_t *ri = (const uint64_t *)all[i].data() + p;
+            if (sj[i] != ri[j]) {
+                if (i == me || j == me)
+                    HLOG_ERROR("%s: rank %d sends %llu elements to rank %d, which expects %llu", coll_name(rq.coll), j, (unsigned long long)sj[i], i,
+                               (unsigned long long)ri[j]);
+                rc = HCCL_E_PARA;
+            }
+        }
+        (void)rj;
+    }
+    return rc;
 }
 
 // ------------------------------------------------------------------------------------------------ p2p
@@ -1265,9 +1369,11 @@ HcclResult Communicator::maybe_retry(const OpRequest &rq, HcclResult failure)
     // re-arms flags under a common new sequence and executes the op again.
     const EnvConfig &env = env_config();
     if (!env.retry_enable || all_local_ || nranks_ == 1) return failure;
+    // an op whose output overlaps its input has destroyed what a second run would need (reference: retry-inplace rule,
+    // coll_alg_operator.cc:588, decided from the byte ranges of IsHcclOpInplace)
     bool inplace = false;
     for (int li = 0; li < nlocal(); ++li)
-        if (rq.in && rq.out && rq.in[li] == rq.out[li] && rq.coll != COLL_BROADCAST) inplace = true;
+        if (overlap_kind(rq, li) != 0) inplace = true;
     HcclResult rc = failure;
     for (int attempt = 1; attempt <= env.retry_max && rc != HCCL_SUCCESS; ++attempt) {
         struct Vote { uint64_t op_index; uint32_t can_retry; uint32_t code; } v{op_index_, inplace ? 0u : 1u, (uint32_t)rc};

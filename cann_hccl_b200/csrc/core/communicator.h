@@ -180,6 +180,8 @@ private:
     int pipe_mode_for(int coll) const;  // PipeMode of a collective, -1 when it has no pipelined kernel
     HcclResult tp_workspace(const std::string &key, size_t data_bytes, int M, void **ws_out);
     void tp_release_workspaces();
+    int overlap_kind(const OpRequest &rq, int li) const;
+    HcclResult a2av_check(const OpRequest &rq);
     HcclResult consistency_check(const OpRequest &rq, int algo, uint64_t zc_in = 0, uint64_t zc_out = 0);
     HcclResult maybe_retry(const OpRequest &rq, HcclResult failure);
     void heartbeat_loop();
@@ -253,6 +255,7 @@ private:
     std::mutex hb_mu_;
     std::condition_variable hb_cv_;
     uint64_t op_index_ = 0;                  // API-level op counter (one per collective call)
+    uint64_t a2av_calls_ = 0;                // AlltoAllV / VC calls so far (which of them get their count matrix checked)
     std::function<void(uint64_t)> fault_hook_;
     std::unique_ptr<P2pBackend> p2p_;
     struct TopoEntry { int rank; uint32_t pid; int device; std::string host; };

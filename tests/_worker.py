@@ -46,6 +46,28 @@ def scenario_allreduce_ring_8mb(c, p, r, args):
     print("check_result: success  aveg_time(us): %.1f  alg_bandwidth(GB/s): %.3f  data_size: %d" % (dt * 1e6, n * 4 / dt / 1e9, n * 4))
 
 
+def scenario_a2av_mismatch(c, p, r, args):
+    """Rank 1 expects one element more from rank 0 than rank 0 sends: every rank gets HCCL_E_PARA, nothing hangs; a
+    consistent call afterwards works."""
+    lib = L.lib()
+    sc = np.full(p, 4, np.uint64)
+    rcnt = np.full(p, 4, np.uint64)
+    if r == 1:
+        rcnt[0] = 5
+    sd = np.arange(p, dtype=np.uint64) * 4
+    rd = np.arange(p, dtype=np.uint64) * 8
+    x = np.full(4 * p, float(r), np.float32)
+    y = np.zeros(8 * p, np.float32)
+    rc = lib.HcclAlltoAllV(x.ctypes.data, sc.ctypes.data, sd.ctypes.data, L.FP32, y.ctypes.data, rcnt.ctypes.data, rd.ctypes.data, L.FP32, c.handle, None)
+    assert rc == L.E_PARA, rc
+    rcnt[:] = 4
+    rc = lib.HcclAlltoAllV(x.ctypes.data, sc.ctypes.data, sd.ctypes.data, L.FP32, y.ctypes.data, rcnt.ctypes.data, rd.ctypes.data, L.FP32, c.handle, None)
+    assert rc == 0, rc
+    for q in range(p):
+        np.testing.assert_array_equal(y[q * 8:q * 8 + 4], np.full(4, float(q), np.float32))
+    print("a2av_mismatch ok")
+
+
 def scenario_sweep(c, p, r, args):
     n = 10_000
     for algo in (L.ALGO_AUTO, L.ALGO_MESH, L.ALGO_MESH_ONESHOT, L.ALGO_RING, L.ALGO_RHD):

@@ -74,6 +74,45 @@ def test_pipelined_algorithms_fall_back_on_cpu_ranks(comms, p):
         np.testing.assert_array_equal(b, want)
 
 
+def test_buffer_overlap_rules(comms):
+    """In place means one of the forms the op defines (same pointer; own block at its position of the larger buffer).
+    Buffers that overlap in any other way are refused before anything runs, whatever the algorithm."""
+    p, n = 4, 1000
+    c = comms(p)
+    base = [np.arange(2 * n * p, dtype=np.float32) + r for r in range(p)]
+    # AllReduce: shifted by one element -> refused; equal pointers -> fine
+    with pytest.raises(H.HcclError) as e:
+        c.all_reduce([b[:n] for b in base], [b[1:n + 1] for b in base])
+    assert e.value.code == L.E_PARA
+    ins = [b[:n].copy() for b in base]
+    ref = np_reduce(ins, L.SUM)
+    views = [b[:n] for b in base]
+    c.all_reduce(views, views)
+    for v in views:
+        np.testing.assert_allclose(v, ref, **tol(np.float32, p))
+    # AllGather: the send buffer inside the receive buffer but not at the rank's own block -> refused
+    full = [np.zeros(n * p, np.float32) for _ in range(p)]
+    with pytest.raises(H.HcclError) as e:
+        c.all_gather([f[:n] for f in full], full)          # every rank offers block 0: only right for rank 0
+    assert e.value.code == L.E_PARA
+    gs = make_inputs(p, n, np.float32)
+    for r in range(p):
+        full[r][r * n:(r + 1) * n] = gs[r]
+    c.all_gather([full[r][r * n:(r + 1) * n] for r in range(p)], full)
+    for f in full:
+        np.testing.assert_array_equal(f, np.concatenate(gs))
+    # ReduceScatter: receive buffer = the rank's own block of the send buffer is in place; any other block is refused
+    xs = make_inputs(p, n * p, np.float32)
+    want = np_reduce(xs, L.SUM)
+    work = [x.copy() for x in xs]
+    with pytest.raises(H.HcclError) as e:
+        c.reduce_scatter(work, [w[n // 2:n // 2 + n] for w in work])
+    assert e.value.code == L.E_PARA
+    c.reduce_scatter(work, [work[r][r * n:(r + 1) * n] for r in range(p)])
+    for r in range(p):
+        np.testing.assert_allclose(work[r][r * n:(r + 1) * n], want[r * n:(r + 1) * n], **tol(np.float32, p))
+
+
 def test_allreduce_bf16_bits(comms):
     """bf16 travels as uint16 through numpy; the library reduces it in fp32 and rounds once."""
     import ctypes as C
@@ -260,6 +299,22 @@ def test_all_to_all_v(comms, p, algo, scale):
             got = outs[j][int(rd[j, i]):int(rd[j, i] + m[i, j])]
             want = ins[i][int(sd[i, j]):int(sd[i, j] + m[i, j])]
             np.testing.assert_array_equal(got, want)
+
+
+def test_all_to_all_v_count_matrix_mismatch_is_refused(comms):
+    """What rank i sends to j must be what j expects from i; a matrix that disagrees is refused before any data moves."""
+    p = 3
+    c = comms(p)
+    m = np.full((p, p), 5, np.uint64)
+    rc = np.ascontiguousarray(m.T)
+    rc[2, 0] = 6                                        # rank 2 expects 6 elements from rank 0, which sends 5
+    sd = np.tile(np.arange(p, dtype=np.uint64) * 5, (p, 1))
+    rd = np.tile(np.arange(p, dtype=np.uint64) * 6, (p, 1))
+    ins = [np.zeros(32, np.float32) for _ in range(p)]
+    outs = [np.zeros(32, np.float32) for _ in range(p)]
+    with pytest.raises(H.HcclError) as e:
+        c.all_to_all_v(ins, m, sd, outs, rc, rd)
+    assert e.value.code == L.E_PARA
 
 
 def test_barrier_and_single_rank(comms):

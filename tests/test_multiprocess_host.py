@@ -22,6 +22,11 @@ def test_send_recv_batch(p):
     assert all("sendrecv ok" in out for _, out in res)
 
 
+def test_alltoallv_count_matrix_cross_check():
+    res = run_ranks(3, "a2av_mismatch")
+    assert all("a2av_mismatch ok" in out for _, out in res)
+
+
 def test_sub_communicator():
     res = run_ranks(4, "subcomm")
     assert all("subcomm ok" in out for _, out in res)
