@@ -595,9 +595,21 @@ HcclResult Communicator::collective(const OpRequest &rq)
         if (fault_hook_) fault_hook_(op_index_);
     }
     HcclResult ready = check_ready();
-    // a failure reported by a peer while this rank was between ops counts as a failure of this op: with operator
-    // retry enabled the rank joins the peers' retry round instead of giving up
-    bool peer_failed = ready != HCCL_SUCCESS && remote_error_.load() == (uint32_t)ready && env_config().retry_enable;
+    const bool dev = settings_.transport == TR_DEVICE;
+    const bool can_retry = env_config().retry_enable && !all_local_ && nranks_ > 1 && (ready == HCCL_E_TIMEOUT || ready == HCCL_E_REMOTE);
+    bool own_fail = false;
+    for (auto *st : status_) own_fail = own_fail || (st && st->code != 0);
+    if (ready != HCCL_SUCCESS && can_retry && dev && own_fail) {
+        // device transport: a kernel reports its failure after the call that launched it has returned, so the op to run
+        // again is the previous one; the current op follows once that one has gone through
+        HcclResult rr = retry_last_op(ready);
+        if (rr != HCCL_SUCCESS) return rr;
+        ready = HCCL_SUCCESS;
+    }
+    // a failure reported by a peer while this rank was between ops (its own kernels all finished) is a failure of the op it
+    // is about to start, which the peer has launched already: with operator retry enabled the rank joins the peers' retry
+    // round for this op instead of giving up
+    bool peer_failed = ready != HCCL_SUCCESS && remote_error_.load() == (uint32_t)ready && can_retry;
     if (ready != HCCL_SUCCESS && !peer_failed) return ready;
     for (int li = 0; li < nlocal(); ++li)
         CHK_RET_LOG(overlap_kind(rq, li) == 2, HCCL_E_PARA,
@@ -606,10 +618,11 @@ HcclResult Communicator::collective(const OpRequest &rq)
     StateGuard guard(state_, CS_INUSE);
     const bool nvtx = env_config().nvtx;
     if (nvtx) nvtxRangePushA(coll_name(rq.coll));
+    if (dev && !calibrating_) remember_op(rq);
     HcclResult rc = peer_failed ? ready : run_collective_once(rq);
     if (rc != HCCL_SUCCESS && (rc == HCCL_E_TIMEOUT || rc == HCCL_E_REMOTE)) {
         stats_.timeouts++;
-        rc = maybe_retry(rq, rc);
+        rc = maybe_retry(rq, rc, op_index_);
     }
     if (rc == HCCL_SUCCESS && env_config().overflow_check) rc = overflow_scan(rq);
     if (nvtx) nvtxRangePop();
@@ -900,6 +913,11 @@ HcclResult Communicator::run_ll_allreduce(const OpRequest &rq)
         a.nranks = nranks_;
         a.tag = tag;
         a.parity = (uint32_t)(ll_seq_ & 1);
+        // the LL path does not consume a plan sequence number: its op-execution id lives in a range of its own
+        a.exit_counter = ctx_[li].exit_counter;
+        a.dev_tail = ctx_[li].dev_tail;
+        a.exe_id = (1ull << 62) | ll_seq_;
+        status_[li]->head = a.exe_id;
     }
     stats_.launches++;
     return launch_ar_ll(args.data(), nl, rq.dtype, rq.redop, rq.stream);
@@ -1246,6 +1264,13 @@ HcclResult Communicator::sync_stream(void *stream)
     if (settings_.transport == TR_DEVICE) {
         cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream);
         CHK_RET_LOG(e != cudaSuccess, HCCL_E_RUNTIME, "stream synchronize failed: %s", cudaGetErrorString(e));
+        HcclResult err = async_error();
+        if ((err == HCCL_E_TIMEOUT || err == HCCL_E_REMOTE) && env_config().retry_enable && !all_local_ && nranks_ > 1) {
+            std::lock_guard<std::mutex> lk(op_mu_);
+            err = async_error();  // another thread's call may have dealt with it meanwhile
+            if (err == HCCL_E_TIMEOUT || err == HCCL_E_REMOTE) return retry_last_op(err);
+        }
+        return err;
     }
     return async_error();
 }
@@ -1362,13 +1387,59 @@ void Communicator::heartbeat_loop()
     }
 }
 
-HcclResult Communicator::maybe_retry(const OpRequest &rq, HcclResult failure)
+void Communicator::remember_op(const OpRequest &rq)
+{
+    LastOp &l = last_op_;
+    const int nl = nlocal(), p = nranks_;
+    l.valid = true;
+    l.op_index = op_index_;
+    l.first_seq = seq_;
+    l.rq = rq;
+    l.in.assign(nl, nullptr);
+    l.out.assign(nl, nullptr);
+    for (int li = 0; li < nl; ++li) { l.in[li] = rq.in ? rq.in[li] : nullptr; l.out[li] = rq.out ? rq.out[li] : nullptr; }
+    l.rq.in = rq.in ? l.in.data() : nullptr;
+    l.rq.out = rq.out ? l.out.data() : nullptr;
+    auto keep = [&](const uint64_t *&field, std::vector<uint64_t> &store, size_t n) {
+        if (!field) return;
+        store.assign(field, field + n);
+        field = store.data();
+    };
+    keep(l.rq.counts, l.counts, p); keep(l.rq.displs, l.displs, p);
+    keep(l.rq.send_counts, l.sc, (size_t)nl * p); keep(l.rq.send_displs, l.sd, (size_t)nl * p);
+    keep(l.rq.recv_counts, l.rc, (size_t)nl * p); keep(l.rq.recv_displs, l.rd, (size_t)nl * p);
+    l.retriable = true;
+    for (int li = 0; li < nl; ++li)
+        if (overlap_kind(rq, li) != 0) l.retriable = false;  // its output overwrote what a second run would read
+}
+
+// Device transport: a kernel of the newest collective gave up (bounded wait, or a peer's failure learnt from the heartbeat).
+// All ranks meet at the hub, agree to run that op again, re-arm the flags under a common new sequence and re-launch it;
+// the attempt is awaited on its stream so that its outcome is known before anything else is launched.
+HcclResult Communicator::retry_last_op(HcclResult failure)
+{
+    if (!last_op_.valid) return failure;
+    uint64_t failed_seq = 0;
+    for (auto *st : status_)
+        if (st && st->code) failed_seq = std::max<uint64_t>(failed_seq, st->seq);
+    if (failed_seq && failed_seq < last_op_.first_seq) {
+        HLOG_ERROR("operator retry: the failure belongs to an op older than the newest one (sequence %llu < %llu); only the newest op can be re-run",
+                   (unsigned long long)failed_seq, (unsigned long long)last_op_.first_seq);
+        return failure;
+    }
+    stats_.timeouts++;
+    StateGuard guard(state_, CS_INUSE);
+    return maybe_retry(last_op_.rq, failure, last_op_.op_index);
+}
+
+HcclResult Communicator::maybe_retry(const OpRequest &rq, HcclResult failure, uint64_t op_index)
 {
     // Operator retry (reference: cluster_maintenance/recovery/operator_retry, max 3 attempts): every rank that
     // failed meets at the hub, agrees that all members failed the same op and can re-run it (input untouched),
     // re-arms flags under a common new sequence and executes the op again.
     const EnvConfig &env = env_config();
     if (!env.retry_enable || all_local_ || nranks_ == 1) return failure;
+    const bool dev = settings_.transport == TR_DEVICE;
     // an op whose output overlaps its input has destroyed what a second run would need (reference: retry-inplace rule,
     // coll_alg_operator.cc:588, decided from the byte ranges of IsHcclOpInplace)
     bool inplace = false;
@@ -1376,10 +1447,10 @@ HcclResult Communicator::maybe_retry(const OpRequest &rq, HcclResult failure)
         if (overlap_kind(rq, li) != 0) inplace = true;
     HcclResult rc = failure;
     for (int attempt = 1; attempt <= env.retry_max && rc != HCCL_SUCCESS; ++attempt) {
-        struct Vote { uint64_t op_index; uint32_t can_retry; uint32_t code; } v{op_index_, inplace ? 0u : 1u, (uint32_t)rc};
+        struct Vote { uint64_t op_index; uint32_t can_retry; uint32_t code; } v{op_index, inplace ? 0u : 1u, (uint32_t)rc};
         std::vector<std::string> votes;
         char tag[96];
-        snprintf(tag, sizeof(tag), "/retry/%llu/%d", (unsigned long long)op_index_, attempt);
+        snprintf(tag, sizeof(tag), "/retry/%llu/%d", (unsigned long long)op_index, attempt);
         int tmo = env.retry_hold_ms + (int)(ctx_[0].timeout_ns / 1000000) + 2000;
         HcclResult rr = hub_->rendezvous(key_prefix_ + tag, nranks_, rank(), std::string((const char *)&v, sizeof(v)), &votes, tmo);
         if (rr != HCCL_SUCCESS) return failure;  // not everyone arrived: some rank did not fail this op or is gone
@@ -1387,9 +1458,9 @@ HcclResult Communicator::maybe_retry(const OpRequest &rq, HcclResult failure)
         for (auto &s : votes) {
             Vote o;
             memcpy(&o, s.data(), sizeof(o));
-            ok &= o.op_index == op_index_ && o.can_retry;
+            ok &= o.op_index == op_index && o.can_retry;
         }
-        if (!ok) { HLOG_ERROR("op %llu cannot be retried (in-place input or ranks out of step)", (unsigned long long)op_index_); return failure; }
+        if (!ok) { HLOG_ERROR("op %llu cannot be retried (in-place input or ranks out of step)", (unsigned long long)op_index); return failure; }
         usleep((useconds_t)env.retry_interval_ms * 1000);
         state_.store(CS_SUSPENDED);
         HcclResult rs = resume_locked();
@@ -1397,7 +1468,16 @@ HcclResult Communicator::maybe_retry(const OpRequest &rq, HcclResult failure)
         state_.store(CS_INUSE);
         stats_.retries++;
         HLOG_WARN("retrying %s (attempt %d of %d)", coll_name(rq.coll), attempt, env.retry_max);
+        fault::before_attempt(rank(), op_index, attempt);
+        if (dev) last_op_.first_seq = seq_;
         rc = run_collective_once(rq);
+        if (dev && rc == HCCL_SUCCESS) {
+            // the launch is asynchronous: its outcome is in the status block once the stream has drained
+            cudaError_t e = cudaStreamSynchronize((cudaStream_t)rq.stream);
+            if (e != cudaSuccess) return HCCL_E_RUNTIME;
+            rc = async_error();
+            if (rc != HCCL_SUCCESS && rc != HCCL_E_TIMEOUT && rc != HCCL_E_REMOTE) return rc;
+        }
     }
     return rc;
 }

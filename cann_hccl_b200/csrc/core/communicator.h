@@ -183,7 +183,20 @@ private:
     int overlap_kind(const OpRequest &rq, int li) const;
     HcclResult a2av_check(const OpRequest &rq);
     HcclResult consistency_check(const OpRequest &rq, int algo, uint64_t zc_in = 0, uint64_t zc_out = 0);
-    HcclResult maybe_retry(const OpRequest &rq, HcclResult failure);
+    HcclResult maybe_retry(const OpRequest &rq, HcclResult failure, uint64_t op_index);
+    // Device transport: the newest collective as it was issued (deep copy), so that a failure its kernel reports later,
+    // at the next call or at a synchronisation, can be answered by running it again.
+    struct LastOp {
+        bool valid = false, retriable = false;
+        uint64_t op_index = 0, first_seq = 0;
+        OpRequest rq;
+        std::vector<const void *> in;
+        std::vector<void *> out;
+        std::vector<uint64_t> counts, displs, sc, sd, rc, rd;
+    };
+    LastOp last_op_;
+    void remember_op(const OpRequest &rq);
+    HcclResult retry_last_op(HcclResult failure);
     void heartbeat_loop();
     void record_trace(const OpRequest &rq, int algo, int nchan, uint64_t bytes, double us);
     HcclResult overflow_scan(const OpRequest &rq);

@@ -10,7 +10,7 @@
 namespace hcclb {
 namespace fault {
 namespace {
-struct Rule { std::string kind; long rank = -1, op = -1, ms = 0, after = 0; };
+struct Rule { std::string kind; long rank = -1, op = -1, ms = 0, after = 0, attempts = 0; };
 std::vector<Rule> g_rules;
 std::mutex g_mu;
 bool g_loaded = false;
@@ -40,6 +40,7 @@ void load_locked()
             r.op = field(args, "op", -1);
             r.ms = field(args, "ms", 0);
             r.after = field(args, "after", 0);
+            r.attempts = field(args, "attempts", 0);
             g_rules.push_back(r);
         }
         if (end == std::string::npos) break;
@@ -70,6 +71,20 @@ void before_op(int rank, uint64_t op_index)
             _exit(17);
         }
     }
+}
+void before_attempt(int rank, uint64_t op_index, int attempt)
+{
+    std::vector<Rule> rules;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        if (!g_loaded) load_locked();
+        rules = g_rules;
+    }
+    for (auto &r : rules)
+        if (r.kind == "stall_rank" && r.rank == rank && r.op == (long)op_index && attempt <= r.attempts) {
+            HLOG_WARN("fault injection: rank %d stalls %ld ms before retry %d of op %llu", rank, r.ms, attempt, (unsigned long long)op_index);
+            usleep((useconds_t)r.ms * 1000);
+        }
 }
 bool drop_heartbeat(int rank)
 {

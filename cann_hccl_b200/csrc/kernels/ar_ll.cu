@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(kLlThreads) ar_ll_kernel(const LlArgsArray arg
                 for (int k = 0; k < E; ++k) acc[k] = ll_op<OP>(acc[k], N::up(v.e[k]));
             }
         }
-        if (failed) return;
+        if (failed) return;  // head stays ahead of tail: the heartbeat reports the op as stuck / failed
         Pay8<T> r;
 #pragma unroll
         for (int k = 0; k < E; ++k) r.e[k] = N::down(acc[k]);
@@ -133,6 +133,15 @@ __global__ void __launch_bounds__(kLlThreads) ar_ll_kernel(const LlArgsArray arg
         else
             for (int k = 0; k < E; ++k)
                 if (e0 + k < a.count) out[e0 + k] = r.e[k];
+    }
+    // op-execution counter: the last CTA of this rank moves the tail up to the head the host set at launch
+    __syncthreads();
+    if (threadIdx.x == 0 && a.exit_counter) {
+        __threadfence();
+        if (atomicAdd(a.exit_counter, 1u) == gridDim.x - 1) {
+            *a.exit_counter = 0;
+            *a.dev_tail = a.exe_id;
+        }
     }
 }
 

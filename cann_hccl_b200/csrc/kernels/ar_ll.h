@@ -16,6 +16,9 @@ struct LlArgs {
     DevStatus *status;
     volatile uint32_t *abort;
     uint32_t *local_fail;
+    uint32_t *exit_counter;   // device counter that finds the last CTA of the op
+    uint64_t *dev_tail;       // device word of the op-execution counter: set to `exe_id` when the op has completed
+    uint64_t exe_id;          // value the host wrote into the status block's head when it launched the op
     int32_t rank, nranks;
     uint32_t tag, parity;
 };

@@ -264,67 +264,42 @@ def _adopted_vmm_memory(c, p, r, nvls):
     print("rank %d adopted vmm memory ok" % r)
 
 
-def _time_repeat(c, fn, iters):
-    fn(3)
-    c.barrier()
-    torch.cuda.synchronize()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    fn(iters)
-    b.record()
-    torch.cuda.synchronize()
-    return a.elapsed_time(b) * 1e3 / iters
+def scenario_retry(c, p, r, args):
+    """Operator retry on the device transport.  HCCL_FAULT_INJECT stalls rank 1 ON THE HOST before it launches its 2nd
+    collective, for longer than the bound of the device waits: the peers' kernels give up (status block, no fault), the
+    failure surfaces at the next synchronisation, all ranks vote over the hub and the op runs again."""
+    n = 200_000
+    for i in range(4):
+        x = torch.full((n,), float(r + i), device="cuda")
+        out = torch.zeros(n, device="cuda")
+        c.all_reduce(x, out, algo=L.ALGO_MESH)
+        rc = c.sync()
+        assert rc == 0, (rc, c.describe_status())
+        assert torch.all(out == float(sum(q + i for q in range(p)))), "allreduce %d wrong after retry" % i
+    st = c.stats()
+    print("rank %d retries %d timeouts %d" % (r, st["retries"], st["timeouts"]))
+    assert st["retries"] >= 1
+    print("rank %d retry ok" % r)
 
 
-def scenario_perf(c, p, r, args):
-    """Device-timed look at the algorithms, issued from C (hccl_test style), next to ncclAllReduce issued the same way."""
-    c.calibrate()
-    if r == 0:
-        print("model", c.stats()["model"])
-    sizes = [int(a) for a in args] if args else [8 << 10, 64 << 10, 512 << 10, 4 << 20, 64 << 20, 256 << 20]
-    buf_bytes = max(sizes) * 2
-    x = torch.rand(buf_bytes // 4, device="cuda")
-    y = torch.empty_like(x)
-    nv = c.has_nvls()
-    for size in sizes:
-        n = size // 4
-        nwin = max(1, min(16, buf_bytes // size))
-        iters = 30 if size <= (4 << 20) else 8
-        rows = []
-        t = _time_repeat(c, lambda it: c.nccl_allreduce_repeat(y, y, n, L.FP32, it, size, nwin), iters)
-        rows.append(("nccl", 0, t))
-        algos = [L.ALGO_AUTO, L.ALGO_LL, L.ALGO_MESH_ONESHOT, L.ALGO_MESH, L.ALGO_RING, L.ALGO_RHD, L.ALGO_MESH_PIPE] + ([L.ALGO_NVLS, L.ALGO_NVLS_ONESHOT, L.ALGO_NVLS_PIPE] if nv else [])
-        if os.environ.get("PERF_ALGOS"):
-            algos = [L.ALGO_NAMES.index(x) for x in os.environ["PERF_ALGOS"].split(",") if x in L.ALGO_NAMES and (nv or "nvls" not in x)]
-        for algo in algos:
-            if algo in (L.ALGO_MESH_ONESHOT, L.ALGO_NVLS_ONESHOT) and size > (4 << 20) and p > 2:
-                continue
-            if algo in (L.ALGO_MESH_PIPE, L.ALGO_NVLS_PIPE) and size < (4 << 20):
-                continue
-            if algo == L.ALGO_LL and size > (1 << 20):
-                continue
-            chans = [int(x) for x in os.environ.get("PERF_NCHAN", "0").split(",")]
-            for nchan in chans:
-                t = _time_repeat(c, lambda it: c.repeat(L.ALLREDUCE, x, y, n, L.FP32, it, size, nwin, algo=algo, nchan=nchan), iters)
-                rows.append((L.ALGO_NAMES[algo], nchan, t))
-                if r == 0 and os.environ.get("HCCL_KERNEL_TRACE") and nchan == 0:
-                    tr = c.kernel_trace(0)
-                    if tr:
-                        print("  launch %s" % c.last_launch)
-                        print("  trace %s size %d: " % (L.ALGO_NAMES[algo], size) + " ".join("s%d[w%.0f m%.0f g%.0f]" % (i, w, m, g or 0) for i, w, m, g in tr[:14]))
-        if nv and size >= (1 << 20) and os.environ.get("PERF_ZC", "1") == "1":
-            hz, (zb,) = c.symmetric_empty(n * nwin, torch.float32)
-            zb.uniform_(-1, 1)
-            c.repeat(L.ALLREDUCE, zb, zb, n, L.FP32, nwin, size, nwin)  # first touch of every window (agreement over the hub)
-            t = _time_repeat(c, lambda it: c.repeat(L.ALLREDUCE, zb, zb, n, L.FP32, it, size, nwin), iters)
-            rows.append(("zero_copy", 0, t))
-            del zb
-            c.mem_free(hz)
-        ok(c)
-        if r == 0:
-            for name, nchan, t in rows:
-                print("size %10d  %-13s nchan %3d  %9.1f us  %7.1f GB/s" % (size, name, nchan, t, size / t / 1e3))
-    ok(c)
+def scenario_retry_exhausted(c, p, r, args):
+    """The stall also hits every retry: after the configured number of attempts the failure is returned, and the
+    communicator works again once it has been resumed."""
+    n = 50_000
+    x = torch.full((n,), float(r), device="cuda")
+    out = torch.zeros(n, device="cuda")
+    c.all_reduce(x, out, algo=L.ALGO_MESH)
+    assert c.sync() == 0
+    c.all_reduce(x, out, algo=L.ALGO_MESH)      # op 2: stalled on rank 1, and again on each retry
+    rc = c.sync()
+    assert rc in (L.E_TIMEOUT, L.E_REMOTE), rc
+    assert c.stats()["retries"] == 3, c.stats()
+    c.resume()
+    out.zero_()
+    c.all_reduce(x, out, algo=L.ALGO_MESH)
+    assert c.sync() == 0, c.describe_status()
+    assert torch.all(out == float(sum(range(p))))
+    print("rank %d retry exhausted ok" % r)
 
 
 def scenario_fused_tp(c, p, r, args):
@@ -360,66 +335,6 @@ def scenario_fused_tp(c, p, r, args):
     err = float((o.float() - full[r * Ms:(r + 1) * Ms]).norm() / full.norm())
     assert err < 2e-2, err
     print("rank %d fused_tp ok" % r)
-
-
-def scenario_tp_shapes(c, p, r, args):
-    """Fused AG+GEMM / GEMM+RS against the plain tcgen05 GEMM of the same per-rank shape (device-timed)."""
-    from cann_hccl_b200.parallel import fused_tp
-    M, N, K = [int(a) for a in args[:3]]
-
-    def t(fn, iters=10):
-        for _ in range(3):
-            fn()
-        c.barrier()
-        torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(iters):
-            fn()
-        b.record()
-        torch.cuda.synchronize()
-        return a.elapsed_time(b) / iters
-    xs = torch.randn(M // p, K, device="cuda").to(torch.bfloat16)
-    xf = torch.randn(M, K, device="cuda").to(torch.bfloat16)
-    w = torch.randn(N, K, device="cuda").to(torch.bfloat16)
-    y = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-    o = torch.empty(M // p, N, device="cuda", dtype=torch.bfloat16)
-    t_plain = t(lambda: fused_tp.gemm(xf, w, out=y))
-    t_ag = t(lambda: fused_tp.all_gather_matmul(c, xs, w, out=y))
-    t_rs = t(lambda: fused_tp.matmul_reduce_scatter(c, xf, w, out=o))
-    handle, bufs = c.symmetric_empty(xs.numel(), torch.bfloat16)
-    xz = bufs[0].view_as(xs)
-    xz.copy_(xs)
-    t_agz = t(lambda: fused_tp.all_gather_matmul(c, xz, w, out=y))
-    torch.cuda.synchronize()
-    ok(c)
-    if r == 0:
-        print("TPSHAPE M%d N%d K%d p%d: plain %.3f ms, ag+gemm %.3f ms (registered shard %.3f ms), gemm+rs %.3f ms" % (M, N, K, p, t_plain, t_ag, t_agz, t_rs))
-
-
-def scenario_extras(c, p, r, args):
-    """bench_extras (config-e shapes and MoE) with torch.distributed NCCL as the baseline."""
-    import json
-    import torch.distributed as dist
-    from cann_hccl_b200.parallel import bench_extras
-    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-    os.environ.setdefault("MASTER_PORT", "29533")
-    dist.init_process_group("nccl", rank=r, world_size=p, device_id=torch.device("cuda", r))
-
-    def sync():
-        torch.cuda.synchronize()
-        dist.barrier()
-        torch.cuda.synchronize()
-
-    def mx(v):
-        t = torch.tensor([v], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-    res = bench_extras.run(c, p, r, dist, mx, sync, None)
-    if r == 0:
-        print("EXTRAS " + json.dumps(res))
-    dist.barrier()
-    dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -69,3 +69,24 @@ def test_fused_tp_multi_gpu(p):
         pytest.skip("needs %d GPUs" % p)
     outs = run_gpu_ranks(p, "fused_tp")
     assert all("fused_tp ok" in o for _, o in outs)
+
+
+RETRY_ENV = {"HCCL_OP_RETRY_ENABLE": "L0:1", "HCCL_OP_RETRY_PARAMS": "MaxCnt:3,HoldTime:3000,IntervalTime:50", "HCCL_EXEC_TIMEOUT_MS": "400",
+             "HCCL_CALIBRATE": "0", "HCCL_NVLS_ENABLE": "0", "NCCL_NVLS_ENABLE": "0", "HCCL_HEARTBEAT_INTERVAL_MS": "50"}
+
+
+def test_operator_retry_on_gpus():
+    """A host-side stall of one rank makes the other rank's bounded device waits run out; the op is voted on and re-run."""
+    if ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(RETRY_ENV, HCCL_FAULT_INJECT="stall_rank:rank=1,op=2,ms=1500")
+    outs = run_gpu_ranks(2, "retry", env=env, timeout=180)
+    assert all("retry ok" in o for _, o in outs)
+
+
+def test_operator_retry_gives_up_after_max_attempts():
+    if ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(RETRY_ENV, HCCL_FAULT_INJECT="stall_rank:rank=1,op=2,ms=1500,attempts=3")
+    outs = run_gpu_ranks(2, "retry_exhausted", env=env, timeout=240)
+    assert all("retry exhausted ok" in o for _, o in outs)
