@@ -120,6 +120,7 @@ struct Plan {
     std::vector<std::vector<Step>> steps;  // [local rank index]
     int nchan = 1;
     uint64_t stage_bytes = 0;  // staging bytes touched per rank (must fit one half)
+    bool intra_rank_waits = false;  // some CTA of a rank waits for another CTA of the same rank: all CTAs must be resident together
     std::string name;          // "<collective>/<algorithm>"
 };
 

@@ -1085,7 +1085,13 @@ HcclResult build_plan(const OpDesc &d, const std::vector<int> &local, Plan *plan
     }
     if (!ok) return HCCL_E_NOT_SUPPORT;
     plan->steps.clear();
-    for (int r : local) plan->steps.push_back(std::move(P.s[r]));
+    plan->intra_rank_waits = false;
+    for (int r : local) {
+        // a wait that covers the executing rank itself is a dependency between that rank's own CTAs
+        for (const Step &st : P.s[r])
+            if (st.wait_rank != RANK_NONE && (st.flags & SF_INCLUDE_SELF)) plan->intra_rank_waits = true;
+        plan->steps.push_back(std::move(P.s[r]));
+    }
     plan->nchan = d.nchan;
     plan->stage_bytes = plan_stage_bytes(d);
     plan->name = std::string(coll_name(d.coll)) + "/" + algo_name(d.algo);

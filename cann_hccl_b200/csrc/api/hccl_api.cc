@@ -920,6 +920,24 @@ HcclResult HcclCommResume(HcclComm comm)
     GET_COMM("HcclCommResume");
     return c->resume();
 }
+// Process-wide abort handler (reference: ProcessTaskAbortHandleCallback, task_abort_handler.cc:28-128): runs one stage over
+// every communicator of `device` (-1: all), each within `timeoutSec` (0 = no limit).  0 success, 1 failure, 2 time-out.
+int32_t HcclB200TaskAbort(int32_t device, int32_t stage, uint32_t timeoutSec)
+{
+    std::vector<Communicator *> comms;
+    {
+        std::lock_guard<std::mutex> lk(g_comm_mu);
+        for (auto *c : g_comms)
+            if (device < 0 || c->transport() != TR_DEVICE || c->device() == device) comms.push_back(c);
+    }
+    const int budget_ms = (int)std::min<uint64_t>((uint64_t)timeoutSec * 1000, 0x7fffffff);
+    for (auto *c : comms) {
+        HcclResult rc = stage == 0 ? c->suspend_entry(budget_ms) : (stage == 1 ? c->stop_exec(budget_ms) : c->clean(budget_ms));
+        if (rc == HCCL_E_TIMEOUT) { HLOG_ERROR("task abort stage %d timed out on communicator %s", stage, c->name().c_str()); return 2; }
+        if (rc != HCCL_SUCCESS && rc != HCCL_E_SUSPENDING) { HLOG_ERROR("task abort stage %d failed on communicator %s (%d)", stage, c->name().c_str(), (int)rc); return 1; }
+    }
+    return 0;
+}
 
 // Zero-copy registration (reference: zero_copy_memory_agent.cc, request types SET_MEMORY_RANGE .. DEACTIVATE_COMM_MEMORY).
 // HcclCommSetMemoryRange reserves an address range; HcclCommActivateCommMemory, called by every rank of the communicator

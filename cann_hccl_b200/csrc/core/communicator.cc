@@ -393,7 +393,7 @@ HcclResult Communicator::run_plan(const Plan &plan, const void *dev_steps_base, 
     }
     if (settings_.transport == TR_DEVICE) {
         // map local index -> context: the plan may cover a subset of the local ranks (local Send/Recv)
-        return launch_exec_plan((const RankCtx *)dev_ctx_, args.data(), nl, plan.nchan, rq.stream);
+        return launch_exec_plan((const RankCtx *)dev_ctx_, args.data(), nl, plan.nchan, rq.stream, plan.intra_rank_waits);
     }
     if (nl == 1) return exec_plan_host(ctx_[0], args[0]);
     std::vector<HcclResult> rcs(nl, HCCL_SUCCESS);
@@ -1200,12 +1200,77 @@ HcclResult Communicator::local_send_recv(int src, int dst, const void *sbuf, voi
 }
 
 // ------------------------------------------------------------------------------------------------ health
-HcclResult Communicator::suspend()
+// Staged abort (reference: TaskAbortHandler stages 0 / 1 / 2 = Suspend / StopExec / Clean, each with its own time budget,
+// framework/communicator/impl/task_abort_handler.cc:28-128; HcclCommunicator::Suspend / StopExec / Clean).
+//   stage 0  suspend_entry: the communicator takes no new operation (HCCL_E_SUSPENDING) and the abort word is raised, which
+//            ends the waits of CPU ranks and of kernels alike; an API call that is inside the library is given the budget
+//            to leave it.
+//   stage 1  stop_exec: the budget covers the exit of the kernels in flight, observed through an event recorded behind
+//            the newest launch (never a blocking synchronisation).
+//   stage 2  clean: status blocks, arrival counters and failure words are cleared locally.  The flags are re-armed under a
+//            new common sequence by resume(), which is collective.
+// Each stage returns HCCL_E_TIMEOUT when its budget runs out (0 = no limit) and can be called again.
+HcclResult Communicator::suspend_entry(int budget_ms)
 {
-    // Raise the abort word polled by every wait (reference: Suspend/StopExec, hccl_communicator.cc:4383-4500).
     for (auto *a : abort_) *a = 1;
     state_.store(CS_SUSPENDED);
+    const double t0 = now_us();
+    while (!op_mu_.try_lock()) {
+        if (budget_ms > 0 && now_us() - t0 > budget_ms * 1e3) return HCCL_E_TIMEOUT;
+        usleep(200);
+    }
+    op_mu_.unlock();
     return HCCL_SUCCESS;
+}
+
+HcclResult Communicator::stop_exec(int budget_ms)
+{
+    for (auto *a : abort_) *a = 1;
+    state_.store(CS_SUSPENDED);
+    if (settings_.transport != TR_DEVICE) return HCCL_SUCCESS;  // CPU ranks run inside the API call that stage 0 waited for
+    cudaSetDevice(settings_.device);
+    cudaEvent_t ev = nullptr;
+    if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) return HCCL_E_RUNTIME;
+    // the legacy default stream waits for every blocking stream of the context; streams created non-blocking are covered by
+    // the bounded device waits themselves (the abort word ends them within microseconds)
+    cudaEventRecord(ev, 0);
+    const double t0 = now_us();
+    HcclResult rc = HCCL_SUCCESS;
+    for (;;) {
+        cudaError_t q = cudaEventQuery(ev);
+        if (q == cudaSuccess) break;
+        if (q != cudaErrorNotReady) { rc = HCCL_E_RUNTIME; break; }
+        if (budget_ms > 0 && now_us() - t0 > budget_ms * 1e3) { rc = HCCL_E_TIMEOUT; break; }
+        usleep(200);
+    }
+    cudaEventDestroy(ev);
+    return rc;
+}
+
+HcclResult Communicator::clean(int budget_ms)
+{
+    const double t0 = now_us();
+    std::unique_lock<std::mutex> lk(op_mu_, std::defer_lock);
+    while (!lk.try_lock()) {
+        if (budget_ms > 0 && now_us() - t0 > budget_ms * 1e3) return HCCL_E_TIMEOUT;
+        usleep(200);
+    }
+    const bool dev = settings_.transport == TR_DEVICE;
+    if (dev) cudaSetDevice(settings_.device);
+    for (int li = 0; li < nlocal(); ++li) memset(status_[li], 0, sizeof(DevStatus));
+    if (dev && dev_exit_)
+        for (int li = 0; li < nlocal(); ++li) cudaMemsetAsync((uint32_t *)dev_exit_ + 4 * li, 0, sizeof(uint32_t) * 2, 0);
+    if (dev && dev_pipe_cnt_) cudaMemsetAsync(dev_pipe_cnt_, 0, sizeof(uint32_t) * kPipeCounterWords * nlocal(), 0);
+    last_op_.valid = false;
+    return HCCL_SUCCESS;
+}
+
+HcclResult Communicator::suspend()
+{
+    // HcclCommSuspend = stages 0 and 1 without a budget (reference: Suspend/StopExec, hccl_communicator.cc:4383-4500).
+    HcclResult rc = suspend_entry(0);
+    if (rc != HCCL_SUCCESS) return rc;
+    return stop_exec(0);
 }
 
 HcclResult Communicator::resume()

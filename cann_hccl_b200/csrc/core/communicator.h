@@ -112,6 +112,10 @@ public:
     // NCCL all-reduce baseline on the p2p backend's communicator (benchmarks only).
     HcclResult nccl_baseline_allreduce(const void *send, void *recv, uint64_t count, int dtype, int op, void *stream);
     HcclResult suspend();
+    // The three stages of an abort, each with a time budget in milliseconds (0 = none); HCCL_E_TIMEOUT when it runs out.
+    HcclResult suspend_entry(int budget_ms);
+    HcclResult stop_exec(int budget_ms);
+    HcclResult clean(int budget_ms);
     HcclResult resume();
     HcclResult resume_locked();
     HcclResult async_error();  // first error seen by this rank or reported by a peer
@@ -290,7 +294,7 @@ private:
 // Plain tcgen05 GEMM C[M,N] = A[M,K] * B[N,K]^T in bf16 (no communicator needed).
 HcclResult gemm_bf16_plain(const void *A, const void *B, void *C, int M, int N, int K, void *stream);
 // Device executor entry (kernels/exec_plan.cu).
-HcclResult launch_exec_plan(const RankCtx *dev_ctx, const ExecArgs *args, int nlocal, int nchan, void *stream);
+HcclResult launch_exec_plan(const RankCtx *dev_ctx, const ExecArgs *args, int nlocal, int nchan, void *stream, bool co_resident = false);
 // Unique identifier helper used by HcclGetRootInfo.
 std::string make_identifier(const std::string &ip, int port);
 // Process-wide registry of hubs started by HcclGetRootInfo (the communicator created by the same process with the

@@ -54,7 +54,7 @@ static const void *exec_kernel_for(int dtype, int op)
     }
 }
 
-HcclResult launch_exec_plan(const RankCtx *dev_ctx, const ExecArgs *args, int nlocal, int nchan, void *stream)
+HcclResult launch_exec_plan(const RankCtx *dev_ctx, const ExecArgs *args, int nlocal, int nchan, void *stream, bool co_resident)
 {
     if (nlocal < 1 || nlocal > kMaxRanks || nchan < 1 || nchan > kMaxChannels) return HCCL_E_PARA;
     ExecArgsArray arr;
@@ -63,8 +63,11 @@ HcclResult launch_exec_plan(const RankCtx *dev_ctx, const ExecArgs *args, int nl
     const void *fn = exec_kernel_for(args[0].dtype, args[0].redop);
     void *kargs[] = {(void *)&dev_ctx, (void *)&arr};
     cudaError_t e;
-    // virtual ranks of one GPU wait on one another: all their CTAs must be resident at the same time
-    if (nlocal > 1) e = cudaLaunchCooperativeKernel(fn, grid, block, kargs, 0, (cudaStream_t)stream);
+    // Virtual ranks of one GPU wait on one another, and some plans make a rank's CTAs wait on each other (a barrier over
+    // its own channels, CTA groups handing chunks on): all those CTAs must be resident at the same time, or a waiting CTA
+    // could occupy the SM that the CTA it waits for needs while another kernel holds the rest of the GPU.  A cooperative
+    // launch guarantees the co-residency (and fails at launch when the grid cannot fit).
+    if (nlocal > 1 || co_resident) e = cudaLaunchCooperativeKernel(fn, grid, block, kargs, 0, (cudaStream_t)stream);
     else e = cudaLaunchKernel(fn, grid, block, kargs, 0, (cudaStream_t)stream);
     if (e != cudaSuccess) {
         HLOG_ERROR("executor launch failed (grid %dx%d): %s", nchan, nlocal, cudaGetErrorString(e));

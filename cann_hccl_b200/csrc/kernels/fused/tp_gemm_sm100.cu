@@ -742,7 +742,10 @@ HcclResult launch_tp_gemm(TpGemmParams *P, const void *const *A, const void *con
     }
     dim3 grid((unsigned)(n_gemm + n_comm_ctas), (unsigned)nlocal), block(kThreads);
     cudaError_t e;
-    if (nlocal > 1) {
+    // AG and RS mode make CTAs of one rank wait on each other (GEMM CTAs on the data-movement CTAs, the reduce tail on the
+    // other CTAs' tiles): a cooperative launch guarantees that all of them are resident together even when another kernel
+    // shares the GPU.  The plain GEMM has no such dependency.
+    if (nlocal > 1 || P0.mode != TP_MODE_PLAIN) {
         void *kargs[] = {(void *)&arr};
         e = cudaLaunchCooperativeKernel((const void *)tp_gemm_kernel, grid, block, kargs, smem, (cudaStream_t)stream);
     } else {

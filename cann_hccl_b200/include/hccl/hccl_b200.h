@@ -145,6 +145,11 @@ extern HcclResult HcclB200Exchange(HcclComm comm, const char *tag, const void *m
  * device array of per-local-rank contexts with peer staging / flag pointers, plus the next op sequence number. */
 extern HcclResult HcclB200GetDeviceContext(HcclComm comm, void **devCtxArray, uint64_t *nextSeq);
 extern HcclResult HcclB200ReloadEnv(void);
+/* Staged abort over every communicator of `device` (-1: all devices and CPU communicators), the role of the reference's
+ * task-abort callback: stage 0 suspends (no new operations, waits in flight are told to end), stage 1 waits for the kernels
+ * in flight to exit, stage 2 clears status blocks and counters; HcclCommResume (collective) makes the communicators usable
+ * again.  Each communicator gets `timeoutSec` per stage (0 = no limit).  Returns 0 = done, 1 = failed, 2 = timed out. */
+extern int32_t HcclB200TaskAbort(int32_t device, int32_t stage, uint32_t timeoutSec);
 
 #ifdef __cplusplus
 }

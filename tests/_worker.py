@@ -5,6 +5,7 @@ import time
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+import ctypes as C  # noqa: E402
 import numpy as np  # noqa: E402
 
 import cann_hccl_b200 as H  # noqa: E402
@@ -345,6 +346,45 @@ def scenario_suspend_resume(c, p, r, args):
     c.all_reduce(x, out)
     np.testing.assert_array_equal(out, np.full(64, p, np.float32))
     print("suspend/resume ok")
+
+
+def scenario_staged_abort(c, p, r, args):
+    """The three abort stages with time budgets (HcclB200TaskAbort).  Rank 1 enters its 2nd collective late (host-side
+    stall of 3 s inside the call), so rank 0 sits in a bounded wait: stage 0 tells both to stop.  On rank 1 the stalled
+    call cannot leave within a 1 s budget (result 2 = timed out); asked again without limit it succeeds."""
+    import threading
+    lib = L.lib()
+    lib.HcclB200TaskAbort.restype = C.c_int32
+    lib.HcclB200TaskAbort.argtypes = [C.c_int32, C.c_int32, C.c_uint32]
+    x = np.ones(64, np.float32)
+    c.all_reduce(x, x.copy())
+    res = {}
+
+    def op():
+        try:
+            c.all_reduce(x, x.copy())
+            res["rc"] = 0
+        except H.HcclError as e:
+            res["rc"] = e.code
+    t = threading.Thread(target=op)
+    t.start()
+    time.sleep(0.5)                                  # both ranks are inside the call now (rank 1 in its stall)
+    first = lib.HcclB200TaskAbort(-1, 0, 1)
+    if r == 1:
+        assert first == 2, first                     # the stalled call holds the communicator beyond the budget
+        assert lib.HcclB200TaskAbort(-1, 0, 0) == 0  # no limit: returns once the call has left
+    else:
+        assert first == 0, first
+    t.join()
+    assert res["rc"] == L.E_SUSPENDING, res
+    assert lib.HcclB200TaskAbort(-1, 1, 5) == 0
+    assert lib.HcclB200TaskAbort(-1, 2, 5) == 0
+    assert c.status().code == 0
+    c.resume()
+    out = np.zeros_like(x)
+    c.all_reduce(x, out)
+    np.testing.assert_array_equal(out, np.full(64, p, np.float32))
+    print("staged abort ok")
 
 
 def scenario_stuck(c, p, r, args):

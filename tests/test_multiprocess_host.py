@@ -27,6 +27,12 @@ def test_alltoallv_count_matrix_cross_check():
     assert all("a2av_mismatch ok" in out for _, out in res)
 
 
+def test_staged_abort_with_budgets():
+    env = {"HCCL_EXEC_TIMEOUT_MS": "20000", "HCCL_FAULT_INJECT": "stall_rank:rank=1,op=2,ms=3000"}
+    res = run_ranks(2, "staged_abort", env=env)
+    assert all("staged abort ok" in out for _, out in res)
+
+
 def test_sub_communicator():
     res = run_ranks(4, "subcomm")
     assert all("subcomm ok" in out for _, out in res)
