@@ -17,6 +17,7 @@
 #include "common/log.h"
 #include "core/communicator.h"
 #include "hccl/hccl_b200.h"
+#include "core/topo_probe.h"
 #include "health/consistency.h"
 #include "health/fault_inject.h"
 #include "kernels/moe_a2a.h"
@@ -919,6 +920,12 @@ HcclResult HcclCommResume(HcclComm comm)
 {
     GET_COMM("HcclCommResume");
     return c->resume();
+}
+// NVLink attributes of a GPU as JSON (no communicator needed; `device` is the NVML index when CUDA is absent).
+HcclResult HcclB200ProbeLinks(int32_t device, char *json, size_t cap)
+{
+    CHK_RET_LOG(!json, HCCL_E_PTR, "HcclB200ProbeLinks: json is null");
+    return copy_out(link_topo_json(probe_links(device, std::string())), json, cap);
 }
 // Process-wide abort handler (reference: ProcessTaskAbortHandleCallback, task_abort_handler.cc:28-128): runs one stage over
 // every communicator of `device` (-1: all), each within `timeoutSec` (0 = no limit).  0 success, 1 failure, 2 time-out.

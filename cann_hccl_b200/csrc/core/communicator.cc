@@ -20,6 +20,7 @@
 #include "kernels/pipe_coll.h"
 #include <nvtx3/nvToolsExt.h>
 #include <fstream>
+#include "core/topo_probe.h"
 #include "p2p/p2p_backend.h"
 #include "transport/host_exec.h"
 
@@ -261,6 +262,21 @@ HcclResult Communicator::init_common()
         CHK_RET_LOG(cudaMalloc(&dev_ctx_, sizeof(RankCtx) * nl) != cudaSuccess, HCCL_E_MEMORY, "cudaMalloc failed");
         CHK_RET_LOG(cudaMemcpy(dev_ctx_, ctx_.data(), sizeof(RankCtx) * nl, cudaMemcpyHostToDevice) != cudaSuccess, HCCL_E_RUNTIME, "cudaMemcpy failed");
         cudaDeviceSynchronize();
+    }
+    if (dev) {
+        // link attributes of this GPU: the selector's default bandwidths come from what the device reports (a measured
+        // calibration, when it runs, replaces them)
+        char bus[32] = {0};
+        std::string pci = cudaDeviceGetPCIBusId(bus, sizeof(bus), settings_.device) == cudaSuccess ? std::string(bus) : std::string();
+        links_ = probe_links(settings_.device, pci);
+        int mc = 0;
+        cudaDeviceGetAttribute(&mc, (cudaDeviceAttr)132 /* cudaDevAttrMulticastSupported, not named by every runtime header */, settings_.device);
+        cudaGetLastError();
+        links_.multicast = nvls_ || mc != 0;
+        if (links_.probed && links_.egress_gbps() > 0) {
+            model_.beta_gbps = 0.72 * links_.egress_gbps();   // what peer loads / stores of one kernel reach of the nominal rate
+            model_.nvls_gbps = 0.55 * links_.egress_gbps();   // in-switch reductions run at about half the link rate per GPU
+        }
     }
     trace_.resize(kTraceCap);
     HLOG_INFO("communicator %s: %d ranks, %d local, transport %s, staging 2x%zu MB, nvls %d", name_.c_str(), nranks_, nl,
@@ -1616,6 +1632,7 @@ std::string Communicator::topo_json()
         o << (r ? "," : "") << "{\"rank\":" << e.rank << ",\"host\":\"" << e.host << "\",\"pid\":" << e.pid << ",\"device\":" << (dev ? e.device : -1) << "}";
     }
     o << "]";
+    if (dev) o << ",\"links\":" << link_topo_json(links_);
     if (dev) {
         // peer-access matrix over the devices that appear in the rank table (1 = this pair can map each other's memory)
         std::vector<int> devs;

@@ -17,6 +17,7 @@
 #include "algo/selector.h"
 #include "bootstrap/hub.h"
 #include "core/symmem.h"
+#include "core/topo_probe.h"
 
 namespace hcclb {
 
@@ -243,6 +244,7 @@ private:
     std::map<std::string, bool> checked_;
     std::map<std::pair<int, int>, uint32_t> p2p_rounds_;  // (src,dst) -> rounds exchanged
     CostModel model_;
+    LinkTopo links_;                        // NVLink attributes of this rank's GPU (device transport)
     // Measured times per collective, (size bucket, algorithm), from calibrate(); empty until calibrated.  Where a table exists
     // the selector picks the fastest measured algorithm that is allowed for the (dtype, op) at hand instead of the model's guess.
     struct TunedTable {

@@ -145,6 +145,9 @@ extern HcclResult HcclB200Exchange(HcclComm comm, const char *tag, const void *m
  * device array of per-local-rank contexts with peer staging / flag pointers, plus the next op sequence number. */
 extern HcclResult HcclB200GetDeviceContext(HcclComm comm, void **devCtxArray, uint64_t *nextSeq);
 extern HcclResult HcclB200ReloadEnv(void);
+/* NVLink attributes of a GPU as JSON: ports, active links, links that end in an NVSwitch, NVLink generation, bandwidth per
+ * link and direction, multicast capability.  Read from the management library (HCCL_NVML_LIB names another one). */
+extern HcclResult HcclB200ProbeLinks(int32_t device, char *json, size_t cap);
 /* Staged abort over every communicator of `device` (-1: all devices and CPU communicators), the role of the reference's
  * task-abort callback: stage 0 suspends (no new operations, waits in flight are told to end), stage 1 waits for the kernels
  * in flight to exit, stage 2 clears status blocks and counters; HcclCommResume (collective) makes the communicators usable
