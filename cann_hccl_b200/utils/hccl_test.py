@@ -4,6 +4,11 @@ output `data_size`, `aveg_time` us, `alg_bandwidth` GB/s, `check_result`).
 
     python -m cann_hccl_b200.utils.hccl_test all_reduce_test -b 8K -e 64M -f 2 -d fp32 -o sum -p 8
     python -m cann_hccl_b200.utils.hccl_test all_gather_test -b 1K -e 1M -f 4 -d int32 -p 4 --host     # CPU ranks
+    python -m cann_hccl_b200.utils.hccl_test all_reduce_test -b 1M -e 1G -p 8 --algo mesh_pipe,nvls_pipe --nccl --trace
+
+`--algo` takes one algorithm or a comma-separated list (one timed column per name after the selector's own choice),
+`--nccl` adds the same collective through torch.distributed's NCCL backend on the same buffers, `--trace` prints the
+in-kernel stage times of the newest pipelined launch of rank 0 (wait / work / publish per stage, microseconds).
 
 One process per rank is started by this program itself (no mpirun): rank 0 writes the root info to a temporary file, the
 others read it.  On GPUs rank r uses device r; the timed calls are issued back to back from C and timed with CUDA events
@@ -120,10 +125,24 @@ def worker(a):
           "uint64": L.UINT64, "fp16": L.FP16, "fp32": L.FP32, "fp64": L.FP64, "bfp16": L.BFP16}[a.dtype]
     es = 2 if a.dtype == "bfp16" else np.dtype(NP_DTYPES[a.dtype]).itemsize
     op = OPS[a.op]
-    algo = L.ALGO_NAMES.index(a.algo) if a.algo else L.ALGO_AUTO
+    names = [x for x in a.algo.split(",") if x] if a.algo else []
+    for x in names:
+        if x not in L.ALGO_NAMES:
+            raise SystemExit("unknown algorithm %r (known: %s)" % (x, ", ".join(L.ALGO_NAMES)))
+    # one name: that algorithm replaces the selector (as before); several: the selector's choice first, then a column each
+    algo = L.ALGO_NAMES.index(names[0]) if len(names) == 1 else L.ALGO_AUTO
+    extra_algos = names if len(names) > 1 else []
+    dist = None
+    if a.nccl and device and p > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", str(29600 + (os.getppid() % 300)))
+        dist.init_process_group("nccl", rank=rank, world_size=p, device_id=torch.device("cuda", torch.cuda.current_device()))
     if rank == 0:
         print("the minbytes is %d, maxbytes is %d, iters is %d, warmup_iters is %d" % (a.minbytes, a.maxbytes, a.iters, a.warmup))
-        print("%-16s %-16s %-22s %s" % ("data_size(Bytes):", "aveg_time(us):", "alg_bandwidth(GB/s):", "check_result:"))
+        head = "%-16s %-16s %-22s %-14s" % ("data_size(Bytes):", "aveg_time(us):", "alg_bandwidth(GB/s):", "check_result:")
+        head += "".join(" %-16s" % (x + "(us):") for x in extra_algos) + (" %-16s %-16s" % ("nccl_time(us):", "nccl_bw(GB/s):") if dist else "")
+        print(head)
     size = a.minbytes
     failed = False
     while size <= a.maxbytes:
@@ -166,33 +185,65 @@ def worker(a):
                     ok = bool(np.allclose(got.astype(np.float64), np.asarray(ref, np.float64), rtol=tol, atol=tol))
                 else:
                     ok = bool(np.array_equal(got, ref.astype(got.dtype)))
-        call(a.warmup)
-        comm.barrier()
-        if device:
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            call(a.iters)
-            e1.record()
-            torch.cuda.synchronize()
-            assert comm.sync() == 0, comm.describe_status()
-            us = e0.elapsed_time(e1) * 1e3 / a.iters
-        else:
+        def timed(fn):
+            fn(a.warmup)
+            comm.barrier()
+            if device:
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn(a.iters)
+                e1.record()
+                torch.cuda.synchronize()
+                assert comm.sync() == 0, comm.describe_status()
+                return e0.elapsed_time(e1) * 1e3 / a.iters
             t0 = time.perf_counter()
-            call(a.iters)
-            us = (time.perf_counter() - t0) * 1e6 / a.iters
+            fn(a.iters)
+            return (time.perf_counter() - t0) * 1e6 / a.iters
+        times = [timed(call)]
+        for x in extra_algos:
+            kx = dict(kw, algo=L.ALGO_NAMES.index(x))
+            try:
+                times.append(timed(lambda k: comm.repeat(coll, send, recv, count, hd, k, **kx) if k > 0 else None))
+            except H.HcclError:
+                times.append(float("nan"))  # the algorithm does not exist for this collective / type / size
+        if a.trace and rank == 0 and device:
+            import ctypes as C
+            buf = (C.c_uint64 * 16)()
+            ns = C.c_int(0)
+            if L.lib().HcclB200GetKernelTrace(comm.handle, 0, buf, 16, C.byref(ns)) == 0 and buf[0] not in (0, 2 ** 64 - 1):
+                print("    stages of the newest pipelined launch (us): " + " | ".join(
+                    "stage %d wait %.1f work %.1f publish %.1f" % (k, buf[1 + 4 * k] / 1e3, buf[2 + 4 * k] / 1e3, buf[3 + 4 * k] / 1e3) for k in range(3)))
+        if dist is not None:
+            nccl_fn = {"all_reduce_test": lambda: dist.all_reduce(recv if recv is not send else send, op={0: dist.ReduceOp.SUM, 1: dist.ReduceOp.PRODUCT, 2: dist.ReduceOp.MAX, 3: dist.ReduceOp.MIN}[op]),
+                       "all_gather_test": lambda: dist.all_gather_into_tensor(recv, send),
+                       "reduce_scatter_test": lambda: dist.reduce_scatter_tensor(recv, send),
+                       "broadcast_test": lambda: dist.broadcast(send, src=a.root),
+                       "reduce_test": lambda: dist.reduce(send, dst=a.root),
+                       "scatter_test": lambda: dist.scatter(recv, list(send.chunk(p)) if rank == a.root else None, src=a.root),
+                       "gather_test": lambda: dist.gather(send, list(recv.chunk(p)) if rank == a.root else None, dst=a.root),
+                       "alltoall_test": lambda: dist.all_to_all_single(recv, send)}[a.test]
+            times.append(timed(lambda k: [nccl_fn() for _ in range(k)]))
         # maximum over ranks and the conjunction of the checks, gathered over the control plane
         import struct
-        blob = comm.exchange("t%d" % size, struct.pack("<dI", us, 1 if ok else 0))
-        vals = [struct.unpack("<dI", b) for b in blob]
-        us = max(v[0] for v in vals)
-        ok = all(v[1] for v in vals)
+        fmt = "<%ddI" % len(times)
+        blob = comm.exchange("t%d" % size, struct.pack(fmt, *times, 1 if ok else 0))
+        vals = [struct.unpack(fmt, b) for b in blob]
+        times = [max(v[i] for v in vals) for i in range(len(times))]
+        us = times[0]
+        ok = all(v[-1] for v in vals)
         failed |= not ok
         if rank == 0:
-            print("%-16d %-16.2f %-22.5f %s" % (count * es, us, count * es / us / 1e3, "success" if ok else "failed"), flush=True)
+            line = "%-16d %-16.2f %-22.5f %-14s" % (count * es, us, count * es / us / 1e3, "success" if ok else "failed")
+            line += "".join(" %-16.2f" % t for t in times[1:1 + len(extra_algos)])
+            if dist is not None:
+                line += " %-16.2f %-16.5f" % (times[-1], count * es / times[-1] / 1e3)
+            print(line, flush=True)
         del send, recv
         size = size * a.factor if a.factor > 1 else size + max(1, a.step)
     code = comm.destroy()
+    if dist is not None:
+        dist.destroy_process_group()
     return 1 if failed or code != 0 else 0
 
 
@@ -210,13 +261,18 @@ def main(argv=None):
     ap.add_argument("-w", "--warmup", type=int, default=5)
     ap.add_argument("-c", "--check", type=int, default=1)
     ap.add_argument("-r", "--root", type=int, default=0)
-    ap.add_argument("--algo", default="", help="force an algorithm (mesh, ring, rhd, nvls, ...)")
+    ap.add_argument("--algo", default="", help="force an algorithm (mesh, ring, rhd, nvls, ...); a comma-separated list adds one timed column per name")
+    ap.add_argument("--nccl", action="store_true", help="also time the same collective through torch.distributed (NCCL) on the same buffers")
+    ap.add_argument("--trace", action="store_true", help="print the in-kernel stage times of the newest pipelined launch (sets HCCL_KERNEL_TRACE=1)")
     ap.add_argument("--host", action="store_true", help="CPU ranks over the host-memory transport")
-    ap.add_argument("--buffsize", type=int, default=640, help="staging MB per direction (HCCL_BUFFSIZE)")
+    ap.add_argument("--buffsize", type=int, default=200, help="staging MB per direction (HCCL_BUFFSIZE)")
     ap.add_argument("--rank", type=int, default=-1, help=argparse.SUPPRESS)
     ap.add_argument("--root-file", default="", help=argparse.SUPPRESS)
     a = ap.parse_args(argv)
     a.minbytes, a.maxbytes = parse_size(a.minbytes), parse_size(a.maxbytes)
+    os.environ.setdefault("HCCL_EXEC_TIMEOUT_MS", "30000")  # a lost rank must not leave the others' waits polling for long
+    if a.trace:
+        os.environ["HCCL_KERNEL_TRACE"] = "1"
     if a.rank >= 0:
         return worker(a)
     if a.nranks <= 0:
