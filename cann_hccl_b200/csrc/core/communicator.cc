@@ -15,6 +15,7 @@
 #include "common/log.h"
 #include "health/consistency.h"
 #include "health/fault_inject.h"
+#include "kernels/a2av.h"
 #include "kernels/ar_ll.h"
 #include "kernels/overflow.h"
 #include "kernels/pipe_coll.h"
@@ -727,6 +728,17 @@ HcclResult Communicator::run_collective_once(const OpRequest &rq)
         sel.algo = ALGO_MESH_ONESHOT;  // unaligned or oversized: the plan executor handles every layout
     }
 
+    if ((is_a2av || rq.coll == COLL_ALLTOALL) && settings_.transport == TR_DEVICE && p > 1 && (rq.algo == ALGO_AUTO || rq.algo == ALGO_DIRECT) &&
+        forced_algo_for(env_config(), rq.coll).empty()) {
+        HcclResult arc = run_a2av(rq);
+        uint64_t abytes = sel_count * es;
+        stats_.ops[rq.coll]++;
+        stats_.bytes[rq.coll] += abytes;
+        stats_.algo_hist[ALGO_DIRECT]++;
+        record_trace(rq, ALGO_DIRECT, 0, abytes, now_us() - t0);
+        return arc;
+    }
+    CHK_RET_LOG(rq.algo == ALGO_DIRECT || sel.algo == ALGO_DIRECT, HCCL_E_NOT_SUPPORT, "the parametric AlltoAll kernel needs the device transport and more than one rank");
     if (sel.algo == ALGO_MESH_PIPE || sel.algo == ALGO_NVLS_PIPE) {
         if (settings_.transport == TR_DEVICE && pipe_mode_for(rq.coll) >= 0) {
             HcclResult prc = run_pipe(rq, sel.algo == ALGO_NVLS_PIPE);
@@ -901,6 +913,41 @@ HcclResult Communicator::run_pipe(const OpRequest &rq, bool want_mc)
             cudaMemsetAsync((uint64_t *)dev_trace_ + (size_t)li * kTraceWords, 0xff, 8, (cudaStream_t)rq.stream);
         }
     HcclResult rc = launch_pipe_coll((const RankCtx *)dev_ctx_, args.data(), nl, rq.redop, rq.stream);
+    ++seq_;
+    return rc;
+}
+
+// AlltoAll / AlltoAllV / AlltoAllVC on the device transport: the parametric kernel (kernels/a2av.cu).  Counts and
+// displacements go into the launch arguments; nothing is built, allocated or copied to the device for a new count matrix.
+HcclResult Communicator::run_a2av(const OpRequest &rq)
+{
+    const int p = nranks_, nl = nlocal(), es = dtype_size(rq.dtype);
+    // lanes per ordered pair: all CTAs of a launch must fit the GPU at once when virtual ranks share it
+    int lanes = std::max(1, std::min(4, 148 / (2 * p * nl)));
+    uint64_t sub = std::min<uint64_t>(2u << 20, settings_.stage_half_bytes / ((uint64_t)p * lanes * 2)) / 256 * 256;
+    while (sub < 4096 && lanes > 1) { --lanes; sub = std::min<uint64_t>(2u << 20, settings_.stage_half_bytes / ((uint64_t)p * lanes * 2)) / 256 * 256; }
+    CHK_RET_LOG(sub < 256, HCCL_E_MEMORY, "staging buffer too small for AlltoAllV over %d ranks", p);
+    std::vector<A2avArgs> args(nl);
+    for (int li = 0; li < nl; ++li) {
+        A2avArgs &a = args[li];
+        memset(&a, 0, sizeof(a));
+        a.in = (const uint8_t *)rq.in[li];
+        a.out = (uint8_t *)rq.out[li];
+        for (int j = 0; j < p; ++j) {
+            if (rq.coll == COLL_ALLTOALL) {
+                a.send_counts[j] = a.recv_counts[j] = rq.count;
+                a.send_displs[j] = a.recv_displs[j] = (uint64_t)j * rq.count;
+            } else {
+                a.send_counts[j] = rq.send_counts[(size_t)li * p + j]; a.send_displs[j] = rq.send_displs[(size_t)li * p + j];
+                a.recv_counts[j] = rq.recv_counts[(size_t)li * p + j]; a.recv_displs[j] = rq.recv_displs[(size_t)li * p + j];
+            }
+        }
+        a.seq = seq_; a.sub_bytes = sub; a.dtype = rq.dtype; a.lanes = lanes;
+        (void)es;
+        status_[li]->head = seq_;
+    }
+    stats_.launches++;
+    HcclResult rc = launch_a2av((const RankCtx *)dev_ctx_, args.data(), nl, p, rq.stream);
     ++seq_;
     return rc;
 }

@@ -18,7 +18,7 @@ enum { HCCL_B200_ALLREDUCE = 0, HCCL_B200_BROADCAST, HCCL_B200_REDUCE_SCATTER, H
        HCCL_B200_ALLTOALLV, HCCL_B200_ALLTOALLVC, HCCL_B200_REDUCE, HCCL_B200_GATHER };
 enum { HCCL_B200_ALGO_AUTO = 0, HCCL_B200_ALGO_MESH, HCCL_B200_ALGO_MESH_ONESHOT, HCCL_B200_ALGO_RING,
        HCCL_B200_ALGO_RHD, HCCL_B200_ALGO_PAIRWISE, HCCL_B200_ALGO_STAR, HCCL_B200_ALGO_TREE, HCCL_B200_ALGO_NVLS,
-       HCCL_B200_ALGO_NVLS_ONESHOT, HCCL_B200_ALGO_SINGLE, HCCL_B200_ALGO_MESH_PIPE, HCCL_B200_ALGO_NVLS_PIPE, HCCL_B200_ALGO_NVLS_ZEROCOPY, HCCL_B200_ALGO_LL };
+       HCCL_B200_ALGO_NVLS_ONESHOT, HCCL_B200_ALGO_SINGLE, HCCL_B200_ALGO_MESH_PIPE, HCCL_B200_ALGO_NVLS_PIPE, HCCL_B200_ALGO_NVLS_ZEROCOPY, HCCL_B200_ALGO_LL, HCCL_B200_ALGO_DIRECT };
 
 typedef struct HcclB200OpDef {
     int32_t coll;       /* HCCL_B200_* collective */

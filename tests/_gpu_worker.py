@@ -171,6 +171,22 @@ def scenario_collectives(c, p, r, args):
         ok(c)
         for q in range(p):
             assert torch.equal(out[q * n:(q + 1) * n], xs[q][r * n:(r + 1) * n])
+    # parametric AlltoAllV kernel (auto selection): uneven counts, blocks of several rounds, every rank its own row
+    import numpy as np
+    rng = np.random.default_rng(99)
+    m = rng.integers(0, 900_000 // p, (p, p)).astype(np.uint64)
+    m[0, p - 1] = 0
+    sd = np.concatenate([[0], np.cumsum(m[r])[:-1]]).astype(np.uint64)
+    rd = np.concatenate([[0], np.cumsum(m[:, r])[:-1]]).astype(np.uint64)
+    rows = [inp(q, int(m[q].sum()) + 1, torch.float32, seed=17) for q in range(p)]
+    vout = torch.zeros(int(m[:, r].sum()) + 1, device="cuda")
+    for _ in range(2):
+        c.all_to_all_v(rows[r], m[r].copy(), sd, vout, np.ascontiguousarray(m[:, r]), rd)
+    ok(c)
+    assert c.trace()[-1]["algo"] == "direct", c.trace()[-1]
+    for q in range(p):
+        sq = np.concatenate([[0], np.cumsum(m[q])[:-1]])
+        assert torch.equal(vout[int(rd[q]):int(rd[q] + m[q, r])], rows[q][int(sq[r]):int(sq[r] + m[q, r])])
     c.barrier()
     ok(c)
     # Send/Recv ring over the NCCL p2p backend

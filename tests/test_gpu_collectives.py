@@ -289,6 +289,52 @@ def test_all_to_all_and_v(comms, p, algo):
             assert torch.equal(vout[j][int(rd[j, i]):int(rd[j, i] + m[i, j])], vin[i][int(sd[i, j]):int(sd[i, j] + m[i, j])])
 
 
+@pytest.mark.parametrize("p", [2, 3, 8])
+def test_all_to_all_v_parametric_kernel(comms, p):
+    """Auto selection on the device runs the parametric kernel: counts travel as launch arguments, so hundreds of distinct
+    count matrices build no plan and allocate nothing; blocks larger than a sub-slot go in acknowledged rounds."""
+    import numpy as np
+    c = comms(p)
+    rng = np.random.default_rng(11)
+    cap = 200_000 // p
+    vin = [torch.randn(cap * p + 8, device="cuda") for _ in range(p)]
+    vout = [torch.zeros(cap * p + 8, device="cuda") for _ in range(p)]
+    # 4 MB staging halves / (p ranks x lanes x 2) gives sub-slots far below 4 x cap bytes: several rounds per pair
+    plans0 = None
+    free0 = None
+    for it in range(120):
+        m = rng.integers(0, cap if it % 7 else 64, (p, p)).astype(np.uint64)
+        if it % 5 == 0:
+            m[0, p - 1] = 0
+        sd = np.zeros((p, p), np.uint64)
+        rd = np.zeros((p, p), np.uint64)
+        for i in range(p):
+            sd[i] = np.concatenate([[0], np.cumsum(m[i])[:-1]])
+            rd[i] = np.concatenate([[0], np.cumsum(m[:, i])[:-1]])
+        c.all_to_all_v(vin, m, sd, vout, np.ascontiguousarray(m.T), rd)
+        if it in (0, 60, 119):
+            ok(c)
+            assert c.trace()[-1]["algo"] == "direct"
+            for i in range(p):
+                for j in range(p):
+                    assert torch.equal(vout[j][int(rd[j, i]):int(rd[j, i] + m[i, j])], vin[i][int(sd[i, j]):int(sd[i, j] + m[i, j])])
+        if it == 0:
+            torch.cuda.synchronize()
+            plans0, free0 = c.stats()["plans_built"], torch.cuda.mem_get_info()[0]
+    ok(c)
+    assert c.stats()["plans_built"] == plans0
+    assert torch.cuda.mem_get_info()[0] == free0
+    # uniform AlltoAll through the same kernel
+    n = 70_001
+    ins = rnd(p, n * p, torch.float32, seed=8)
+    outs = [torch.zeros(n * p, device="cuda") for _ in range(p)]
+    c.all_to_all(ins, outs)
+    ok(c)
+    for r in range(p):
+        for q in range(p):
+            assert torch.equal(outs[r][q * n:(q + 1) * n], ins[q][r * n:(r + 1) * n])
+
+
 def test_v_variants_barrier_sendrecv(comms):
     import numpy as np
     p = 4
