@@ -56,14 +56,18 @@ def collective_sweeps(comm, world, rank, dist, max_over_ranks, sync, max_bytes, 
 
     def t_ours(coll, send, recv, count, dtype, iters, **kw):
         comm.repeat(coll, send, recv, count, dtype, 2, **kw)
-        sync()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        comm.repeat(coll, send, recv, count, dtype, iters, **kw)
-        b.record()
-        torch.cuda.synchronize()
-        assert comm.sync() == 0, comm.describe_status()
-        return max_over_ranks(a.elapsed_time(b) / iters)
+        best = None
+        for _ in range(2):  # the better of two timed loops: one stall of a shared host does not decide a row
+            sync()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            comm.repeat(coll, send, recv, count, dtype, iters, **kw)
+            b.record()
+            torch.cuda.synchronize()
+            assert comm.sync() == 0, comm.describe_status()
+            t = max_over_ranks(a.elapsed_time(b) / iters)
+            best = t if best is None else min(best, t)
+        return best
 
     specs = [("allgather", L.ALLGATHER, (torch.float32, torch.bfloat16), (L.ALGO_RING, L.ALGO_RHD)),
              ("reducescatter", L.REDUCE_SCATTER, (torch.float32, torch.bfloat16), (L.ALGO_RING, L.ALGO_RHD)),
@@ -103,7 +107,7 @@ def collective_sweeps(comm, world, rank, dist, max_over_ranks, sync, max_bytes, 
                           L.REDUCE: lambda: dist.reduce(send, dst=0),
                           L.SCATTER: lambda: dist.scatter(recv, list(send.chunk(world)) if rank == 0 else None, src=0),
                           L.GATHER: lambda: dist.gather(send, list(recv.chunk(world)) if rank == 0 else None, dst=0)}[coll]
-                    tn = max_over_ranks(_time(fn, iters, sync, warm=2))
+                    tn = min(max_over_ranks(_time(fn, iters, sync, warm=2)), max_over_ranks(_time(fn, iters, sync, warm=0)))
                     row["nccl_time_us"] = round(tn * 1e3, 2)
                     row["nccl_alg_bandwidth_GBps"] = round(size / tn / 1e6, 2)
                     row["vs_nccl"] = round(tn / t, 3)

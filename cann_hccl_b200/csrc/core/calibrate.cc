@@ -2,8 +2,8 @@
 // every rank selects with identical numbers:
 //   1. the cost model's constants: launch overhead, flag-hop latency (alpha), peer bandwidth (beta), in-switch bandwidth and
 //      local copy throughput (gamma), the bandwidths taken on messages of 32 MiB and more;
-//   2. a measured table per collective (AllReduce, AllGather, ReduceScatter, Broadcast): every candidate algorithm at a
-//      ladder of sizes.  Where a table exists the selector takes the fastest measured algorithm that is legal for the
+//   2. a measured table per collective (AllReduce, AllGather, ReduceScatter, Broadcast, Reduce, Scatter, Gather): every
+//      candidate algorithm at a ladder of sizes.  Where a table exists the selector takes the fastest measured algorithm that is legal for the
 //      (type, operator, determinism) at hand, and falls back on the model elsewhere.
 // Runs once when a device communicator with more than one rank is created (HCCL_CALIBRATE=0 skips it; HcclB200Calibrate
 // repeats it on demand).  The reference selects every op from one cost model with a fixed 60 us step latency
@@ -65,9 +65,9 @@ HcclResult Communicator::calibrate(void *stream)
         ~Restore() { c->stats_ = s; c->op_index_ = oi; c->calibrating_ = false; if (own) cudaStreamDestroy(st); }
     } restore{this, stats0, op_index0, st, own_stream};
 
-    // largest message per rank: 64 MiB for AllReduce / Broadcast, 32 MiB per rank for AllGather / ReduceScatter (whose other
-    // buffer is p times as large); virtual ranks of one GPU and small staging buffers scale it down
-    uint64_t cap_mb = env.calibrate_max_mb > 0 ? (uint64_t)env.calibrate_max_mb : 64;
+    // largest message per rank: 256 MiB for AllReduce / Broadcast / Reduce, half of that per rank for the collectives whose
+    // other buffer is p times as large; virtual ranks of one GPU and small staging buffers scale it down
+    uint64_t cap_mb = env.calibrate_max_mb > 0 ? (uint64_t)env.calibrate_max_mb : 256;
     if (all_local_) cap_mb = std::min<uint64_t>(cap_mb, 4);
     const uint64_t max_ar = std::max<uint64_t>(64u << 10, std::min<uint64_t>(cap_mb << 20, settings_.stage_half_bytes * 4));
     const uint64_t max_blk = std::max<uint64_t>(64u << 10, max_ar / 2);
@@ -100,8 +100,8 @@ HcclResult Communicator::calibrate(void *stream)
         for (int li = 0; li < nl; ++li) {
             uint8_t *s0 = (uint8_t *)small[li], *b0 = (uint8_t *)big[li];
             switch (coll) {
-                case COLL_ALLGATHER: in[li] = s0 + off; out[li] = b0; break;                 // small -> big
-                case COLL_REDUCE_SCATTER: in[li] = b0; out[li] = s0 + off; break;            // big -> small
+                case COLL_ALLGATHER: case COLL_GATHER: in[li] = s0 + off; out[li] = b0; break;          // small -> big
+                case COLL_REDUCE_SCATTER: case COLL_SCATTER: in[li] = b0; out[li] = s0 + off; break;    // big -> small
                 case COLL_BROADCAST: in[li] = s0 + off; out[li] = s0 + off; break;           // in place, as the API has it
                 default: in[li] = s0 + off; out[li] = s0 + small_bytes + off; break;         // AllReduce, Barrier
             }
@@ -146,11 +146,15 @@ HcclResult Communicator::calibrate(void *stream)
         {COLL_ALLGATHER, {ALGO_MESH, ALGO_PAIRWISE, ALGO_RING, ALGO_NVLS, ALGO_MESH_PIPE}},
         {COLL_REDUCE_SCATTER, {ALGO_MESH, ALGO_RING, ALGO_NVLS, ALGO_MESH_PIPE, ALGO_NVLS_PIPE}},
         {COLL_BROADCAST, {ALGO_STAR, ALGO_RING, ALGO_TREE, ALGO_NVLS, ALGO_MESH_PIPE, ALGO_NVLS_PIPE}},
+        {COLL_REDUCE, {ALGO_STAR, ALGO_RING, ALGO_TREE, ALGO_RHD}},
+        {COLL_SCATTER, {ALGO_STAR, ALGO_RING}},
+        {COLL_GATHER, {ALGO_STAR, ALGO_RING}},
     };
     std::vector<double> mine;
     std::vector<std::vector<uint64_t>> ladders;
     for (auto &cd : cands) {
-        const uint64_t top = cd.coll == COLL_ALLGATHER || cd.coll == COLL_REDUCE_SCATTER ? max_blk : max_ar;
+        const bool blocked = cd.coll == COLL_ALLGATHER || cd.coll == COLL_REDUCE_SCATTER || cd.coll == COLL_SCATTER || cd.coll == COLL_GATHER;
+        const uint64_t top = blocked ? max_blk : max_ar;
         std::vector<uint64_t> sizes;
         for (uint64_t sz = 16u << 10; sz <= top; sz *= 4) sizes.push_back(sz);
         if (sizes.empty() || sizes.back() != top) sizes.push_back(top);

@@ -3,7 +3,7 @@
 #include "algo/plan.h"
 namespace hcclb {
 constexpr int kLlThreads = 256;
-constexpr uint64_t kLlMaxPayload = 1u << 20;          // largest message the LL path takes (bytes)
+constexpr uint64_t kLlMaxPayload = 2u << 20;          // largest message the LL path takes (bytes); mailboxes cost 4 x ranks x this per rank
 constexpr uint64_t kLlSlotBytes = 2 * kLlMaxPayload;  // 16-byte lines carry 8 payload bytes
 struct LlArgs {
     uint8_t *ll[kMaxRanks];   // mailbox region of rank q mapped into this rank's address space

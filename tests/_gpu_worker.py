@@ -306,8 +306,11 @@ def scenario_retry_exhausted(c, p, r, args):
     out = torch.zeros(n, device="cuda")
     c.all_reduce(x, out, algo=L.ALGO_MESH)
     assert c.sync() == 0
-    c.all_reduce(x, out, algo=L.ALGO_MESH)      # op 2: stalled on rank 1, and again on each retry
-    rc = c.sync()
+    try:
+        c.all_reduce(x, out, algo=L.ALGO_MESH)  # op 2: stalled on rank 1, and again on each retry
+        rc = c.sync()                           # the rank whose kernels gave up learns it here ...
+    except H.HcclError as e:
+        rc = e.code                             # ... the stalled rank joined the retry rounds from inside the call
     assert rc in (L.E_TIMEOUT, L.E_REMOTE), rc
     assert c.stats()["retries"] == 3, c.stats()
     c.resume()
