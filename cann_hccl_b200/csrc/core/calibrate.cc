@@ -156,7 +156,8 @@ HcclResult Communicator::calibrate(void *stream)
         const bool blocked = cd.coll == COLL_ALLGATHER || cd.coll == COLL_REDUCE_SCATTER || cd.coll == COLL_SCATTER || cd.coll == COLL_GATHER;
         const uint64_t top = blocked ? max_blk : max_ar;
         std::vector<uint64_t> sizes;
-        for (uint64_t sz = 16u << 10; sz <= top; sz *= 4) sizes.push_back(sz);
+        // steps of 4x, of 2x between 256 KiB and 16 MiB where the algorithms cross over
+        for (uint64_t sz = 16u << 10; sz <= top; sz *= (sz >= (256u << 10) && sz < (16u << 20) ? 2 : 4)) sizes.push_back(sz);
         if (sizes.empty() || sizes.back() != top) sizes.push_back(top);
         ladders.push_back(sizes);
         for (uint64_t sz : sizes) {
@@ -166,7 +167,7 @@ HcclResult Communicator::calibrate(void *stream)
                 const bool is_nvls = a == ALGO_NVLS || a == ALGO_NVLS_ONESHOT || a == ALGO_NVLS_PIPE;
                 const bool is_pipe = a == ALGO_MESH_PIPE || a == ALGO_NVLS_PIPE;
                 bool skip = !listed || (is_nvls && !nvls_);
-                skip = skip || (a == ALGO_LL && (!ll_ok_ || sz > kLlMaxPayload));
+                skip = skip || (a == ALGO_LL && (!ll_ok_ || sz > ll_max_bytes()));
                 skip = skip || (is_pipe && sz < (1u << 20));                                                   // three stages of hand-offs cost tens of microseconds
                 skip = skip || ((a == ALGO_MESH_ONESHOT || a == ALGO_NVLS_ONESHOT) && sz > (8u << 20) && p > 2);  // (p-1) times the bytes
                 skip = skip || ((a == ALGO_RING || a == ALGO_TREE) && sz < (256u << 10) && cd.coll != COLL_BROADCAST);

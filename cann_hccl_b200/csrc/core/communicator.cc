@@ -447,7 +447,7 @@ Selection Communicator::select(int coll, uint64_t count, int dtype, int redop) c
     si.expansion_mode = settings_.expansion_mode ? settings_.expansion_mode : env.expansion_mode;
     si.max_channels = si.device ? (nranks_ == 1 ? 128 : 64) : 2;  // a single rank never waits: all SMs may copy
     si.forced = forced_algo_for(env, coll);
-    si.ll_max_bytes = ll_ok_ ? kLlMaxPayload : 0;
+    si.ll_max_bytes = ll_ok_ ? ll_max_bytes() : 0;
     Selection s = select_algo(si, model_);
     const int table_coll = coll == COLL_ALLGATHER_V ? COLL_ALLGATHER : (coll == COLL_REDUCE_SCATTER_V ? COLL_REDUCE_SCATTER : coll);
     auto tt = tuned_.find(table_coll);
@@ -714,7 +714,7 @@ HcclResult Communicator::run_collective_once(const OpRequest &rq)
     if (is_a2av) CHK_RET(a2av_check(rq));
     CHK_RET(consistency_check(rq, sel.algo, use_zc ? ((uint64_t)zc[0].hin << 48) ^ zc[0].oin : 0, use_zc ? ((uint64_t)zc[0].hout << 48) ^ zc[0].oout : 0));
     if (sel.algo == ALGO_LL) {
-        bool fits = rq.coll == COLL_ALLREDUCE && ll_ok_ && rq.count * es <= kLlMaxPayload;
+        bool fits = rq.coll == COLL_ALLREDUCE && ll_ok_ && rq.count * es <= ll_max_bytes();
         for (int li = 0; li < nl && fits; ++li) fits = (((uintptr_t)rq.in[li] | (uintptr_t)rq.out[li]) & 7) == 0;
         if (fits) {
             HcclResult lrc = run_ll_allreduce(rq);
@@ -952,9 +952,17 @@ HcclResult Communicator::run_a2av(const OpRequest &rq)
     return rc;
 }
 
+uint64_t Communicator::ll_max_bytes() const
+{
+    return nranks_ >= 3 ? std::max<uint64_t>(kLlMaxPayload, ll_two_shot_max(nranks_)) : kLlMaxPayload;
+}
+
 HcclResult Communicator::run_ll_allreduce(const OpRequest &rq)
 {
     int nl = nlocal();
+    // two-shot from three ranks on once the message is large enough for the saved link bytes to pay for the second hop
+    const uint64_t bytes = rq.count * (uint64_t)dtype_size(rq.dtype);
+    const bool two_shot = nranks_ >= 3 && bytes >= ll_two_shot_min_ && bytes <= ll_two_shot_max(nranks_);
     ++ll_seq_;
     uint32_t tag = (uint32_t)(ll_seq_ & 0xffffffffu);
     if (tag == 0) { ++ll_seq_; tag = 1; }
@@ -976,6 +984,7 @@ HcclResult Communicator::run_ll_allreduce(const OpRequest &rq)
         a.nranks = nranks_;
         a.tag = tag;
         a.parity = (uint32_t)(ll_seq_ & 1);
+        a.two_shot = two_shot ? 1u : 0u;
         // the LL path does not consume a plan sequence number: its op-execution id lives in a range of its own
         a.exit_counter = ctx_[li].exit_counter;
         a.dev_tail = ctx_[li].dev_tail;

@@ -236,6 +236,8 @@ private:
     uint64_t p2p_slot_ = 0;
     uint64_t ll_seq_ = 0;                  // number of LL operations issued (tag and mailbox parity)
     bool ll_ok_ = false;
+    uint64_t ll_two_shot_min_ = 256u << 10;  // from this size on the LL path of three and more ranks goes two-shot
+    uint64_t ll_max_bytes() const;            // largest message the LL path takes on this communicator
 
     std::mutex op_mu_;
     std::atomic<int> state_{CS_IDLE};

@@ -6,6 +6,12 @@
 // (algorithm/base/alg_aiv_template/aiv_all_reduce_910b_smalldata.h: one-shot, <= 64 KB); there the flag is a
 // separate 32-byte word and the wait is unbounded, here the flag travels with the data and every poll is bounded.
 //
+// Two-shot form for three and more ranks and messages of a few MiB (the reference's mid-data class,
+// alg_aiv_template/aiv_all_reduce_910b_middata.h): a rank pushes slice q of its input to rank q only, reduces its own slice
+// from the p - 1 lines it polls, stores the result and pushes it, again as tagged lines, to every peer, and collects the
+// other slices the same way.  Each byte crosses a link about 4 (p - 1) / p times instead of 2 (p - 1) times, still with no
+// fence and no separate flag hop.
+//
 // Mailboxes are double buffered by the parity of the LL operation count: a rank can only start LL operation k+2 after
 // it has received every peer's lines of k+1, which those peers sent after they finished reading k.
 #include <cuda_bf16.h>
@@ -145,8 +151,139 @@ __global__ void __launch_bounds__(kLlThreads) ar_ll_kernel(const LlArgsArray arg
     }
 }
 
-template <class T> const void *ll_kernel_of(int op)
+// Polls one line until both tags match; false when the wait was given up (the first failure of the rank is recorded).
+__device__ __forceinline__ bool ll_poll(const LlArgs &a, const uint8_t *src, uint64_t deadline, int peer, uint4 &l)
 {
+    l = ld_line(src);
+    for (uint32_t it = 0; l.y != a.tag || l.w != a.tag; ++it) {
+        if ((it & 255) == 255) {
+            int code = 0;
+            if (global_timer_ns() > deadline) code = HCCL_E_TIMEOUT;
+            else if (*(volatile uint32_t *)a.local_fail) code = (int)*(volatile uint32_t *)a.local_fail;
+            else if ((it & 8191) == 8191 && *a.abort) code = *a.abort == 2 ? HCCL_E_REMOTE : HCCL_E_SUSPENDING;
+            if (code) {
+                if (atomicCAS(a.local_fail, 0u, (uint32_t)code) == 0u) {
+                    DevStatus *s = a.status;
+                    s->step = 0; s->peer = peer; s->chan = blockIdx.x; s->expected = a.tag; s->seen = l.y; s->seq = a.seq;
+                    __threadfence_system();
+                    *(volatile uint32_t *)&s->code = (uint32_t)code;
+                }
+                return false;
+            }
+        }
+        l = ld_line(src);
+    }
+    return true;
+}
+
+// Two-shot: the mailbox half of a parity holds area A (slices pushed to their owner, one piece per source rank) followed by
+// area B (reduced slices pushed by their owner, one piece per owner); a piece is piece_bytes long.
+template <class T, int OP>
+__global__ void __launch_bounds__(kLlThreads) ar_ll2_kernel(const LlArgsArray args)
+{
+    const LlArgs &a = args.a[blockIdx.y];
+    using N = LNum<T>;
+    using Acc = typename N::Acc;
+    constexpr int E = 8 / sizeof(T);
+    const int me = a.rank, p = a.nranks;
+    const uint64_t nlines = (a.count + E - 1) / E;
+    const uint64_t ls = (nlines + p - 1) / p;  // lines per slice
+    const uint64_t half = (uint64_t)p * a.slot_bytes, piece = half / 2 / p;
+    const uint64_t base_a = (uint64_t)a.parity * half, base_b = base_a + half / 2;
+    const uint64_t deadline = global_timer_ns() + a.timeout_ns;
+    const T *in = (const T *)a.in;
+    T *out = (T *)a.out;
+    const uint64_t first = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (uint64_t)gridDim.x * blockDim.x;
+    auto load_mine = [&](uint64_t line) {
+        Pay8<T> mine;
+        const uint64_t e0 = line * E;
+        if (e0 + E <= a.count) mine.u = *(const uint2 *)(in + e0);
+        else {
+            mine.u = make_uint2(0, 0);
+            for (int k = 0; k < E; ++k)
+                if (e0 + k < a.count) mine.e[k] = in[e0 + k];
+        }
+        return mine;
+    };
+    auto store_out = [&](uint64_t line, Pay8<T> r) {
+        const uint64_t e0 = line * E;
+        if (e0 + E <= a.count) *(uint2 *)(out + e0) = r.u;
+        else
+            for (int k = 0; k < E; ++k)
+                if (e0 + k < a.count) out[e0 + k] = r.e[k];
+    };
+    const uint64_t my_lo = ls * me < nlines ? ls * me : nlines, my_hi = my_lo + ls < nlines ? my_lo + ls : nlines;
+    // phase 1: every line outside my slice goes to its owner's area A, piece `me`
+    for (uint64_t line = first; line < nlines; line += stride) {
+        const int q = (int)(line / ls);
+        if (q == me) continue;
+        Pay8<T> mine = load_mine(line);
+        st_line(a.ll[q] + base_a + (uint64_t)me * piece + (line - (uint64_t)q * ls) * 16, mine.u.x, mine.u.y, a.tag);
+    }
+    // phase 2: reduce my slice in rank order, store it and push it to every peer's area B, piece `me`
+    bool failed = false;
+    for (uint64_t line = my_lo + first; line < my_hi && !failed; line += stride) {
+        const uint64_t jj = line - my_lo;
+        Pay8<T> mine = load_mine(line);
+        Acc acc[E];
+        for (int q = 0; q < p && !failed; ++q) {
+            Pay8<T> v;
+            if (q == me) v = mine;
+            else {
+                uint4 l;
+                if (!ll_poll(a, a.ll[me] + base_a + (uint64_t)q * piece + jj * 16, deadline, q, l)) { failed = true; break; }
+                v.u = make_uint2(l.x, l.z);
+            }
+            if (q == 0) {
+#pragma unroll
+                for (int k = 0; k < E; ++k) acc[k] = N::up(v.e[k]);
+            } else {
+#pragma unroll
+                for (int k = 0; k < E; ++k) acc[k] = ll_op<OP>(acc[k], N::up(v.e[k]));
+            }
+        }
+        if (failed) break;
+        Pay8<T> r;
+#pragma unroll
+        for (int k = 0; k < E; ++k) r.e[k] = N::down(acc[k]);
+        store_out(line, r);
+        for (int i = 1; i < p; ++i) {
+            int q = me + i;
+            if (q >= p) q -= p;
+            st_line(a.ll[q] + base_b + (uint64_t)me * piece + jj * 16, r.u.x, r.u.y, a.tag);
+        }
+    }
+    // phase 3: the other slices arrive reduced in area B
+    for (uint64_t line = first; line < nlines && !failed; line += stride) {
+        const int q = (int)(line / ls);
+        if (q == me) continue;
+        uint4 l;
+        if (!ll_poll(a, a.ll[me] + base_b + (uint64_t)q * piece + (line - (uint64_t)q * ls) * 16, deadline, q, l)) { failed = true; break; }
+        Pay8<T> r;
+        r.u = make_uint2(l.x, l.z);
+        store_out(line, r);
+    }
+    if (failed) return;  // head stays ahead of tail: the heartbeat reports the op as stuck / failed
+    __syncthreads();
+    if (threadIdx.x == 0 && a.exit_counter) {
+        __threadfence();
+        if (atomicAdd(a.exit_counter, 1u) == gridDim.x - 1) {
+            *a.exit_counter = 0;
+            *a.dev_tail = a.exe_id;
+        }
+    }
+}
+
+template <class T> const void *ll_kernel_of(int op, bool two_shot)
+{
+    if (two_shot) {
+        switch (op) {
+            case HCCL_REDUCE_SUM: return (const void *)ar_ll2_kernel<T, HCCL_REDUCE_SUM>;
+            case HCCL_REDUCE_PROD: return (const void *)ar_ll2_kernel<T, HCCL_REDUCE_PROD>;
+            case HCCL_REDUCE_MAX: return (const void *)ar_ll2_kernel<T, HCCL_REDUCE_MAX>;
+            default: return (const void *)ar_ll2_kernel<T, HCCL_REDUCE_MIN>;
+        }
+    }
     switch (op) {
         case HCCL_REDUCE_SUM: return (const void *)ar_ll_kernel<T, HCCL_REDUCE_SUM>;
         case HCCL_REDUCE_PROD: return (const void *)ar_ll_kernel<T, HCCL_REDUCE_PROD>;
@@ -160,19 +297,20 @@ template <class T> const void *ll_kernel_of(int op)
 HcclResult launch_ar_ll(const LlArgs *args, int nlocal, int dtype, int op, void *stream)
 {
     const void *fn = nullptr;
+    const bool two = args[0].two_shot != 0;
     switch (dtype) {
-        case HCCL_DATA_TYPE_INT8: fn = ll_kernel_of<int8_t>(op); break;
-        case HCCL_DATA_TYPE_UINT8: fn = ll_kernel_of<uint8_t>(op); break;
-        case HCCL_DATA_TYPE_INT16: fn = ll_kernel_of<int16_t>(op); break;
-        case HCCL_DATA_TYPE_UINT16: fn = ll_kernel_of<uint16_t>(op); break;
-        case HCCL_DATA_TYPE_INT32: fn = ll_kernel_of<int32_t>(op); break;
-        case HCCL_DATA_TYPE_UINT32: fn = ll_kernel_of<uint32_t>(op); break;
-        case HCCL_DATA_TYPE_INT64: fn = ll_kernel_of<long long>(op); break;
-        case HCCL_DATA_TYPE_UINT64: fn = ll_kernel_of<unsigned long long>(op); break;
-        case HCCL_DATA_TYPE_FP32: fn = ll_kernel_of<float>(op); break;
-        case HCCL_DATA_TYPE_FP64: fn = ll_kernel_of<double>(op); break;
-        case HCCL_DATA_TYPE_FP16: fn = ll_kernel_of<__half>(op); break;
-        case HCCL_DATA_TYPE_BFP16: fn = ll_kernel_of<__nv_bfloat16>(op); break;
+        case HCCL_DATA_TYPE_INT8: fn = ll_kernel_of<int8_t>(op, two); break;
+        case HCCL_DATA_TYPE_UINT8: fn = ll_kernel_of<uint8_t>(op, two); break;
+        case HCCL_DATA_TYPE_INT16: fn = ll_kernel_of<int16_t>(op, two); break;
+        case HCCL_DATA_TYPE_UINT16: fn = ll_kernel_of<uint16_t>(op, two); break;
+        case HCCL_DATA_TYPE_INT32: fn = ll_kernel_of<int32_t>(op, two); break;
+        case HCCL_DATA_TYPE_UINT32: fn = ll_kernel_of<uint32_t>(op, two); break;
+        case HCCL_DATA_TYPE_INT64: fn = ll_kernel_of<long long>(op, two); break;
+        case HCCL_DATA_TYPE_UINT64: fn = ll_kernel_of<unsigned long long>(op, two); break;
+        case HCCL_DATA_TYPE_FP32: fn = ll_kernel_of<float>(op, two); break;
+        case HCCL_DATA_TYPE_FP64: fn = ll_kernel_of<double>(op, two); break;
+        case HCCL_DATA_TYPE_FP16: fn = ll_kernel_of<__half>(op, two); break;
+        case HCCL_DATA_TYPE_BFP16: fn = ll_kernel_of<__nv_bfloat16>(op, two); break;
         default: return HCCL_E_NOT_SUPPORT;
     }
     if (nlocal < 1 || nlocal > kMaxRanks) return HCCL_E_PARA;
@@ -181,7 +319,7 @@ HcclResult launch_ar_ll(const LlArgs *args, int nlocal, int dtype, int op, void 
     int es = dtype_size(dtype);
     uint64_t nlines = (args[0].count * es + 7) / 8;
     unsigned ctas = (unsigned)((nlines + kLlThreads - 1) / kLlThreads);
-    unsigned cap = nlocal > 1 ? (unsigned)(128 / nlocal) : 96u;
+    unsigned cap = nlocal > 1 ? (unsigned)(128 / nlocal) : (two ? 128u : 96u);
     if (ctas > cap) ctas = cap;
     if (ctas < 1) ctas = 1;
     dim3 grid(ctas, (unsigned)nlocal), block(kLlThreads);

@@ -5,6 +5,9 @@ namespace hcclb {
 constexpr int kLlThreads = 256;
 constexpr uint64_t kLlMaxPayload = 2u << 20;          // largest message the LL path takes (bytes); mailboxes cost 4 x ranks x this per rank
 constexpr uint64_t kLlSlotBytes = 2 * kLlMaxPayload;  // 16-byte lines carry 8 payload bytes
+// Largest message of the two-shot form: its two areas of p pieces share the mailbox half of p slots, a piece carries 1/p of
+// the message at 50 % payload.
+HCCLB_HD uint64_t ll_two_shot_max(int p) { return (uint64_t)p * kLlSlotBytes / 4 / 16 * 16; }
 struct LlArgs {
     uint8_t *ll[kMaxRanks];   // mailbox region of rank q mapped into this rank's address space
     const void *in;
@@ -21,6 +24,7 @@ struct LlArgs {
     uint64_t exe_id;          // value the host wrote into the status block's head when it launched the op
     int32_t rank, nranks;
     uint32_t tag, parity;
+    uint32_t two_shot, pad;   // 1: slices go to their owners, reduced slices come back (three ranks and more)
 };
 struct LlArgsArray {
     LlArgs a[kMaxRanks];

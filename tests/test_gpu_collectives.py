@@ -106,6 +106,25 @@ def test_allreduce_low_latency_protocol(comms, p, dtype, op):
     assert c.stats()["algos"].get("ll", 0) >= 12
 
 
+@pytest.mark.parametrize("p", [3, 4, 8])
+@pytest.mark.parametrize("dtype,op", [(torch.float32, L.SUM), (torch.bfloat16, L.MAX), (torch.int32, L.MIN), (torch.float64, L.PROD)])
+def test_allreduce_low_latency_two_shot(comms, p, dtype, op):
+    """From 256 KiB on, three and more ranks run the LL protocol two-shot: slices to their owners, reduced slices back."""
+    c = comms(p)
+    for n in (70_001, 262_144, (p << 20) // dtype.itemsize):   # odd tail; even; the largest message the mailboxes take
+        if n * dtype.itemsize < (256 << 10):
+            n = (300 << 10) // dtype.itemsize + 3
+        ins = rnd(p, n, dtype, seed=n % 61)
+        outs = [torch.zeros(n, device="cuda", dtype=dtype) for _ in range(p)]
+        for _ in range(3):  # repeated calls alternate the mailbox parity
+            c.all_reduce(ins, outs, op=op, algo=L.ALGO_LL)
+        ok(c)
+        assert c.trace()[-1]["algo"] == "ll"
+        ref = ref_reduce(ins, op)
+        for o in outs:
+            close(o, ref, dtype, p)
+
+
 PIPE_SIZES = (5, 70_001, 3_000_000)  # part of a chunk; one chunk; twelve chunks through a four-slot ring (4 MB staging halves)
 
 
