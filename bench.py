@@ -12,7 +12,8 @@ launching stream; the time is the max over ranks.  The K-step block is repeated 
 timed, and the median block is reported (so that the clock samples cover a loaded GPU).  The NCCL baseline is
 ncclAllReduce issued by the same kind of loop on the same buffers.  Successive steps rotate through buffer sets whose
 total size exceeds the 126 MB L2, so no step finds its input in cache.  The JSON line also carries:
-  sweep            AllReduce 8 KiB .. 1 GiB, sum fp32 with every algorithm forced next to `auto` and NCCL
+  sweep            AllReduce 8 KiB .. 1 GiB, sum fp32 with every algorithm forced next to `auto` and NCCL; from 1 MiB on also
+                   both libraries on registered memory (this library's symmetric pool, NCCL's registered pool)
   sweep_variants   the same sizes for max / bf16 (auto and NCCL)
   extras           the other collectives' sweeps, the fused tensor-parallel kernels and the MoE exchange (bench_extras.py)
   e2e              pinned host -> device copy of the input, the collective, device -> host copy of the result, every step,
@@ -44,26 +45,57 @@ UNAVAILABLE = ("yzh1703456/cann-hccl needs the CANN toolkit, Ascend NPUs and the
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs (queries only)."""
+    """Samples SM clocks and throttle reasons of one GPU while the timed region runs.  Queries only: through the management
+    library's Python binding (a sample takes well under a millisecond), or nvidia-smi when the binding is missing."""
+
+    REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4))
 
     def __init__(self, index):
         self.index = index
-        self.rows = []
+        self.sm, self.mx, self.reasons = [], [], set()
         self._stop = threading.Event()
         self._th = None
+        self._nv = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = int(visible.split(",")[index]) if visible and visible.split(",")[index].strip().isdigit() else index
+            self._nv = (pynvml, pynvml.nvmlDeviceGetHandleByIndex(phys))
+        except Exception:
+            self._nv = None
+
+    def _sample_nvml(self):
+        nv, h = self._nv
+        self.sm.append(float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)))
+        self.mx.append(float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)))
+        bits = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(h))
+        for name, bit in self.REASONS:
+            if bits & bit:
+                self.reasons.add(name)
+
+    def _sample_smi(self):
+        q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
+            "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+        out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + q, "--format=csv,noheader,nounits"],
+                             capture_output=True, text=True, timeout=5).stdout.strip()
+        r = [c.strip() for c in out.splitlines()[0].split(",")]
+        self.sm.append(float(r[0]))
+        self.mx.append(float(r[1]))
+        for i, (name, _) in enumerate(self.REASONS):
+            if r[2 + i].lower().startswith("active"):
+                self.reasons.add(name)
 
     def _run(self):
-        q = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
-            "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
         while not self._stop.is_set():
             try:
-                out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + q, "--format=csv,noheader,nounits"],
-                                     capture_output=True, text=True, timeout=5).stdout.strip()
-                if out:
-                    self.rows.append([c.strip() for c in out.splitlines()[0].split(",")])
+                if self._nv:
+                    self._sample_nvml()
+                else:
+                    self._sample_smi()
             except Exception:
                 pass
-            self._stop.wait(0.05)
+            self._stop.wait(0.02)
 
     def start(self):
         self._th = threading.Thread(target=self._run, daemon=True)
@@ -73,20 +105,9 @@ class ClockSampler:
         self._stop.set()
         if self._th:
             self._th.join(timeout=6)
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
-            try:
-                sm.append(float(r[0]))
-                mx.append(float(r[1]))
-                for i, n in enumerate(names):
-                    if r[3 + i].lower().startswith("active"):
-                        reasons.add(n)
-            except Exception:
-                pass
-        sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
-                "samples": len(sm)}
+        sm = sorted(self.sm)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(self.mx) if self.mx else None, "reasons": sorted(self.reasons),
+                "samples": len(sm), "source": "nvml" if self._nv else "nvidia-smi"}
 
 
 def setup_dist(args):
@@ -321,10 +342,35 @@ def main():
     e2e_nccl_ms = e2e_rate(torch, e2e_step_nccl, e2e_steps, sync, max_over_ranks) if dist is not None else None
 
     # ---------------------------------------------------------------- hccl_test-shaped AllReduce sweeps
-    def sweep_rows(dtype_t, dtype_h, op_h, op_nccl, forced):
+    def sweep_rows(dtype_t, dtype_h, op_h, op_nccl, forced, registered=False):
         rows = []
         es = dtype_t.itemsize
         top = max(args.sweep_max, 8 << 10)
+        # registered-memory columns: this library on tensors of its symmetric pool (ordinary torch tensors that the peers map:
+        # zero-copy), and NCCL on tensors of its own registered pool (ncclMemAlloc + window registration through torch)
+        z_in = z_out = nz = None
+        if registered and comm.has_nvls():
+            try:
+                zpool = comm.symmetric_pool()
+                with torch.cuda.use_mem_pool(zpool):
+                    z_in = torch.empty(top // es, device="cuda", dtype=dtype_t)
+                    z_out = torch.empty(top // es, device="cuda", dtype=dtype_t)
+                z_in.uniform_(-1, 1)
+            except Exception as e:
+                z_in = z_out = None
+                if rank == 0:
+                    print("symmetric pool unavailable: %r" % (e,), file=sys.stderr)
+            try:
+                backend = dist.distributed_c10d._get_default_group()._get_backend(torch.device("cuda"))
+                npool = torch.cuda.MemPool(backend.mem_allocator)
+                with torch.cuda.use_mem_pool(npool):
+                    nz = torch.empty(top // es, device="cuda", dtype=dtype_t)
+                backend.register_mem_pool(npool)
+                nz.uniform_(-1, 1)
+            except Exception as e:
+                nz = None
+                if rank == 0:
+                    print("NCCL registered pool unavailable: %r" % (e,), file=sys.stderr)
         cap_elems = min(2 * top, 2 << 30) // es               # up to 2 GiB per buffer: small messages rotate through windows
         sw_in = torch.empty(cap_elems, device="cuda", dtype=dtype_t)
         sw_in.uniform_(-1, 1)
@@ -377,6 +423,21 @@ def main():
                 row["nccl_time_us"] = round(t_n * 1e3, 2)
                 row["nccl_alg_bandwidth_GBps"] = round(size / t_n / 1e6, 2)
                 row["vs_nccl"] = round(t_n / t_auto, 3)
+            if size >= (1 << 20):
+                zwin = max(1, min(8, top // size))
+                if z_in is not None:
+                    t_z = t_of(lambda k: comm.repeat(L.ALLREDUCE, z_in, z_out, cnt, dtype_h, k, size, zwin, op=op_h))
+                    row["registered_us"] = round(t_z * 1e3, 2)
+                    row["registered_algo"] = comm.trace()[-1]["algo"]
+                if nz is not None:
+                    def nccl_reg(k):
+                        for i in range(k):
+                            o = (i % zwin) * cnt
+                            dist.all_reduce(nz[o:o + cnt], op=op_nccl)
+                    t_nz = t_of(nccl_reg)
+                    row["nccl_registered_us"] = round(t_nz * 1e3, 2)
+                    if z_in is not None:
+                        row["registered_vs_nccl_registered"] = round(t_nz / t_z, 3)
             rows.append(row)
             size *= 2
         assert comm.sync() == 0, comm.describe_status()
@@ -392,14 +453,27 @@ def main():
             dist.all_reduce(refv, op=op_nccl)
             tol = 1e-5 * world if dtype_t == torch.float32 else 2e-2 * world
             ok = all_ok(bool(torch.allclose(y.float(), refv.float(), rtol=tol, atol=tol)))
-        del sw_in, sw_out
+        if z_in is not None:
+            # check_result of the zero-copy path at 4 MiB
+            cnt = (4 << 20) // es
+            x = z_in[:cnt].clone()
+            refv = x.clone()
+            dist.all_reduce(refv, op=op_nccl)
+            z_in[:cnt].copy_(x)
+            comm.all_reduce(z_in[:cnt], z_out[:cnt], op=op_h)
+            assert comm.sync() == 0, comm.describe_status()
+            tol = 1e-5 * world if dtype_t == torch.float32 else 2e-2 * world
+            ok = ok and all_ok(bool(torch.allclose(z_out[:cnt].float(), refv.float(), rtol=tol, atol=tol)))
+            del z_in, z_out, x, refv
+            comm.release_symmetric_pool()
+        del sw_in, sw_out, nz
         torch.cuda.empty_cache()
         return rows, ok
 
     sweep, variants = [], {}
     if not args.no_sweep and world > 1:
         forced = ["ll", "mesh_oneshot", "mesh", "ring", "rhd", "nvls_oneshot", "nvls", "mesh_pipe", "nvls_pipe"]
-        sweep, ok = sweep_rows(torch.float32, L.FP32, L.SUM, dist.ReduceOp.SUM, forced)
+        sweep, ok = sweep_rows(torch.float32, L.FP32, L.SUM, dist.ReduceOp.SUM, forced, registered=True)
         if not ok:
             failures.append("sweep sum fp32 check_result")
         for name, dt, hd_, oph, opn in (("max_fp32", torch.float32, L.FP32, L.MAX, dist.ReduceOp.MAX),

@@ -24,9 +24,9 @@ DTYPE_SIZE = {INT8: 1, INT16: 2, INT32: 4, FP16: 2, FP32: 4, INT64: 8, UINT64: 8
 (ALLREDUCE, BROADCAST, REDUCE_SCATTER, REDUCE_SCATTER_V, SCATTER, ALLGATHER, ALLGATHER_V, BARRIER, ALLTOALL,
  ALLTOALLV, ALLTOALLVC, REDUCE, GATHER) = range(13)
 (ALGO_AUTO, ALGO_MESH, ALGO_MESH_ONESHOT, ALGO_RING, ALGO_RHD, ALGO_PAIRWISE, ALGO_STAR, ALGO_TREE, ALGO_NVLS,
- ALGO_NVLS_ONESHOT, ALGO_SINGLE, ALGO_MESH_PIPE, ALGO_NVLS_PIPE, ALGO_NVLS_ZC, ALGO_LL, ALGO_DIRECT) = range(16)
+ ALGO_NVLS_ONESHOT, ALGO_SINGLE, ALGO_MESH_PIPE, ALGO_NVLS_PIPE, ALGO_NVLS_ZC, ALGO_LL, ALGO_MESH_ZC, ALGO_DIRECT) = range(17)
 ALGO_NAMES = ["auto", "mesh", "mesh_oneshot", "ring", "rhd", "pairwise", "star", "tree", "nvls", "nvls_oneshot", "single",
-              "mesh_pipe", "nvls_pipe", "nvls_zerocopy", "ll", "direct"]
+              "mesh_pipe", "nvls_pipe", "nvls_zerocopy", "ll", "mesh_zerocopy", "direct"]
 
 
 class RootInfo(C.Structure):
@@ -178,6 +178,7 @@ def lib():
         "HcclB200Exchange": [vp, C.c_char_p, vp, C.c_size_t, vp],
         "HcclB200GetDeviceContext": [vp, P(vp), P(u64)],
         "HcclB200ReloadEnv": [],
+        "HcclB200PoolBind": [vp],
         "HcclB200PlanCheck": [i32, i32, u32, u64, C.c_int, u32, u64, i32, C.c_int64, C.c_char_p, C.c_size_t],
         "HcclB200Put": [vp, u32, i32, u32, C.c_size_t, vp, C.c_size_t, vp],
         "HcclB200Get": [vp, u32, i32, u32, C.c_size_t, vp, C.c_size_t, vp],

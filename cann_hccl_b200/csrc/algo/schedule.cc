@@ -15,7 +15,7 @@ const char *coll_name(int c)
 const char *algo_name(int a)
 {
     static const char *n[] = {"auto", "mesh", "mesh_oneshot", "ring", "rhd", "pairwise", "star", "tree", "nvls",
-                              "nvls_oneshot", "single", "mesh_pipe", "nvls_pipe", "nvls_zerocopy", "ll", "direct"};
+                              "nvls_oneshot", "single", "mesh_pipe", "nvls_pipe", "nvls_zerocopy", "ll", "mesh_zerocopy", "direct"};
     return (a >= 0 && a < ALGO_COUNT) ? n[a] : "unknown";
 }
 int algo_from_name(const std::string &s)

@@ -34,6 +34,7 @@ enum AlgoId : int {
     ALGO_NVLS_PIPE,     // same with in-switch reduction (multimem.ld_reduce) and multicast stores
     ALGO_NVLS_ZC,       // AllReduce on registered symmetric buffers: multimem.ld_reduce from the send buffers, multimem.st into the receive buffers, no staging
     ALGO_LL,            // AllReduce, small messages: data and flag travel together in 16-byte lines (device only)
+    ALGO_MESH_ZC,       // AllReduce (two ranks) / ReduceScatter / AllGather on a registered send buffer: peers read it in place (kernels/pipe_coll.*)
     ALGO_DIRECT,        // AlltoAll family: parametric kernel, counts travel as launch arguments (kernels/a2av.cu; device only)
     ALGO_COUNT
 };

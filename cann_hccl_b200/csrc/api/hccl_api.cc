@@ -25,6 +25,18 @@
 using namespace hcclb;
 
 namespace {
+// state of the framework allocator pool (HcclB200PoolBind, hcclb200_torch_malloc / _free)
+std::mutex g_pool_mu;
+Communicator *g_pool_comm = nullptr;
+struct PoolBlock { void *ptr; size_t bytes; int handle; bool in_use; };
+std::vector<PoolBlock> g_pool_blocks;
+void pool_forget(Communicator *c)
+{
+    std::lock_guard<std::mutex> lk(g_pool_mu);
+    if (g_pool_comm != c) return;
+    g_pool_blocks.clear();  // the communicator releases its symmetric memory itself
+    g_pool_comm = nullptr;
+}
 constexpr uint64_t kSysMaxCount = 0x7FFFFFFFFull;  // reference: SYS_MAX_COUNT
 std::mutex g_comm_mu;
 std::set<Communicator *> g_comms;
@@ -346,6 +358,7 @@ HcclResult HcclCommDestroy(HcclComm comm)
     }
     HcclResult rc = c->destroy();
     if (rc == HCCL_E_AGAIN) track(c);
+    else pool_forget(c);
     return rc;
 }
 
@@ -826,6 +839,51 @@ HcclResult HcclB200MemFree(HcclComm comm, int32_t handle)
     GET_COMM("HcclB200MemFree");
     return c->sym_free(handle);
 }
+// ---- allocator hooks for frameworks with pluggable device allocators (torch.cuda.memory.CUDAPluggableAllocator /
+// torch.cuda.MemPool): tensors created inside such a pool live in registered symmetric memory, so collectives on them
+// take the zero-copy paths without any call of this API by the user.  The pool is bound to ONE communicator with one local
+// rank; an allocation is a collective (every rank's allocator has to ask for the same sizes in the same order, which
+// same-program ranks do).  Blocks that the framework returns are kept and handed out again for the same size: releasing
+// symmetric memory is collective as well, and a framework frees at moments of its own choosing; everything is released
+// when the communicator is destroyed or the pool is unbound.
+HcclResult HcclB200PoolBind(HcclComm comm)
+{
+    std::lock_guard<std::mutex> lk(g_pool_mu);
+    if (!comm) {  // unbind: the blocks go back with a collective release each (all ranks unbind together)
+        if (g_pool_comm && as_comm((HcclComm)g_pool_comm))
+            for (auto &b : g_pool_blocks) g_pool_comm->sym_free(b.handle);
+        g_pool_blocks.clear();
+        g_pool_comm = nullptr;
+        return HCCL_SUCCESS;
+    }
+    GET_COMM("HcclB200PoolBind");
+    CHK_RET_LOG(c->nlocal() != 1 || c->transport() != TR_DEVICE, HCCL_E_NOT_SUPPORT, "the allocator pool needs a device communicator with one rank per process");
+    CHK_RET_LOG(g_pool_comm && g_pool_comm != c, HCCL_E_PARA, "the allocator pool is bound to another communicator");
+    g_pool_comm = c;
+    return HCCL_SUCCESS;
+}
+void *hcclb200_torch_malloc(ssize_t size, int device, void *stream)
+{
+    (void)stream;
+    std::lock_guard<std::mutex> lk(g_pool_mu);
+    if (!g_pool_comm || !as_comm((HcclComm)g_pool_comm) || size <= 0 || device != g_pool_comm->device()) return nullptr;
+    const size_t bytes = ((size_t)size + 255) / 256 * 256;
+    for (auto &b : g_pool_blocks)
+        if (!b.in_use && b.bytes == bytes) { b.in_use = true; return b.ptr; }
+    void *ptr = nullptr;
+    int h = 0;
+    if (g_pool_comm->sym_alloc(bytes, &ptr, &h) != HCCL_SUCCESS) return nullptr;
+    g_pool_blocks.push_back(PoolBlock{ptr, bytes, h, true});
+    return ptr;
+}
+void hcclb200_torch_free(void *ptr, ssize_t size, int device, void *stream)
+{
+    (void)size; (void)device; (void)stream;
+    std::lock_guard<std::mutex> lk(g_pool_mu);
+    for (auto &b : g_pool_blocks)
+        if (b.ptr == ptr) { b.in_use = false; return; }
+}
+
 HcclResult HcclB200MemQuery(HcclComm comm, int32_t handle, void **peerPtrs, void **mcPtrs, size_t *bytes)
 {
     GET_COMM("HcclB200MemQuery");

@@ -683,7 +683,9 @@ HcclResult Communicator::run_collective_once(const OpRequest &rq)
     std::vector<ZcInfo> zc(nl);
     bool use_zc = false;
     const bool host_tr = settings_.transport == TR_HOST;  // the host executor emulates the multicast accesses rank by rank
-    if (rq.coll == COLL_ALLREDUCE && p > 1 && (nvls_ || host_tr) && !user_segs_.empty() && (rq.algo == ALGO_AUTO || rq.algo == ALGO_NVLS_ZC) &&
+    // (two ranks: the in-switch reduction gains nothing over reading the one peer directly, which the peer-mapping form below does)
+    if (rq.coll == COLL_ALLREDUCE && (p > 2 || (p == 2 && (rq.algo == ALGO_NVLS_ZC || host_tr))) && (nvls_ || host_tr) && !user_segs_.empty() &&
+        (rq.algo == ALGO_AUTO || rq.algo == ALGO_NVLS_ZC) &&
         (rq.algo == ALGO_NVLS_ZC || rq.count * es >= (512u << 10)) && !deterministic() &&
         nvls_reduce_supported(rq.dtype, rq.redop, rq.count * es) && forced_algo_for(env_config(), rq.coll).empty()) {
         bool mine = true;
@@ -728,6 +730,36 @@ HcclResult Communicator::run_collective_once(const OpRequest &rq)
         sel.algo = ALGO_MESH_ONESHOT;  // unaligned or oversized: the plan executor handles every layout
     }
 
+    // registered send buffer (the same allocation and offset on every rank, by the contract of symmetric memory): two-rank
+    // AllReduce, ReduceScatter and AllGather let the peers read it where it is
+    if (!use_zc && settings_.transport == TR_DEVICE && p > 1 && !user_segs_.empty() && (rq.algo == ALGO_AUTO || rq.algo == ALGO_MESH_ZC) &&
+        ((rq.coll == COLL_ALLREDUCE && p == 2) || rq.coll == COLL_REDUCE_SCATTER || rq.coll == COLL_ALLGATHER) &&
+        (rq.algo == ALGO_MESH_ZC || rq.count * es >= (1u << 20)) && forced_algo_for(env_config(), rq.coll).empty()) {
+        const size_t in_bytes = (size_t)rq.count * es * (rq.coll == COLL_REDUCE_SCATTER ? p : 1);
+        int h0 = 0;
+        size_t o0 = 0;
+        bool mine = true;
+        for (int li = 0; li < nl && mine; ++li) {
+            size_t o = 0;
+            int h = find_user_seg(li, rq.in[li], in_bytes, &o);
+            if (li == 0) { h0 = h; o0 = o; }
+            mine = h != 0 && h == h0 && o == o0 && (o & 15) == 0;
+            // AllReduce in place would overwrite what the peer is still reading: that form stays on the staged paths
+            if (rq.coll == COLL_ALLREDUCE && overlap_kind(rq, li) != 0) mine = false;
+        }
+        if (mine) {
+            CHK_RET(consistency_check(rq, ALGO_MESH_ZC, ((uint64_t)h0 << 48) ^ o0, 0));
+            HcclResult zrc = run_pipe(rq, false, h0, o0);
+            uint64_t zbytes = sel_count * es;
+            stats_.ops[rq.coll]++;
+            stats_.bytes[rq.coll] += zbytes;
+            stats_.algo_hist[ALGO_MESH_ZC]++;
+            record_trace(rq, ALGO_MESH_ZC, 0, zbytes, now_us() - t0);
+            return zrc;
+        }
+        CHK_RET_LOG(rq.algo == ALGO_MESH_ZC, HCCL_E_PARA, "zero-copy needs the send buffer in registered symmetric memory at the same offset on every rank");
+    }
+    CHK_RET_LOG(rq.algo == ALGO_MESH_ZC, HCCL_E_NOT_SUPPORT, "zero-copy over peer mappings exists for two-rank AllReduce, ReduceScatter and AllGather on the device transport");
     if ((is_a2av || rq.coll == COLL_ALLTOALL) && settings_.transport == TR_DEVICE && p > 1 && (rq.algo == ALGO_AUTO || rq.algo == ALGO_DIRECT) &&
         forced_algo_for(env_config(), rq.coll).empty()) {
         HcclResult arc = run_a2av(rq);
@@ -841,11 +873,35 @@ int Communicator::pipe_mode_for(int coll) const
 // time.  (Shorter chunks at both ends of the message, to fill and drain the pipeline sooner, measured slower: the flag
 // hops of the extra chunks cost more than the fill saves.)  Every choice below depends only on facts that all ranks share (sizes, type, operator,
 // environment), never on a rank's own pointers: the kernels take unaligned buffers on slower paths instead.
-HcclResult Communicator::run_pipe(const OpRequest &rq, bool want_mc)
+HcclResult Communicator::run_pipe(const OpRequest &rq, bool want_mc, int zc_handle, size_t zc_off)
 {
     const EnvConfig &env = env_config();
     const int p = nranks_, nl = nlocal(), es = dtype_size(rq.dtype);
     int mode = pipe_mode_for(rq.coll);
+    if (zc_handle) {
+        // the send buffers are registered: one round, no staging; one gate CTA plus as many readers as 64 KiB pieces justify
+        mode = rq.coll == COLL_ALLREDUCE ? PM_AR1_ZC : (rq.coll == COLL_REDUCE_SCATTER ? PM_RS_ZC : PM_AG_ZC);
+        const uint64_t bytes = rq.count * (uint64_t)es * (mode == PM_AG_ZC ? (uint64_t)(p - 1) : 1);
+        const int budget = all_local_ ? std::max(2, 128 / nl) : 128;
+        const int readers = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)budget - 1, bytes / (64u << 10)));
+        std::vector<PipeArgs> zargs(nl);
+        for (int li = 0; li < nl; ++li) {
+            PipeArgs &a = zargs[li];
+            memset(&a, 0, sizeof(a));
+            a.in = (const uint8_t *)rq.in[li];
+            a.out = (uint8_t *)rq.out[li];
+            a.count = rq.count; a.chunk_elems = std::max<uint64_t>(1, rq.count); a.seq = seq_;
+            a.mode = mode; a.dtype = rq.dtype; a.root = rq.root; a.nslots = 1;
+            a.n1 = 1; a.n2 = readers; a.n3 = 0; a.g1 = a.g2 = a.g3 = 1;
+            a.z_in_peer = (const uint8_t *const *)user_peer_tabs_[zc_handle][li];
+            a.z_in_off = zc_off;
+            status_[li]->head = seq_;
+        }
+        stats_.launches++;
+        HcclResult zrc = launch_pipe_coll((const RankCtx *)dev_ctx_, zargs.data(), nl, rq.redop, rq.stream);
+        ++seq_;
+        return zrc;
+    }
     const uint64_t block_bytes = rq.count * (uint64_t)es;
     const bool reducing = rq.coll == COLL_ALLREDUCE || rq.coll == COLL_REDUCE_SCATTER;
     const bool use_mc = want_mc && nvls_ && block_bytes % 16 == 0 && (!reducing || nvls_reduce_supported(rq.dtype, rq.redop, block_bytes)) && !deterministic();

@@ -181,7 +181,7 @@ private:
     HcclResult get_plan(const OpDesc &d, const std::string &key, CachedPlan **out);
     HcclResult run_collective_once(const OpRequest &rq);
     HcclResult run_ll_allreduce(const OpRequest &rq);
-    HcclResult run_pipe(const OpRequest &rq, bool want_mc);
+    HcclResult run_pipe(const OpRequest &rq, bool want_mc, int zc_handle = 0, size_t zc_off = 0);
     HcclResult run_a2av(const OpRequest &rq);
     int pipe_mode_for(int coll) const;  // PipeMode of a collective, -1 when it has no pipelined kernel
     HcclResult tp_workspace(const std::string &key, size_t data_bytes, int M, void **ws_out);

@@ -52,6 +52,7 @@ HcclResult launch_pipe_coll(const RankCtx *dev_ctx, const PipeArgs *args, int nl
     const int nb = bcast ? a0.n1 : a0.n1 + a0.n2 + (three ? a0.n3 : 0);
     if (nb < 1 || nb > kMaxChannels || a0.nslots < 1 || a0.nslots > kPipeMaxSlots || a0.chunk_elems == 0) return HCCL_E_PARA;
     if (a0.n1 < 1 || (!bcast && a0.n2 < 1) || (three && a0.n3 < 1)) return HCCL_E_PARA;
+    if (pipe_mode_is_zc(a0.mode) && !a0.z_in_peer) return HCCL_E_PARA;
     if (a0.g1 < 1 || a0.g2 < 1 || a0.g3 < 1) return HCCL_E_PARA;
     PipeArgsArray arr;
     for (int i = 0; i < nlocal; ++i) arr.a[i] = args[i];

@@ -424,7 +424,60 @@ __global__ void __launch_bounds__(kExecThreads, 1) pipe_coll_kernel(const RankCt
         }
     };
 
-    for (uint64_t ch = (uint64_t)group; ch < nchunks && !s_fail; ch += (uint64_t)ngroup) {
+    if (pipe_mode_is_zc(mode)) {
+        // ---- zero-copy modes: no staging, one round.  Flag words of slot 0 carry the hand-shake.
+        const uint64_t now = base + 1;
+        if (role == 0) {
+            // gate: this rank's send buffer is complete (stream order) and may be read; then hold the kernel, and with it
+            // everything the caller enqueues behind it, until every peer has finished reading
+            if (tid < p && tid != me) st_release_sys(c.flags[tid] + pipe_flag_index(kPipeWordReady, me, 0), now);
+            if (tid < p && tid != me) {
+                uint64_t seen;
+                int rc = wait_flag_ge(c.flags[me] + pipe_flag_index(kPipeWordDone, tid, 0), now, w, seen);
+                if (rc) { report_failure(c, a.seq, rc, 1, tid, b, now, seen); s_fail = rc; }
+            }
+        } else {
+            if (tid < p && tid != me) {
+                uint64_t seen;
+                int rc = wait_flag_ge(c.flags[me] + pipe_flag_index(kPipeWordReady, tid, 0), now, w, seen);
+                if (rc) { report_failure(c, a.seq, rc, 0, tid, b, now, seen); s_fail = rc; }
+            }
+            __syncthreads();
+            if (!s_fail) {
+                uint64_t lo, hi;
+                chan_range(a.count, es, nrole, idx, lo, hi);
+                auto peer_in = [&](int q) { return q == me ? a.in : a.z_in_peer[q] + a.z_in_off; };
+                if (mode == PM_AG_ZC) {
+                    if (tid < p) {
+                        const int q = me + tid < p ? me + tid : me + tid - p;  // segment 0 is my own block
+                        s_src[tid] = peer_in(q) + lo * es;
+                        s_dst[tid] = a.out + ((uint64_t)q * a.count + lo) * es;
+                        s_bytes[tid] = hi > lo && !(q == me && s_dst[tid] == s_src[tid]) ? (hi - lo) * es : 0;
+                    }
+                    __syncthreads();
+                    copy_segments(p);
+                } else {
+                    if (tid < p) s_src[tid] = peer_in(tid) + ((mode == PM_RS_ZC ? (uint64_t)me * a.count : 0) + lo) * es;
+                    if (tid == 0) s_dst[0] = a.out + lo * es;
+                    __syncthreads();
+                    reduce_sources(1, hi > lo ? hi - lo : 0);
+                }
+            }
+            // the last CTA of the stage tells the peers that this rank has finished reading their buffers
+            __syncthreads();
+            if (tid == 0) {
+                __threadfence();
+                uint32_t *cnt = c.pipe_cnt + kPipeMaxSlots;
+                const unsigned prev = nrole > 1 ? atomicAdd(cnt, 1u) : 0u;
+                const int last = prev == (unsigned)(nrole - 1);
+                if (last && nrole > 1) { atomicExch(cnt, 0u); __threadfence(); }
+                s_last = last;
+            }
+            __syncthreads();
+            if (s_last && !s_fail && tid < p && tid != me) st_release_sys(c.flags[tid] + pipe_flag_index(kPipeWordDone, me, 0), now);
+        }
+    }
+    for (uint64_t ch = (uint64_t)group; ch < nchunks && !s_fail && !pipe_mode_is_zc(mode); ch += (uint64_t)ngroup) {
         const int slot = (int)(ch % (uint64_t)K);
         const uint64_t soff = half_off + (uint64_t)slot * slot_bytes;
         const uint64_t e0 = ch * ce;

@@ -26,6 +26,12 @@ enum PipeMode : int32_t {
     PM_AG_PULL,     // AllGather: copy-in of my block | pull the peers' blocks straight into the receive buffer
     PM_BC_MC,       // Broadcast: root multicasts the chunk into every slot | the others copy out
     PM_BC_PUSH,     // Broadcast chain root -> root+1 -> ...: every rank copies its slot out and on into its successor's slot
+    // zero-copy: the send buffer of every rank lies in registered symmetric memory, so the peers read it where it is.  No
+    // staging and no chunks: one gate CTA tells the peers that this rank has entered the op and holds the kernel until
+    // they have finished reading, the other CTAs split the whole message.
+    PM_AR1_ZC,      // AllReduce one-shot: every rank reduces all p send buffers into its receive buffer (two ranks: optimal)
+    PM_RS_ZC,       // ReduceScatter: every rank reduces its block of all p send buffers into its receive buffer
+    PM_AG_ZC,       // AllGather: every rank pulls the peers' send buffers straight into its receive buffer
     PM_COUNT
 };
 
@@ -53,6 +59,8 @@ struct PipeArgs {
     int32_t n1, n2, n3;    // CTAs per stage (two-shot AllReduce uses all three, Broadcast only n1, the other modes the first two)
     int32_t g1, g2, g3;    // groups per stage: group g of G takes the chunks c with c % G == g (CTAs of a stage divisible by G)
     int32_t pad;
+    const uint8_t *const *z_in_peer;  // zero-copy modes: device table of every rank's mapping of the registered allocation that holds `in`
+    uint64_t z_in_off;                // ... and the offset of `in` inside it (the same on every rank)
 };
 struct PipeArgsArray {
     PipeArgs a[kMaxRanks];
@@ -71,6 +79,7 @@ HCCLB_HD uint64_t pipe_slot_bytes(int mode, uint64_t chunk_elems, int es, int p)
 HCCLB_HD bool pipe_mode_is_mc(int mode) { return mode == PM_AR2_MC || mode == PM_AR1_MC || mode == PM_RS_MC || mode == PM_BC_MC; }
 HCCLB_HD bool pipe_mode_is_bcast(int mode) { return mode == PM_BC_MC || mode == PM_BC_PUSH; }
 HCCLB_HD bool pipe_mode_has_copy_out(int mode) { return mode == PM_AR2_MC || mode == PM_AR2_PUSH; }
+HCCLB_HD bool pipe_mode_is_zc(int mode) { return mode == PM_AR1_ZC || mode == PM_RS_ZC || mode == PM_AG_ZC; }
 
 // One launch runs the listed local ranks (more than one: virtual ranks of one GPU).  Always a cooperative launch: the
 // stages of a rank wait on one another, so all CTAs have to be resident together.

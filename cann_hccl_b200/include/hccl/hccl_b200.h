@@ -7,6 +7,7 @@
  */
 #ifndef HCCL_B200_H_
 #define HCCL_B200_H_
+#include <sys/types.h>
 #include "hccl.h"
 #ifdef __cplusplus
 extern "C" {
@@ -18,7 +19,7 @@ enum { HCCL_B200_ALLREDUCE = 0, HCCL_B200_BROADCAST, HCCL_B200_REDUCE_SCATTER, H
        HCCL_B200_ALLTOALLV, HCCL_B200_ALLTOALLVC, HCCL_B200_REDUCE, HCCL_B200_GATHER };
 enum { HCCL_B200_ALGO_AUTO = 0, HCCL_B200_ALGO_MESH, HCCL_B200_ALGO_MESH_ONESHOT, HCCL_B200_ALGO_RING,
        HCCL_B200_ALGO_RHD, HCCL_B200_ALGO_PAIRWISE, HCCL_B200_ALGO_STAR, HCCL_B200_ALGO_TREE, HCCL_B200_ALGO_NVLS,
-       HCCL_B200_ALGO_NVLS_ONESHOT, HCCL_B200_ALGO_SINGLE, HCCL_B200_ALGO_MESH_PIPE, HCCL_B200_ALGO_NVLS_PIPE, HCCL_B200_ALGO_NVLS_ZEROCOPY, HCCL_B200_ALGO_LL, HCCL_B200_ALGO_DIRECT };
+       HCCL_B200_ALGO_NVLS_ONESHOT, HCCL_B200_ALGO_SINGLE, HCCL_B200_ALGO_MESH_PIPE, HCCL_B200_ALGO_NVLS_PIPE, HCCL_B200_ALGO_NVLS_ZEROCOPY, HCCL_B200_ALGO_LL, HCCL_B200_ALGO_MESH_ZEROCOPY, HCCL_B200_ALGO_DIRECT };
 
 typedef struct HcclB200OpDef {
     int32_t coll;       /* HCCL_B200_* collective */
@@ -118,6 +119,14 @@ extern HcclResult HcclB200MemAlloc(HcclComm comm, size_t bytes, void **localPtrs
 extern HcclResult HcclB200MemAdopt(HcclComm comm, void *const *localPtrs, size_t bytes, const uint64_t *drvHandles, size_t handleOffset,
                                    int32_t *handle);
 extern HcclResult HcclB200MemFree(HcclComm comm, int32_t handle);
+/* Allocator hooks for frameworks with pluggable device allocators (torch.cuda.memory.CUDAPluggableAllocator + MemPool):
+ * after HcclB200PoolBind(comm), hcclb200_torch_malloc / hcclb200_torch_free serve the framework's pool from registered
+ * symmetric memory of that communicator, so collectives on tensors of the pool run zero-copy.  Allocation is collective
+ * (same sizes in the same order on every rank); freed blocks are reused, and released when the pool is unbound
+ * (HcclB200PoolBind(NULL), collective) or the communicator is destroyed. */
+extern HcclResult HcclB200PoolBind(HcclComm comm);
+extern void *hcclb200_torch_malloc(ssize_t size, int device, void *stream);
+extern void hcclb200_torch_free(void *ptr, ssize_t size, int device, void *stream);
 /* peerPtrs[local * nRanks + q] = rank q's copy as mapped for the local rank; mcPtrs[local] = multicast mapping or NULL. */
 extern HcclResult HcclB200MemQuery(HcclComm comm, int32_t handle, void **peerPtrs, void **mcPtrs, size_t *bytes);
 /* One-sided transfers on symmetric memory (role of the reference's one_sided_service interface,

@@ -351,6 +351,26 @@ class Communicator:
                 bufs.append(np.frombuffer(raw, dtype=dtype, count=numel))
         return handle, bufs
 
+    def symmetric_pool(self):
+        """A torch.cuda.MemPool whose blocks are registered symmetric memory of this communicator.  Tensors created under
+        `with torch.cuda.use_mem_pool(pool):` are ordinary torch tensors, and collectives on them take the zero-copy paths
+        (peers read and write them in place, no staging copy) without further calls.  Every rank has to create its tensors
+        in the same order and with the same sizes inside the pool (allocation is collective).  One pool per process; call
+        release_symmetric_pool() on every rank (or destroy the communicator) to give the memory back."""
+        import torch
+        L.check(L.lib().HcclB200PoolBind(self._h), "HcclB200PoolBind")
+        if getattr(self, "_pool", None) is None:
+            alloc = torch.cuda.memory.CUDAPluggableAllocator(L.LIB_PATH, "hcclb200_torch_malloc", "hcclb200_torch_free")
+            self._pool_alloc = alloc
+            self._pool = torch.cuda.MemPool(alloc.allocator())
+        return self._pool
+
+    def release_symmetric_pool(self):
+        """Collective: drops the pool (its tensors must be gone) and releases its symmetric memory on every rank."""
+        self._pool = None
+        self._pool_alloc = None
+        L.check(L.lib().HcclB200PoolBind(None), "HcclB200PoolBind")
+
     def mem_adopt(self, bufs, drv_handles=None):
         """Register caller-owned buffers (one per local rank; numpy arrays or torch tensors of equal byte size) as a symmetric
         allocation.  drv_handles: driver allocation handles behind the buffers (one rank per GPU).  Returns the handle for

@@ -100,6 +100,23 @@ def scenario_collectives(c, p, r, args):
         del zin, zout
         c.mem_free(hin)
         c.mem_free(hout)
+    if nvls:  # tensors of the symmetric pool are ordinary torch tensors and run zero-copy without further calls
+        n = 3_000_000
+        pool = c.symmetric_pool()
+        with torch.cuda.use_mem_pool(pool):
+            pa = torch.empty(n, device="cuda")
+            pb = torch.empty(n, device="cuda")
+        xs = [inp(q, n, torch.float32, seed=23) for q in range(p)]
+        pa.copy_(xs[r])
+        c.all_reduce(pa, pb)
+        ok(c)
+        assert c.trace()[-1]["algo"] == "nvls_zerocopy", c.trace()[-1]
+        close(pb, red(xs, L.SUM), torch.float32, p)
+        del pa, pb
+        torch.cuda.synchronize()
+        c.barrier()
+        ok(c)
+        c.release_symmetric_pool()
     _adopted_vmm_memory(c, p, r, nvls)
     for algo in [L.ALGO_MESH, L.ALGO_RING, L.ALGO_RHD] + ([L.ALGO_NVLS] if nvls else []):
         n = 40_000
