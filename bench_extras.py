@@ -71,7 +71,7 @@ def collective_sweeps(comm, world, rank, dist, max_over_ranks, sync, max_bytes, 
 
     specs = [("allgather", L.ALLGATHER, (torch.float32, torch.bfloat16), (L.ALGO_RING, L.ALGO_RHD)),
              ("reducescatter", L.REDUCE_SCATTER, (torch.float32, torch.bfloat16), (L.ALGO_RING, L.ALGO_RHD)),
-             ("broadcast", L.BROADCAST, (torch.float32,), ()), ("reduce", L.REDUCE, (torch.float32,), ()),
+             ("broadcast", L.BROADCAST, (torch.float32,), ()), ("reduce", L.REDUCE, (torch.float32,), (L.ALGO_MESH_PIPE, L.ALGO_TREE)),
              ("scatter", L.SCATTER, (torch.float32,), ()), ("gather", L.GATHER, (torch.float32,), ())]
     hd = {torch.float32: L.FP32, torch.bfloat16: L.BFP16}
     for name, coll, dtypes, forced in specs:

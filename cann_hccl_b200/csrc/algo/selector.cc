@@ -48,7 +48,7 @@ static bool algo_exists(int coll, int algo)
         case COLL_REDUCE_SCATTER_V: return algo == ALGO_MESH || algo == ALGO_RING || algo == ALGO_NVLS;
         case COLL_ALLGATHER_V: return algo == ALGO_MESH || algo == ALGO_RING || algo == ALGO_NVLS || algo == ALGO_PAIRWISE;
         case COLL_BROADCAST: return algo == ALGO_STAR || algo == ALGO_RING || algo == ALGO_TREE || algo == ALGO_NVLS || algo == ALGO_MESH_PIPE || algo == ALGO_NVLS_PIPE;
-        case COLL_REDUCE: return algo == ALGO_STAR || algo == ALGO_RING || algo == ALGO_TREE || algo == ALGO_RHD;
+        case COLL_REDUCE: return algo == ALGO_STAR || algo == ALGO_RING || algo == ALGO_TREE || algo == ALGO_RHD || algo == ALGO_MESH_PIPE;
         case COLL_SCATTER: case COLL_GATHER: return algo == ALGO_STAR || algo == ALGO_RING;
         case COLL_ALLTOALL: case COLL_ALLTOALLV: case COLL_ALLTOALLVC: return algo == ALGO_MESH || algo == ALGO_PAIRWISE;
         default: return false;
@@ -118,6 +118,7 @@ double estimate_us(int coll, int algo, uint64_t bytes, int p, const CostModel &m
                 case ALGO_RING: return L + (p - 1 + 3) * (a + s) + (1.0 + (p - 2) / 4.0) * n / B;
                 case ALGO_TREE: return L + lg * (a + s) + lg * n / B;
                 case ALGO_RHD: return L + (lg + 1 + (pow2 ? 0 : 1)) * (a + s) + 2 * f * n / B;
+                case ALGO_MESH_PIPE: return L + 3 * a + 2 * f * n / B + 3 * chunk / B;  // the root takes in p-1 pushed and p-1 reduced slices
             }
             break;
         case COLL_SCATTER: case COLL_GATHER:

@@ -146,7 +146,7 @@ HcclResult Communicator::calibrate(void *stream)
         {COLL_ALLGATHER, {ALGO_MESH, ALGO_PAIRWISE, ALGO_RING, ALGO_NVLS, ALGO_MESH_PIPE}},
         {COLL_REDUCE_SCATTER, {ALGO_MESH, ALGO_RING, ALGO_NVLS, ALGO_MESH_PIPE, ALGO_NVLS_PIPE}},
         {COLL_BROADCAST, {ALGO_STAR, ALGO_RING, ALGO_TREE, ALGO_NVLS, ALGO_MESH_PIPE, ALGO_NVLS_PIPE}},
-        {COLL_REDUCE, {ALGO_STAR, ALGO_RING, ALGO_TREE, ALGO_RHD}},
+        {COLL_REDUCE, {ALGO_STAR, ALGO_RING, ALGO_TREE, ALGO_RHD, ALGO_MESH_PIPE}},
         {COLL_SCATTER, {ALGO_STAR, ALGO_RING}},
         {COLL_GATHER, {ALGO_STAR, ALGO_RING}},
     };

@@ -783,7 +783,7 @@ HcclResult Communicator::run_collective_once(const OpRequest &rq)
         }
         // CPU ranks have no pipelined executor: the plain schedule of the same family moves the same bytes
         const bool mc = sel.algo == ALGO_NVLS_PIPE;
-        sel.algo = rq.coll == COLL_BROADCAST ? (mc ? ALGO_NVLS : ALGO_RING) : (mc ? ALGO_NVLS : ALGO_MESH);
+        sel.algo = rq.coll == COLL_REDUCE ? ALGO_TREE : rq.coll == COLL_BROADCAST ? (mc ? ALGO_NVLS : ALGO_RING) : (mc ? ALGO_NVLS : ALGO_MESH);
     }
 
     OpDesc d;
@@ -863,6 +863,7 @@ int Communicator::pipe_mode_for(int coll) const
         case COLL_REDUCE_SCATTER: return PM_RS_PUSH;
         case COLL_ALLGATHER: return PM_AG_PULL;
         case COLL_BROADCAST: return PM_BC_PUSH;
+        case COLL_REDUCE: return PM_RD_PUSH;
         default: return -1;
     }
 }
@@ -912,7 +913,7 @@ HcclResult Communicator::run_pipe(const OpRequest &rq, bool want_mc, int zc_hand
         else if (mode == PM_BC_PUSH) mode = PM_BC_MC;
     }
     // a chunk of ce elements per block moves about fan * ce elements over a rank's links
-    const uint64_t fan = (mode == PM_AR2_MC || mode == PM_AR2_PUSH || pipe_mode_is_bcast(mode)) ? 1 : (uint64_t)(p - 1);
+    const uint64_t fan = (pipe_mode_has_copy_out(mode) || pipe_mode_is_bcast(mode)) ? 1 : (uint64_t)(p - 1);
     uint64_t link_total = block_bytes * fan;
     uint64_t lc = env.pipe_chunk_bytes ? env.pipe_chunk_bytes : std::min<uint64_t>(8u << 20, std::max<uint64_t>(1u << 20, link_total / 2));
     int nslots = env.pipe_slots > 0 ? std::min(env.pipe_slots, kPipeMaxSlots) : kPipeMaxSlots;

@@ -477,7 +477,9 @@ __global__ void __launch_bounds__(kExecThreads, 1) pipe_coll_kernel(const RankCt
             if (s_last && !s_fail && tid < p && tid != me) st_release_sys(c.flags[tid] + pipe_flag_index(kPipeWordDone, me, 0), now);
         }
     }
-    for (uint64_t ch = (uint64_t)group; ch < nchunks && !s_fail && !pipe_mode_is_zc(mode); ch += (uint64_t)ngroup) {
+    // Reduce: only the root has a receive buffer, the copy-out CTAs of the other ranks have nothing to do
+    const bool idle = pipe_mode_is_zc(mode) || (mode == PM_RD_PUSH && role == 2 && me != a.root);
+    for (uint64_t ch = (uint64_t)group; ch < nchunks && !s_fail && !idle; ch += (uint64_t)ngroup) {
         const int slot = (int)(ch % (uint64_t)K);
         const uint64_t soff = half_off + (uint64_t)slot * slot_bytes;
         const uint64_t e0 = ch * ce;
@@ -498,6 +500,13 @@ __global__ void __launch_bounds__(kExecThreads, 1) pipe_coll_kernel(const RankCt
                 else if (role == 1) { ww0 = kPipeWordReady; wm0 = all; if (old) { ww1 = kPipeWordOut; wm1 = all; } sw0 = kPipeWordDone; sm0 = all; }
                 else { ww0 = kPipeWordDone; wm0 = all; sw0 = kPipeWordOut; sm0 = all; }
                 break;
+            case PM_RD_PUSH: {
+                const uint32_t rootm = 1u << a.root;
+                if (role == 0) { if (old) { ww0 = kPipeWordDone; wm0 = all; wv0 = old; } sw0 = kPipeWordReady; sm0 = all; }
+                else if (role == 1) { ww0 = kPipeWordReady; wm0 = all; if (old) { ww1 = kPipeWordOut; wm1 = rootm; } sw0 = kPipeWordDone; sm0 = all; }
+                else { ww0 = kPipeWordDone; wm0 = all; sw0 = kPipeWordOut; sm0 = all; }  // the root only (see the loop bound)
+                break;
+            }
             case PM_AR1_MC: case PM_AR1_PUSH: case PM_RS_MC: case PM_RS_PUSH:
                 if (role == 0) { if (old) { ww0 = kPipeWordDone; wm0 = all; wv0 = old; } sw0 = kPipeWordReady; sm0 = all; }
                 else { ww0 = kPipeWordReady; wm0 = all; sw0 = kPipeWordDone; sm0 = all; }
@@ -567,12 +576,12 @@ __global__ void __launch_bounds__(kExecThreads, 1) pipe_coll_kernel(const RankCt
                     nseg = p;
                     break;
                 }
-                case PM_AR2_PUSH: case PM_RS_PUSH: case PM_AR1_PUSH: {
+                case PM_AR2_PUSH: case PM_RD_PUSH: case PM_RS_PUSH: case PM_AR1_PUSH: {
                     // segment k goes to rank q = me + 1 + k: its slice of my chunk (two-shot), its block of my chunk
                     // (ReduceScatter), or the whole chunk (one-shot)
                     if (tid < p - 1) {
                         const int q = me + 1 + tid < p ? me + 1 + tid : me + 1 + tid - p;
-                        if (mode == PM_AR2_PUSH) {
+                        if (mode == PM_AR2_PUSH || mode == PM_RD_PUSH) {
                             chan_range(shi(q) - slo(q), es, gsize, gidx, lo, hi);
                             s_src[tid] = a.in + (e0 + slo(q) + lo) * es;
                             s_dst[tid] = c.stage[q] + soff + ((uint64_t)me * se + lo) * es;
@@ -616,6 +625,17 @@ __global__ void __launch_bounds__(kExecThreads, 1) pipe_coll_kernel(const RankCt
                     }
                     __syncthreads();
                     reduce_sources(p, hi > lo ? hi - lo : 0);
+                    break;
+                }
+                case PM_RD_PUSH: {
+                    chan_range(shi(me) - slo(me), es, gsize, gidx, lo, hi);
+                    if (tid < p) {
+                        const uint64_t mo = (e0 + slo(me) + lo) * es;
+                        s_src[tid] = tid == me ? a.in + mo : mine + soff + ((uint64_t)tid * se + lo) * es;
+                        if (tid == 0) s_dst[0] = me == a.root ? a.out + mo : c.stage[a.root] + soff + (ce + slo(me) + lo) * es;
+                    }
+                    __syncthreads();
+                    reduce_sources(1, hi > lo ? hi - lo : 0);
                     break;
                 }
                 case PM_AR1_MC: case PM_RS_MC: {
@@ -666,9 +686,10 @@ __global__ void __launch_bounds__(kExecThreads, 1) pipe_coll_kernel(const RankCt
             // copy-out of the two-shot AllReduce; push mode: my own slice was written by the reduce stage already
             chan_range(nc, es, gsize, gidx, lo, hi);
             if (tid == 0) {
-                const uint64_t roff = mode == PM_AR2_PUSH ? ce * es : 0;
+                const bool push = mode == PM_AR2_PUSH || mode == PM_RD_PUSH;
+                const uint64_t roff = push ? ce * es : 0;
                 uint64_t a0 = lo, a1 = hi, b0 = hi, b1 = hi;
-                if (mode == PM_AR2_PUSH) { a1 = hi < slo(me) ? hi : slo(me); b0 = lo > shi(me) ? lo : shi(me); }
+                if (push) { a1 = hi < slo(me) ? hi : slo(me); b0 = lo > shi(me) ? lo : shi(me); }
                 s_src[0] = mine + soff + roff + a0 * es; s_dst[0] = a.out + (e0 + a0) * es; s_bytes[0] = a1 > a0 ? (a1 - a0) * es : 0;
                 s_src[1] = mine + soff + roff + b0 * es; s_dst[1] = a.out + (e0 + b0) * es; s_bytes[1] = b1 > b0 ? (b1 - b0) * es : 0;
             }

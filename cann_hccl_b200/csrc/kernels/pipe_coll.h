@@ -32,6 +32,8 @@ enum PipeMode : int32_t {
     PM_AR1_ZC,      // AllReduce one-shot: every rank reduces all p send buffers into its receive buffer (two ranks: optimal)
     PM_RS_ZC,       // ReduceScatter: every rank reduces its block of all p send buffers into its receive buffer
     PM_AG_ZC,       // AllGather: every rank pulls the peers' send buffers straight into its receive buffer
+    // Reduce: the two-shot AllReduce with the reduced slices stored to the root only, which alone copies out
+    PM_RD_PUSH,     // Reduce: push slice q to rank q | reduce my slice locally, store the result to the root | root: copy-out
     PM_COUNT
 };
 
@@ -71,14 +73,14 @@ HCCLB_HD uint64_t pipe_slot_bytes(int mode, uint64_t chunk_elems, int es, int p)
 {
     const uint64_t c = chunk_elems * (uint64_t)es;
     switch (mode) {
-        case PM_AR2_PUSH: return 2 * c;  // the p pushed slices, then the p reduced slices
+        case PM_AR2_PUSH: case PM_RD_PUSH: return 2 * c;  // the p pushed slices, then the p reduced slices
         case PM_AR1_PUSH: case PM_RS_MC: case PM_RS_PUSH: return (uint64_t)p * c;
         default: return c;
     }
 }
 HCCLB_HD bool pipe_mode_is_mc(int mode) { return mode == PM_AR2_MC || mode == PM_AR1_MC || mode == PM_RS_MC || mode == PM_BC_MC; }
 HCCLB_HD bool pipe_mode_is_bcast(int mode) { return mode == PM_BC_MC || mode == PM_BC_PUSH; }
-HCCLB_HD bool pipe_mode_has_copy_out(int mode) { return mode == PM_AR2_MC || mode == PM_AR2_PUSH; }
+HCCLB_HD bool pipe_mode_has_copy_out(int mode) { return mode == PM_AR2_MC || mode == PM_AR2_PUSH || mode == PM_RD_PUSH; }
 HCCLB_HD bool pipe_mode_is_zc(int mode) { return mode == PM_AR1_ZC || mode == PM_RS_ZC || mode == PM_AG_ZC; }
 
 // One launch runs the listed local ranks (more than one: virtual ranks of one GPU).  Always a cooperative launch: the

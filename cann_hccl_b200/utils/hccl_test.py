@@ -99,12 +99,15 @@ def worker(a):
     import cann_hccl_b200 as H
     from cann_hccl_b200 import _lib as L
     device = not a.host
+    local = bool(a.local)  # every rank a virtual rank of this process's GPU: one cooperative launch per collective
     torch = None
     if device:
         import torch
         torch.cuda.set_device(rank % torch.cuda.device_count())
     # rendezvous through a file
-    if rank == 0:
+    if local:
+        info = None
+    elif rank == 0:
         info = H.Communicator.get_root_info()
         with open(a.root_file + ".tmp", "wb") as f:
             f.write(info)
@@ -118,7 +121,10 @@ def worker(a):
         info = open(a.root_file, "rb").read()
     cfg = L.CommConfig.default()
     cfg.hcclBufferSize = a.buffsize
-    comm = H.Communicator.init_root(p, info, rank, config=cfg, device=device)
+    if local:
+        comm = H.Communicator.init_local(p, device=True, device_id=torch.cuda.current_device(), config=cfg)
+    else:
+        comm = H.Communicator.init_root(p, info, rank, config=cfg, device=device)
     coll = {"all_reduce_test": L.ALLREDUCE, "all_gather_test": L.ALLGATHER, "reduce_scatter_test": L.REDUCE_SCATTER, "broadcast_test": L.BROADCAST,
             "reduce_test": L.REDUCE, "scatter_test": L.SCATTER, "gather_test": L.GATHER, "alltoall_test": L.ALLTOALL}[a.test]
     hd = {"int8": L.INT8, "uint8": L.UINT8, "int16": L.INT16, "uint16": L.UINT16, "int32": L.INT32, "uint32": L.UINT32, "int64": L.INT64,
@@ -133,7 +139,7 @@ def worker(a):
     algo = L.ALGO_NAMES.index(names[0]) if len(names) == 1 else L.ALGO_AUTO
     extra_algos = names if len(names) > 1 else []
     dist = None
-    if a.nccl and device and p > 1:
+    if a.nccl and device and p > 1 and not local:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", str(29600 + (os.getppid() % 300)))
@@ -149,7 +155,12 @@ def worker(a):
         count = max(1, size // es)
         n_in, n_out = in_elems(a.test, count, p), out_elems(a.test, count, p)
         mine = make_input(rank, n_in, a.dtype)
-        if device:
+        if local:
+            tdt = {"bfp16": torch.bfloat16}.get(a.dtype)
+            send = [torch.from_numpy(make_input(q, n_in, a.dtype)).cuda() for q in range(p)]
+            send = [x.to(tdt) for x in send] if tdt else send
+            recv = send if a.test == "broadcast_test" else [torch.zeros(n_out, device="cuda", dtype=send[0].dtype) for _ in range(p)]
+        elif device:
             tdt = {"bfp16": torch.bfloat16}.get(a.dtype)
             send = torch.from_numpy(mine).cuda().to(tdt) if tdt else torch.from_numpy(mine).cuda()
             recv = send if a.test == "broadcast_test" else torch.zeros(n_out, device="cuda", dtype=send.dtype)
@@ -172,22 +183,25 @@ def worker(a):
         ok = True
         if a.check:
             ins = [make_input(q, n_in, a.dtype) for q in range(p)]
-            ref = reference(a.test, ins, op, p, rank, a.root, count)
-            if ref is not None:
+            for vr, got_t in (enumerate(recv) if local else ((rank, recv),)):
+                ref = reference(a.test, ins, op, p, vr, a.root, count)
+                if ref is None:
+                    continue
                 if device:
-                    got = recv.float().cpu().numpy() if a.dtype in ("bfp16", "fp16") else recv.cpu().numpy()
+                    got = got_t.float().cpu().numpy() if a.dtype in ("bfp16", "fp16") else got_t.cpu().numpy()
                 elif a.dtype == "bfp16":
-                    got = (recv.astype(np.uint32) << 16).view(np.float32)
+                    got = (got_t.astype(np.uint32) << 16).view(np.float32)
                 else:
-                    got = recv
+                    got = got_t
                 if np.asarray(ref).dtype.kind == "f" or got.dtype.kind == "f":
                     tol = {"fp64": 1e-12, "fp32": 1e-5, "fp16": 4e-3, "bfp16": 2e-2}.get(a.dtype, 1e-5) * max(1, p // 2)
-                    ok = bool(np.allclose(got.astype(np.float64), np.asarray(ref, np.float64), rtol=tol, atol=tol))
+                    ok = ok and bool(np.allclose(got.astype(np.float64), np.asarray(ref, np.float64), rtol=tol, atol=tol))
                 else:
-                    ok = bool(np.array_equal(got, ref.astype(got.dtype)))
+                    ok = ok and bool(np.array_equal(got, ref.astype(got.dtype)))
         def timed(fn):
             fn(a.warmup)
-            comm.barrier()
+            if not local:
+                comm.barrier()
             if device:
                 torch.cuda.synchronize()
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -227,7 +241,8 @@ def worker(a):
         # maximum over ranks and the conjunction of the checks, gathered over the control plane
         import struct
         fmt = "<%ddI" % len(times)
-        blob = comm.exchange("t%d" % size, struct.pack(fmt, *times, 1 if ok else 0))
+        mine_blob = struct.pack(fmt, *times, 1 if ok else 0)
+        blob = [mine_blob] if local else comm.exchange("t%d" % size, mine_blob)
         vals = [struct.unpack(fmt, b) for b in blob]
         times = [max(v[i] for v in vals) for i in range(len(times))]
         us = times[0]
@@ -265,6 +280,8 @@ def main(argv=None):
     ap.add_argument("--nccl", action="store_true", help="also time the same collective through torch.distributed (NCCL) on the same buffers")
     ap.add_argument("--trace", action="store_true", help="print the in-kernel stage times of the newest pipelined launch (sets HCCL_KERNEL_TRACE=1)")
     ap.add_argument("--host", action="store_true", help="CPU ranks over the host-memory transport")
+    ap.add_argument("--local", action="store_true", help="all ranks as virtual ranks of ONE GPU in one process (one cooperative launch per "
+                    "collective); chosen automatically when -p asks for more ranks than GPUs are visible")
     ap.add_argument("--buffsize", type=int, default=200, help="staging MB per direction (HCCL_BUFFSIZE)")
     ap.add_argument("--rank", type=int, default=-1, help=argparse.SUPPRESS)
     ap.add_argument("--root-file", default="", help=argparse.SUPPRESS)
@@ -281,6 +298,12 @@ def main(argv=None):
         else:
             import torch
             a.nranks = max(1, torch.cuda.device_count())
+    if not a.host:
+        import torch
+        # kernels of different ranks wait on one another, so ranks never share a GPU as separate processes
+        if a.local or a.nranks > torch.cuda.device_count():
+            a.local, a.rank = True, 0
+            return worker(a)
     tmp = tempfile.mkdtemp(prefix="hccl_test_")
     root_file = os.path.join(tmp, "root.bin")
     base = [sys.executable, "-m", "cann_hccl_b200.utils.hccl_test"] + [x for x in (argv if argv is not None else sys.argv[1:])]

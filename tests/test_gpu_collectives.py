@@ -207,6 +207,34 @@ def test_pipelined_broadcast_chain(comms, p):
             assert torch.equal(b, want)
 
 
+@pytest.mark.parametrize("p", [2, 3, 4, 8])
+@pytest.mark.parametrize("dtype,op", [(torch.float32, L.SUM), (torch.bfloat16, L.MAX)])
+def test_pipelined_reduce(comms, p, dtype, op):
+    """Reduce as a pipelined two-shot: slices to their owners, reduced slices to the root, which alone copies out."""
+    c = comms(p)
+    for n, root in ((5, 0), (70_001, p - 1), (3_000_000, 1)):
+        ins = rnd(p, n, dtype, seed=n % 67)
+        keep = [x.clone() for x in ins]
+        outs = [torch.full((n,), 7, device="cuda", dtype=dtype) for _ in range(p)]
+        c.reduce(ins, outs, root, op=op, algo=L.ALGO_MESH_PIPE)
+        ok(c)
+        assert c.trace()[-1]["algo"] == "mesh_pipe"
+        close(outs[root], ref_reduce(keep, op), dtype, p)
+        for r in range(p):
+            assert torch.equal(ins[r], keep[r])
+            if r != root:
+                assert bool((outs[r] == 7).all())  # only the root's receive buffer is written
+    # in place on the root, back to back (the staging halves alternate)
+    n = 1_200_000
+    ins = rnd(p, n, torch.float32, seed=3)
+    ref = ref_reduce(ins, L.SUM)
+    for _ in range(3):
+        xs = [x.clone() for x in ins]
+        c.reduce(xs, xs, 0, algo=L.ALGO_MESH_PIPE)
+    ok(c)
+    close(xs[0], ref, torch.float32, p)
+
+
 def test_allreduce_staging_loop_in_place_unaligned(comms):
     p = 4
     c = comms(p)
