@@ -222,11 +222,32 @@ def reference_arm(args):
         line["stand_in"] = {"impl": "nccl_baseline", "error": repr(e)[:300]}
         rank = int(os.environ.get("RANK", "0"))
     if rank == 0:
-        print(json.dumps(line))
+        emit_json(line)
     return 0
 
 
+_REAL_STDOUT = None
+
+
+def quiet_stdout():
+    """Libraries print banners on the process's standard output (NCCL its version line, for one).  The result line has to be
+    the only line there, so file descriptor 1 points at standard error until `emit_json` writes the result."""
+    global _REAL_STDOUT
+    if _REAL_STDOUT is None:
+        sys.stdout.flush()
+        _REAL_STDOUT = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit_json(obj):
+    sys.stdout.flush()
+    if _REAL_STDOUT is not None:
+        os.dup2(_REAL_STDOUT, 1)
+    print(json.dumps(obj), flush=True)
+
+
 def main():
+    quiet_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
@@ -523,7 +544,7 @@ def main():
         dist.barrier()
         dist.destroy_process_group()
     if rank == 0:
-        print(json.dumps(result))
+        emit_json(result)
     return 0 if not failures else 1
 
 

@@ -156,8 +156,8 @@ HcclResult Communicator::calibrate(void *stream)
         const bool blocked = cd.coll == COLL_ALLGATHER || cd.coll == COLL_REDUCE_SCATTER || cd.coll == COLL_SCATTER || cd.coll == COLL_GATHER;
         const uint64_t top = blocked ? max_blk : max_ar;
         std::vector<uint64_t> sizes;
-        // steps of 4x, of 2x between 256 KiB and 16 MiB where the algorithms cross over
-        for (uint64_t sz = 16u << 10; sz <= top; sz *= (sz >= (256u << 10) && sz < (16u << 20) ? 2 : 4)) sizes.push_back(sz);
+        // steps of 4x, of 2x from 256 KiB on: that is where the algorithms cross over
+        for (uint64_t sz = 16u << 10; sz <= top; sz *= (sz >= (256u << 10) ? 2 : 4)) sizes.push_back(sz);
         if (sizes.empty() || sizes.back() != top) sizes.push_back(top);
         ladders.push_back(sizes);
         for (uint64_t sz : sizes) {

@@ -92,7 +92,7 @@ def scenario_collectives(c, p, r, args):
         zout.zero_()
         c.all_reduce(zin, zout)
         ok(c)
-        assert c.trace()[-1]["algo"] == "nvls_zerocopy", c.trace()[-1]
+        assert c.trace()[-1]["algo"] == ("nvls_zerocopy" if p > 2 else "mesh_zerocopy"), c.trace()[-1]
         close(zout, red(xs, L.SUM), torch.float32, p)
         c.all_reduce(zin, zin)  # in place
         ok(c)
@@ -110,7 +110,7 @@ def scenario_collectives(c, p, r, args):
         pa.copy_(xs[r])
         c.all_reduce(pa, pb)
         ok(c)
-        assert c.trace()[-1]["algo"] == "nvls_zerocopy", c.trace()[-1]
+        assert c.trace()[-1]["algo"] == ("nvls_zerocopy" if p > 2 else "mesh_zerocopy"), c.trace()[-1]
         close(pb, red(xs, L.SUM), torch.float32, p)
         del pa, pb
         torch.cuda.synchronize()
@@ -275,7 +275,7 @@ def _adopted_vmm_memory(c, p, r, nvls):
     c.all_reduce(zin, zout)
     ok(c)
     if nvls:
-        assert c.trace()[-1]["algo"] == "nvls_zerocopy", c.trace()[-1]
+        assert c.trace()[-1]["algo"] == ("nvls_zerocopy" if p > 2 else "mesh_zerocopy"), c.trace()[-1]
     close(zout, red(xs, L.SUM), torch.float32, p)
     torch.cuda.synchronize()
     c.barrier()
@@ -286,7 +286,7 @@ def _adopted_vmm_memory(c, p, r, nvls):
     zout.zero_()
     c.all_reduce(zin, zout)     # registration gone: staged path on the same memory
     ok(c)
-    assert c.trace()[-1]["algo"] != "nvls_zerocopy"
+    assert c.trace()[-1]["algo"] not in ("nvls_zerocopy", "mesh_zerocopy")
     close(zout, red(xs, L.SUM), torch.float32, p)
     torch.cuda.synchronize()
     del zin, zout
