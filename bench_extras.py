@@ -256,6 +256,8 @@ def run(comm, world, rank, dist, max_over_ranks, sync, max_bytes, failures, want
             out["moe"] = moe.bench(comm, world, rank, dist, max_over_ranks, sync)
             if out["moe"].get("check_max_abs_err", 0) > 0.25:
                 failures.append("moe check_max_abs_err")
+            if out["moe"].get("alltoallv_api_check_max_abs_err", 0) > 0.25:
+                failures.append("moe alltoallv_api_check_max_abs_err")
         except Exception as e:
             out["moe"] = {"error": repr(e)[:300]}
             failures.append("moe raised")

@@ -3,7 +3,8 @@ import ctypes as C
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "lib", "libhccl_b200.so")
+# HCCL_B200_LIB: another build of the library (a sanitizer build, for one)
+LIB_PATH = os.environ.get("HCCL_B200_LIB") or os.path.join(_PKG, "lib", "libhccl_b200.so")
 
 HCCL_ROOT_INFO_BYTES = 4108
 COMM_NAME_MAX_LENGTH = 128
@@ -159,6 +160,7 @@ def lib():
         "HcclB200MoeDispatch": [vp, vp, vp, vp, C.c_int64, i32, i32, i32, i32, i32, i32, P(vp), vp, C.c_int64, vp],
         "HcclB200MoeCombine": [P(vp), vp, vp, vp, C.c_int64, i32, i32, i32, i32, i32, i32, vp, C.c_int64, vp],
         "HcclB200GemmBf16": [vp, vp, vp, i32, i32, i32, vp],
+        "HcclB200GemmLaunchCounts": [P(u64), P(u64)],
         "HcclB200AllGatherMatmul": [vp, P(vp), P(vp), P(vp), i32, i32, i32, vp],
         "HcclB200MatmulReduceScatter": [vp, P(vp), P(vp), P(vp), i32, i32, i32, vp],
         "HcclB200GetKernelTrace": [vp, u32, P(u64), C.c_size_t, P(i32)],

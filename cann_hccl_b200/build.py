@@ -1,9 +1,17 @@
 """Build the native library in-tree: every .cc with g++, every .cu with nvcc for sm_100a, one shared object.
 
-    python -m cann_hccl_b200.build [--force] [--verbose]
+    python -m cann_hccl_b200.build [--force] [--verbose] [--sanitize=address|thread]
 
 The shared library lands in cann_hccl_b200/lib/libhccl_b200.so.  Objects are rebuilt when their source or any
 header is newer.  nvcc cross-compiles, so this works on machines without a GPU.
+
+--sanitize builds a second library, lib/libhccl_b200_<kind>.so, whose host code is instrumented by the address or the
+thread sanitizer (objects under build_<kind>/).  Run the CPU suite on it with
+
+    LD_PRELOAD=$(gcc -print-file-name=libasan.so) ASAN_OPTIONS=detect_leaks=0 \
+        HCCL_B200_LIB=cann_hccl_b200/lib/libhccl_b200_address.so python -m pytest tests -m "not gpu"
+
+(libtsan.so and TSAN_OPTIONS for the thread sanitizer).
 """
 import os
 import subprocess
@@ -59,11 +67,21 @@ def _compile(src, obj, verbose):
     return obj
 
 
-def lib_path():
-    return os.path.join(LIB, "libhccl_b200.so")
+def lib_path(sanitize=None):
+    return os.path.join(LIB, "libhccl_b200_%s.so" % sanitize if sanitize else "libhccl_b200.so")
 
 
-def build(force=False, verbose=False):
+def build(force=False, verbose=False, sanitize=None):
+    global OBJ, CXXFLAGS, NVCCFLAGS
+    san_link = []
+    if sanitize:
+        if sanitize not in ("address", "thread"):
+            raise ValueError("--sanitize takes address or thread")
+        flag = "-fsanitize=" + sanitize
+        OBJ = os.path.join(PKG, "build_" + sanitize)
+        CXXFLAGS = [f for f in CXXFLAGS if f != "-O2"] + ["-O1", "-fno-omit-frame-pointer", flag]
+        NVCCFLAGS = NVCCFLAGS + ["-Xcompiler", flag + ",-fno-omit-frame-pointer"]
+        san_link = ["-Xcompiler", flag]
     os.makedirs(OBJ, exist_ok=True)
     os.makedirs(LIB, exist_ok=True)
     hdr = _newest_header()
@@ -76,9 +94,9 @@ def build(force=False, verbose=False):
             jobs.append((src, obj))
     with ThreadPoolExecutor(max_workers=max(1, os.cpu_count() or 4)) as ex:
         list(ex.map(lambda j: _compile(j[0], j[1], verbose), jobs))
-    out = lib_path()
+    out = lib_path(sanitize)
     if jobs or not os.path.exists(out):
-        cmd = [NVCC] + ARCH + ["-shared", "-o", out] + objs + ["-lpthread", "-ldl", "-lrt"]
+        cmd = [NVCC] + ARCH + ["-shared", "-o", out] + objs + san_link + ["-lpthread", "-ldl", "-lrt"]
         if verbose:
             print(" ".join(cmd), flush=True)
         r = subprocess.run(cmd, capture_output=True, text=True)
@@ -88,4 +106,5 @@ def build(force=False, verbose=False):
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv or "-v" in sys.argv))
+    _san = [a.split("=", 1)[1] for a in sys.argv if a.startswith("--sanitize=")]
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv or "-v" in sys.argv, sanitize=_san[0] if _san else None))

@@ -713,6 +713,12 @@ HcclResult HcclB200GemmBf16(const void *A, const void *B, void *C, int32_t M, in
     CHK_RET_LOG(!A || !B || !C, HCCL_E_PTR, "[EI0003] HcclB200GemmBf16: null pointer");
     return gemm_bf16_plain(A, B, C, M, N, K, stream);
 }
+HcclResult HcclB200GemmLaunchCounts(uint64_t *single, uint64_t *pair)
+{
+    CHK_RET_LOG(!single || !pair, HCCL_E_PTR, "[EI0003] HcclB200GemmLaunchCounts: null pointer");
+    tp_gemm_launch_counts(single, pair);
+    return HCCL_SUCCESS;
+}
 HcclResult HcclB200AllGatherMatmul(HcclComm comm, void *const *xShards, void *const *weights, void *const *outs, int32_t M, int32_t N, int32_t K,
                                    aclrtStream stream)
 {

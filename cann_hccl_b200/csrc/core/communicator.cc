@@ -399,7 +399,7 @@ HcclResult Communicator::run_plan(const Plan &plan, const void *dev_steps_base, 
             a.z_out_mc = zc_args_[li].out_mc ? zc_args_[li].out_mc + zc_args_[li].oout : nullptr;
             a.z_in_off = zc_args_[li].oin; a.z_out_off = zc_args_[li].oout;
         }
-        if (track_done && settings_.transport == TR_DEVICE) status_[li]->head = seq;  // completion (tail) is a device word
+        if (track_done && settings_.transport == TR_DEVICE) __atomic_store_n(&status_[li]->head, (uint64_t)seq, __ATOMIC_RELAXED);  // completion (tail) is a device word
     }
     stats_.launches++;
     if (settings_.transport == TR_DEVICE && dev_trace_) {
@@ -896,7 +896,7 @@ HcclResult Communicator::run_pipe(const OpRequest &rq, bool want_mc, int zc_hand
             a.n1 = 1; a.n2 = readers; a.n3 = 0; a.g1 = a.g2 = a.g3 = 1;
             a.z_in_peer = (const uint8_t *const *)user_peer_tabs_[zc_handle][li];
             a.z_in_off = zc_off;
-            status_[li]->head = seq_;
+            __atomic_store_n(&status_[li]->head, (uint64_t)seq_, __ATOMIC_RELAXED);
         }
         stats_.launches++;
         HcclResult zrc = launch_pipe_coll((const RankCtx *)dev_ctx_, zargs.data(), nl, rq.redop, rq.stream);
@@ -961,7 +961,7 @@ HcclResult Communicator::run_pipe(const OpRequest &rq, bool want_mc, int zc_hand
         a.count = rq.count; a.chunk_elems = ce; a.seq = seq_;
         a.mode = mode; a.dtype = rq.dtype; a.root = rq.root; a.nslots = nslots;
         a.n1 = n[0]; a.n2 = n[1]; a.n3 = n[2]; a.g1 = g[0]; a.g2 = g[1]; a.g3 = g[2];
-        status_[li]->head = seq_;
+        __atomic_store_n(&status_[li]->head, (uint64_t)seq_, __ATOMIC_RELAXED);
     }
     stats_.launches++;
     if (dev_trace_)
@@ -1001,7 +1001,7 @@ HcclResult Communicator::run_a2av(const OpRequest &rq)
         }
         a.seq = seq_; a.sub_bytes = sub; a.dtype = rq.dtype; a.lanes = lanes;
         (void)es;
-        status_[li]->head = seq_;
+        __atomic_store_n(&status_[li]->head, (uint64_t)seq_, __ATOMIC_RELAXED);
     }
     stats_.launches++;
     HcclResult rc = launch_a2av((const RankCtx *)dev_ctx_, args.data(), nl, p, rq.stream);
@@ -1046,7 +1046,7 @@ HcclResult Communicator::run_ll_allreduce(const OpRequest &rq)
         a.exit_counter = ctx_[li].exit_counter;
         a.dev_tail = ctx_[li].dev_tail;
         a.exe_id = (1ull << 62) | ll_seq_;
-        status_[li]->head = a.exe_id;
+        __atomic_store_n(&status_[li]->head, (uint64_t)a.exe_id, __ATOMIC_RELAXED);
     }
     stats_.launches++;
     return launch_ar_ll(args.data(), nl, rq.dtype, rq.redop, rq.stream);
@@ -1539,9 +1539,11 @@ void Communicator::heartbeat_loop()
                 cudaStreamSynchronize((cudaStream_t)hb_stream_) == cudaSuccess)
                 s->tail = tail;
         }
-        m.head = s->head; m.tail = s->tail;
+        // the executing thread (or the GPU) writes these words while this thread reads them
+        m.head = __atomic_load_n(&s->head, __ATOMIC_RELAXED); m.tail = __atomic_load_n(&s->tail, __ATOMIC_RELAXED);
         m.status = PEER_OK;
-        if (s->code != 0) { m.status = PEER_ERROR; m.error_code = s->code; }
+        const uint32_t code_now = __atomic_load_n(&s->code, __ATOMIC_ACQUIRE);
+        if (code_now != 0) { m.status = PEER_ERROR; m.error_code = code_now; }
         // stuck: an op started (head) and its completion (tail) has not followed for the configured time
         // (reference: Heartbeat::StuckDetection, heartbeat.cc:1073-1104, comparing OpExeCounter head/tail)
         if (m.head != m.tail && m.head == last_head && m.tail == last_tail) {
@@ -1571,7 +1573,10 @@ void Communicator::heartbeat_loop()
                     uint32_t code = st == PEER_STUCK ? HCCL_E_TIMEOUT : HCCL_E_REMOTE;
                     remote_bad_rank_.store((int)sum.first_bad_rank);
                     remote_error_.store(code);
-                    for (auto *a : abort_) if (*a == 0) *a = 2;  // in-flight waits give up instead of running into their bound
+                    for (auto *a : abort_) {  // in-flight waits give up instead of running into their bound
+                        uint32_t zero = 0;
+                        __atomic_compare_exchange_n(a, &zero, 2u, false, __ATOMIC_RELEASE, __ATOMIC_RELAXED);
+                    }
                     HLOG_ERROR("heartbeat: rank %u reported %s", sum.first_bad_rank, st == PEER_LOST ? "lost" : st == PEER_STUCK ? "stuck" : "error");
                 }
             }

@@ -298,6 +298,8 @@ private:
 
 // Plain tcgen05 GEMM C[M,N] = A[M,K] * B[N,K]^T in bf16 (no communicator needed).
 HcclResult gemm_bf16_plain(const void *A, const void *B, void *C, int M, int N, int K, void *stream);
+// Launches of the fused GEMM kernels in this process: one CTA per tile / clusters of two CTAs per 256 x 256 tile.
+void tp_gemm_launch_counts(uint64_t *single, uint64_t *pair);
 // Device executor entry (kernels/exec_plan.cu).
 HcclResult launch_exec_plan(const RankCtx *dev_ctx, const ExecArgs *args, int nlocal, int nchan, void *stream, bool co_resident = false);
 // Unique identifier helper used by HcclGetRootInfo.

@@ -34,4 +34,5 @@ inline size_t tp_flag_words(int M, int nranks) { return (size_t)4 * nranks + (si
 // Fills the tensor maps and launches.  `A` / `B` per local rank.  n_comm_ctas data-movement CTAs per rank.
 HcclResult launch_tp_gemm(TpGemmParams *P, const void *const *A, const void *const *B, int nlocal, int n_comm_ctas, void *stream);
 size_t tp_gemm_smem_bytes();
+void tp_gemm_launch_counts(uint64_t *single, uint64_t *pair);
 }  // namespace hcclb

@@ -8,6 +8,12 @@
 //   warp 0    feeds a 4-stage shared-memory ring with TMA (cp.async.bulk.tensor, 128-byte swizzle, never multicast,
 //             always from this GPU's own memory);
 //   warp 1    issues tcgen05.mma (128x256x16, cta_group::1) into one of two 256-column TMEM accumulators;
+//             pair variant (tp_gemm_pair_kernel, clusters of two CTAs, used when every rank's rows are a multiple of
+//             256): the two CTAs of a cluster own the upper and lower 128 rows of a 256x256 tile, each loads its own
+//             rows of A and HALF of the tile's B rows (plain, non-multicast TMA loads that complete on the leader
+//             CTA's barrier), and the leader's warp 1 issues tcgen05.mma.cta_group::2 (256x256x16) which reads both
+//             CTAs' shared memory and writes both CTAs' TMEM: B crosses L2 -> SM once per pair instead of once per CTA
+//             and a stage shrinks from 48 to 32 KB (six stages instead of four);
 //   warps 2-5 drain the other accumulator with tcgen05.ld, convert to bf16 and send each 128-byte row piece off with a
 //             bulk asynchronous store (to local memory, or in RS mode straight into the owner rank's receive slot
 //             over NVLink, followed by a counter increment there);
@@ -27,9 +33,11 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <atomic>
 #include <mutex>
 #include <algorithm>
 #include <cstring>
+#include "common/env.h"
 #include "common/log.h"
 #include "core/device_api.h"
 #include "kernels/fused/tp_gemm.h"
@@ -42,20 +50,25 @@ namespace {
 
 constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16;
 constexpr int kStages = 4;
+constexpr int kStagesPair = 6;                        // pair variant: a stage holds 128 rows of A and 128 rows of B
+constexpr int kMaxStages = kStagesPair;
 constexpr int kMaxPanels = 60;
 constexpr int kMaxCommCtas = 32;  // data-movement CTAs per rank (AG), bound of the per-CTA ready words
 constexpr int kThreads = 256;  // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue, warps 6-7 move data between GPUs (AG)
 constexpr uint32_t kABytes = BM * BK * 2, kBBytes = BN * BK * 2, kStageBytes = kABytes + kBBytes;
+constexpr uint32_t kBBytesPair = kBBytes / 2, kStageBytesPair = kABytes + kBBytesPair;
+static_assert(kStagesPair * kStageBytesPair <= kStages * kStageBytes, "both variants share the tile buffers");
 constexpr uint32_t kTmemCols = 512;
 constexpr int kCommBuf = 32 * 1024, kCommDepth = 6;  // bulk-copy ring of a data-movement CTA (lives in the tile buffers)
 constexpr int kEpiCols = 64, kEpiStride = kEpiCols * 2 + 16;  // epilogue chunk: 64 bf16 per row, padded against bank conflicts
+constexpr uint64_t kPairWaitNs = 4000000000ull;     // pair variant: longest wait on a barrier that the other CTA completes
 constexpr uint32_t kSpinLimit = 1u << 28;            // iterations of an mbarrier poll before it gives up (seconds)
 
 struct SharedStorage {
     alignas(1024) uint8_t tiles[kStages * kStageBytes];
     alignas(16) uint8_t epi[128 * kEpiStride];          // one 128-byte (+16 pad) row slot per epilogue thread
-    alignas(8) uint64_t full_bar[kStages];
-    uint64_t empty_bar[kStages];
+    alignas(8) uint64_t full_bar[kMaxStages];
+    uint64_t empty_bar[kMaxStages];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
     uint64_t comm_bar[kCommDepth];
@@ -96,6 +109,64 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     }
     *fail = HCCL_E_TIMEOUT;
     return false;
+}
+// Cluster-scope forms for the pair variant: barriers that the other CTA of the pair (its threads, its TMA loads or the
+// leader's multicast commits) completes.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t *bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+template <bool kCluster>
+__device__ __forceinline__ bool mbar_wait_t(uint64_t *bar, uint32_t parity, volatile uint32_t *fail)
+{
+    if constexpr (!kCluster) {
+        return mbar_wait(bar, parity, fail);
+    } else {
+        // the other CTA of the pair learns of a failure only through its own waits: bound them by time, a few seconds
+        uint64_t t0 = 0;
+        for (uint32_t it = 0; it < kSpinLimit; ++it) {
+            if (mbar_try_wait_cluster(bar, parity)) return true;
+            if ((it & 1023) == 1023) {
+                if (*fail) return false;
+                const uint64_t now = global_timer_ns();
+                if (t0 == 0) t0 = now;
+                else if (now - t0 > kPairWaitNs) break;
+            }
+        }
+        *fail = HCCL_E_TIMEOUT;
+        return false;
+    }
+}
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Address of the same shared-memory location in CTA `rank` of this cluster (shared::cluster window).
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t cta_addr, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(cta_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// TMA load of the pair variant: the data lands in this CTA's shared memory, the bytes are counted on the barrier at
+// `bar_cluster_addr`, which may belong to the other CTA of the pair (no multicast: one load, one destination).
+__device__ __forceinline__ void tma_load_2d_pair(void *dst, const CUtensorMap *map, uint32_t bar_cluster_addr, int x, int y)
+{
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y) : "memory");
 }
 __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, uint64_t *bar, int x, int y)
 {
@@ -147,6 +218,20 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t b
 __device__ __forceinline__ void umma_commit(uint64_t *bar)
 {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Pair variant: D fp32, A and B bf16 K-major, N = 256, M = 256 (128 rows per CTA); issued by one thread of the leader CTA.
+constexpr uint32_t kInstrDescPair = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate)
+{
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(kInstrDescPair), "r"(accumulate), "r"(0u) : "memory");
+}
+// Arrives on the barrier at this offset in BOTH CTAs of the pair once the MMAs issued so far are complete.
+__device__ __forceinline__ void umma_commit_pair(uint64_t *bar)
+{
+    const uint16_t both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"(both) : "memory");
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
 {
@@ -486,23 +571,37 @@ __device__ void reduce_tail_rs(const TpGemmParams &P, SharedStorage &S, int pw, 
 }
 
 // ---------------------------------------------------------------------------------------------- the kernel
-__global__ void __launch_bounds__(kThreads, 1) tp_gemm_kernel(const __grid_constant__ TpGemmParamsArray PA)
+// kPair: the CTAs 2i and 2i+1 form a cluster and share 256 x 256 tiles (see the head of the file).  A pair walks the tile
+// order in units of two m tiles: the tile coordinates are computed on a grid of m_tiles / 2 row blocks and CTA r of the pair
+// takes row block 2 * mp + r.  Everything per row block (AG readiness, RS delivery counters, the epilogue) stays as it is.
+template <bool kPair>
+__device__ __forceinline__ void tp_gemm_body(const TpGemmParams &P, SharedStorage &S)
 {
-    const TpGemmParams &P = PA.r[blockIdx.y];
-    extern __shared__ uint8_t smem_raw[];
-    SharedStorage &S = *(SharedStorage *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    constexpr int kSt = kPair ? kStagesPair : kStages;
+    constexpr uint32_t kStB = kPair ? kStageBytesPair : kStageBytes;
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int m_tiles = P.M / BM, n_tiles = P.N / BN, k_iters = P.K / BK;
     const int total_tiles = m_tiles * n_tiles;
     const int pw = panel_width(P, n_tiles), npanels = (n_tiles + pw - 1) / pw;
     volatile uint32_t *fail = &S.fail;
+    const uint32_t cta_r = kPair ? cluster_ctarank() : 0u;   // 0: leader of the pair (issues the MMAs)
+    // work units of the tile loops: tiles for single CTAs, pairs of tiles (same n tile, m tiles 2 mp and 2 mp + 1) for pairs
+    const int unit_first = kPair ? (int)blockIdx.x / 2 : (int)blockIdx.x;
+    const int unit_step = kPair ? P.n_gemm_ctas / 2 : P.n_gemm_ctas;
+    const int units = kPair ? total_tiles / 2 : total_tiles;
+    const int um_tiles = kPair ? m_tiles / 2 : m_tiles;
+    auto unit_coords = [&](int t, int &mt, int &nt, int &panel) {
+        tile_coords(P, t, n_tiles, um_tiles, pw, mt, nt, panel);
+        if (kPair) mt = 2 * mt + (int)cta_r;
+    };
 
     if (threadIdx.x == 0) {
         S.fail = 0;
         S.gemm_done = 0;
         S.early_count = 0;
-        for (int i = 0; i < kStages; ++i) { mbar_init(&S.full_bar[i], 1); mbar_init(&S.empty_bar[i], 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(&S.tmem_full[i], 1); mbar_init(&S.tmem_empty[i], 128); }
+        for (int i = 0; i < kSt; ++i) { mbar_init(&S.full_bar[i], 1); mbar_init(&S.empty_bar[i], 1); }
+        // pair: the epilogue threads of both CTAs release an accumulator on the leader's barrier
+        for (int i = 0; i < 2; ++i) { mbar_init(&S.tmem_full[i], 1); mbar_init(&S.tmem_empty[i], kPair ? 256 : 128); }
         for (int i = 0; i < kCommDepth; ++i) mbar_init(&S.comm_bar[i], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -513,12 +612,19 @@ __global__ void __launch_bounds__(kThreads, 1) tp_gemm_kernel(const __grid_const
         if (threadIdx.x == 0) bulk_wait_all<0>();
         return;
     }
-    if (warp == 1) {  // TMEM allocation by one full warp
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&S.tmem_base)), "r"(kTmemCols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (warp == 1) {  // TMEM allocation by one full warp (pair: by one warp of each CTA, all 512 columns, so both get base 0)
+        if (kPair) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&S.tmem_base)), "r"(kTmemCols) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&S.tmem_base)), "r"(kTmemCols) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
+    // pair: the other CTA's barriers are initialised and its TMEM is allocated before anything of mine reaches them
+    if (kPair) cluster_sync_all();
     tc_fence_after();
     const uint32_t tmem_base = S.tmem_base;
     const uint64_t deadline = global_timer_ns() + P.timeout_ns;
@@ -528,9 +634,10 @@ __global__ void __launch_bounds__(kThreads, 1) tp_gemm_kernel(const __grid_const
         if (elect_one()) {
             uint32_t it = 0;
             const uint64_t *chunk_ready = P.mode == TP_MODE_AG ? P.flags[P.rank] + 2 * P.nranks : nullptr;
-            for (int t = blockIdx.x; t < total_tiles && !*fail; t += P.n_gemm_ctas) {
+            // pair: the bytes of both CTAs' loads are counted on the leader's barrier, which the leader arms for both
+            for (int t = unit_first; t < units && !*fail; t += unit_step) {
                 int mt, nt, panel;
-                tile_coords(P, t, n_tiles, m_tiles, pw, mt, nt, panel);
+                unit_coords(t, mt, nt, panel);
                 const CUtensorMap *amap = &P.tmA;
                 int arow = mt * BM;
                 if (chunk_ready) {
@@ -544,38 +651,48 @@ __global__ void __launch_bounds__(kThreads, 1) tp_gemm_kernel(const __grid_const
                     }
                 }
                 for (int k = 0; k < k_iters; ++k, ++it) {
-                    uint32_t s = it % kStages, ph = (it / kStages) & 1;
-                    if (!mbar_wait(&S.empty_bar[s], ph ^ 1, fail)) { report(P, *fail, 700); break; }
-                    uint8_t *sa = S.tiles + (size_t)s * kStageBytes, *sb = sa + kABytes;
-                    mbar_expect_tx(&S.full_bar[s], kStageBytes);
-                    tma_load_2d(sa, amap, &S.full_bar[s], k * BK, arow);
-                    tma_load_2d(sb, &P.tmB, &S.full_bar[s], k * BK, nt * BN);
+                    uint32_t s = it % kSt, ph = (it / kSt) & 1;
+                    if (!mbar_wait_t<kPair>(&S.empty_bar[s], ph ^ 1, fail)) { report(P, *fail, 700); break; }
+                    uint8_t *sa = S.tiles + (size_t)s * kStB, *sb = sa + kABytes;
+                    if (kPair) {
+                        if (cta_r == 0) mbar_expect_tx(&S.full_bar[s], 2 * kStageBytesPair);
+                        const uint32_t full_leader = mapa_u32(smem_u32(&S.full_bar[s]), 0);
+                        tma_load_2d_pair(sa, amap, full_leader, k * BK, arow);
+                        tma_load_2d_pair(sb, &P.tmB, full_leader, k * BK, nt * BN + (int)cta_r * (BN / 2));  // my half of the B rows
+                    } else {
+                        mbar_expect_tx(&S.full_bar[s], kStageBytes);
+                        tma_load_2d(sa, amap, &S.full_bar[s], k * BK, arow);
+                        tma_load_2d(sb, &P.tmB, &S.full_bar[s], k * BK, nt * BN);
+                    }
                 }
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
-        if (elect_one()) {
+        if ((!kPair || cta_r == 0) && elect_one()) {  // pair: only the leader issues; its MMAs read both CTAs' stages
             uint32_t it = 0, tile_i = 0;
-            for (int t = blockIdx.x; t < total_tiles && !*fail; t += P.n_gemm_ctas, ++tile_i) {
+            for (int t = unit_first; t < units && !*fail; t += unit_step, ++tile_i) {
                 uint32_t buf = tile_i & 1, use = tile_i >> 1;
-                if (!mbar_wait(&S.tmem_empty[buf], (use & 1) ^ 1, fail)) { report(P, *fail, 800); break; }
+                if (!mbar_wait_t<kPair>(&S.tmem_empty[buf], (use & 1) ^ 1, fail)) { report(P, *fail, 800); break; }
                 tc_fence_after();
                 uint32_t d = tmem_base + buf * BN;
                 for (int k = 0; k < k_iters; ++k, ++it) {
-                    uint32_t s = it % kStages, ph = (it / kStages) & 1;
-                    if (!mbar_wait(&S.full_bar[s], ph, fail)) { report(P, *fail, 900); break; }
+                    uint32_t s = it % kSt, ph = (it / kSt) & 1;
+                    if (!mbar_wait_t<kPair>(&S.full_bar[s], ph, fail)) { report(P, *fail, 900); break; }
                     tc_fence_after();
-                    uint8_t *sa = S.tiles + (size_t)s * kStageBytes, *sb = sa + kABytes;
+                    uint8_t *sa = S.tiles + (size_t)s * kStB, *sb = sa + kABytes;
                     uint64_t da = make_smem_desc(sa), db = make_smem_desc(sb);
 #pragma unroll
                     for (int kk = 0; kk < BK / UMMA_K; ++kk) {
                         // advance 16 bf16 = 32 bytes along K inside the 128-byte swizzle atom: +2 in 16-byte units
-                        umma(d, da + (uint64_t)(2 * kk), db + (uint64_t)(2 * kk), (k | kk) != 0);
+                        if (kPair) umma_pair(d, da + (uint64_t)(2 * kk), db + (uint64_t)(2 * kk), (k | kk) != 0);
+                        else umma(d, da + (uint64_t)(2 * kk), db + (uint64_t)(2 * kk), (k | kk) != 0);
                     }
-                    umma_commit(&S.empty_bar[s]);  // frees the stage when the MMAs that read it are done
+                    // frees the stage (pair: in both CTAs) when the MMAs that read it are done
+                    if (kPair) umma_commit_pair(&S.empty_bar[s]); else umma_commit(&S.empty_bar[s]);
                 }
-                umma_commit(&S.tmem_full[buf]);    // accumulator complete
+                // accumulator complete (pair: each CTA's epilogue waits on its own barrier)
+                if (kPair) umma_commit_pair(&S.tmem_full[buf]); else umma_commit(&S.tmem_full[buf]);
             }
         }
     } else if (warp >= 2 && warp < 6) {
@@ -583,11 +700,11 @@ __global__ void __launch_bounds__(kThreads, 1) tp_gemm_kernel(const __grid_const
         const int q4 = warp & 3;  // a warp may only touch the TMEM lane quarter given by its index modulo 4
         uint32_t tile_i = 0, owner_ok = 0;
         const int per = P.nranks > 0 ? m_tiles / P.nranks : m_tiles;
-        for (int t = blockIdx.x; t < total_tiles && !*fail; t += P.n_gemm_ctas, ++tile_i) {
+        for (int t = unit_first; t < units && !*fail; t += unit_step, ++tile_i) {
             int mt, nt, panel;
-            tile_coords(P, t, n_tiles, m_tiles, pw, mt, nt, panel);
+            unit_coords(t, mt, nt, panel);
             uint32_t buf = tile_i & 1, use = tile_i >> 1;
-            if (!mbar_wait(&S.tmem_full[buf], use & 1, fail)) { report(P, *fail, 1000); break; }
+            if (!mbar_wait_t<kPair>(&S.tmem_full[buf], use & 1, fail)) { report(P, *fail, 1000); break; }
             tc_fence_after();
             const int row = mt * BM + q4 * 32 + lane;
             __nv_bfloat16 *dst_row;
@@ -638,7 +755,8 @@ __global__ void __launch_bounds__(kThreads, 1) tp_gemm_kernel(const __grid_const
                 bulk_commit();
             }
             tc_fence_before();
-            mbar_arrive(&S.tmem_empty[buf]);  // 128 arrivals free the accumulator for the tile after next
+            // 128 arrivals (pair: 256, on the leader's barrier) free the accumulator for the tile after next
+            if (kPair) mbar_arrive_cluster(mapa_u32(smem_u32(&S.tmem_empty[buf]), 0)); else mbar_arrive(&S.tmem_empty[buf]);
             if (P.mode == TP_MODE_RS) {
                 // the four epilogue warps finished their rows: one of them publishes the tile to the owner
                 // (no fence per thread: 128 system-scope fences per tile cost more than the whole transfer; the completed
@@ -661,11 +779,30 @@ __global__ void __launch_bounds__(kThreads, 1) tp_gemm_kernel(const __grid_const
     }
     tc_fence_before();
     __syncthreads();
+    // pair: the leader's MMAs read my stages and write my TMEM, and its commits arrive on my barriers: neither CTA lets go of
+    // its shared memory or TMEM before both are through (every wait above is bounded, so both get here)
+    if (kPair) cluster_sync_all();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+        if (kPair) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
     if (P.mode == TP_MODE_RS && !__syncthreads_or((int)*fail)) reduce_tail_rs(P, S, pw, npanels);
+}
+
+__global__ void __launch_bounds__(kThreads, 1) tp_gemm_kernel(const __grid_constant__ TpGemmParamsArray PA)
+{
+    extern __shared__ uint8_t smem_raw[];
+    SharedStorage &S = *(SharedStorage *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    tp_gemm_body<false>(PA.r[blockIdx.y], S);
+}
+
+// Launched with clusters of two CTAs along x.
+__global__ void __launch_bounds__(kThreads, 1) tp_gemm_pair_kernel(const __grid_constant__ TpGemmParamsArray PA)
+{
+    extern __shared__ uint8_t smem_raw[];
+    SharedStorage &S = *(SharedStorage *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    tp_gemm_body<true>(PA.r[blockIdx.y], S);
 }
 
 HcclResult encode_2d(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint32_t box_rows)
@@ -690,6 +827,13 @@ HcclResult encode_2d(CUtensorMap *map, const void *base, uint64_t rows, uint64_t
 
 size_t tp_gemm_smem_bytes() { return sizeof(SharedStorage) + 1024; }
 
+static std::atomic<uint64_t> g_launches[2];
+void tp_gemm_launch_counts(uint64_t *single, uint64_t *pair)
+{
+    *single = g_launches[0].load();
+    *pair = g_launches[1].load();
+}
+
 HcclResult launch_tp_gemm(TpGemmParams *P, const void *const *A, const void *const *B, int nlocal, int n_comm_ctas, void *stream)
 {
     if (nlocal < 1 || nlocal > kTpMaxLocal) return HCCL_E_PARA;
@@ -713,6 +857,36 @@ HcclResult launch_tp_gemm(TpGemmParams *P, const void *const *A, const void *con
     if (n_comm_ctas > kMaxCommCtas) n_comm_ctas = kMaxCommCtas;
     // with communication every rank must run the same grid (completion counters count CTAs)
     int total = (P0.M / BM) * (P0.N / BN);
+    // pair variant (clusters of two CTAs on 256 x 256 tiles): every rank's rows must come in pairs of 128-row blocks.  The
+    // choice depends on the shape and the environment only, so every rank makes the same one.
+    const int rows_per_rank = P0.mode == TP_MODE_PLAIN || P0.nranks < 1 ? P0.M : P0.M / P0.nranks;
+    const bool pair = env_config().tp_gemm_pair && rows_per_rank % (2 * BM) == 0 && per_rank >= 4;
+    if (pair) {
+        // clusters that can be resident together (a cluster needs both of its SMs inside one GPC): asked once per device
+        static std::mutex occ_mu;
+        static int occ_clusters[64] = {0};
+        int max_clusters = 0;
+        {
+            std::lock_guard<std::mutex> lk(occ_mu);
+            if (dev >= 0 && dev < 64 && occ_clusters[dev] > 0) max_clusters = occ_clusters[dev];
+            else {
+                cudaFuncSetAttribute((const void *)tp_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tp_gemm_smem_bytes());
+                cudaLaunchConfig_t q;
+                memset(&q, 0, sizeof(q));
+                q.gridDim = dim3((unsigned)(sms & ~1)); q.blockDim = dim3(kThreads); q.dynamicSmemBytes = tp_gemm_smem_bytes();
+                cudaLaunchAttribute qa[1];
+                qa[0].id = cudaLaunchAttributeClusterDimension;
+                qa[0].val.clusterDim.x = 2; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
+                q.attrs = qa; q.numAttrs = 1;
+                cudaError_t oe = cudaOccupancyMaxActiveClusters(&max_clusters, (const void *)tp_gemm_pair_kernel, &q);
+                if (oe != cudaSuccess || max_clusters < 2) { HLOG_ERROR("cluster occupancy query failed: %s", cudaGetErrorString(oe)); return HCCL_E_RUNTIME; }
+                if (dev >= 0 && dev < 64) occ_clusters[dev] = max_clusters;
+            }
+        }
+        per_rank = std::min(per_rank, 2 * max_clusters / nlocal);
+        per_rank &= ~1;
+        if (n_comm_ctas) n_comm_ctas = std::min((n_comm_ctas + 1) & ~1, std::max(2, (per_rank / 4) & ~1));
+    }
     int n_gemm = P0.mode == TP_MODE_PLAIN ? std::min(total, per_rank) : per_rank - n_comm_ctas;
     TpGemmParamsArray arr;
     memset(&arr, 0, sizeof(arr));
@@ -724,35 +898,48 @@ HcclResult launch_tp_gemm(TpGemmParams *P, const void *const *A, const void *con
             if (((uintptr_t)P[i].x_shard) & 15) return HCCL_E_PARA;
             CHK_RET(encode_2d(&P[i].tmX, P[i].x_shard, (uint64_t)(P[i].M / P[i].nranks), (uint64_t)P[i].K, BM));
         }
-        CHK_RET(encode_2d(&P[i].tmB, B[i], (uint64_t)P[i].N, (uint64_t)P[i].K, BN));
+        CHK_RET(encode_2d(&P[i].tmB, B[i], (uint64_t)P[i].N, (uint64_t)P[i].K, pair ? BN / 2 : BN));  // pair: a CTA loads half of the tile's B rows
         arr.r[i] = P[i];
     }
     // the opt-in to large dynamic shared memory belongs to the (device, function) pair: once per device, not per process
     // (a process may drive several GPUs, one thread each)
     static std::mutex attr_mu;
-    static bool attr_set[64] = {false};
+    static bool attr_set[2][64] = {{false}};
     size_t smem = tp_gemm_smem_bytes();
+    const void *fn = pair ? (const void *)tp_gemm_pair_kernel : (const void *)tp_gemm_kernel;
     {
         std::lock_guard<std::mutex> lk(attr_mu);
-        if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-            cudaError_t e = cudaFuncSetAttribute(tp_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (dev < 0 || dev >= 64 || !attr_set[pair][dev]) {
+            cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) { HLOG_ERROR("cannot raise dynamic shared memory to %zu: %s", smem, cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
-            if (dev >= 0 && dev < 64) attr_set[dev] = true;
+            if (dev >= 0 && dev < 64) attr_set[pair][dev] = true;
         }
     }
     dim3 grid((unsigned)(n_gemm + n_comm_ctas), (unsigned)nlocal), block(kThreads);
-    cudaError_t e;
     // AG and RS mode make CTAs of one rank wait on each other (GEMM CTAs on the data-movement CTAs, the reduce tail on the
     // other CTAs' tiles): a cooperative launch guarantees that all of them are resident together even when another kernel
     // shares the GPU.  The plain GEMM has no such dependency.
-    if (nlocal > 1 || P0.mode != TP_MODE_PLAIN) {
-        void *kargs[] = {(void *)&arr};
-        e = cudaLaunchCooperativeKernel((const void *)tp_gemm_kernel, grid, block, kargs, smem, (cudaStream_t)stream);
-    } else {
-        tp_gemm_kernel<<<grid, block, smem, (cudaStream_t)stream>>>(arr);
-        e = cudaGetLastError();
+    const bool coop = nlocal > 1 || P0.mode != TP_MODE_PLAIN;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attrs[2];
+    unsigned na = 0;
+    if (pair) {
+        attrs[na].id = cudaLaunchAttributeClusterDimension;
+        attrs[na].val.clusterDim.x = 2; attrs[na].val.clusterDim.y = 1; attrs[na].val.clusterDim.z = 1;
+        ++na;
     }
-    if (e != cudaSuccess) { HLOG_ERROR("fused GEMM launch failed: %s", cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
+    if (coop) {
+        attrs[na].id = cudaLaunchAttributeCooperative;
+        attrs[na].val.cooperative = 1;
+        ++na;
+    }
+    cfg.attrs = attrs; cfg.numAttrs = na;
+    void *kargs[] = {(void *)&arr};
+    cudaError_t e = cudaLaunchKernelExC(&cfg, fn, kargs);
+    if (e != cudaSuccess) { HLOG_ERROR("fused GEMM launch failed (%s%s): %s", pair ? "pair " : "", coop ? "cooperative" : "plain", cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
+    g_launches[pair ? 1 : 0]++;
     return HCCL_SUCCESS;
 }
 

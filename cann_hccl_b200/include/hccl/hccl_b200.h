@@ -80,6 +80,9 @@ extern HcclResult HcclB200MoeCombine(void *const *yPeers, const int32_t *topkIdx
 /* ---- fused tensor-parallel kernels (tcgen05 GEMM + NVLink transfer in one sm_100a kernel); bf16, weights [N, K] ---- */
 /* C[M,N] = A[M,K] * B[N,K]^T (no communication). M % 128 == 0, N % 256 == 0, K % 64 == 0. */
 extern HcclResult HcclB200GemmBf16(const void *A, const void *B, void *C, int32_t M, int32_t N, int32_t K, aclrtStream stream);
+/* Launches of the fused GEMM kernels in this process so far: *single on one CTA per tile (tcgen05 cta_group::1), *pair on
+ * clusters of two CTAs per 256 x 256 tile (cta_group::2; HCCL_TP_GEMM_PAIR, shapes whose rows per rank are a multiple of 256). */
+extern HcclResult HcclB200GemmLaunchCounts(uint64_t *single, uint64_t *pair);
 /* Column-parallel layer: outs = all_gather_rows(xShards [M/p, K]) * weights[N, K]^T -> [M, N].  One pointer per local rank. */
 extern HcclResult HcclB200AllGatherMatmul(HcclComm comm, void *const *xShards, void *const *weights, void *const *outs, int32_t M,
                                           int32_t N, int32_t K, aclrtStream stream);

@@ -180,5 +180,23 @@ def bench(comm, world, rank, dist, max_over_ranks, sync, tokens=8192, hidden=716
         out["nccl_a2a_ms"] = round(timed(base), 4)
         out["nccl_check_max_abs_err"] = round(float((res.float() - x.float()).abs().max()), 4)
         out["speedup_vs_nccl"] = round(out["nccl_a2a_ms"] / best, 3)
+        # ---- the same schedule with this library's HcclAlltoAllV (parametric kernel: counts are launch arguments) as transport
+        sc = [c * hidden for c in s_l]
+        rcv = [c * hidden for c in r_l]
+        sd = [sum(sc[:i]) for i in range(world)]
+        rd = [sum(rcv[:i]) for i in range(world)]
+        sflat, rflat, bflat = sbuf.view(-1), rbuf.view(-1), back.view(-1)
+
+        def through_api():
+            torch.index_select(x, 0, tok_of, out=sbuf)
+            comm.all_to_all_v(sflat, sc, sd, rflat, rcv, rd)              # dispatch
+            comm.all_to_all_v(rflat, rcv, rd, bflat, sc, sd)              # combine transport (identity experts)
+            torch.index_select(back, 0, inv, out=perm)
+            torch.bmm(gates_b, perm.view(tokens, topk, hidden), out=res3)
+        res.zero_()
+        out["alltoallv_api_ms"] = round(timed(through_api), 4)
+        assert comm.sync() == 0, comm.describe_status()
+        out["alltoallv_api_check_max_abs_err"] = round(float((res.float() - x.float()).abs().max()), 4)
+        out["alltoallv_api_speedup_vs_nccl"] = round(out["nccl_a2a_ms"] / out["alltoallv_api_ms"], 3)
     ex.close()
     return out

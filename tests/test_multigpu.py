@@ -90,3 +90,52 @@ def test_operator_retry_gives_up_after_max_attempts():
     env = dict(RETRY_ENV, HCCL_FAULT_INJECT="stall_rank:rank=1,op=2,ms=1500,attempts=3")
     outs = run_gpu_ranks(2, "retry_exhausted", env=env, timeout=240)
     assert all("retry exhausted ok" in o for _, o in outs)
+
+
+def test_comm_init_all_fused_kernels_two_gpus():
+    """One process, one thread per GPU (HcclCommInitAll): the fused kernels need their shared-memory opt-in on every device
+    of the process, and the threads share the process-wide workspace table."""
+    if ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    code = """
+import ctypes as C, threading, torch
+import cann_hccl_b200 as H
+from cann_hccl_b200 import _lib as L
+from cann_hccl_b200.parallel import fused_tp
+n = 2
+devs = (C.c_int32 * n)(0, 1); comms = (C.c_void_p * n)()
+L.check(L.lib().HcclCommInitAll(n, devs, comms), 'HcclCommInitAll')
+cs = [H.Communicator(comms[i], True) for i in range(n)]
+Ms, K, N = 256, 1024, 768
+def g(q, shape, seed, scale=1.0):
+    return (torch.randn(*shape, generator=torch.Generator().manual_seed(100 * seed + q)) * scale).to(torch.bfloat16)
+xs = [g(q, (Ms, K), 1) for q in range(n)]
+ws = [g(q, (N, K), 2, 0.05) for q in range(n)]
+hs = [g(q, (Ms * n, K), 3) for q in range(n)]
+errs = [None] * n
+def run(i):
+    try:
+        torch.cuda.set_device(i)
+        x, w, h = xs[i].cuda(), ws[i].cuda(), hs[i].cuda()
+        for _ in range(3):
+            y = fused_tp.all_gather_matmul(cs[i], x, w)
+            o = fused_tp.matmul_reduce_scatter(cs[i], h, w)
+        torch.cuda.synchronize()
+        assert cs[i].sync() == 0, cs[i].describe_status()
+        ref = torch.cat([t.float() for t in xs]) @ ws[i].float().t()
+        e1 = float((y.float().cpu() - ref).norm() / ref.norm())
+        full = sum(hq.float() @ wq.float().t() for hq, wq in zip(hs, ws))
+        e2 = float((o.float().cpu() - full[i * Ms:(i + 1) * Ms]).norm() / full.norm())
+        errs[i] = (e1, e2)
+    except Exception as e:
+        errs[i] = repr(e)
+ts = [threading.Thread(target=run, args=(i,)) for i in range(n)]
+[t.start() for t in ts]; [t.join() for t in ts]
+assert all(isinstance(e, tuple) and e[0] < 1e-2 and e[1] < 2e-2 for e in errs), errs
+ts = [threading.Thread(target=lambda c=c: c.destroy()) for c in cs]
+[t.start() for t in ts]; [t.join() for t in ts]
+print('INITALL FUSED OK', errs)
+"""
+    env = dict(os.environ, HCCL_EXEC_TIMEOUT_MS="20000", HCCL_CALIBRATE="0")
+    out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, cwd=os.path.dirname(HERE), timeout=300)
+    assert "INITALL FUSED OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
