@@ -256,6 +256,7 @@ def main():
     ap.add_argument("--sweep-max", type=int, default=1 << 30, help="largest per-rank message of the sweeps (bytes)")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the other collectives / fused-TP / MoE side tables")
+    ap.add_argument("--extras", default="collectives,fused_tp,moe", help="side tables to run: any of collectives, fused_tp, moe (comma-separated)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -509,7 +510,8 @@ def main():
     if not args.no_extras:
         try:
             import bench_extras
-            extras = bench_extras.run(comm, world, rank, dist, max_over_ranks, sync, min(args.sweep_max, 1 << 30), failures)
+            extras = bench_extras.run(comm, world, rank, dist, max_over_ranks, sync, min(args.sweep_max, 1 << 30), failures,
+                                      want=tuple(x for x in args.extras.split(",") if x))
         except Exception as e:  # side tables never take the headline down, but the run is marked failed
             extras = {"error": repr(e)[:300]}
             failures.append("extras raised")

@@ -42,7 +42,7 @@ struct EnvConfig {
     int pipe_slots = 0;            // HCCL_PIPE_SLOTS: ring depth of the pipelined kernels (0 = default, at most 16)
     int pipe_ctas[3] = {0, 0, 0};  // HCCL_PIPE_CTAS "a,b,c": CTAs of the copy-in / transfer / copy-out stage (0 = default)
     int pipe_groups[3] = {0, 0, 0};  // HCCL_PIPE_GROUPS "a,b,c": groups per stage that take chunks in turn (0 = default)
-    bool tp_gemm_pair = false;     // HCCL_TP_GEMM_PAIR: fused GEMM kernels on clusters of two CTAs (256 x 256 tiles, tcgen05 cta_group::2)
+    bool tp_gemm_pair = true;      // HCCL_TP_GEMM_PAIR=0: fused GEMM kernels on single CTAs only (default: clusters of two CTAs on 256 x 256 tiles, tcgen05 cta_group::2, where the shape allows)
     std::string ncc_lib;           // HCCL_NCCL_LIB: path of libnccl.so.2 for Send/Recv
     bool whitelist_enable = false; // HCCL_WHITELIST_DISABLE=0 switches the connection whitelist on (HCCL convention: 1 = off, the default)
     std::string whitelist_file;    // HCCL_WHITELIST_FILE: JSON {"host_ip": ["a.b.c.d", ...]} of addresses that may connect to the bootstrap hub

@@ -980,7 +980,9 @@ HcclResult Communicator::run_a2av(const OpRequest &rq)
 {
     const int p = nranks_, nl = nlocal(), es = dtype_size(rq.dtype);
     // lanes per ordered pair: all CTAs of a launch must fit the GPU at once when virtual ranks share it
-    int lanes = std::max(1, std::min(4, 148 / (2 * p * nl)));
+    // (a copy-engine driven CTA moves about 45 GB/s: 16 to 32 sending CTAs per rank carry the link rate; the lane count is
+    // part of the slot layout on the receiver, so it depends on the rank count only, never on a rank's own counts)
+    int lanes = std::max(1, std::min(kA2avMaxLanes, 128 / (2 * p * nl)));
     uint64_t sub = std::min<uint64_t>(2u << 20, settings_.stage_half_bytes / ((uint64_t)p * lanes * 2)) / 256 * 256;
     while (sub < 4096 && lanes > 1) { --lanes; sub = std::min<uint64_t>(2u << 20, settings_.stage_half_bytes / ((uint64_t)p * lanes * 2)) / 256 * 256; }
     CHK_RET_LOG(sub < 256, HCCL_E_MEMORY, "staging buffer too small for AlltoAllV over %d ranks", p);

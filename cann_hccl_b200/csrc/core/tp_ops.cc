@@ -144,6 +144,12 @@ HcclResult Communicator::tp_matmul_reduce_scatter(const void *const *h, const vo
     int nl = nlocal();
     CHK_RET_LOG(nl > kTpMaxLocal, HCCL_E_NOT_SUPPORT, "at most %d virtual ranks per GPU for the fused kernels", kTpMaxLocal);
     CHK_RET_LOG(M % (128 * nranks_) != 0, HCCL_E_PARA, "M (%d) must be a multiple of 128 x ranks (%d)", M, 128 * nranks_);
+    if (nranks_ == 1) {
+        // nothing to reduce or scatter: the product goes straight to the output, without a pass through a receive slot
+        stats_.launches++;
+        stats_.ops[COLL_REDUCE_SCATTER]++;
+        return gemm_bf16_plain(h[0], w[0], out[0], M, N, K, stream);
+    }
     std::ostringstream key;
     key << "rs:" << M << ':' << N << ':' << K;  // the panel layout of the completion counters depends on K as well
     void *wsp = nullptr;

@@ -10,7 +10,7 @@
 
 namespace hcclb {
 
-constexpr int kA2avMaxLanes = 8;
+constexpr int kA2avMaxLanes = 32;
 
 struct A2avArgs {
     const uint8_t *in;

@@ -206,29 +206,30 @@ def test_tensor_parallel_mlp_forward(comms):
         assert rel_err(got, want) < 3e-2
 
 
-def test_zz_pair_variant_was_used_when_requested():
-    """With HCCL_TP_GEMM_PAIR=1 the shapes above whose rows per rank come in multiples of 256 ran on clusters of two CTAs."""
+def test_zz_pair_variant_was_used_unless_switched_off():
+    """Shapes whose rows per rank come in multiples of 256 run on clusters of two CTAs; HCCL_TP_GEMM_PAIR=0 keeps every
+    launch on single CTAs."""
     import ctypes as C
     import os
     _need_gpu()
     single, pair = C.c_uint64(0), C.c_uint64(0)
     L.check(L.lib().HcclB200GemmLaunchCounts(C.byref(single), C.byref(pair)), "HcclB200GemmLaunchCounts")
-    if os.environ.get("HCCL_TP_GEMM_PAIR") == "1":
-        assert pair.value > 0 and single.value > 0, (single.value, pair.value)
+    if os.environ.get("HCCL_TP_GEMM_PAIR") == "0":
+        assert pair.value == 0 and single.value > 0, (single.value, pair.value)
     else:
-        assert pair.value == 0, (single.value, pair.value)
+        assert pair.value > 0 and single.value > 0, (single.value, pair.value)
 
 
-def test_zzz_whole_file_again_on_cta_pairs():
-    """Runs this file once more in a child process with the pair variant switched on (clusters of two CTAs sharing 256 x 256
-    tiles, tcgen05 cta_group::2): same shapes, same references."""
+def test_zzz_whole_file_again_on_single_ctas():
+    """Runs this file once more in a child process with the pair variant switched off (one CTA per 128 x 256 tile, tcgen05
+    cta_group::1): same shapes, same references."""
     import os
     import subprocess
     import sys
     _need_gpu()
-    if os.environ.get("HCCL_TP_GEMM_PAIR") == "1":
-        pytest.skip("already the pair run")
-    env = dict(os.environ, HCCL_TP_GEMM_PAIR="1")
+    if os.environ.get("HCCL_TP_GEMM_PAIR") == "0":
+        pytest.skip("already the single-CTA run")
+    env = dict(os.environ, HCCL_TP_GEMM_PAIR="0")
     r = subprocess.run([sys.executable, "-m", "pytest", os.path.abspath(__file__), "-x", "-q", "-m", "gpu"], env=env, capture_output=True, text=True,
                        cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))), timeout=1200)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-1500:]
