@@ -686,7 +686,8 @@ HcclResult Communicator::run_collective_once(const OpRequest &rq)
     // (two ranks: the in-switch reduction gains nothing over reading the one peer directly, which the peer-mapping form below does)
     if (rq.coll == COLL_ALLREDUCE && (p > 2 || (p == 2 && (rq.algo == ALGO_NVLS_ZC || host_tr))) && (nvls_ || host_tr) && !user_segs_.empty() &&
         (rq.algo == ALGO_AUTO || rq.algo == ALGO_NVLS_ZC) &&
-        (rq.algo == ALGO_NVLS_ZC || rq.count * es >= (512u << 10)) && !deterministic() &&
+        // (below 4 MiB the LL kernels are faster than the in-switch round trip even on registered buffers: measured on 4 GPUs)
+        (rq.algo == ALGO_NVLS_ZC || rq.count * es >= (ll_ok_ && !host_tr ? (4u << 20) : (512u << 10))) && !deterministic() &&
         nvls_reduce_supported(rq.dtype, rq.redop, rq.count * es) && forced_algo_for(env_config(), rq.coll).empty()) {
         bool mine = true;
         for (int li = 0; li < nl && mine; ++li) {
@@ -917,7 +918,8 @@ HcclResult Communicator::run_pipe(const OpRequest &rq, bool want_mc, int zc_hand
     uint64_t link_total = block_bytes * fan;
     uint64_t lc = env.pipe_chunk_bytes ? env.pipe_chunk_bytes : std::min<uint64_t>(8u << 20, std::max<uint64_t>(1u << 20, link_total / 2));
     int nslots = env.pipe_slots > 0 ? std::min(env.pipe_slots, kPipeMaxSlots) : kPipeMaxSlots;
-    const uint64_t unit = (uint64_t)p * (256 / es);  // elements: slices of a chunk stay 256-byte aligned
+    // elements: slices of a chunk stay 256-byte aligned (Reduce cuts a chunk into p - 1 slices and a slot into p - 1 source areas)
+    const uint64_t unit = (mode == PM_RD_PUSH ? (uint64_t)p * std::max(1, p - 1) : (uint64_t)p) * (256 / es);
     auto slot_of = [&](uint64_t ce) { return pipe_slot_bytes(mode, ce, es, p); };
     uint64_t ce = std::max<uint64_t>(unit, lc / fan / es / unit * unit);
     while (nslots > 4 && slot_of(ce) * nslots > settings_.stage_half_bytes) --nslots;

@@ -477,7 +477,14 @@ __global__ void __launch_bounds__(kExecThreads, 1) pipe_coll_kernel(const RankCt
             if (s_last && !s_fail && tid < p && tid != me) st_release_sys(c.flags[tid] + pipe_flag_index(kPipeWordDone, me, 0), now);
         }
     }
-    // Reduce: only the root has a receive buffer, the copy-out CTAs of the other ranks have nothing to do
+    // Reduce: every rank but the root owns a slice of each chunk (two ranks: the root owns all of it), so that the root only
+    // takes in reduced slices: one message's worth of bytes over each rank's links in each direction.  Owner k is rank
+    // rd_owner(k); an owner's slot holds the slices of its p - 1 sources, rd_se elements apart.
+    const int rd_nown = p == 2 ? 1 : p - 1;
+    auto rd_owner = [&](int k) { return p == 2 ? (int)a.root : (a.root + 1 + k < p ? a.root + 1 + k : a.root + 1 + k - p); };
+    const int rd_mine = p == 2 ? (me == a.root ? 0 : -1) : (me == a.root ? -1 : (me > a.root ? me - a.root - 1 : me + p - a.root - 1));
+    const uint64_t rd_se = ce / (uint64_t)rd_nown;
+    // only the root has a receive buffer, the copy-out CTAs of the other ranks have nothing to do
     const bool idle = pipe_mode_is_zc(mode) || (mode == PM_RD_PUSH && role == 2 && me != a.root);
     for (uint64_t ch = (uint64_t)group; ch < nchunks && !s_fail && !idle; ch += (uint64_t)ngroup) {
         const int slot = (int)(ch % (uint64_t)K);
@@ -549,6 +556,10 @@ __global__ void __launch_bounds__(kExecThreads, 1) pipe_coll_kernel(const RankCt
         const uint64_t per = round_up_u64(ceil_div_u64(nc, (uint64_t)p), vec);
         auto slo = [&](int q) { return per * (uint64_t)q < nc ? per * (uint64_t)q : nc; };
         auto shi = [&](int q) { return per * (uint64_t)(q + 1) < nc ? per * (uint64_t)(q + 1) : nc; };
+        // Reduce: the slices of a chunk belong to the owners (rd_nown of them), slice k = [rd_lo(k), rd_hi(k))
+        const uint64_t rd_per = round_up_u64(ceil_div_u64(nc, (uint64_t)rd_nown), vec);
+        auto rd_lo = [&](int k) { return rd_per * (uint64_t)k < nc ? rd_per * (uint64_t)k : nc; };
+        auto rd_hi = [&](int k) { return rd_per * (uint64_t)(k + 1) < nc ? rd_per * (uint64_t)(k + 1) : nc; };
         if (role == 0) {
             int nseg = 1;
             switch (mode) {
@@ -576,12 +587,25 @@ __global__ void __launch_bounds__(kExecThreads, 1) pipe_coll_kernel(const RankCt
                     nseg = p;
                     break;
                 }
-                case PM_AR2_PUSH: case PM_RD_PUSH: case PM_RS_PUSH: case PM_AR1_PUSH: {
+                case PM_RD_PUSH: {
+                    // my slice for owner k goes into that owner's slot, at my position among its p - 1 sources
+                    nseg = rd_nown - (rd_mine >= 0 ? 1 : 0);
+                    if (tid < nseg) {
+                        const int k = rd_mine >= 0 && tid >= rd_mine ? tid + 1 : tid;  // owners but me
+                        const int q = rd_owner(k);
+                        chan_range(rd_hi(k) - rd_lo(k), es, gsize, gidx, lo, hi);
+                        s_src[tid] = a.in + (e0 + rd_lo(k) + lo) * es;
+                        s_dst[tid] = c.stage[q] + soff + ((uint64_t)(me < q ? me : me - 1) * rd_se + lo) * es;
+                        s_bytes[tid] = hi > lo ? (hi - lo) * es : 0;
+                    }
+                    break;
+                }
+                case PM_AR2_PUSH: case PM_RS_PUSH: case PM_AR1_PUSH: {
                     // segment k goes to rank q = me + 1 + k: its slice of my chunk (two-shot), its block of my chunk
                     // (ReduceScatter), or the whole chunk (one-shot)
                     if (tid < p - 1) {
                         const int q = me + 1 + tid < p ? me + 1 + tid : me + 1 + tid - p;
-                        if (mode == PM_AR2_PUSH || mode == PM_RD_PUSH) {
+                        if (mode == PM_AR2_PUSH) {
                             chan_range(shi(q) - slo(q), es, gsize, gidx, lo, hi);
                             s_src[tid] = a.in + (e0 + slo(q) + lo) * es;
                             s_dst[tid] = c.stage[q] + soff + ((uint64_t)me * se + lo) * es;
@@ -628,11 +652,12 @@ __global__ void __launch_bounds__(kExecThreads, 1) pipe_coll_kernel(const RankCt
                     break;
                 }
                 case PM_RD_PUSH: {
-                    chan_range(shi(me) - slo(me), es, gsize, gidx, lo, hi);
+                    if (rd_mine < 0) break;  // not an owner: nothing to reduce (the stage still publishes, for the slot bookkeeping)
+                    chan_range(rd_hi(rd_mine) - rd_lo(rd_mine), es, gsize, gidx, lo, hi);
                     if (tid < p) {
-                        const uint64_t mo = (e0 + slo(me) + lo) * es;
-                        s_src[tid] = tid == me ? a.in + mo : mine + soff + ((uint64_t)tid * se + lo) * es;
-                        if (tid == 0) s_dst[0] = me == a.root ? a.out + mo : c.stage[a.root] + soff + (ce + slo(me) + lo) * es;
+                        const uint64_t mo = (e0 + rd_lo(rd_mine) + lo) * es;
+                        s_src[tid] = tid == me ? a.in + mo : mine + soff + ((uint64_t)(tid < me ? tid : tid - 1) * rd_se + lo) * es;
+                        if (tid == 0) s_dst[0] = me == a.root ? a.out + mo : c.stage[a.root] + soff + (ce + rd_lo(rd_mine) + lo) * es;
                     }
                     __syncthreads();
                     reduce_sources(1, hi > lo ? hi - lo : 0);
@@ -688,8 +713,11 @@ __global__ void __launch_bounds__(kExecThreads, 1) pipe_coll_kernel(const RankCt
             if (tid == 0) {
                 const bool push = mode == PM_AR2_PUSH || mode == PM_RD_PUSH;
                 const uint64_t roff = push ? ce * es : 0;
+                // what the reduce stage of this rank wrote straight to the receive buffer: its own slice
+                uint64_t own_lo = slo(me), own_hi = shi(me);
+                if (mode == PM_RD_PUSH) { own_lo = rd_mine >= 0 ? rd_lo(rd_mine) : 0; own_hi = rd_mine >= 0 ? rd_hi(rd_mine) : 0; }
                 uint64_t a0 = lo, a1 = hi, b0 = hi, b1 = hi;
-                if (push) { a1 = hi < slo(me) ? hi : slo(me); b0 = lo > shi(me) ? lo : shi(me); }
+                if (push) { a1 = hi < own_lo ? hi : own_lo; b0 = lo > own_hi ? lo : own_hi; if (a1 < a0) a1 = a0; }
                 s_src[0] = mine + soff + roff + a0 * es; s_dst[0] = a.out + (e0 + a0) * es; s_bytes[0] = a1 > a0 ? (a1 - a0) * es : 0;
                 s_src[1] = mine + soff + roff + b0 * es; s_dst[1] = a.out + (e0 + b0) * es; s_bytes[1] = b1 > b0 ? (b1 - b0) * es : 0;
             }

@@ -33,7 +33,7 @@ enum PipeMode : int32_t {
     PM_RS_ZC,       // ReduceScatter: every rank reduces its block of all p send buffers into its receive buffer
     PM_AG_ZC,       // AllGather: every rank pulls the peers' send buffers straight into its receive buffer
     // Reduce: the two-shot AllReduce with the reduced slices stored to the root only, which alone copies out
-    PM_RD_PUSH,     // Reduce: push slice q to rank q | reduce my slice locally, store the result to the root | root: copy-out
+    PM_RD_PUSH,     // Reduce: push slice k to its owner (every rank but the root) | owners reduce, store the result to the root | root: copy-out
     PM_COUNT
 };
 

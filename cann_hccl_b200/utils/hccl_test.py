@@ -215,19 +215,30 @@ def worker(a):
             fn(a.iters)
             return (time.perf_counter() - t0) * 1e6 / a.iters
         times = [timed(call)]
+        notes = []
+
+        def stage_times(label):
+            """In-kernel stage times of the newest launch when that was a pipelined kernel (its trace has another layout)."""
+            if not (a.trace and rank == 0 and device):
+                return
+            last = comm.trace()[-1]["algo"]
+            text = "    %s ran %s" % (label, last)
+            if last in ("mesh_pipe", "nvls_pipe", "mesh_zerocopy"):
+                import ctypes as C
+                buf = (C.c_uint64 * 16)()
+                ns = C.c_int(0)
+                if L.lib().HcclB200GetKernelTrace(comm.handle, 0, buf, 16, C.byref(ns)) == 0 and buf[0] not in (0, 2 ** 64 - 1):
+                    text += "; stage times of its newest launch (us): " + " | ".join(
+                        "stage %d wait %.1f work %.1f publish %.1f" % (k, buf[1 + 4 * k] / 1e3, buf[2 + 4 * k] / 1e3, buf[3 + 4 * k] / 1e3) for k in range(3))
+            notes.append(text)
+        stage_times("the selector's choice:")
         for x in extra_algos:
             kx = dict(kw, algo=L.ALGO_NAMES.index(x))
             try:
                 times.append(timed(lambda k: comm.repeat(coll, send, recv, count, hd, k, **kx) if k > 0 else None))
+                stage_times("forced %s:" % x)
             except H.HcclError:
                 times.append(float("nan"))  # the algorithm does not exist for this collective / type / size
-        if a.trace and rank == 0 and device:
-            import ctypes as C
-            buf = (C.c_uint64 * 16)()
-            ns = C.c_int(0)
-            if L.lib().HcclB200GetKernelTrace(comm.handle, 0, buf, 16, C.byref(ns)) == 0 and buf[0] not in (0, 2 ** 64 - 1):
-                print("    stages of the newest pipelined launch (us): " + " | ".join(
-                    "stage %d wait %.1f work %.1f publish %.1f" % (k, buf[1 + 4 * k] / 1e3, buf[2 + 4 * k] / 1e3, buf[3 + 4 * k] / 1e3) for k in range(3)))
         if dist is not None:
             nccl_fn = {"all_reduce_test": lambda: dist.all_reduce(recv if recv is not send else send, op={0: dist.ReduceOp.SUM, 1: dist.ReduceOp.PRODUCT, 2: dist.ReduceOp.MAX, 3: dist.ReduceOp.MIN}[op]),
                        "all_gather_test": lambda: dist.all_gather_into_tensor(recv, send),
@@ -254,6 +265,8 @@ def worker(a):
             if dist is not None:
                 line += " %-16.2f %-16.5f" % (times[-1], count * es / times[-1] / 1e3)
             print(line, flush=True)
+            for t in notes:
+                print(t, flush=True)
         del send, recv
         size = size * a.factor if a.factor > 1 else size + max(1, a.step)
     code = comm.destroy()

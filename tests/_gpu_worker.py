@@ -84,7 +84,7 @@ def scenario_collectives(c, p, r, args):
                     raise AssertionError("allreduce n=%d algo=%s dtype=%s op=%d: %d bad elements, first %d last %d\n%s" % (
                         n, L.ALGO_NAMES[algo], dtype, op, int(bad.sum()), int(idx[0]), int(idx[-1]), str(e)[:300]))
     if nvls:  # zero-copy on registered symmetric memory
-        n = 1_000_000
+        n = 2_000_000
         hin, (zin,) = c.symmetric_empty(n, torch.float32)
         hout, (zout,) = c.symmetric_empty(n, torch.float32)
         xs = [inp(q, n, torch.float32, seed=21) for q in range(p)]
