@@ -718,7 +718,6 @@ HcclResult Communicator::run_collective_once(const OpRequest &rq)
     CHK_RET(consistency_check(rq, sel.algo, use_zc ? ((uint64_t)zc[0].hin << 48) ^ zc[0].oin : 0, use_zc ? ((uint64_t)zc[0].hout << 48) ^ zc[0].oout : 0));
     if (sel.algo == ALGO_LL) {
         bool fits = rq.coll == COLL_ALLREDUCE && ll_ok_ && rq.count * es <= ll_max_bytes();
-        for (int li = 0; li < nl && fits; ++li) fits = (((uintptr_t)rq.in[li] | (uintptr_t)rq.out[li]) & 7) == 0;
         if (fits) {
             HcclResult lrc = run_ll_allreduce(rq);
             stats_.ops[rq.coll]++;
@@ -728,7 +727,7 @@ HcclResult Communicator::run_collective_once(const OpRequest &rq)
             return lrc;
         }
         CHK_RET_LOG(rq.algo == ALGO_LL && !ll_ok_, HCCL_E_NOT_SUPPORT, "the LL AllReduce needs the device transport and more than one rank");
-        sel.algo = ALGO_MESH_ONESHOT;  // unaligned or oversized: the plan executor handles every layout
+        sel.algo = ALGO_MESH_ONESHOT;  // oversized (a decision every rank makes alike: it depends on the count only)
     }
 
     // registered send buffer (the same allocation and offset on every rank, by the contract of symmetric memory): two-rank

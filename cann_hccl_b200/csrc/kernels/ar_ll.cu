@@ -66,11 +66,14 @@ __global__ void __launch_bounds__(kLlThreads) ar_ll_kernel(const LlArgsArray arg
     const uint64_t deadline = global_timer_ns() + a.timeout_ns;
     const T *in = (const T *)a.in;
     T *out = (T *)a.out;
+    // buffers that are only element-aligned take the element-wise path: which path a rank takes is its own business, the
+    // lines on the wire are the same
+    const bool in8 = ((uintptr_t)in & 7) == 0, out8 = ((uintptr_t)out & 7) == 0;
     const uint64_t first = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (uint64_t)gridDim.x * blockDim.x;
     auto load_mine = [&](uint64_t line) {
         Pay8<T> mine;
         const uint64_t e0 = line * E;
-        if (e0 + E <= a.count) mine.u = *(const uint2 *)(in + e0);
+        if (in8 && e0 + E <= a.count) mine.u = *(const uint2 *)(in + e0);
         else {
             mine.u = make_uint2(0, 0);
             for (int k = 0; k < E; ++k)
@@ -135,7 +138,7 @@ __global__ void __launch_bounds__(kLlThreads) ar_ll_kernel(const LlArgsArray arg
         Pay8<T> r;
 #pragma unroll
         for (int k = 0; k < E; ++k) r.e[k] = N::down(acc[k]);
-        if (e0 + E <= a.count) *(uint2 *)(out + e0) = r.u;
+        if (out8 && e0 + E <= a.count) *(uint2 *)(out + e0) = r.u;
         else
             for (int k = 0; k < E; ++k)
                 if (e0 + k < a.count) out[e0 + k] = r.e[k];
@@ -193,11 +196,14 @@ __global__ void __launch_bounds__(kLlThreads) ar_ll2_kernel(const LlArgsArray ar
     const uint64_t deadline = global_timer_ns() + a.timeout_ns;
     const T *in = (const T *)a.in;
     T *out = (T *)a.out;
+    // buffers that are only element-aligned take the element-wise path: which path a rank takes is its own business, the
+    // lines on the wire are the same
+    const bool in8 = ((uintptr_t)in & 7) == 0, out8 = ((uintptr_t)out & 7) == 0;
     const uint64_t first = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (uint64_t)gridDim.x * blockDim.x;
     auto load_mine = [&](uint64_t line) {
         Pay8<T> mine;
         const uint64_t e0 = line * E;
-        if (e0 + E <= a.count) mine.u = *(const uint2 *)(in + e0);
+        if (in8 && e0 + E <= a.count) mine.u = *(const uint2 *)(in + e0);
         else {
             mine.u = make_uint2(0, 0);
             for (int k = 0; k < E; ++k)
@@ -207,7 +213,7 @@ __global__ void __launch_bounds__(kLlThreads) ar_ll2_kernel(const LlArgsArray ar
     };
     auto store_out = [&](uint64_t line, Pay8<T> r) {
         const uint64_t e0 = line * E;
-        if (e0 + E <= a.count) *(uint2 *)(out + e0) = r.u;
+        if (out8 && e0 + E <= a.count) *(uint2 *)(out + e0) = r.u;
         else
             for (int k = 0; k < E; ++k)
                 if (e0 + k < a.count) out[e0 + k] = r.e[k];

@@ -106,6 +106,25 @@ def test_allreduce_low_latency_protocol(comms, p, dtype, op):
     assert c.stats()["algos"].get("ll", 0) >= 12
 
 
+@pytest.mark.parametrize("p", [2, 4])
+def test_allreduce_low_latency_element_aligned_views(comms, p):
+    """Views that are only element-aligned on SOME ranks: every rank still runs the LL kernels (which path a rank's loads and
+    stores take is its own business), so the ranks cannot end up in different algorithms."""
+    c = comms(p)
+    for dtype, n in ((torch.float32, 10_001), (torch.bfloat16, 33_333), (torch.float32, 150_000)):  # one-shot; one-shot; two-shot on four ranks
+        base_in = rnd(p, n + 3, dtype, seed=n % 53)
+        base_out = [torch.zeros(n + 3, device="cuda", dtype=dtype) for _ in range(p)]
+        ins = [base_in[r][(r % 2):(r % 2) + n] for r in range(p)]          # odd ranks start one element in
+        outs = [base_out[r][((r + 1) % 2) * 3:((r + 1) % 2) * 3 + n] for r in range(p)]  # even ranks' outputs start three elements in
+        for _ in range(2):
+            c.all_reduce(ins, outs, algo=L.ALGO_LL)
+        ok(c)
+        assert c.trace()[-1]["algo"] == "ll"
+        ref = ref_reduce(ins, L.SUM)
+        for o in outs:
+            close(o, ref, dtype, p)
+
+
 @pytest.mark.parametrize("p", [3, 4, 8])
 @pytest.mark.parametrize("dtype,op", [(torch.float32, L.SUM), (torch.bfloat16, L.MAX), (torch.int32, L.MIN), (torch.float64, L.PROD)])
 def test_allreduce_low_latency_two_shot(comms, p, dtype, op):
