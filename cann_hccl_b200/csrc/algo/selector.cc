@@ -43,8 +43,8 @@ static bool algo_exists(int coll, int algo)
 {
     switch (coll) {
         case COLL_ALLREDUCE: return algo == ALGO_MESH || algo == ALGO_MESH_ONESHOT || algo == ALGO_RING || algo == ALGO_RHD || algo == ALGO_NVLS || algo == ALGO_NVLS_ONESHOT || algo == ALGO_MESH_PIPE || algo == ALGO_NVLS_PIPE || algo == ALGO_LL || algo == ALGO_NVLS_ZC;
-        case COLL_REDUCE_SCATTER: return algo == ALGO_MESH || algo == ALGO_RING || algo == ALGO_RHD || algo == ALGO_NVLS || algo == ALGO_MESH_PIPE || algo == ALGO_NVLS_PIPE;
-        case COLL_ALLGATHER: return algo == ALGO_MESH || algo == ALGO_RING || algo == ALGO_RHD || algo == ALGO_NVLS || algo == ALGO_PAIRWISE || algo == ALGO_MESH_PIPE;
+        case COLL_REDUCE_SCATTER: return algo == ALGO_MESH || algo == ALGO_RING || algo == ALGO_RHD || algo == ALGO_NVLS || algo == ALGO_MESH_PIPE || algo == ALGO_NVLS_PIPE || algo == ALGO_LL;
+        case COLL_ALLGATHER: return algo == ALGO_MESH || algo == ALGO_RING || algo == ALGO_RHD || algo == ALGO_NVLS || algo == ALGO_PAIRWISE || algo == ALGO_MESH_PIPE || algo == ALGO_LL;
         case COLL_REDUCE_SCATTER_V: return algo == ALGO_MESH || algo == ALGO_RING || algo == ALGO_NVLS;
         case COLL_ALLGATHER_V: return algo == ALGO_MESH || algo == ALGO_RING || algo == ALGO_NVLS || algo == ALGO_PAIRWISE;
         case COLL_BROADCAST: return algo == ALGO_STAR || algo == ALGO_RING || algo == ALGO_TREE || algo == ALGO_NVLS || algo == ALGO_MESH_PIPE || algo == ALGO_NVLS_PIPE;
@@ -84,6 +84,7 @@ double estimate_us(int coll, int algo, uint64_t bytes, int p, const CostModel &m
             break;
         case COLL_REDUCE_SCATTER: case COLL_REDUCE_SCATTER_V:  // bytes = one rank's result
             switch (algo) {
+                case ALGO_LL: return L + 0.6 * a + 2.0 * (p - 1) * n / B + p * n / G;  // lines carry 50 % payload; no fence, no flag hop
                 case ALGO_MESH: return L + a + (p - 1) * n / B + p * n / G + (p + 1) * s;
                 case ALGO_RING: return L + (p - 1) * (a + s) + (p - 1) * n / B;
                 case ALGO_RHD: return L + (lg + (pow2 ? 0 : 1)) * (a + s) + (pow2 ? (p - 1) : (2 * p - 1)) * n / B + p * n / G;
@@ -94,6 +95,7 @@ double estimate_us(int coll, int algo, uint64_t bytes, int p, const CostModel &m
             break;
         case COLL_ALLGATHER: case COLL_ALLGATHER_V:  // bytes = one rank's contribution
             switch (algo) {
+                case ALGO_LL: return L + 0.6 * a + 2.0 * (p - 1) * n / B + p * n / G;
                 case ALGO_MESH: return L + a + (p - 1) * n / B + n / G + 2 * s;
                 case ALGO_RING: return L + (p - 1) * (a + s) + (p - 1) * n / B;
                 case ALGO_PAIRWISE: return L + a + (p - 1) * n / B + (p - 1) * n / G + (p + 1) * s;  // push: no staging copy, copy-out per slot

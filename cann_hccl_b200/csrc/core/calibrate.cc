@@ -143,8 +143,8 @@ HcclResult Communicator::calibrate(void *stream)
     // ---- measured tables
     const std::vector<Candidate> cands = {
         {COLL_ALLREDUCE, {ALGO_LL, ALGO_MESH_ONESHOT, ALGO_NVLS_ONESHOT, ALGO_MESH, ALGO_NVLS, ALGO_RING, ALGO_MESH_PIPE, ALGO_NVLS_PIPE}},
-        {COLL_ALLGATHER, {ALGO_MESH, ALGO_PAIRWISE, ALGO_RING, ALGO_NVLS, ALGO_MESH_PIPE}},
-        {COLL_REDUCE_SCATTER, {ALGO_MESH, ALGO_RING, ALGO_NVLS, ALGO_MESH_PIPE, ALGO_NVLS_PIPE}},
+        {COLL_ALLGATHER, {ALGO_LL, ALGO_MESH, ALGO_PAIRWISE, ALGO_RING, ALGO_NVLS, ALGO_MESH_PIPE}},
+        {COLL_REDUCE_SCATTER, {ALGO_LL, ALGO_MESH, ALGO_RING, ALGO_NVLS, ALGO_MESH_PIPE, ALGO_NVLS_PIPE}},
         {COLL_BROADCAST, {ALGO_STAR, ALGO_RING, ALGO_TREE, ALGO_NVLS, ALGO_MESH_PIPE, ALGO_NVLS_PIPE}},
         {COLL_REDUCE, {ALGO_STAR, ALGO_RING, ALGO_TREE, ALGO_RHD, ALGO_MESH_PIPE}},
         {COLL_SCATTER, {ALGO_STAR, ALGO_RING}},
@@ -167,7 +167,7 @@ HcclResult Communicator::calibrate(void *stream)
                 const bool is_nvls = a == ALGO_NVLS || a == ALGO_NVLS_ONESHOT || a == ALGO_NVLS_PIPE;
                 const bool is_pipe = a == ALGO_MESH_PIPE || a == ALGO_NVLS_PIPE;
                 bool skip = !listed || (is_nvls && !nvls_);
-                skip = skip || (a == ALGO_LL && (!ll_ok_ || sz > ll_max_bytes()));
+                skip = skip || (a == ALGO_LL && (!ll_ok_ || sz > (cd.coll == COLL_ALLREDUCE ? ll_max_bytes() : ll_block_max())));
                 skip = skip || (is_pipe && sz < (1u << 20));                                                   // three stages of hand-offs cost tens of microseconds
                 skip = skip || ((a == ALGO_MESH_ONESHOT || a == ALGO_NVLS_ONESHOT) && sz > (8u << 20) && p > 2);  // (p-1) times the bytes
                 skip = skip || ((a == ALGO_RING || a == ALGO_TREE) && sz < (256u << 10) && cd.coll != COLL_BROADCAST);

@@ -253,7 +253,10 @@ HcclResult Communicator::init_common()
         x.status = status_[li];
         x.abort = abort_[li];
         x.exit_counter = dev ? (uint32_t *)dev_exit_ + 4 * li : nullptr;
-        x.dev_tail = dev ? (uint64_t *)((uint32_t *)dev_exit_ + 4 * li + 2) : nullptr;
+        // completion word of the op-execution counter: host-mapped, so that the heartbeat thread reads it without a CUDA call
+        // (a CUDA call can wait for seconds behind an allocation or a mapping made by another thread of the process, and a
+        // silent heartbeat makes the peers report this rank as lost)
+        x.dev_tail = dev ? (uint64_t *)(pb + align_up(sizeof(DevStatus), 64) + 16) : nullptr;
         x.pipe_cnt = dev ? (uint32_t *)dev_pipe_cnt_ + (size_t)li * kPipeCounterWords : nullptr;
         x.stage_half = half;
         x.trace = dev_trace_ ? (uint64_t *)dev_trace_ + (size_t)li * kTraceWords : nullptr;
@@ -447,7 +450,7 @@ Selection Communicator::select(int coll, uint64_t count, int dtype, int redop) c
     si.expansion_mode = settings_.expansion_mode ? settings_.expansion_mode : env.expansion_mode;
     si.max_channels = si.device ? (nranks_ == 1 ? 128 : 64) : 2;  // a single rank never waits: all SMs may copy
     si.forced = forced_algo_for(env, coll);
-    si.ll_max_bytes = ll_ok_ ? ll_max_bytes() : 0;
+    si.ll_max_bytes = !ll_ok_ ? 0 : (coll == COLL_ALLREDUCE ? ll_max_bytes() : ll_block_max());
     Selection s = select_algo(si, model_);
     const int table_coll = coll == COLL_ALLGATHER_V ? COLL_ALLGATHER : (coll == COLL_REDUCE_SCATTER_V ? COLL_REDUCE_SCATTER : coll);
     auto tt = tuned_.find(table_coll);
@@ -469,7 +472,7 @@ Selection Communicator::select(int coll, uint64_t count, int dtype, int redop) c
             double t = tb.us[best_b][a];
             if (t <= 0) continue;
             if ((a == ALGO_NVLS || a == ALGO_NVLS_ONESHOT || a == ALGO_NVLS_PIPE) && !nvls_ok) continue;
-            if (a == ALGO_LL && (si.bytes > si.ll_max_bytes || si.expansion_mode == 1)) continue;
+            if (a == ALGO_LL && (si.bytes > si.ll_max_bytes || si.expansion_mode == 1 || is_v)) continue;
             if ((a == ALGO_MESH_PIPE || a == ALGO_NVLS_PIPE) && (is_v || si.expansion_mode == 1)) continue;
             if (is_v && (a == ALGO_RHD || a == ALGO_PAIRWISE) && coll == COLL_REDUCE_SCATTER_V) continue;
             if (bt < 0 || t < bt) { bt = t; s.algo = a; }
@@ -717,7 +720,8 @@ HcclResult Communicator::run_collective_once(const OpRequest &rq)
     if (is_a2av) CHK_RET(a2av_check(rq));
     CHK_RET(consistency_check(rq, sel.algo, use_zc ? ((uint64_t)zc[0].hin << 48) ^ zc[0].oin : 0, use_zc ? ((uint64_t)zc[0].hout << 48) ^ zc[0].oout : 0));
     if (sel.algo == ALGO_LL) {
-        bool fits = rq.coll == COLL_ALLREDUCE && ll_ok_ && rq.count * es <= ll_max_bytes();
+        const bool blocked = rq.coll == COLL_REDUCE_SCATTER || rq.coll == COLL_ALLGATHER;  // count = one rank's block
+        bool fits = ll_ok_ && ((rq.coll == COLL_ALLREDUCE && rq.count * es <= ll_max_bytes()) || (blocked && rq.count * es <= ll_block_max()));
         if (fits) {
             HcclResult lrc = run_ll_allreduce(rq);
             stats_.ops[rq.coll]++;
@@ -726,8 +730,9 @@ HcclResult Communicator::run_collective_once(const OpRequest &rq)
             record_trace(rq, ALGO_LL, 0, rq.count * es, now_us() - t0);
             return lrc;
         }
-        CHK_RET_LOG(rq.algo == ALGO_LL && !ll_ok_, HCCL_E_NOT_SUPPORT, "the LL AllReduce needs the device transport and more than one rank");
-        sel.algo = ALGO_MESH_ONESHOT;  // oversized (a decision every rank makes alike: it depends on the count only)
+        CHK_RET_LOG(rq.algo == ALGO_LL && !ll_ok_, HCCL_E_NOT_SUPPORT, "the LL kernels need the device transport and more than one rank");
+        CHK_RET_LOG(rq.algo == ALGO_LL && !blocked && rq.coll != COLL_ALLREDUCE, HCCL_E_NOT_SUPPORT, "the LL protocol exists for AllReduce, ReduceScatter and AllGather");
+        sel.algo = blocked ? ALGO_MESH : ALGO_MESH_ONESHOT;  // oversized (a decision every rank makes alike: it depends on the count only)
     }
 
     // registered send buffer (the same allocation and offset on every rank, by the contract of symmetric memory): two-rank
@@ -1022,7 +1027,9 @@ HcclResult Communicator::run_ll_allreduce(const OpRequest &rq)
     int nl = nlocal();
     // two-shot from three ranks on once the message is large enough for the saved link bytes to pay for the second hop
     const uint64_t bytes = rq.count * (uint64_t)dtype_size(rq.dtype);
-    const bool two_shot = nranks_ >= 3 && bytes >= ll_two_shot_min_ && bytes <= ll_two_shot_max(nranks_);
+    uint32_t kind = nranks_ >= 3 && bytes >= ll_two_shot_min_ && bytes <= ll_two_shot_max(nranks_) ? LL_AR_TWOSHOT : LL_AR_ONESHOT;
+    if (rq.coll == COLL_REDUCE_SCATTER) kind = LL_REDUCE_SCATTER;
+    else if (rq.coll == COLL_ALLGATHER) kind = LL_ALLGATHER;
     ++ll_seq_;
     uint32_t tag = (uint32_t)(ll_seq_ & 0xffffffffu);
     if (tag == 0) { ++ll_seq_; tag = 1; }
@@ -1044,7 +1051,7 @@ HcclResult Communicator::run_ll_allreduce(const OpRequest &rq)
         a.nranks = nranks_;
         a.tag = tag;
         a.parity = (uint32_t)(ll_seq_ & 1);
-        a.two_shot = two_shot ? 1u : 0u;
+        a.two_shot = kind;
         // the LL path does not consume a plan sequence number: its op-execution id lives in a range of its own
         a.exit_counter = ctx_[li].exit_counter;
         a.dev_tail = ctx_[li].dev_tail;
@@ -1532,15 +1539,7 @@ void Communicator::heartbeat_loop()
         m.epoch = (uint32_t)resume_gen_.load();
         DevStatus *s = status_[0];
         if (settings_.transport == TR_DEVICE && ctx_[0].dev_tail) {
-            if (!hb_stream_) {
-                cudaSetDevice(settings_.device);
-                cudaStream_t st;
-                if (cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) == cudaSuccess) hb_stream_ = st;
-            }
-            uint64_t tail = 0;
-            if (hb_stream_ && cudaMemcpyAsync(&tail, ctx_[0].dev_tail, 8, cudaMemcpyDeviceToHost, (cudaStream_t)hb_stream_) == cudaSuccess &&
-                cudaStreamSynchronize((cudaStream_t)hb_stream_) == cudaSuccess)
-                s->tail = tail;
+            s->tail = __atomic_load_n((volatile uint64_t *)ctx_[0].dev_tail, __ATOMIC_RELAXED);
         }
         // the executing thread (or the GPU) writes these words while this thread reads them
         m.head = __atomic_load_n(&s->head, __ATOMIC_RELAXED); m.tail = __atomic_load_n(&s->tail, __ATOMIC_RELAXED);

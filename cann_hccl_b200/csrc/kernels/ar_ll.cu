@@ -280,8 +280,123 @@ __global__ void __launch_bounds__(kLlThreads) ar_ll2_kernel(const LlArgsArray ar
     }
 }
 
-template <class T> const void *ll_kernel_of(int op, bool two_shot)
+// ReduceScatter and AllGather in the LL protocol: the two phases of the two-shot AllReduce as collectives of their own.
+// a.count = elements of one rank's block.  ReduceScatter: block q of my input goes to its owner's area A (piece `me`), I
+// reduce my block from the p - 1 pieces that arrive plus my own.  AllGather: my block goes to area B (piece `me`) of every
+// peer, the peers' blocks arrive in mine.  Blocks start wherever the caller's count puts them, so loads and stores fall back
+// to single elements where a block is not 8-byte aligned.
+template <class T, int OP>
+__global__ void __launch_bounds__(kLlThreads) ll_rsag_kernel(const LlArgsArray args)
 {
+    const LlArgs &a = args.a[blockIdx.y];
+    using N = LNum<T>;
+    using Acc = typename N::Acc;
+    constexpr int E = 8 / sizeof(T);
+    const int me = a.rank, p = a.nranks;
+    const bool rs = a.two_shot == LL_REDUCE_SCATTER;
+    const uint64_t bl = (a.count + E - 1) / E;  // lines per block
+    const uint64_t half = (uint64_t)p * a.slot_bytes, piece = half / 2 / p;
+    const uint64_t base_a = (uint64_t)a.parity * half, base_b = base_a + half / 2;
+    const uint64_t deadline = global_timer_ns() + a.timeout_ns;
+    const T *in = (const T *)a.in;
+    T *out = (T *)a.out;
+    const uint64_t first = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (uint64_t)gridDim.x * blockDim.x;
+    auto load_blk = [&](const T *base, uint64_t line) {
+        Pay8<T> v;
+        const uint64_t e0 = line * E;
+        if ((((uintptr_t)base) & 7) == 0 && e0 + E <= a.count) v.u = *(const uint2 *)(base + e0);
+        else {
+            v.u = make_uint2(0, 0);
+            for (int k = 0; k < E; ++k)
+                if (e0 + k < a.count) v.e[k] = base[e0 + k];
+        }
+        return v;
+    };
+    auto store_blk = [&](T *base, uint64_t line, Pay8<T> r) {
+        const uint64_t e0 = line * E;
+        if ((((uintptr_t)base) & 7) == 0 && e0 + E <= a.count) *(uint2 *)(base + e0) = r.u;
+        else
+            for (int k = 0; k < E; ++k)
+                if (e0 + k < a.count) base[e0 + k] = r.e[k];
+    };
+    bool failed = false;
+    if (rs) {
+        for (uint64_t idx = first; idx < bl * (uint64_t)p; idx += stride) {
+            const int q = (int)(idx / bl);
+            if (q == me) continue;
+            const uint64_t line = idx - (uint64_t)q * bl;
+            Pay8<T> v = load_blk(in + (uint64_t)q * a.count, line);
+            st_line(a.ll[q] + base_a + (uint64_t)me * piece + line * 16, v.u.x, v.u.y, a.tag);
+        }
+        for (uint64_t line = first; line < bl && !failed; line += stride) {
+            Pay8<T> mine = load_blk(in + (uint64_t)me * a.count, line);
+            Acc acc[E];
+            for (int q = 0; q < p && !failed; ++q) {
+                Pay8<T> v;
+                if (q == me) v = mine;
+                else {
+                    uint4 l;
+                    if (!ll_poll(a, a.ll[me] + base_a + (uint64_t)q * piece + line * 16, deadline, q, l)) { failed = true; break; }
+                    v.u = make_uint2(l.x, l.z);
+                }
+                if (q == 0) {
+#pragma unroll
+                    for (int k = 0; k < E; ++k) acc[k] = N::up(v.e[k]);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < E; ++k) acc[k] = ll_op<OP>(acc[k], N::up(v.e[k]));
+                }
+            }
+            if (failed) break;
+            Pay8<T> r;
+#pragma unroll
+            for (int k = 0; k < E; ++k) r.e[k] = N::down(acc[k]);
+            store_blk(out, line, r);
+        }
+    } else {
+        T *own = out + (uint64_t)me * a.count;
+        for (uint64_t line = first; line < bl; line += stride) {
+            Pay8<T> v = load_blk(in, line);
+            for (int i = 1; i < p; ++i) {
+                int q = me + i;
+                if (q >= p) q -= p;
+                st_line(a.ll[q] + base_b + (uint64_t)me * piece + line * 16, v.u.x, v.u.y, a.tag);
+            }
+            if ((const T *)own != in) store_blk(own, line, v);
+        }
+        for (uint64_t idx = first; idx < bl * (uint64_t)p && !failed; idx += stride) {
+            const int q = (int)(idx / bl);
+            if (q == me) continue;
+            const uint64_t line = idx - (uint64_t)q * bl;
+            uint4 l;
+            if (!ll_poll(a, a.ll[me] + base_b + (uint64_t)q * piece + line * 16, deadline, q, l)) { failed = true; break; }
+            Pay8<T> r;
+            r.u = make_uint2(l.x, l.z);
+            store_blk(out + (uint64_t)q * a.count, line, r);
+        }
+    }
+    if (failed) return;  // head stays ahead of tail: the heartbeat reports the op as stuck / failed
+    __syncthreads();
+    if (threadIdx.x == 0 && a.exit_counter) {
+        __threadfence();
+        if (atomicAdd(a.exit_counter, 1u) == gridDim.x - 1) {
+            *a.exit_counter = 0;
+            *a.dev_tail = a.exe_id;
+        }
+    }
+}
+
+template <class T> const void *ll_kernel_of(int op, uint32_t kind)
+{
+    const bool two_shot = kind == LL_AR_TWOSHOT;
+    if (kind == LL_REDUCE_SCATTER || kind == LL_ALLGATHER) {
+        switch (kind == LL_ALLGATHER ? (int)HCCL_REDUCE_SUM : op) {  // AllGather reduces nothing: one instance serves it
+            case HCCL_REDUCE_SUM: return (const void *)ll_rsag_kernel<T, HCCL_REDUCE_SUM>;
+            case HCCL_REDUCE_PROD: return (const void *)ll_rsag_kernel<T, HCCL_REDUCE_PROD>;
+            case HCCL_REDUCE_MAX: return (const void *)ll_rsag_kernel<T, HCCL_REDUCE_MAX>;
+            default: return (const void *)ll_rsag_kernel<T, HCCL_REDUCE_MIN>;
+        }
+    }
     if (two_shot) {
         switch (op) {
             case HCCL_REDUCE_SUM: return (const void *)ar_ll2_kernel<T, HCCL_REDUCE_SUM>;
@@ -303,7 +418,7 @@ template <class T> const void *ll_kernel_of(int op, bool two_shot)
 HcclResult launch_ar_ll(const LlArgs *args, int nlocal, int dtype, int op, void *stream)
 {
     const void *fn = nullptr;
-    const bool two = args[0].two_shot != 0;
+    const uint32_t two = args[0].two_shot;  // LlKind
     switch (dtype) {
         case HCCL_DATA_TYPE_INT8: fn = ll_kernel_of<int8_t>(op, two); break;
         case HCCL_DATA_TYPE_UINT8: fn = ll_kernel_of<uint8_t>(op, two); break;
@@ -323,7 +438,8 @@ HcclResult launch_ar_ll(const LlArgs *args, int nlocal, int dtype, int op, void 
     LlArgsArray arr;
     for (int i = 0; i < nlocal; ++i) arr.a[i] = args[i];
     int es = dtype_size(dtype);
-    uint64_t nlines = (args[0].count * es + 7) / 8;
+    // lines a rank handles: the message (AllReduce), or the p blocks that pass through its hands (ReduceScatter / AllGather)
+    uint64_t nlines = (args[0].count * es + 7) / 8 * (two >= LL_REDUCE_SCATTER ? (uint64_t)args[0].nranks : 1);
     unsigned ctas = (unsigned)((nlines + kLlThreads - 1) / kLlThreads);
     unsigned cap = nlocal > 1 ? (unsigned)(128 / nlocal) : (two ? 128u : 96u);
     if (ctas > cap) ctas = cap;

@@ -8,6 +8,9 @@ constexpr uint64_t kLlSlotBytes = 2 * kLlMaxPayload;  // 16-byte lines carry 8 p
 // Largest message of the two-shot form: its two areas of p pieces share the mailbox half of p slots, a piece carries 1/p of
 // the message at 50 % payload.
 HCCLB_HD uint64_t ll_two_shot_max(int p) { return (uint64_t)p * kLlSlotBytes / 4 / 16 * 16; }
+// Largest block (bytes per rank) of the LL ReduceScatter / AllGather: one piece of an area at 50 % payload.
+HCCLB_HD uint64_t ll_block_max() { return kLlSlotBytes / 4 / 16 * 16; }
+enum LlKind : uint32_t { LL_AR_ONESHOT = 0, LL_AR_TWOSHOT = 1, LL_REDUCE_SCATTER = 2, LL_ALLGATHER = 3 };
 struct LlArgs {
     uint8_t *ll[kMaxRanks];   // mailbox region of rank q mapped into this rank's address space
     const void *in;
@@ -24,7 +27,8 @@ struct LlArgs {
     uint64_t exe_id;          // value the host wrote into the status block's head when it launched the op
     int32_t rank, nranks;
     uint32_t tag, parity;
-    uint32_t two_shot, pad;   // 1: slices go to their owners, reduced slices come back (three ranks and more)
+    uint32_t two_shot, pad;   // LlKind: 1 = slices go to their owners, reduced slices come back; 2 / 3 = the two halves of that as
+                              // ReduceScatter and AllGather (count = elements of one rank's block)
 };
 struct LlArgsArray {
     LlArgs a[kMaxRanks];

@@ -144,6 +144,58 @@ def test_allreduce_low_latency_two_shot(comms, p, dtype, op):
             close(o, ref, dtype, p)
 
 
+@pytest.mark.parametrize("p", [2, 3, 4, 8])
+@pytest.mark.parametrize("dtype,op", [(torch.float32, L.SUM), (torch.bfloat16, L.MAX), (torch.int32, L.MIN), (torch.float64, L.PROD)])
+def test_reduce_scatter_and_allgather_low_latency(comms, p, dtype, op):
+    """The two halves of the two-shot LL AllReduce as collectives of their own; odd counts put the blocks at element-aligned
+    addresses only."""
+    c = comms(p)
+    for n in (1, 1_001, 65_537, (1 << 20) // dtype.itemsize):   # per-rank block; the last is the largest the mailboxes take
+        ins = rnd(p, n * p, dtype, seed=n % 59)
+        outs = [torch.zeros(n, device="cuda", dtype=dtype) for _ in range(p)]
+        for _ in range(3):  # repeated calls alternate the mailbox parity
+            c.reduce_scatter(ins, outs, op=op, algo=L.ALGO_LL)
+        ok(c)
+        assert c.trace()[-1]["algo"] == "ll"
+        ref = ref_reduce(ins, op)
+        for r, o in enumerate(outs):
+            close(o, ref[r * n:(r + 1) * n], dtype, p)
+        gs = rnd(p, n, dtype, seed=n % 47)
+        gout = [torch.zeros(n * p, device="cuda", dtype=dtype) for _ in range(p)]
+        for _ in range(2):
+            c.all_gather(gs, gout, algo=L.ALGO_LL)
+        ok(c)
+        assert c.trace()[-1]["algo"] == "ll"
+        for o in gout:
+            assert torch.equal(o, torch.cat(gs))
+    # in place: AllGather with every rank's block already at its position, ReduceScatter onto the rank's own block
+    n = 30_001
+    full = [torch.zeros(n * p, device="cuda") for _ in range(p)]
+    gs = rnd(p, n, torch.float32, seed=2)
+    for r in range(p):
+        full[r][r * n:(r + 1) * n] = gs[r]
+    c.all_gather([full[r][r * n:(r + 1) * n] for r in range(p)], full, algo=L.ALGO_LL)
+    ok(c)
+    for o in full:
+        assert torch.equal(o, torch.cat(gs))
+    ins = rnd(p, n * p, torch.float32, seed=3)
+    ref = ref_reduce(ins, L.SUM)
+    c.reduce_scatter(ins, [ins[r][r * n:(r + 1) * n] for r in range(p)], algo=L.ALGO_LL)
+    ok(c)
+    for r in range(p):
+        close(ins[r][r * n:(r + 1) * n], ref[r * n:(r + 1) * n], torch.float32, p)
+    # one block too large for the mailboxes: the plan executor takes over
+    n = (1 << 20) // 4 + 64
+    ins = rnd(p, n * p, torch.float32, seed=4)
+    outs = [torch.zeros(n, device="cuda") for _ in range(p)]
+    c.reduce_scatter(ins, outs, algo=L.ALGO_LL)
+    ok(c)
+    assert c.trace()[-1]["algo"] == "mesh"
+    ref = ref_reduce(ins, L.SUM)
+    for r, o in enumerate(outs):
+        close(o, ref[r * n:(r + 1) * n], torch.float32, p)
+
+
 PIPE_SIZES = (5, 70_001, 3_000_000)  # part of a chunk; one chunk; twelve chunks through a four-slot ring (4 MB staging halves)
 
 
