@@ -263,6 +263,8 @@ def main():
 
     # bounded device waits: a rank that is lost must not leave the other GPUs' CTAs polling for half an hour on a shared box
     os.environ.setdefault("HCCL_EXEC_TIMEOUT_MS", "30000")
+    # a benchmark wants no quick verdict on a silent peer: on a loaded host a rank may be held up for seconds by allocations
+    os.environ.setdefault("HCCL_HEARTBEAT_LOST_MS", "20000")
     torch, dist, world, rank, local_rank = setup_dist(args)
     import cann_hccl_b200 as H
     from cann_hccl_b200 import _lib as L
