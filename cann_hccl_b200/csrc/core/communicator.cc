@@ -293,7 +293,6 @@ Communicator::~Communicator()
     hb_stop_.store(true);
     { std::lock_guard<std::mutex> lk(hb_mu_); hb_cv_.notify_all(); }
     if (hb_thread_.joinable()) hb_thread_.join();
-    if (hb_stream_) cudaStreamDestroy((cudaStream_t)hb_stream_);
     p2p_.reset();
     bool dev = settings_.transport == TR_DEVICE;
     if (dev) {

@@ -230,7 +230,6 @@ private:
     void *dev_ctx_ = nullptr;              // device array of RankCtx
     void *dev_exit_ = nullptr;
     void *dev_pipe_cnt_ = nullptr;         // arrival counters of the pipelined kernels (kPipeCounterWords per local rank)
-    void *hb_stream_ = nullptr;            // stream of the heartbeat thread (device counter read-back)
     void *dev_trace_ = nullptr;            // in-kernel timestamp buffers (kTraceWords per local rank) when enabled
     void *pinned_ = nullptr;               // host-mapped block holding status + abort words
     uint64_t p2p_slot_ = 0;
