@@ -919,7 +919,8 @@ HcclResult launch_tp_gemm(TpGemmParams *P, const void *const *A, const void *con
     // AG and RS mode make CTAs of one rank wait on each other (GEMM CTAs on the data-movement CTAs, the reduce tail on the
     // other CTAs' tiles): a cooperative launch guarantees that all of them are resident together even when another kernel
     // shares the GPU.  The plain GEMM has no such dependency.
-    const bool coop = nlocal > 1 || P0.mode != TP_MODE_PLAIN;
+    // (a single rank in AG mode has no data-movement CTAs and waits for nobody)
+    const bool coop = nlocal > 1 || P0.mode == TP_MODE_RS || (P0.mode == TP_MODE_AG && P0.nranks > 1);
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = (cudaStream_t)stream;
