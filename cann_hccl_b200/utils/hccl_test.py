@@ -29,7 +29,7 @@ import time
 import numpy as np
 
 TESTS = ("all_reduce_test", "all_gather_test", "reduce_scatter_test", "broadcast_test", "reduce_test", "scatter_test", "gather_test",
-         "alltoall_test")
+         "alltoall_test", "alltoallv_test")
 NP_DTYPES = {"int8": np.int8, "uint8": np.uint8, "int16": np.int16, "uint16": np.uint16, "int32": np.int32, "uint32": np.uint32,
              "int64": np.int64, "uint64": np.uint64, "fp16": np.float16, "fp32": np.float32, "fp64": np.float64, "bfp16": None}
 OPS = {"sum": 0, "prod": 1, "max": 2, "min": 3}
@@ -80,7 +80,23 @@ def reference(test, ins, op, p, rank, root, count):
         return ins[root][rank * count:(rank + 1) * count]
     if test == "alltoall_test":
         return np.concatenate([ins[q][rank * count:(rank + 1) * count] for q in range(p)])
+    if test == "alltoallv_test":
+        m = a2av_matrix(count, p)
+        return np.concatenate([ins[q][int(m[q, :rank].sum()):int(m[q, :rank + 1].sum())] for q in range(p)])
     raise ValueError(test)
+
+
+def a2av_matrix(count, p):
+    """Count matrix of alltoallv_test: rank i sends count * ((i + j) % 4 + 1) / 4 elements to rank j (at least one)."""
+    return np.array([[max(1, count * ((i + j) % 4 + 1) // 4) for j in range(p)] for i in range(p)], dtype=np.uint64)
+
+
+def a2av_rows(m, ranks):
+    """(send counts, send displacements, receive counts, receive displacements) of the listed ranks, one row per rank."""
+    sc = np.stack([m[r] for r in ranks])
+    rc = np.stack([m[:, r] for r in ranks])
+    excl = lambda c: np.concatenate([np.zeros((c.shape[0], 1), np.uint64), np.cumsum(c, axis=1)[:, :-1]], axis=1).astype(np.uint64)
+    return sc, excl(sc), rc, excl(rc)
 
 
 def in_elems(test, count, p):
@@ -126,7 +142,7 @@ def worker(a):
     else:
         comm = H.Communicator.init_root(p, info, rank, config=cfg, device=device)
     coll = {"all_reduce_test": L.ALLREDUCE, "all_gather_test": L.ALLGATHER, "reduce_scatter_test": L.REDUCE_SCATTER, "broadcast_test": L.BROADCAST,
-            "reduce_test": L.REDUCE, "scatter_test": L.SCATTER, "gather_test": L.GATHER, "alltoall_test": L.ALLTOALL}[a.test]
+            "reduce_test": L.REDUCE, "scatter_test": L.SCATTER, "gather_test": L.GATHER, "alltoall_test": L.ALLTOALL, "alltoallv_test": L.ALLTOALLV}[a.test]
     hd = {"int8": L.INT8, "uint8": L.UINT8, "int16": L.INT16, "uint16": L.UINT16, "int32": L.INT32, "uint32": L.UINT32, "int64": L.INT64,
           "uint64": L.UINT64, "fp16": L.FP16, "fp32": L.FP32, "fp64": L.FP64, "bfp16": L.BFP16}[a.dtype]
     es = 2 if a.dtype == "bfp16" else np.dtype(NP_DTYPES[a.dtype]).itemsize
@@ -153,13 +169,17 @@ def worker(a):
     failed = False
     while size <= a.maxbytes:
         count = max(1, size // es)
-        n_in, n_out = in_elems(a.test, count, p), out_elems(a.test, count, p)
+        v = a.test == "alltoallv_test"
+        mat = a2av_matrix(count, p) if v else None
+        n_in_of = (lambda q: int(mat[q].sum())) if v else (lambda q: in_elems(a.test, count, p))
+        n_out_of = (lambda q: int(mat[:, q].sum())) if v else (lambda q: out_elems(a.test, count, p))
+        n_in, n_out = n_in_of(rank), n_out_of(rank)
         mine = make_input(rank, n_in, a.dtype)
         if local:
             tdt = {"bfp16": torch.bfloat16}.get(a.dtype)
-            send = [torch.from_numpy(make_input(q, n_in, a.dtype)).cuda() for q in range(p)]
+            send = [torch.from_numpy(make_input(q, n_in_of(q), a.dtype)).cuda() for q in range(p)]
             send = [x.to(tdt) for x in send] if tdt else send
-            recv = send if a.test == "broadcast_test" else [torch.zeros(n_out, device="cuda", dtype=send[0].dtype) for _ in range(p)]
+            recv = send if a.test == "broadcast_test" else [torch.zeros(n_out_of(q), device="cuda", dtype=send[0].dtype) for q in range(p)]
         elif device:
             tdt = {"bfp16": torch.bfloat16}.get(a.dtype)
             send = torch.from_numpy(mine).cuda().to(tdt) if tdt else torch.from_numpy(mine).cuda()
@@ -172,9 +192,16 @@ def worker(a):
             recv = send if a.test == "broadcast_test" else np.zeros(n_out, send.dtype)
         kw = dict(op=op, root=a.root, algo=algo)
 
-        def call(k):
-            if k > 0:
-                comm.repeat(coll, send, recv, count, hd, k, **kw)
+        rows = a2av_rows(mat, range(p) if local else [rank]) if v else None
+
+        def call(k, **over):
+            if k <= 0:
+                return
+            if v:  # the count matrix travels with every call: a Python loop instead of the C loop
+                for _ in range(k):
+                    comm.all_to_all_v(send, rows[0], rows[1], recv, rows[2], rows[3], algo=dict(kw, **over)["algo"])
+            else:
+                comm.repeat(coll, send, recv, count, hd, k, **dict(kw, **over))
 
         # one checked call, then warm-up and the timed loop
         call(1)
@@ -182,7 +209,7 @@ def worker(a):
             assert comm.sync() == 0, comm.describe_status()
         ok = True
         if a.check:
-            ins = [make_input(q, n_in, a.dtype) for q in range(p)]
+            ins = [make_input(q, n_in_of(q), a.dtype) for q in range(p)]
             for vr, got_t in (enumerate(recv) if local else ((rank, recv),)):
                 ref = reference(a.test, ins, op, p, vr, a.root, count)
                 if ref is None:
@@ -235,7 +262,7 @@ def worker(a):
         for x in extra_algos:
             kx = dict(kw, algo=L.ALGO_NAMES.index(x))
             try:
-                times.append(timed(lambda k: comm.repeat(coll, send, recv, count, hd, k, **kx) if k > 0 else None))
+                times.append(timed(lambda k: call(k, algo=kx["algo"])))
                 stage_times("forced %s:" % x)
             except H.HcclError:
                 times.append(float("nan"))  # the algorithm does not exist for this collective / type / size
@@ -247,7 +274,8 @@ def worker(a):
                        "reduce_test": lambda: dist.reduce(send, dst=a.root),
                        "scatter_test": lambda: dist.scatter(recv, list(send.chunk(p)) if rank == a.root else None, src=a.root),
                        "gather_test": lambda: dist.gather(send, list(recv.chunk(p)) if rank == a.root else None, dst=a.root),
-                       "alltoall_test": lambda: dist.all_to_all_single(recv, send)}[a.test]
+                       "alltoall_test": lambda: dist.all_to_all_single(recv, send),
+                       "alltoallv_test": lambda: dist.all_to_all_single(recv, send, [int(x) for x in mat[:, rank]], [int(x) for x in mat[rank]])}[a.test]
             times.append(timed(lambda k: [nccl_fn() for _ in range(k)]))
         # maximum over ranks and the conjunction of the checks, gathered over the control plane
         import struct

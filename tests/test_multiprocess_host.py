@@ -115,6 +115,8 @@ def test_stuck_detection_via_heartbeat():
     ["reduce_scatter_test", "-b", "1K", "-e", "16K", "-f", "4", "-d", "bfp16", "-o", "max", "-p", "2"],
     ["all_gather_test", "-b", "1000", "-e", "3000", "-f", "0", "-i", "1000", "-d", "int8", "-p", "4", "--algo", "ring"],
     ["broadcast_test", "-b", "4K", "-e", "4K", "-d", "int64", "-p", "3", "-r", "1"],
+    ["alltoallv_test", "-b", "2K", "-e", "32K", "-f", "4", "-d", "fp32", "-p", "3", "--algo", "mesh,pairwise"],
+    ["reduce_test", "-b", "4K", "-e", "64K", "-f", "4", "-d", "fp32", "-o", "sum", "-p", "4", "-r", "2", "--algo", "mesh_pipe"],
 ])
 def test_hccl_test_command_line(argv):
     """The hccl_test-shaped CLI prints the reference tool's columns and reports success for every size (CPU ranks)."""
