@@ -129,8 +129,10 @@ HcclResult Communicator::tp_all_gather_matmul(const void *const *x_shard, const 
     }
     stats_.launches++;
     stats_.ops[COLL_ALLGATHER]++;
-    int ncomm = 8;  // the launcher drops them for a single rank
-    if (const char *e = getenv("HCCL_TP_COMM_CTAS")) ncomm = std::max(1, atoi(e));
+    // data-movement CTAs (the launcher drops them for a single rank).  Read once per process: the completion counters of a
+    // workspace count these CTAs over all calls, so the number must not change between two calls on the same shape.
+    static const int ncomm_env = [] { const char *e = getenv("HCCL_TP_COMM_CTAS"); return e ? std::max(1, atoi(e)) : 8; }();
+    int ncomm = ncomm_env;
     HcclResult rc = launch_tp_gemm(P.data(), A.data(), B.data(), nl, ncomm, stream);
     if (rc != HCCL_SUCCESS) --ws.epoch;  // rejected before any kernel ran: the counters still stand at the previous call
     return rc;
