@@ -310,3 +310,33 @@ def test_plan_verifier_property_sweep():
         assert rc == L.SUCCESS, (coll, L.ALGO_NAMES[algo], p, count, dtype, nchan, msg.value)
 
     run()
+
+
+def test_library_override_and_sanitizer_build_names(tmp_path):
+    """HCCL_B200_LIB makes the Python layer load another build of the library (a sanitizer build, for one); the build script
+    names those builds after the sanitizer and refuses anything but address and thread."""
+    import subprocess
+    import sys
+    from cann_hccl_b200 import build as B
+    assert B.lib_path().endswith("libhccl_b200.so")
+    assert B.lib_path("thread").endswith("libhccl_b200_thread.so")
+    with pytest.raises(ValueError):
+        B.build(sanitize="memory")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    alias = tmp_path / "libhccl_b200_copy.so"
+    os.symlink(B.lib_path(), alias)
+    code = "import cann_hccl_b200._lib as L; L.lib(); print(L.LIB_PATH)"
+    out = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, HCCL_B200_LIB=str(alias)), cwd=root, capture_output=True, text=True, timeout=120)
+    assert out.stdout.strip().endswith("libhccl_b200_copy.so"), out.stdout + out.stderr
+
+
+def test_hccl_test_alltoallv_count_matrix_is_consistent():
+    from cann_hccl_b200.utils import hccl_test as T
+    for p in (2, 3, 8):
+        m = T.a2av_matrix(1000, p)
+        sc, sd, rc, rd = T.a2av_rows(m, range(p))
+        assert (sc == m).all() and (rc == m.T).all() and (m >= 1).all()
+        for r in range(p):
+            assert sd[r][0] == 0 and rd[r][0] == 0
+            assert all(sd[r][j + 1] == sd[r][j] + sc[r][j] for j in range(p - 1))
+            assert all(rd[r][j + 1] == rd[r][j] + rc[r][j] for j in range(p - 1))
