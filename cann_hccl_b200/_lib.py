@@ -182,6 +182,7 @@ def lib():
         "HcclB200ReloadEnv": [],
         "HcclB200PoolBind": [vp],
         "HcclB200PlanCheck": [i32, i32, u32, u64, C.c_int, u32, u64, i32, C.c_int64, C.c_char_p, C.c_size_t],
+        "HcclB200PlanRaceCheck": [i32, i32, u32, u64, C.c_int, u32, u32, i32, i32, i32, C.c_char_p, C.c_size_t],
         "HcclB200Put": [vp, u32, i32, u32, C.c_size_t, vp, C.c_size_t, vp],
         "HcclB200Get": [vp, u32, i32, u32, C.c_size_t, vp, C.c_size_t, vp],
         "HcclB200GetTopoJson": [vp, C.c_char_p, C.c_size_t],

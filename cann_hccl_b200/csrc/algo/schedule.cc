@@ -291,12 +291,18 @@ void ar_ring(Prog &P, const OpDesc &d)
 // Halving (reduce-scatter) inside the power-of-two block.  range_off(b) = staging byte offset of the start of block
 // slice b (b in 0..B), elements between two boundaries are contiguous in staging.  On return lastidx[r] is each
 // rank's newest step.  When out_of(b) != ~0 the final step of block rank b also writes its slice to BUF_OUT there.
+// Every halving step reduces into the rank's own staging range, split among its channels by the length of THAT step's
+// range: the lane of a channel in one step overlaps the lanes of other channels in the step before.  So the channels of a
+// rank meet before every step (`barrier_first`: also before the first one, when the caller has not just done so); the
+// partner then waits for that meeting point, which lies behind all of the rank's channels.
 template <class OffFn, class OutFn>
-void hd_reduce_scatter(Prog &P, const HdBlock &H, OffFn range_off, OutFn out_of)
+void hd_reduce_scatter(Prog &P, const HdBlock &H, OffFn range_off, OutFn out_of, bool barrier_first)
 {
     int B = H.B;
     std::vector<int> lo(B, 0), hi(B, B);
     for (int width = B; width > 1; width /= 2) {
+        if (width != B || barrier_first)
+            for (int b = 0; b < B; ++b) P.own_channels_barrier(H.rank_of(b));
         std::vector<int> prev(P.p);
         for (int r = 0; r < P.p; ++r) prev[r] = P.last(r);
         for (int b = 0; b < B; ++b) {
@@ -343,7 +349,7 @@ void ar_rhd(Prog &P, const OpDesc &d)
     // the halving steps write the receive buffer in ranges unrelated to the lanes of the input reads above
     for (int r = 0; r < P.p; ++r) P.own_channels_barrier(r);
     auto off = [&](int b) { return S.off(b) * P.es; };
-    hd_reduce_scatter(P, H, off, [&](int b) { return uoff + S.off(b) * P.es; });
+    hd_reduce_scatter(P, H, off, [&](int b) { return uoff + S.off(b) * P.es; }, false);
     // doubling (all-gather) inside the block
     {
         int B = H.B;
@@ -465,7 +471,10 @@ void rs_rhd(Prog &P, const Slots &S, uint64_t out_off)
         H.ranks_of(b, lo, hi);
         return S.st_off[lo];
     };
-    hd_reduce_scatter(P, H, off, [](int) { return ~0ull; });
+    hd_reduce_scatter(P, H, off, [](int) { return ~0ull; }, false);
+    // a folded pair's block spans two slots, so the lanes of the last halving step are not the lanes of the copy-out below:
+    // the channels of such a rank meet once more (power-of-two rank counts: same range, same lanes, nothing to do)
+    for (int r = 0; r < H.part1; r += 2) P.own_channels_barrier(r);
     std::vector<int> lastidx(p);
     for (int r = 0; r < p; ++r) lastidx[r] = P.last(r);
     for (int r = 0; r < p; ++r) {
@@ -738,9 +747,10 @@ void reduce_rhd(Prog &P, const OpDesc &d)
         st.sig_rank = RANK_ALL;
         P.add(r, st);
     }
-    P.own_channels_barrier(d.root);  // in place at the root: all of its input reads before its first output write
+    // in place at the root: all of its input reads before its first output write (block ranks meet in the halving steps anyway)
+    if (H.block_of(d.root) < 0) P.own_channels_barrier(d.root);
     auto off = [&](int b) { return S.off(b) * P.es; };
-    hd_reduce_scatter(P, H, off, [](int) { return ~0ull; });
+    hd_reduce_scatter(P, H, off, [](int) { return ~0ull; }, true);
     std::vector<int> lastidx(P.p);
     for (int r = 0; r < P.p; ++r) lastidx[r] = P.last(r);
     for (int b = 0; b < H.B; ++b) {

@@ -75,4 +75,9 @@ uint64_t plan_stage_bytes(const OpDesc &d);
 // channel, bank and rank fields against their ranges.  HCCL_E_INTERNAL and a description in *why on the first violation.
 HcclResult verify_plan(const OpDesc &d, const std::vector<int> &local, const Plan &plan, uint64_t stage_half, std::string *why);
 
+// Static race detection of a plan built for ALL ranks of `d` (algo/racecheck.cc): any two accesses to overlapping bytes of one
+// buffer, one of them a write, must be ordered by program order and flag waits; unsatisfiable waits and cycles are reported too.
+// `in_place` folds each rank's send and receive buffer into one, as the in-place form of the collective lays them out.
+HcclResult race_check_plan(const OpDesc &d, const Plan &plan, bool in_place, std::string *why);
+
 }  // namespace hcclb

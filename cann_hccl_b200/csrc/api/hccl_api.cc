@@ -954,6 +954,28 @@ HcclResult HcclB200PlanCheck(int32_t coll, int32_t algo, uint32_t nRanks, uint64
     if (message && cap) snprintf(message, cap, "%s", rc == HCCL_SUCCESS ? plan.name.c_str() : why.c_str());
     return rc;
 }
+HcclResult HcclB200PlanRaceCheck(int32_t coll, int32_t algo, uint32_t nRanks, uint64_t count, HcclDataType dataType, uint32_t nChannels,
+                                 uint32_t root, int32_t inPlace, int32_t dropWaitRank, int32_t dropWaitStep, char *message, size_t cap)
+{
+    OpDesc d;
+    d.coll = coll; d.algo = algo; d.nranks = (int)nRanks; d.dtype = dataType; d.nchan = (int)nChannels; d.root = (int)root;
+    d.count = count; d.chunk_off = 0; d.chunk_count = count;
+    std::vector<int> local;
+    for (uint32_t r = 0; r < nRanks; ++r) local.push_back((int)r);
+    Plan plan;
+    CHK_RET(build_plan(d, local, &plan));
+    // self-test of the checker: take one wait out of the plan and see the finding
+    if (dropWaitRank >= 0 && dropWaitRank < (int)plan.steps.size() && dropWaitStep >= 0 && dropWaitStep < (int)plan.steps[dropWaitRank].size()) {
+        Step &st = plan.steps[dropWaitRank][dropWaitStep];
+        CHK_RET_LOG(st.wait_rank == RANK_NONE, HCCL_E_PARA, "step %d of rank %d has no wait to drop", dropWaitStep, dropWaitRank);
+        st.wait_rank = RANK_NONE;
+        st.flags &= (uint8_t)~SF_WAIT_ALLCH;
+    }
+    std::string why;
+    HcclResult rc = race_check_plan(d, plan, inPlace != 0, &why);
+    if (message && cap) snprintf(message, cap, "%s", rc == HCCL_SUCCESS ? plan.name.c_str() : why.c_str());
+    return rc;
+}
 HcclResult HcclB200Exchange(HcclComm comm, const char *tag, const void *mine, size_t len, void *all)
 {
     GET_COMM("HcclB200Exchange");

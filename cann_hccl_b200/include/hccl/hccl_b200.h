@@ -151,6 +151,14 @@ extern HcclResult HcclB200GetOverflowCount(HcclComm comm, uint64_t *count);
  * check firing.  message receives the plan name, or the first violation.  No communicator and no GPU needed. */
 extern HcclResult HcclB200PlanCheck(int32_t coll, int32_t algo, uint32_t nRanks, uint64_t count, HcclDataType dataType, uint32_t nChannels,
                                     uint64_t stageHalfBytes, int32_t skewStep, int64_t skewBytes, char *message, size_t cap);
+/* Static race detection of the plan of (collective, algorithm) for nRanks ranks and nChannels channels (CTAs) per rank: builds the
+ * happens-before relation (program order per rank and channel + flag signal -> wait) and demands that conflicting accesses to
+ * the staging, send and receive buffers are ordered by it; also reports waits that nothing satisfies and cycles.  inPlace != 0
+ * folds each rank's send and receive buffer into one, the way the collective's in-place form lays them out.  dropWaitRank /
+ * dropWaitStep >= 0 remove the wait of that step first (to see the checker find the hole; HCCL_E_PARA when the step has none).
+ * message receives the plan's name, or the first finding. */
+extern HcclResult HcclB200PlanRaceCheck(int32_t coll, int32_t algo, uint32_t nRanks, uint64_t count, HcclDataType dataType, uint32_t nChannels,
+                                        uint32_t root, int32_t inPlace, int32_t dropWaitRank, int32_t dropWaitStep, char *message, size_t cap);
 /* All-gather `len` bytes per rank over the bootstrap hub (control plane; not for bulk data). */
 extern HcclResult HcclB200Exchange(HcclComm comm, const char *tag, const void *mine, size_t len, void *all);
 /* Context handed to custom kernels (role of the reference's MC2 resource export, op_base.cc:3137-3284):
