@@ -962,6 +962,34 @@ HcclResult HcclB200PlanRaceCheck(int32_t coll, int32_t algo, uint32_t nRanks, ui
     d.count = count; d.chunk_off = 0; d.chunk_count = count;
     std::vector<int> local;
     for (uint32_t r = 0; r < nRanks; ++r) local.push_back((int)r);
+    const int p = (int)nRanks;
+    if (coll == COLL_ALLGATHER_V || coll == COLL_REDUCE_SCATTER_V) {
+        // a non-uniform layout derived from `count`: rank j contributes count + 3 j elements (one rank nothing when count is 0 mod 5)
+        uint64_t o = 0;
+        for (int j = 0; j < p; ++j) {
+            uint64_t c = (count % 5 == 0 && j == p / 2) ? 0 : count + 3 * (uint64_t)j;
+            d.counts.push_back(c);
+            d.displs.push_back(o);
+            o += c;
+        }
+        uint64_t mx = 0;
+        for (uint64_t c : d.counts) mx = std::max(mx, c);
+        d.chunk_count = mx;
+    } else if (coll == COLL_ALLTOALLV || coll == COLL_ALLTOALLVC) {
+        // count matrix m[i][j] = count * ((i + 2 j) % 3 + 1) / 3 and slots of about a third of the largest block: several rounds
+        // with acknowledgements per ordered pair
+        std::vector<uint64_t> m((size_t)p * p);
+        for (int i = 0; i < p; ++i)
+            for (int j = 0; j < p; ++j) m[(size_t)i * p + j] = count * (uint64_t)((i + 2 * j) % 3 + 1) / 3;
+        for (int i = 0; i < p; ++i) {
+            uint64_t so = 0, ro = 0;
+            for (int j = 0; j < p; ++j) {
+                d.send_counts.push_back(m[(size_t)i * p + j]); d.send_displs.push_back(so); so += m[(size_t)i * p + j];
+                d.recv_counts.push_back(m[(size_t)j * p + i]); d.recv_displs.push_back(ro); ro += m[(size_t)j * p + i];
+            }
+        }
+        d.slot_bytes = std::max<uint64_t>(256, (count * (uint64_t)dtype_size(dataType) / 3 + 255) / 256 * 256);
+    }
     Plan plan;
     CHK_RET(build_plan(d, local, &plan));
     // self-test of the checker: take one wait out of the plan and see the finding

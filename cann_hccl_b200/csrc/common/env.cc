@@ -157,6 +157,7 @@ EnvConfig parse_env(const std::map<std::string, std::string> &v)
         if (sscanf(s->c_str(), "%d,%d,%d", &a, &b, &d) >= 2 && a >= 1 && b >= 1 && d >= 0 && a <= 16 && b <= 16 && d <= 16) { c.pipe_groups[0] = a; c.pipe_groups[1] = b; c.pipe_groups[2] = d > 0 ? d : 1; }
         else fail(c, "HCCL_PIPE_GROUPS must be a,b[,c] with values in [1,16]");
     }
+    if (auto s = get("HCCL_PLAN_RACE_CHECK")) c.plan_race_check = *s == "1" || lower(*s) == "true";
     if (auto s = get("HCCL_TP_GEMM_PAIR")) c.tp_gemm_pair = !(*s == "0" || lower(*s) == "false");
     if (auto s = get("HCCL_NCCL_LIB")) c.ncc_lib = *s;
     if (auto s = get("HCCL_WHITELIST_DISABLE")) c.whitelist_enable = *s == "0";

@@ -34,6 +34,7 @@ struct EnvConfig {
     int heartbeat_ms = 50;         // HCCL_HEARTBEAT_INTERVAL_MS (reference BROADCAST_INTERVAL 50 ms)
     int stuck_ms = 300000;         // HCCL_STUCK_DETECT_TIME (seconds in env; reference STUCK_INTERVAL 300 s)
     int heartbeat_lost_ms = 3000;  // HCCL_HEARTBEAT_LOST_MS: silence after which a peer counts as lost
+    bool plan_race_check = false;  // HCCL_PLAN_RACE_CHECK=1: every plan goes through the static race check (algo/racecheck.cc) when it is built
     int a2av_check = -1;           // HCCL_ALLTOALLV_CHECK: count-matrix cross-check of AlltoAllV/VC: 1 every call, 0 never, unset = the first 16 calls
     bool calibrate = true;         // HCCL_CALIBRATE=0: device communicators skip the measurement pass at creation
     int calibrate_max_mb = 0;      // HCCL_CALIBRATE_MAX_MB: largest message of the calibration ladder (0 = 64)

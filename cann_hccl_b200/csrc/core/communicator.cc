@@ -360,6 +360,22 @@ HcclResult Communicator::get_plan(const OpDesc &d, const std::string &key, Cache
         HcclResult vrc = verify_plan(d, local_ranks_, cp.plan, d.coll == COLL_SEND || d.coll == COLL_RECV ? 0 : settings_.stage_half_bytes, &why);
         CHK_RET_LOG(vrc != HCCL_SUCCESS, vrc, "plan verification failed: %s", why.c_str());
     }
+    if (env_config().plan_race_check && d.coll != COLL_SEND && d.coll != COLL_RECV) {
+        // debug aid: the happens-before check over the step lists of ALL ranks (built here once more when this process
+        // runs only some of them; AlltoAllV plans need every rank's rows, which only a process with all ranks has)
+        const bool rows_only = (d.coll == COLL_ALLTOALLV || d.coll == COLL_ALLTOALLVC) && (int)local_ranks_.size() != nranks_;
+        if (!rows_only) {
+            std::vector<int> all_ranks;
+            for (int r = 0; r < nranks_; ++r) all_ranks.push_back(r);
+            Plan whole;
+            const Plan *pp = &cp.plan;
+            if ((int)local_ranks_.size() != nranks_) { CHK_RET(build_plan(d, all_ranks, &whole)); pp = &whole; }
+            std::string why;
+            HcclResult rrc = race_check_plan(d, *pp, false, &why);
+            if (rrc == HCCL_SUCCESS) rrc = race_check_plan(d, *pp, true, &why);
+            CHK_RET_LOG(rrc != HCCL_SUCCESS, rrc, "plan race check failed: %s", why.c_str());
+        }
+    }
     if (settings_.transport == TR_DEVICE) {
         for (auto &steps : cp.plan.steps) {
             Step *ds = nullptr;

@@ -39,6 +39,31 @@ def test_every_plan_orders_its_conflicting_accesses(name):
     assert checked > 50
 
 
+@pytest.mark.parametrize("name,coll", [("allgatherv", L.ALLGATHER_V), ("reducescatterv", L.REDUCE_SCATTER_V), ("alltoallv", L.ALLTOALLV),
+                                       ("alltoallvc", L.ALLTOALLVC)])
+def test_variable_count_plans_order_their_conflicting_accesses(name, coll):
+    """Non-uniform layouts (one rank may contribute nothing); AlltoAllV with slots of a third of the largest block, i.e. several
+    rounds per ordered pair whose slot reuse hangs on the acknowledgement flags."""
+    checked = 0
+    for algo in range(len(L.ALGO_NAMES)):
+        for p in (2, 3, 4, 5, 8):
+            for nchan in (1, 2, 3):
+                for n in (5, 7, 1000, 100_003):
+                    rc, msg = race_check(coll, algo, p, n, nchan)
+                    if rc == L.E_NOT_SUPPORT:
+                        continue
+                    checked += 1
+                    assert rc == L.SUCCESS, "%s p=%d nchan=%d n=%d: %s" % (L.ALGO_NAMES[algo], p, nchan, n, msg)
+    assert checked > 50
+
+
+def test_checker_finds_a_dropped_acknowledgement_wait():
+    """AlltoAllV: a sender that does not wait for the acknowledgement of round k - 1 overwrites a slot that is still being read."""
+    assert race_check(L.ALLTOALLV, L.ALGO_PAIRWISE, 3, 100_003, 2)[0] == L.SUCCESS
+    hits = [race_check(L.ALLTOALLV, L.ALGO_PAIRWISE, 3, 100_003, 2, drop=(0, s)) for s in range(1, 14)]
+    assert any(rc == L.E_INTERNAL and "staging" in m for rc, m in hits), hits
+
+
 def test_checker_finds_a_dropped_wait():
     """Take the wait out of a step that needs it: the checker names the two accesses that are no longer ordered."""
     found = 0
@@ -63,3 +88,31 @@ def test_checker_reports_halving_steps_without_a_meeting_point():
     assert rc == L.SUCCESS, msg
     hits = [race_check(L.ALLREDUCE, L.ALGO_RHD, 4, 100_003, 3, drop=(0, s)) for s in range(2, 10)]
     assert any(rc == L.E_INTERNAL and "staging of rank 0" in m and "rank 0 step" in m for rc, m in hits), hits
+
+
+def test_runtime_knob_checks_every_plan_when_it_is_built():
+    """HCCL_PLAN_RACE_CHECK=1: the communicator runs the check (out of place and in place) on every plan it builds."""
+    import os
+    import subprocess
+    import sys
+    code = """
+import numpy as np
+import cann_hccl_b200 as H
+from cann_hccl_b200 import _lib as L
+p = 4
+c = H.Communicator.init_local(p, device=False)
+ins = [np.arange(1000, dtype=np.float32) + r for r in range(p)]
+for algo in (L.ALGO_MESH, L.ALGO_RING, L.ALGO_RHD, L.ALGO_MESH_ONESHOT):
+    outs = [np.zeros(1000, np.float32) for _ in range(p)]
+    c.all_reduce(ins, outs, algo=algo)
+    assert all(np.allclose(o, sum(ins)) for o in outs)
+outs = [np.zeros(250, np.float32) for _ in range(p)]
+c.reduce_scatter(ins, outs, algo=L.ALGO_RHD)
+assert all(np.allclose(outs[r], sum(ins)[r * 250:(r + 1) * 250]) for r in range(p))
+print('RACE CHECK KNOB OK', c.stats()['plans_built'])
+c.destroy()
+"""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, HCCL_PLAN_RACE_CHECK="1", HCCL_TRANSPORT="host")
+    out = subprocess.run([sys.executable, "-c", code], env=env, cwd=root, capture_output=True, text=True, timeout=120)
+    assert "RACE CHECK KNOB OK" in out.stdout, out.stdout + out.stderr
